@@ -1,0 +1,77 @@
+"""ctypes binding of libhesper_b200.so -- the C ABI declared in include/hesper_b200.h.
+
+There is no fallback: if the shared object is missing or a call fails, an
+exception is raised.  Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libhesper_b200.so")
+
+HB200_OK = 0
+FMT_Q8_0 = 8
+FMT_Q4_K = 12
+FMT_I2_S = 36
+
+
+class HesperB200Error(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"hesper_b200 error {code}: {msg}")
+        self.code = code
+
+
+class BitLinearSeg(C.Structure):
+    _fields_ = [("d_packed", C.c_void_p), ("d_scale", C.c_void_p), ("d_residual", C.c_void_p),
+                ("d_y", C.c_void_p), ("d_acc", C.c_void_p), ("N", C.c_int)]
+
+
+class KQuantSeg(C.Structure):
+    _fields_ = [("d_blocks", C.c_void_p), ("d_residual", C.c_void_p), ("d_y", C.c_void_p),
+                ("N", C.c_int)]
+
+
+_vp, _i, _f, _sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
+
+# name -> (restype, argtypes); the single source of truth for the Python side.
+SIGNATURES = {
+    "hb200_ctx_create": (_i, [_i, C.POINTER(_vp)]),
+    "hb200_ctx_destroy": (_i, [_vp]),
+    "hb200_last_error": (C.c_char_p, []),
+    "hb200_version": (_i, []),
+    "hb200_ctx_sm_count": (_i, [_vp]),
+    "hb200_ctx_check": (_i, [_vp, _vp, C.POINTER(C.c_uint32)]),
+    "hb200_bitlinear_forward": (_i, [_vp, _vp, _vp, _i, _i, _vp, _i, _vp, _f, _vp, _vp, _vp, _vp, _vp]),
+    "hb200_bitlinear_forward_multi": (_i, [_vp, C.POINTER(BitLinearSeg), _i, _i, _vp, _i, _vp, _f, _vp, _vp]),
+    "hb200_bitlinear_gateup_relu2": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _f, _vp, _vp]),
+    "hb200_kquant_forward": (_i, [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _f, _vp, _vp, _vp]),
+    "hb200_kquant_forward_multi": (_i, [_vp, _i, C.POINTER(KQuantSeg), _i, _i, _vp, _i, _vp, _f, _vp]),
+    "hb200_kquant_gateup_gelu": (_i, [_vp, _i, _vp, _vp, _i, _i, _vp, _i, _vp, _f, _vp, _vp]),
+    "hb200_attn_workspace_bytes": (_sz, [_vp, _i, _i, _i, _i, _i]),
+    "hb200_attn_decode": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp, _vp]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the shared object and bind every declared symbol (raises if one is missing)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise HesperB200Error(-2, f"{LIB_PATH} is missing: run `python -m hesper_b200.build` "
+                                      "(there is no CPU fallback)")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def check(code: int) -> None:
+    if code != HB200_OK:
+        raise HesperB200Error(code, load().hb200_last_error().decode("utf-8", "replace"))

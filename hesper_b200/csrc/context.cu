@@ -1,0 +1,91 @@
+// context.cu -- context object, error strings and status block of the C ABI.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace hb {
+
+static thread_local char g_err[512] = "no error";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  set_error("CUDA error %s (%s) in %s", cudaGetErrorName(e), cudaGetErrorString(e), what);
+  // clear the sticky-free error so the next call starts clean
+  (void)cudaGetLastError();
+  return HB200_ERR_CUDA;
+}
+
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" const char* hb200_last_error(void) { return g_err; }
+
+extern "C" int hb200_version(void) { return 100; }
+
+extern "C" int hb200_ctx_create(int device, hb200_ctx** out) {
+  HB_REQUIRE(out != nullptr, "ctx_create: null output pointer");
+  *out = nullptr;
+  int count = 0;
+  HB_CUDA(cudaGetDeviceCount(&count));
+  HB_REQUIRE(device >= 0 && device < count, "ctx_create: device %d of %d", device, count);
+  HB_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  HB_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) {
+    set_error("ctx_create: device %d is sm_%d%d; this library is built for sm_100a only", device,
+              prop.major, prop.minor);
+    return HB200_ERR_UNSUPPORTED;
+  }
+  hb200_ctx* c = new hb200_ctx();
+  c->device = device;
+  c->sm_count = prop.multiProcessorCount;
+  c->smem_optin = (int)prop.sharedMemPerBlockOptin;
+  c->pdl = true;
+  const char* env = getenv("HB200_NO_PDL");
+  if (env && env[0] == '1') c->pdl = false;
+  cudaError_t e = cudaMalloc(&c->d_status, 64);
+  if (e != cudaSuccess) {
+    delete c;
+    return cuda_fail(e, "cudaMalloc(status)");
+  }
+  e = cudaMemset(c->d_status, 0, 64);
+  if (e != cudaSuccess) {
+    cudaFree(c->d_status);
+    delete c;
+    return cuda_fail(e, "cudaMemset(status)");
+  }
+  *out = c;
+  return HB200_OK;
+}
+
+extern "C" int hb200_ctx_destroy(hb200_ctx* ctx) {
+  if (!ctx) return HB200_OK;
+  cudaFree(ctx->d_status);
+  delete ctx;
+  return HB200_OK;
+}
+
+extern "C" int hb200_ctx_sm_count(const hb200_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
+
+extern "C" int hb200_ctx_check(hb200_ctx* ctx, hb200_stream stream, uint32_t* flags) {
+  HB_REQUIRE(ctx != nullptr, "ctx_check: null context");
+  HB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  uint32_t host[16];
+  HB_CUDA(cudaMemcpy(host, ctx->d_status, sizeof(host), cudaMemcpyDeviceToHost));
+  if (flags) *flags = host[0];
+  if (host[0] != 0) {
+    HB_CUDA(cudaMemset(ctx->d_status, 0, 64));
+    set_error("device status 0x%x: a bounded wait inside a kernel expired", host[0]);
+    return HB200_ERR_TIMEOUT;
+  }
+  return HB200_OK;
+}

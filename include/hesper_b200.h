@@ -1,0 +1,192 @@
+/*
+ * hesper_b200.h -- C ABI of the B200 (sm_100a) quantized-inference hot path.
+ *
+ * A drop-in for the three operator families that Hesper's Lean layers execute
+ * through the PTX-emitting CUDA backend (native/cuda_bridge.cpp:374-444 behind
+ * Hesper/Backend/CUDA.lean:523-660):
+ *   - BitLinear ternary (i2_s) x int8 matvec       Hesper/Layers/BitLinear.lean
+ *   - GGUF Q4_K / Q8_0 dequant-fused matvec         Hesper/Layers/Linear.lean
+ *   - split-K GQA flash-attention decode (f16 KV)   Hesper/WGSL/FlashAttentionExperiments.lean
+ *
+ * Conventions (they follow the reference's external-kernel hook,
+ * Hesper/Layers/Linear.lean:65-72 and Hesper/Backend/LlamaCppPTX.lean:138-155):
+ *   - every pointer named d_* is a raw device address (a CUdeviceptr carried as
+ *     a pointer); the caller owns every buffer, the library never frees,
+ *     reallocates or retains them beyond the call;
+ *   - `stream` is a CUstream / cudaStream_t (NULL = legacy default stream); all
+ *     work is enqueued on it, nothing synchronises, allocates or calls back, so
+ *     every launch can be captured into a CUDA graph;
+ *   - weights are the verbatim GGUF payload bytes (i2_s packed bytes with a
+ *     separate 4-byte f32 scale buffer; raw Q4_K / Q8_0 blocks);
+ *   - each function returns HB200_OK or a negative code; hb200_last_error()
+ *     gives the message (thread-local).  Nothing throws or aborts;
+ *   - there is no CPU fallback: on a machine without an sm_100 GPU the calls
+ *     fail with HB200_ERR_CUDA.
+ */
+#ifndef HESPER_B200_H
+#define HESPER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+#define HB200_OK 0
+#define HB200_ERR_INVALID (-1)     /* bad argument (shape, alignment, null) */
+#define HB200_ERR_CUDA (-2)        /* a CUDA runtime call failed */
+#define HB200_ERR_UNSUPPORTED (-3) /* shape or format outside what the kernels cover */
+#define HB200_ERR_TIMEOUT (-4)     /* a bounded device-side wait gave up */
+
+/* GGUF tensor type ids (Hesper/GGUF/Types.lean:86-132). */
+#define HB200_FMT_Q8_0 8
+#define HB200_FMT_Q4_K 12
+#define HB200_FMT_I2_S 36
+
+typedef struct hb200_ctx hb200_ctx;
+typedef void *hb200_stream;
+
+/* ---- context ------------------------------------------------------------- */
+
+/* Replaces CUDAContext.init (Hesper/Backend/CUDA.lean:46; native/cuda_bridge.cpp:78-82)
+ * for this path only: binds to `device` (its primary context), reads the SM
+ * count, raises the kernels' dynamic shared-memory limits and allocates one
+ * 64-byte device status block.  No other allocation happens later. */
+int hb200_ctx_create(int device, hb200_ctx **out);
+int hb200_ctx_destroy(hb200_ctx *ctx);
+
+/* Message of the last failing call on this thread (never NULL).
+ * Mirrors cudaErrorString in native/cuda_bridge.cpp:18-30. */
+const char *hb200_last_error(void);
+
+/* Library version: major*10000 + minor*100 + patch. */
+int hb200_version(void);
+
+/* Number of SMs the context sized its grids for. */
+int hb200_ctx_sm_count(const hb200_ctx *ctx);
+
+/* Synchronises `stream`, then reads and clears the device status block.
+ * *flags != 0 means a kernel's bounded wait expired (HB200_ERR_TIMEOUT is
+ * returned as well).  For tests and diagnostics; not on the hot path. */
+int hb200_ctx_check(hb200_ctx *ctx, hb200_stream stream, uint32_t *flags);
+
+/* ---- BitLinear: ternary i2_s weights x int8 activations ------------------- */
+
+/* One output segment of a fused multi-matrix launch: several weight tensors
+ * that consume the same activation vector (q/k/v; gate/up). */
+typedef struct hb200_bitlinear_seg {
+  const void *d_packed;    /* i2_s bytes, N*K/4, 16-byte aligned */
+  const float *d_scale;    /* one f32: per-tensor scale */
+  const float *d_residual; /* nullable, [M][N] added to the output */
+  float *d_y;              /* [M][N] f32 output */
+  int32_t *d_acc;          /* nullable, [M][N] raw int32 accumulators */
+  int N;                   /* output rows of this tensor */
+} hb200_bitlinear_seg;
+
+/* y[m,n] = ((float)acc[m,n] * d[m]) * scale (+ residual[m,n]),
+ * acc[m,n] = sum_k t[n,k] * q[m,k],  q = per-token absmax int8 of x
+ * (d = amax/127, round-half-even), x optionally RMS-normalised first.
+ *
+ * Replaces BitLinear.forward (Hesper/Layers/BitLinear.lean:1226),
+ * forwardWithResidual (:1308) and forwardFusedRMSNormResidual (:1370); the
+ * arithmetic definition is Hesper/Layers/BitLinearSpec.lean:65-91 evaluated on
+ * the int8 activations.
+ *   d_x          [M][K] f32 activations
+ *   d_rms_gamma  nullable [K]; when set x is replaced by RMSNorm(x)*gamma, eps = rms_eps
+ *   d_act_scale  nullable [M]; receives d[m]
+ * K must be a multiple of 128, 1 <= M <= 64. */
+int hb200_bitlinear_forward(hb200_ctx *ctx, const void *d_packed, const float *d_scale,
+                            int K, int N, const float *d_x, int M,
+                            const float *d_rms_gamma, float rms_eps,
+                            const float *d_residual, int32_t *d_acc,
+                            float *d_act_scale, float *d_y, hb200_stream stream);
+
+/* Same, for up to 4 tensors sharing x in ONE launch (fused q/k/v).  The
+ * reference issues three BitLinear.forward calls (Hesper/Layers/Attention.lean:1191-1193). */
+int hb200_bitlinear_forward_multi(hb200_ctx *ctx, const hb200_bitlinear_seg *segs,
+                                  int nseg, int K, const float *d_x, int M,
+                                  const float *d_rms_gamma, float rms_eps,
+                                  float *d_act_scale, hb200_stream stream);
+
+/* y[m,n] = relu(s_g*g[m,n])^2 * (s_u*u[m,n]) with g, u the two ternary matvecs.
+ * Replaces BitLinear.forwardFusedGateUpReluSqrMul (Hesper/Layers/BitLinear.lean:1419,
+ * kernel :553-621). */
+int hb200_bitlinear_gateup_relu2(hb200_ctx *ctx, const void *d_packed_gate,
+                                 const float *d_scale_gate, const void *d_packed_up,
+                                 const float *d_scale_up, int K, int N, const float *d_x,
+                                 int M, const float *d_rms_gamma, float rms_eps,
+                                 float *d_y, hb200_stream stream);
+
+/* ---- GGUF k-quants: Q4_K / Q8_0 dequant-fused matvec ----------------------- */
+
+typedef struct hb200_kquant_seg {
+  const void *d_blocks;    /* raw GGUF blocks, row-major [N][K/blk], 16-byte aligned */
+  const float *d_residual; /* nullable [M][N] */
+  float *d_y;              /* [M][N] */
+  int N;
+} hb200_kquant_seg;
+
+/* y[m,n] = sum_k dequant(W)[n,k] * x[m,k] (+ residual).  f32 activations in and
+ * f32 out; weights stay quantised in HBM.
+ *
+ * Replaces LinearLayer.forward / forwardDP4A (Hesper/Layers/Linear.lean:7115,5713)
+ * and is what the hook Linear.llamaCppDp4aOverride (:65-72, consumed :5723-5740)
+ * binds to: (inputF32Ptr, weightPtr, outputF32Ptr, inDim, outDim, quantTag).
+ *   fmt  HB200_FMT_Q4_K (K % 256 == 0) or HB200_FMT_Q8_0 (K % 32 == 0)
+ *   d_rms_gamma nullable: RMSNorm prologue as forwardFusedRMSNormLinear (:7897 region) */
+int hb200_kquant_forward(hb200_ctx *ctx, int fmt, const void *d_blocks, int K, int N,
+                         const float *d_x, int M, const float *d_rms_gamma, float rms_eps,
+                         const float *d_residual, float *d_y, hb200_stream stream);
+
+/* Up to 4 tensors sharing x in one launch: forwardFusedQKV / forwardFusedNormQKV /
+ * forwardFusedKV (Hesper/Layers/Linear.lean:7413-7660). */
+int hb200_kquant_forward_multi(hb200_ctx *ctx, int fmt, const hb200_kquant_seg *segs,
+                               int nseg, int K, const float *d_x, int M,
+                               const float *d_rms_gamma, float rms_eps,
+                               hb200_stream stream);
+
+/* y = gelu_tanh(x.Wg) * (x.Wu): forwardFusedGateUp / forwardFusedNormGateUp
+ * (Hesper/Layers/Linear.lean:7295,7506); spec Hesper/Layers/FusedFFNSpec.lean:42-122. */
+int hb200_kquant_gateup_gelu(hb200_ctx *ctx, int fmt, const void *d_blocks_gate,
+                             const void *d_blocks_up, int K, int N, const float *d_x,
+                             int M, const float *d_rms_gamma, float rms_eps, float *d_y,
+                             hb200_stream stream);
+
+/* ---- decode attention ------------------------------------------------------ */
+
+/* Bytes of scratch hb200_attn_decode needs for this shape (split-K partials). */
+size_t hb200_attn_workspace_bytes(const hb200_ctx *ctx, int B, int H, int Hkv, int D,
+                                  int max_seq);
+
+/* GQA decode attention, one query token per sequence, f16 KV cache, split-K
+ * over the sequence with all Q heads of a KV head sharing each K/V load.
+ *
+ * Replaces executeFlashAttentionV11 (Hesper/WGSL/FlashAttentionExperiments.lean:572)
+ * = flashAttentionVecParamsKernelV11 (:45) + flashAttentionVecCombineKernel (:495).
+ *   d_q        [B][H][D], f32 (q_is_f16 = 0, the reference's type) or f16
+ *   d_k, d_v   [B][Hkv][max_seq][D] f16: per sequence the cache layout of
+ *              Hesper/WGSL/FlashAttention.lean:590-597
+ *   d_seqlens  [B] int32 valid positions per sequence (reference params[1] = cacheLen);
+ *              the query is the last position, so all of them are visible
+ *   window     0 = full attention; else only the last `window` positions
+ *              (rule of flashAttentionSWAKernel, Hesper/WGSL/FlashAttention.lean:1621-1624)
+ *   d_out      [B][H][D] f32
+ * D in {64, 128, 256}; H/Hkv in {1, 2, 4, 8}. */
+int hb200_attn_decode(hb200_ctx *ctx, const void *d_q, int q_is_f16, const void *d_k,
+                      const void *d_v, const int32_t *d_seqlens, int B, int H, int Hkv,
+                      int D, int max_seq, int window, float scale, void *d_workspace,
+                      size_t workspace_bytes, float *d_out, hb200_stream stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HESPER_B200_H */

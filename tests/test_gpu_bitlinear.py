@@ -1,0 +1,148 @@
+"""GPU parity: ternary x int8 BitLinear through the C ABI vs the CPU oracle.
+Bar: bit-exact int32 accumulators and bit-exact f32 outputs."""
+import numpy as np
+import pytest
+import torch
+
+from hesper_b200 import BitLinear, formats
+from refcases import BITLINEAR_CASES
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("name,K,N,M,seed", BITLINEAR_CASES, ids=[c[0] for c in BITLINEAR_CASES])
+def test_reference_equivalence_cases(ctx, oracle, name, K, N, M, seed):
+    t, x, scale = oracle.gen_bitlinear_case(seed, K, N, M)
+    packed = oracle.i2s_pack(t)
+    y_ref, acc_ref, d_ref = oracle.bitlinear_forward(packed, scale, K, N, x)
+    layer = BitLinear.create_from_bytes(ctx, packed, scale, K, N)
+    y, acc, d = layer.forward(_dev(x), return_acc=True)
+    ctx.check()
+    assert np.array_equal(acc.cpu().numpy(), acc_ref)
+    assert np.array_equal(d.cpu().numpy(), d_ref)
+    assert np.array_equal(y.cpu().numpy(), y_ref)
+    # and inside the reference's own acceptance band against the f32 spec
+    spec = oracle.bitlinear_spec(packed, scale, K, N, x)
+    rms = np.sqrt(np.mean(spec ** 2))
+    assert np.max(np.abs(y.cpu().numpy() - spec)) / rms < 5e-2
+
+
+def test_all_plus_one_kat(ctx):
+    # Tests/CUDA/CUDABitLinearTest.lean:57-71
+    K, N = 128, 8
+    layer = BitLinear.create_from_bytes(ctx, np.full(N * K // 4, 0xAA, np.uint8), 1.0, K, N)
+    y, acc, d = layer.forward(torch.ones(1, K, device="cuda"), return_acc=True)
+    assert torch.all(acc == 127 * K)
+    assert torch.allclose(y, torch.full_like(y, float(K)), rtol=1e-6)
+
+
+@pytest.mark.parametrize("K,N", [(2560, 6912), (6912, 2560), (2560, 2560), (2560, 640),
+                                 (128, 1), (384, 7), (2048, 33), (4096, 1000), (8192, 257)])
+def test_layer_shapes_bit_exact(ctx, oracle, K, N):
+    rng = np.random.default_rng(K * 7 + N)
+    packed = formats.i2s_pack(formats.random_ternary(rng, N, K))
+    scale = float(rng.uniform(0.01, 0.1))
+    x = rng.standard_normal((1, K)).astype(np.float32)
+    y_ref, acc_ref, d_ref = oracle.bitlinear_forward(packed, scale, K, N, x)
+    layer = BitLinear.create_from_bytes(ctx, packed, scale, K, N)
+    y, acc, d = layer.forward(_dev(x), return_acc=True)
+    ctx.check()
+    assert np.array_equal(acc.cpu().numpy(), acc_ref)
+    assert np.array_equal(y.cpu().numpy(), y_ref)
+
+
+@pytest.mark.parametrize("M", [1, 3, 4, 5, 16, 64])
+def test_residual_and_rmsnorm_prologue(ctx, oracle, M):
+    K, N = 2560, 320
+    rng = np.random.default_rng(100 + M)
+    packed = formats.i2s_pack(formats.random_ternary(rng, N, K))
+    scale = 0.037
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    gamma = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    res = rng.standard_normal((M, N)).astype(np.float32)
+    layer = BitLinear.create_from_bytes(ctx, packed, scale, K, N)
+    # residual only
+    y_ref, acc_ref, _ = oracle.bitlinear_forward(packed, scale, K, N, x, residual=res)
+    y, acc, _ = layer.forward_with_residual(_dev(x), _dev(res), return_acc=True)
+    assert np.array_equal(acc.cpu().numpy(), acc_ref)
+    assert np.array_equal(y.cpu().numpy(), y_ref)
+    # RMSNorm prologue + residual
+    y_ref, acc_ref, d_ref = oracle.bitlinear_forward(packed, scale, K, N, x, gamma=gamma, eps=1e-5,
+                                                     residual=res)
+    y, acc, d = layer.forward_fused_rmsnorm_residual(_dev(x), _dev(gamma), _dev(res), eps=1e-5,
+                                                     return_acc=True)
+    ctx.check()
+    assert np.array_equal(d.cpu().numpy(), d_ref)
+    assert np.array_equal(acc.cpu().numpy(), acc_ref)
+    assert np.array_equal(y.cpu().numpy(), y_ref)
+
+
+@pytest.mark.parametrize("K,N,M", [(2560, 6912, 1), (256, 5, 1), (2560, 100, 3), (1024, 64, 8)])
+def test_gate_up_relu2(ctx, oracle, K, N, M):
+    rng = np.random.default_rng(K + N + M)
+    pg = formats.i2s_pack(formats.random_ternary(rng, N, K))
+    pu = formats.i2s_pack(formats.random_ternary(rng, N, K))
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    gamma = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    g = BitLinear.create_from_bytes(ctx, pg, 0.05, K, N)
+    u = BitLinear.create_from_bytes(ctx, pu, 0.03, K, N)
+    for gm in (None, gamma):
+        y_ref = oracle.bitlinear_gateup_relu2(pg, 0.05, pu, 0.03, K, N, x, gamma=gm)
+        y = BitLinear.forward_fused_gate_up_relu_sqr_mul(
+            g, u, _dev(x), rms_gamma=None if gm is None else _dev(gm))
+        ctx.check()
+        assert np.array_equal(y.cpu().numpy(), y_ref)
+
+
+def test_fused_qkv_multi(ctx, oracle):
+    K = 2560
+    rng = np.random.default_rng(5)
+    shapes = [2560, 640, 640]
+    packs = [formats.i2s_pack(formats.random_ternary(rng, n, K)) for n in shapes]
+    scales = [0.02, 0.05, 0.08]
+    x = rng.standard_normal((1, K)).astype(np.float32)
+    gamma = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    layers = [BitLinear.create_from_bytes(ctx, p, s, K, n) for p, s, n in zip(packs, scales, shapes)]
+    ys, accs = BitLinear.forward_multi(layers, _dev(x), rms_gamma=_dev(gamma), return_acc=True)
+    ctx.check()
+    for p, s, n, y, a in zip(packs, scales, shapes, ys, accs):
+        y_ref, acc_ref, _ = oracle.bitlinear_forward(p, s, K, n, x, gamma=gamma)
+        assert np.array_equal(a.cpu().numpy(), acc_ref)
+        assert np.array_equal(y.cpu().numpy(), y_ref)
+
+
+def test_zero_input_and_determinism(ctx, oracle):
+    K, N = 2560, 6912
+    rng = np.random.default_rng(9)
+    packed = formats.i2s_pack(formats.random_ternary(rng, N, K))
+    layer = BitLinear.create_from_bytes(ctx, packed, 0.05, K, N)
+    y, acc, d = layer.forward(torch.zeros(1, K, device="cuda"), return_acc=True)
+    assert not acc.any() and not y.any() and d.item() == 0.0
+    x = _dev(rng.standard_normal((1, K)).astype(np.float32))
+    a = layer.forward(x)
+    b = layer.forward(x)
+    assert torch.equal(a, b)
+
+
+def test_linearity_property_full_size(ctx):
+    """Size-independent check at the benchmark shape: acc(W, q) is linear in the
+    weights' sign, so acc(W) + acc(-W) = 0 for the same activations."""
+    K, N = 2560, 6912
+    rng = np.random.default_rng(11)
+    t = formats.random_ternary(rng, N, K)
+    x = _dev(rng.standard_normal((1, K)).astype(np.float32))
+    a = BitLinear.create_from_bytes(ctx, formats.i2s_pack(t), 1.0, K, N).forward(x, return_acc=True)[1]
+    b = BitLinear.create_from_bytes(ctx, formats.i2s_pack(-t), 1.0, K, N).forward(x, return_acc=True)[1]
+    assert not (a + b).any()
+
+
+def test_bad_arguments_fail_loudly(ctx):
+    from hesper_b200 import HesperB200Error
+    layer = BitLinear.create_from_bytes(ctx, np.zeros(128 * 4 // 4, np.uint8), 1.0, 128, 4)
+    with pytest.raises(HesperB200Error):
+        layer.in_dim = 100  # not a multiple of 128
+        layer.forward(torch.zeros(100, device="cuda"))
