@@ -43,6 +43,7 @@ SIGNATURES = {
     "hb200_version": (_i, []),
     "hb200_ctx_sm_count": (_i, [_vp]),
     "hb200_ctx_check": (_i, [_vp, _vp, C.POINTER(C.c_uint32)]),
+    "hb200_ctx_read_status": (_i, [_vp, _vp, C.POINTER(C.c_uint32)]),
     "hb200_bitlinear_forward": (_i, [_vp, _vp, _vp, _i, _i, _vp, _i, _vp, _f, _vp, _vp, _vp, _vp, _vp]),
     "hb200_bitlinear_forward_multi": (_i, [_vp, C.POINTER(BitLinearSeg), _i, _i, _vp, _i, _vp, _f, _vp, _vp]),
     "hb200_bitlinear_gateup_relu2": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _f, _vp, _vp]),

@@ -52,12 +52,12 @@ extern "C" int hb200_ctx_create(int device, hb200_ctx** out) {
   c->pdl = true;
   const char* env = getenv("HB200_NO_PDL");
   if (env && env[0] == '1') c->pdl = false;
-  cudaError_t e = cudaMalloc(&c->d_status, 64);
+  cudaError_t e = cudaMalloc(&c->d_status, 256);
   if (e != cudaSuccess) {
     delete c;
     return cuda_fail(e, "cudaMalloc(status)");
   }
-  e = cudaMemset(c->d_status, 0, 64);
+  e = cudaMemset(c->d_status, 0, 256);
   if (e != cudaSuccess) {
     cudaFree(c->d_status);
     delete c;
@@ -83,9 +83,16 @@ extern "C" int hb200_ctx_check(hb200_ctx* ctx, hb200_stream stream, uint32_t* fl
   HB_CUDA(cudaMemcpy(host, ctx->d_status, sizeof(host), cudaMemcpyDeviceToHost));
   if (flags) *flags = host[0];
   if (host[0] != 0) {
-    HB_CUDA(cudaMemset(ctx->d_status, 0, 64));
+    HB_CUDA(cudaMemset(ctx->d_status, 0, 256));
     set_error("device status 0x%x: a bounded wait inside a kernel expired", host[0]);
     return HB200_ERR_TIMEOUT;
   }
+  return HB200_OK;
+}
+
+extern "C" int hb200_ctx_read_status(hb200_ctx* ctx, hb200_stream stream, uint32_t words[64]) {
+  HB_REQUIRE(ctx != nullptr && words != nullptr, "ctx_read_status: null argument");
+  HB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  HB_CUDA(cudaMemcpy(words, ctx->d_status, 256, cudaMemcpyDeviceToHost));
   return HB200_OK;
 }

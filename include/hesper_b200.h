@@ -56,7 +56,7 @@ typedef void *hb200_stream;
 /* Replaces CUDAContext.init (Hesper/Backend/CUDA.lean:46; native/cuda_bridge.cpp:78-82)
  * for this path only: binds to `device` (its primary context), reads the SM
  * count, raises the kernels' dynamic shared-memory limits and allocates one
- * 64-byte device status block.  No other allocation happens later. */
+ * 256-byte device status block.  No other allocation happens later. */
 int hb200_ctx_create(int device, hb200_ctx **out);
 int hb200_ctx_destroy(hb200_ctx *ctx);
 
@@ -74,6 +74,10 @@ int hb200_ctx_sm_count(const hb200_ctx *ctx);
  * *flags != 0 means a kernel's bounded wait expired (HB200_ERR_TIMEOUT is
  * returned as well).  For tests and diagnostics; not on the hot path. */
 int hb200_ctx_check(hb200_ctx *ctx, hb200_stream stream, uint32_t *flags);
+
+/* Synchronises `stream` and copies the raw 64-word status block to `words`
+ * without clearing it (word 0 = flags; the rest is kernel debug scratch). */
+int hb200_ctx_read_status(hb200_ctx *ctx, hb200_stream stream, uint32_t words[64]);
 
 /* ---- BitLinear: ternary i2_s weights x int8 activations ------------------- */
 

@@ -268,9 +268,12 @@ ORC_API void orc_rmsnorm_f32(const float *x, const float *gamma, int K, float ep
 }
 
 /* Per-token absmax int8 quantiser.  Rule of the reference's Q8_1 quantiser
- * (Hesper/Layers/Linear.lean:1023-1048; rounding = cvt.rni, Hesper/CUDA/PTX.lean:484)
- * applied to a whole token instead of a 32-block: d = amax/127 (f32),
- * q = rint_ties_even(x/d) in f32, d == 0 -> q = 0.  Returns d. */
+ * (Hesper/Layers/Linear.lean:1023-1048: d = amax/127, round to nearest even as
+ * cvt.rni, Hesper/CUDA/PTX.lean:484; amax == 0 -> q = 0) applied to a whole token
+ * instead of a 32-block, with the division by d carried out as one multiplication
+ * by the f32 reciprocal scale:  d = amax/127,  inv = 127/amax (both IEEE f32
+ * divisions),  q = rint_ties_even(x * inv).  |x*inv| <= 127*(1+2^-23), so no
+ * clamp is needed.  Returns d, the scale the outputs are multiplied by. */
 ORC_API float orc_quant_act_i8(const float *x, int K, int8_t *q) {
   float amax = 0.0f;
   for (int k = 0; k < K; ++k) {
@@ -278,8 +281,9 @@ ORC_API float orc_quant_act_i8(const float *x, int K, int8_t *q) {
     if (a > amax) amax = a;
   }
   float d = amax / 127.0f;
+  float inv = (amax == 0.0f) ? 0.0f : 127.0f / amax;
   for (int k = 0; k < K; ++k) {
-    float v = (d == 0.0f) ? 0.0f : x[k] / d;
+    float v = x[k] * inv;
     q[k] = (int8_t)(int)rintf(v); /* default rounding mode = ties-to-even */
   }
   return d;
