@@ -1,10 +1,427 @@
-// placeholder until the attention kernels land
+// attention.cu -- split-K GQA decode attention over an f16 KV cache for sm_100a.
+//
+// What it computes: for every sequence b and query head h, softmax(scale * q.K^T) V
+// over the cached positions [max(0, len - window), len), i.e. the single-head
+// definition of Hesper/Training/VerifiedBackward.lean:134-142 /
+// Hesper/WGSL/FlashAttention.lean:60-90 with the GQA head map of
+// Hesper/WGSL/FlashAttentionExperiments.lean:71-72.  The reference's production
+// kernel for this is flashAttentionVecParamsKernelV11 (+ combine) in that file
+// (:45, :495, launcher :572): one workgroup per Q head, so a KV head is re-read
+// by each of its Q heads, 8 splits at most, and no batch dimension.
+//
+// How it runs on B200:
+//   * one CTA per (sequence, KV head, split): all G = H/Hkv query heads of the KV
+//     head share every K/V byte read from HBM;
+//   * each of the 4 warps streams its own 16-position chunks global->shared with
+//     16-byte cp.async copies into an XOR-swizzled layout (conflict-free for
+//     ldmatrix), 2 chunks in flight per warp, no CTA-wide barrier in the loop;
+//   * scores and outputs run on the tensor cores in the transposed orientation:
+//     S^T[pos,head] = K[pos,:] . Q^T and O^T[dim,head] = V^T[dim,pos] . P^T, so the
+//     16 rows of an m16n8k16 MMA are all real positions / dims and the 8 columns
+//     hold the query heads; P^T reaches the B-operand layout with movmatrix;
+//     accumulation is f32, the online softmax works in the exp2 domain;
+//   * the 4 warps merge through shared memory; with one split the CTA writes the
+//     normalised output itself, otherwise it writes (max, sum, unnormalised out)
+//     to the workspace and a small combine kernel merges the splits.
+#include <math_constants.h>
+
 #include "common.cuh"
+
+namespace hb {
+
+constexpr int kAttnWarps = 4;
+constexpr int kAttnThreads = kAttnWarps * 32;
+constexpr int kChunk = 16;       // positions per warp step
+constexpr int kMaxSplits = 64;
+
+struct AttnParams {
+  const void* q;
+  const __half* k;
+  const __half* v;
+  const int32_t* seqlens;
+  float* out;        // [B][H][D]
+  float* part_out;   // [B][Hkv][nsplit][8][D]  unnormalised, f32
+  float* part_meta;  // [B][Hkv][nsplit][8][2]  (max in the exp2 domain, sum)
+  int q_is_f16;
+  int B, H, Hkv, G, max_seq, window, nsplit;
+  float scale_log2;  // scale * log2(e)
+};
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const uint32_t n = valid ? 16u : 0u;  // src-size 0: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src),
+               "r"(n)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ uint32_t movmatrix_t(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int D>
+struct AttnCfg {
+  static constexpr int kStages = D >= 256 ? 3 : 4;
+  static constexpr int kRowBytes = D * 2;
+  static constexpr int kTileBytes = kChunk * kRowBytes;  // one of K or V
+  static constexpr int kStageBytes = 2 * kTileBytes;
+  static constexpr int kQBytes = 8 * D * 2;              // Q as f16 [8][D]
+  static constexpr int kSmem = kQBytes + kAttnWarps * kStages * kStageBytes;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __grid_constant__ AttnParams p) {
+  using Cfg = AttnCfg<D>;
+  constexpr int NS = Cfg::kStages;
+  constexpr int CPR = D / 8;   // 16-byte chunks per row
+  constexpr int KS = D / 16;   // k-steps of the score product = m-tiles of the output
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+
+  const int split = blockIdx.x % p.nsplit;
+  const int kvh = (blockIdx.x / p.nsplit) % p.Hkv;
+  const int b = blockIdx.x / (p.nsplit * p.Hkv);
+  const int G = p.G;
+
+  __half* qs = reinterpret_cast<__half*>(smem);  // [8][D], heads >= G are zero
+  uint8_t* stage0 = smem + Cfg::kQBytes + (size_t)warp * NS * Cfg::kStageBytes;
+
+  pdl_trigger();
+  pdl_wait();  // q, the cache and seqlens come from earlier kernels of the step
+
+  const int len = p.seqlens[b];
+  int start = 0;
+  if (p.window > 0 && len > p.window) start = len - p.window;
+  const int nch = (len - start + kChunk - 1) / kChunk;  // chunks of this sequence (<= 0 if empty)
+  const int cps = (nch + p.nsplit - 1) / p.nsplit;      // chunks per split
+  const int c_begin = split * cps;
+  const int c_end = min(nch, c_begin + cps);
+
+  const __half* kbase = p.k + ((size_t)b * p.Hkv + kvh) * (size_t)p.max_seq * D;
+  const __half* vbase = p.v + ((size_t)b * p.Hkv + kvh) * (size_t)p.max_seq * D;
+
+  // chunk c -> stage: rows of 16 positions, 16-byte units XOR-swizzled by (row & 7)
+  auto issue = [&](int c, int st) {
+    uint8_t* ks = stage0 + (size_t)st * Cfg::kStageBytes;
+    uint8_t* vs = ks + Cfg::kTileBytes;
+    const int pos0 = start + c * kChunk;
+#pragma unroll
+    for (int i = 0; i < kChunk * CPR / 32; ++i) {
+      const int qd = lane + 32 * i;
+      const int row = qd / CPR, cc = qd % CPR;
+      const int pos = pos0 + row;
+      const bool ok = pos < len;
+      const size_t goff = (size_t)(ok ? pos : 0) * D + cc * 8;
+      const int soff = row * Cfg::kRowBytes + ((cc ^ (row & 7)) << 4);
+      cp_async16(ks + soff, kbase + goff, ok);
+      cp_async16(vs + soff, vbase + goff, ok);
+    }
+  };
+
+  // prefetch this warp's first NS-1 chunks
+  int cnext = c_begin + warp;
+#pragma unroll
+  for (int i = 0; i < NS - 1; ++i) {
+    if (cnext < c_end) issue(cnext, i);
+    cp_async_commit();
+    cnext += kAttnWarps;
+  }
+
+  // Q -> f16, pre-multiplied by scale*log2(e), heads >= G zero
+  {
+    const size_t qoff = ((size_t)b * p.H + (size_t)kvh * G) * D;
+    for (int i = tid; i < 8 * D; i += kAttnThreads) {
+      const int h = i / D;
+      float v = 0.f;
+      if (h < G)
+        v = p.q_is_f16 ? __half2float(reinterpret_cast<const __half*>(p.q)[qoff + i])
+                       : reinterpret_cast<const float*>(p.q)[qoff + i];
+      qs[i] = __float2half_rn(v * p.scale_log2);
+    }
+  }
+  __syncthreads();
+  uint32_t qb[KS][2];  // B fragments of Q^T: head g, dims 16s+2t(+1) and 16s+2t+8(+9)
+#pragma unroll
+  for (int s = 0; s < KS; ++s) {
+    qb[s][0] = *reinterpret_cast<const uint32_t*>(qs + g * D + 16 * s + 2 * t);
+    qb[s][1] = *reinterpret_cast<const uint32_t*>(qs + g * D + 16 * s + 2 * t + 8);
+  }
+
+  // online softmax state of heads 2t and 2t+1 (replicated over g), exp2 domain
+  float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+  float o[KS][4];  // O^T: dims 16s+g (+8), heads 2t (+1)
+#pragma unroll
+  for (int s = 0; s < KS; ++s) o[s][0] = o[s][1] = o[s][2] = o[s][3] = 0.f;
+
+  int it = 0;
+  for (int c = c_begin + warp; c < c_end; c += kAttnWarps, ++it) {
+    // keep NS-1 chunks in flight
+    if (cnext < c_end) issue(cnext, (it + NS - 1) % NS);
+    cp_async_commit();
+    cnext += kAttnWarps;
+    cp_async_wait<NS - 1>();
+    __syncwarp();
+
+    const uint8_t* ks = stage0 + (size_t)(it % NS) * Cfg::kStageBytes;
+    const uint8_t* vs = ks + Cfg::kTileBytes;
+
+    // ---- S^T = K . Q^T : two accumulation chains to shorten the dependency ----
+    float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+      const int row = lane & 15, hi = lane >> 4;
+      const uint8_t* rbase = ks + row * Cfg::kRowBytes;
+#pragma unroll
+      for (int s = 0; s < KS; s += 2) {
+        uint32_t a[4];
+        ldsm_x4(a, rbase + (((2 * s + hi) ^ (row & 7)) << 4));
+        mma16816(sa, a, qb[s][0], qb[s][1]);
+        ldsm_x4(a, rbase + (((2 * s + 2 + hi) ^ (row & 7)) << 4));
+        mma16816(sb, a, qb[s + 1][0], qb[s + 1][1]);
+      }
+    }
+    const int pos0 = start + c * kChunk;
+    const bool v0 = pos0 + g < len, v1 = pos0 + g + 8 < len;
+    const float s00 = v0 ? sa[0] + sb[0] : -CUDART_INF_F;  // (pos g,   head 2t)
+    const float s01 = v0 ? sa[1] + sb[1] : -CUDART_INF_F;  // (pos g,   head 2t+1)
+    const float s10 = v1 ? sa[2] + sb[2] : -CUDART_INF_F;  // (pos g+8, head 2t)
+    const float s11 = v1 ? sa[3] + sb[3] : -CUDART_INF_F;  // (pos g+8, head 2t+1)
+
+    // ---- online softmax over the 16 positions (over g: lane bits 2..4) ---------
+    float mx0 = fmaxf(s00, s10), mx1 = fmaxf(s01, s11);
+#pragma unroll
+    for (int o_ = 4; o_ < 32; o_ <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o_));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o_));
+    }
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float base0 = mn0 == -CUDART_INF_F ? 0.f : mn0;  // nothing valid yet: avoid inf-inf
+    const float base1 = mn1 == -CUDART_INF_F ? 0.f : mn1;
+    const float al0 = exp2f(m0 - base0), al1 = exp2f(m1 - base1);
+    const float p00 = exp2f(s00 - base0), p01 = exp2f(s01 - base1);
+    const float p10 = exp2f(s10 - base0), p11 = exp2f(s11 - base1);
+    float sum0 = p00 + p10, sum1 = p01 + p11;
+#pragma unroll
+    for (int o_ = 4; o_ < 32; o_ <<= 1) {
+      sum0 += __shfl_xor_sync(0xffffffffu, sum0, o_);
+      sum1 += __shfl_xor_sync(0xffffffffu, sum1, o_);
+    }
+    l0 = l0 * al0 + sum0;
+    l1 = l1 * al1 + sum1;
+    m0 = mn0;
+    m1 = mn1;
+
+    // P^T into the B-operand layout: (pos 2t,2t+1 | head g) and (pos 2t+8,2t+9 | head g)
+    const uint32_t pb0 = movmatrix_t(pack_h2(p00, p01));
+    const uint32_t pb1 = movmatrix_t(pack_h2(p10, p11));
+
+    // ---- O^T = O^T*alpha + V^T . P^T ---------------------------------------------
+    {
+      const int mi = lane >> 3;
+      const int row = (lane & 7) + ((mi >> 1) << 3);
+      const uint8_t* rbase = vs + row * Cfg::kRowBytes;
+#pragma unroll
+      for (int s = 0; s < KS; ++s) {
+        uint32_t a[4];
+        ldsm_x4_t(a, rbase + (((2 * s + (mi & 1)) ^ (row & 7)) << 4));
+        o[s][0] *= al0;
+        o[s][1] *= al1;
+        o[s][2] *= al0;
+        o[s][3] *= al1;
+        mma16816(o[s], a, pb0, pb1);
+      }
+    }
+    __syncwarp();  // the stage may be refilled by the next iteration's copies
+  }
+  cp_async_wait<0>();
+  __syncthreads();  // every warp is done with its stages: reuse them for the merge
+
+  // ---- merge the 4 warps ---------------------------------------------------------
+  float* mo = reinterpret_cast<float*>(smem + Cfg::kQBytes);  // [warps][8 heads][D]
+  float* mm = mo + kAttnWarps * 8 * D;                         // [warps][8][2]
+#pragma unroll
+  for (int s = 0; s < KS; ++s) {
+    float* base = mo + (size_t)warp * 8 * D;
+    base[(2 * t) * D + 16 * s + g] = o[s][0];
+    base[(2 * t + 1) * D + 16 * s + g] = o[s][1];
+    base[(2 * t) * D + 16 * s + g + 8] = o[s][2];
+    base[(2 * t + 1) * D + 16 * s + g + 8] = o[s][3];
+  }
+  if (g == 0) {
+    float* mb = mm + (size_t)warp * 16;
+    mb[(2 * t) * 2] = m0;
+    mb[(2 * t) * 2 + 1] = l0;
+    mb[(2 * t + 1) * 2] = m1;
+    mb[(2 * t + 1) * 2 + 1] = l1;
+  }
+  __syncthreads();
+  for (int i = tid; i < G * D; i += kAttnThreads) {
+    const int h = i / D, d = i % D;
+    float mstar = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) mstar = fmaxf(mstar, mm[w * 16 + h * 2]);
+    float acc = 0.f, lsum = 0.f;
+    if (mstar != -CUDART_INF_F) {
+#pragma unroll
+      for (int w = 0; w < kAttnWarps; ++w) {
+        const float wgt = exp2f(mm[w * 16 + h * 2] - mstar);
+        acc += wgt * mo[((size_t)w * 8 + h) * D + d];
+        lsum += wgt * mm[w * 16 + h * 2 + 1];
+      }
+    }
+    if (p.nsplit == 1) {
+      p.out[((size_t)b * p.H + (size_t)kvh * G + h) * D + d] = lsum > 0.f ? acc / lsum : 0.f;
+    } else {
+      const size_t pi = (((size_t)b * p.Hkv + kvh) * p.nsplit + split) * 8 + h;
+      p.part_out[pi * D + d] = acc;
+      if (d == 0) {
+        p.part_meta[pi * 2] = mstar;
+        p.part_meta[pi * 2 + 1] = lsum;
+      }
+    }
+  }
+}
+
+// Merges the split partials: out = sum_s 2^(m_s - m*) O_s / sum_s 2^(m_s - m*) l_s.
+// Same role as flashAttentionVecCombineKernel (Hesper/WGSL/FlashAttentionExperiments.lean:495).
+__global__ void attn_combine_kernel(const __grid_constant__ AttnParams p, int D) {
+  pdl_trigger();
+  pdl_wait();
+  const int h = blockIdx.x % p.G;
+  const int kvh = (blockIdx.x / p.G) % p.Hkv;
+  const int b = blockIdx.x / (p.G * p.Hkv);
+  const size_t base = ((size_t)b * p.Hkv + kvh) * p.nsplit;
+  float mstar = -CUDART_INF_F;
+  for (int s = 0; s < p.nsplit; ++s) mstar = fmaxf(mstar, p.part_meta[((base + s) * 8 + h) * 2]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f, lsum = 0.f;
+    if (mstar != -CUDART_INF_F) {
+      for (int s = 0; s < p.nsplit; ++s) {
+        const size_t pi = (base + s) * 8 + h;
+        const float wgt = exp2f(p.part_meta[pi * 2] - mstar);
+        acc += wgt * p.part_out[pi * D + d];
+        lsum += wgt * p.part_meta[pi * 2 + 1];
+      }
+    }
+    p.out[((size_t)b * p.H + (size_t)kvh * p.G + h) * D + d] = lsum > 0.f ? acc / lsum : 0.f;
+  }
+}
+
+// Splits per (sequence, KV head): enough CTAs for a few waves over the SMs, but
+// no split shorter than 8 chunks (128 positions) and at most kMaxSplits.
+static int attn_pick_splits(const hb200_ctx* ctx, int B, int Hkv, int max_len) {
+  const long pairs = (long)B * Hkv;
+  const int chunks = (max_len + kChunk - 1) / kChunk;
+  long want = (4L * ctx->sm_count + pairs - 1) / pairs;
+  long cap = chunks / 8;
+  if (cap < 1) cap = 1;
+  if (want > cap) want = cap;
+  if (want > kMaxSplits) want = kMaxSplits;
+  if (want < 1) want = 1;
+  return (int)want;
+}
+
+template <int D>
+static int attn_launch(hb200_ctx* ctx, const AttnParams& p, cudaStream_t st) {
+  using Cfg = AttnCfg<D>;
+  auto kern = attn_decode_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    HB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+    configured = true;
+  }
+  const int grid = p.B * p.Hkv * p.nsplit;
+  HB_CUDA(launch_pdl(kern, dim3(grid), dim3(kAttnThreads), (size_t)Cfg::kSmem, st, ctx->pdl, p));
+  if (p.nsplit > 1) {
+    HB_CUDA(launch_pdl(attn_combine_kernel, dim3(p.B * p.H), dim3(D >= 128 ? 128 : 64), 0, st,
+                       ctx->pdl, p, D));
+  }
+  return HB200_OK;
+}
+
+}  // namespace hb
+
 using namespace hb;
-extern "C" size_t hb200_attn_workspace_bytes(const hb200_ctx*, int, int, int, int, int) { return 0; }
-extern "C" int hb200_attn_decode(hb200_ctx*, const void*, int, const void*, const void*,
-                                 const int32_t*, int, int, int, int, int, int, float, void*, size_t,
-                                 float*, hb200_stream) {
-  set_error("attention: not built yet");
-  return HB200_ERR_UNSUPPORTED;
+
+extern "C" size_t hb200_attn_workspace_bytes(const hb200_ctx* ctx, int B, int H, int Hkv, int D,
+                                             int max_seq) {
+  if (!ctx || B < 1 || Hkv < 1 || D < 1) return 0;
+  (void)H;
+  const int ns = attn_pick_splits(ctx, B, Hkv, max_seq);
+  return (size_t)B * Hkv * ns * 8 * ((size_t)D + 2) * sizeof(float) + 256;
+}
+
+extern "C" int hb200_attn_decode(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d_k,
+                                 const void* d_v, const int32_t* d_seqlens, int B, int H, int Hkv,
+                                 int D, int max_seq, int window, float scale, void* d_workspace,
+                                 size_t workspace_bytes, float* d_out, hb200_stream stream) {
+  HB_REQUIRE(ctx != nullptr, "attn: null context");
+  HB_REQUIRE(d_q && d_k && d_v && d_seqlens && d_out, "attn: null pointer");
+  HB_REQUIRE(B >= 1 && H >= 1 && Hkv >= 1 && H % Hkv == 0, "attn: B=%d H=%d Hkv=%d", B, H, Hkv);
+  const int G = H / Hkv;
+  HB_REQUIRE(G <= 8, "attn: %d query heads per KV head (at most 8)", G);
+  HB_REQUIRE(D == 64 || D == 128 || D == 256, "attn: head_dim %d not in {64,128,256}", D);
+  HB_REQUIRE(max_seq >= 1 && window >= 0, "attn: max_seq=%d window=%d", max_seq, window);
+  HB_REQUIRE(((reinterpret_cast<uintptr_t>(d_k) | reinterpret_cast<uintptr_t>(d_v)) & 15) == 0,
+             "attn: K/V cache must be 16-byte aligned");
+  AttnParams p = {};
+  p.q = d_q;
+  p.k = static_cast<const __half*>(d_k);
+  p.v = static_cast<const __half*>(d_v);
+  p.seqlens = d_seqlens;
+  p.out = d_out;
+  p.q_is_f16 = q_is_f16;
+  p.B = B;
+  p.H = H;
+  p.Hkv = Hkv;
+  p.G = G;
+  p.max_seq = max_seq;
+  p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const int eff_len = (window > 0 && window < max_seq) ? window : max_seq;
+  p.nsplit = attn_pick_splits(ctx, B, Hkv, eff_len);
+  if (p.nsplit > 1) {
+    const size_t po = (size_t)B * Hkv * p.nsplit * 8 * (size_t)D * sizeof(float);
+    const size_t need = po + (size_t)B * Hkv * p.nsplit * 8 * 2 * sizeof(float);
+    HB_REQUIRE(d_workspace != nullptr && workspace_bytes >= need,
+               "attn: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    HB_REQUIRE((reinterpret_cast<uintptr_t>(d_workspace) & 15) == 0,
+               "attn: workspace must be 16-byte aligned");
+    p.part_out = static_cast<float*>(d_workspace);
+    p.part_meta = reinterpret_cast<float*>(static_cast<uint8_t*>(d_workspace) + po);
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (D) {
+    case 64: return attn_launch<64>(ctx, p, st);
+    case 128: return attn_launch<128>(ctx, p, st);
+    default: return attn_launch<256>(ctx, p, st);
+  }
 }

@@ -15,7 +15,7 @@
 //     this layer fly while the previous kernel finishes;
 //   * the integer pipe does the dot products: activations are block-quantised per
 //     32 elements to 16 bits (x ~ dx * (256*hi + lo), hi int8, lo uint8), which is
-//     finer than f16 and keeps the result within 1e-4 of the f64 oracle, while a
+//     finer than f16 and keeps the result within 1e-4 of an f64 evaluation, while a
 //     4-bit quant needs only one AND per 4 weights (the high nibble is used in
 //     place, its factor 16 folded into the activation scale) and two dp4a;
 //   * the work unit of a lane is one 64-weight chunk (a Q4_K sub-block pair or two
