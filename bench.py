@@ -152,6 +152,8 @@ def build_ring(torch, ctx, fmt, K, N, R, seed):
 
 def time_graph(torch, st, fn, steps, warmup):
     """Capture fn() on stream st, replay warmup + steps times, return seconds per step."""
+    # inputs were produced on the default stream: order the side stream after them
+    torch.cuda.synchronize()
     with torch.cuda.stream(st):
         fn()
         st.synchronize()

@@ -11,4 +11,6 @@ from .layers import (  # noqa: F401
     execute_flash_attention_v11, flash_attention_workspace,
 )
 
+from .models import BitNetModel, BitNetShape, random_bitnet_weights  # noqa: F401
+
 __version__ = "0.1.0"

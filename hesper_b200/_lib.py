@@ -28,6 +28,19 @@ class BitLinearSeg(C.Structure):
                 ("d_y", C.c_void_p), ("d_acc", C.c_void_p), ("N", C.c_int)]
 
 
+class BitNetConfig(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("n_layers", "hidden", "n_heads", "n_kv_heads", "head_dim",
+                                       "ffn", "vocab", "max_seq")] + \
+               [("rope_base", C.c_float), ("rms_eps", C.c_float)]
+
+
+class BitNetLayer(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in (
+        "attn_norm", "attn_sub_norm", "ffn_norm", "ffn_sub_norm",
+        "wq", "wk", "wv", "wo", "wgate", "wup", "wdown",
+        "sq", "sk", "sv", "so", "sgate", "sup", "sdown")]
+
+
 class KQuantSeg(C.Structure):
     _fields_ = [("d_blocks", C.c_void_p), ("d_residual", C.c_void_p), ("d_y", C.c_void_p),
                 ("N", C.c_int)]
@@ -51,6 +64,22 @@ SIGNATURES = {
     "hb200_kquant_forward_multi": (_i, [_vp, _i, C.POINTER(KQuantSeg), _i, _i, _vp, _i, _vp, _f, _vp]),
     "hb200_kquant_gateup_gelu": (_i, [_vp, _i, _vp, _vp, _i, _i, _vp, _i, _vp, _f, _vp, _vp]),
     "hb200_attn_workspace_bytes": (_sz, [_vp, _i, _i, _i, _i, _i]),
+    "hb200_embed_lookup": (_i, [_vp, _vp, _i, C.c_long, _i, _vp, _i, _f, _vp, _vp]),
+    "hb200_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _f, _i, _i, _vp, _vp]),
+    "hb200_rope_kv_write": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
+    "hb200_argmax": (_i, [_vp, _vp, C.c_long, _i, _vp, _vp]),
+    "hb200_lmhead_scratch_bytes": (_sz, [_i]),
+    "hb200_lmhead_argmax": (_i, [_vp, _vp, _i, C.c_long, _i, _vp, _i, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "hb200_relu2_mul": (_i, [_vp, _vp, _vp, C.c_long, _vp, _vp]),
+    "hb200_gelu_mul": (_i, [_vp, _vp, _vp, C.c_long, _vp, _vp]),
+    "hb200_add_i32": (_i, [_vp, _vp, _i, _i, _vp]),
+    "hb200_bitnet_create": (_i, [_vp, C.POINTER(BitNetConfig), C.POINTER(BitNetLayer), _vp, _i, _vp, _i, _i, C.POINTER(_vp)]),
+    "hb200_bitnet_destroy": (_i, [_vp]),
+    "hb200_bitnet_reset": (_i, [_vp, _vp]),
+    "hb200_bitnet_step": (_i, [_vp, _vp, _i, _vp]),
+    "hb200_bitnet_logits": (_vp, [_vp]),
+    "hb200_bitnet_tokens": (_vp, [_vp]),
+    "hb200_bitnet_generate": (_i, [_vp, _vp, _i, _i, _i, _vp, C.POINTER(_f), C.POINTER(_f), _vp]),
     "hb200_attn_decode": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp, _vp]),
 }
 

@@ -118,7 +118,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __gr
   pdl_trigger();
   pdl_wait();  // q, the cache and seqlens come from earlier kernels of the step
 
-  const int len = p.seqlens[b];
+  // a length outside [0, max_seq] can only come from a corrupt input: clamp, never overrun
+  const int len = min(max(p.seqlens[b], 0), p.max_seq);
   int start = 0;
   if (p.window > 0 && len > p.window) start = len - p.window;
   const int nch = (len - start + kChunk - 1) / kChunk;  // chunks of this sequence (<= 0 if empty)

@@ -186,6 +186,117 @@ int hb200_attn_decode(hb200_ctx *ctx, const void *d_q, int q_is_f16, const void 
                       int D, int max_seq, int window, float scale, void *d_workspace,
                       size_t workspace_bytes, float *d_out, hb200_stream stream);
 
+
+/* ---- decode-step glue ------------------------------------------------------- */
+
+/* y[m] = table[ids[m]] * scale as f32.  dtype: 0 = bf16, 1 = f16, 2 = f32.
+ * Replaces embeddingLookupKernel (Hesper/Layers/Embedding.lean:116). */
+int hb200_embed_lookup(hb200_ctx *ctx, const void *d_table, int dtype, long V, int K,
+                       const int32_t *d_ids, int M, float scale, float *d_y,
+                       hb200_stream stream);
+
+/* y[m] = (d_add ? d_add[m] : 0) + RMSNorm(x[m]) * gamma.  Replaces RMSNorm.forward and
+ * forwardNormThenAdd (Hesper/Layers/RMSNorm.lean:219,794); formula
+ * Hesper/Training/VerifiedBackward.lean:95-99. */
+int hb200_rmsnorm(hb200_ctx *ctx, const float *d_x, const float *d_gamma, const float *d_add,
+                  float eps, int M, int K, float *d_y, hb200_stream stream);
+
+/* NeoX RoPE (pairs d, d + D/2; angle pos * base^(-2i/D)) on q in place and on k, then
+ * k and v packed to f16 and written into the caches at the token's position.
+ * Replaces ropeKernelDynamic (Hesper/Layers/RoPE.lean:189) + the f16 KV writers
+ * fusedRopeKAndCacheWriteKernelF16 / kvWriteBatchKernelF16 (Hesper/Layers/Attention.lean:701-945).
+ *   d_q [B][H][D] f32, d_k / d_v [B][Hkv][D] f32, caches [B][Hkv][cache_slots][D] f16,
+ *   d_pos [B] int32.  ring != 0 writes slot pos % cache_slots (sliding-window layers). */
+int hb200_rope_kv_write(hb200_ctx *ctx, float *d_q, const float *d_k, const float *d_v,
+                        void *d_k_cache, void *d_v_cache, const int32_t *d_pos, int B, int H,
+                        int Hkv, int D, int cache_slots, int ring, float rope_base,
+                        hb200_stream stream);
+
+/* Greedy argmax over [M][V] logits, first strict maximum.  Replaces argmaxKernel
+ * (Hesper/Models/BitNet.lean:456-479). */
+int hb200_argmax(hb200_ctx *ctx, const float *d_logits, long V, int M, int32_t *d_out,
+                 hb200_stream stream);
+
+/* LM head over a 16-bit table [V][K] (dtype 0 = bf16, 1 = f16) with the final RMSNorm
+ * fused in front (d_rms_gamma nullable) and the greedy argmax fused behind.
+ * Replaces executeMatMulTransposeF16Shared + gpuArgmax (Hesper/Models/BitNet.lean:437-521).
+ *   d_logits   nullable [M][V]
+ *   d_argmax   [M] token ids
+ *   d_scratch  hb200_lmhead_scratch_bytes(M) bytes, zero before the first call (the
+ *              call leaves it zero again)
+ *   d_token_log / d_log_index / log_stride  nullable: token m is also stored at
+ *              d_token_log[m*log_stride + *d_log_index] */
+size_t hb200_lmhead_scratch_bytes(int M);
+int hb200_lmhead_argmax(hb200_ctx *ctx, const void *d_table, int dtype, long V, int K,
+                        const float *d_x, int M, const float *d_rms_gamma, float rms_eps,
+                        float *d_logits, int32_t *d_argmax, void *d_scratch,
+                        int32_t *d_token_log, const int32_t *d_log_index, int log_stride,
+                        hb200_stream stream);
+
+/* y = relu(g)^2 * u (reluSqrMulKernel, Hesper/WGSL/Elementwise.lean:320) and
+ * y = gelu_tanh(g) * u (geluMulKernel, Hesper/Models/Gemma4/Kernels.lean:26). */
+int hb200_relu2_mul(hb200_ctx *ctx, const float *d_gate, const float *d_up, long n, float *d_y,
+                    hb200_stream stream);
+int hb200_gelu_mul(hb200_ctx *ctx, const float *d_gate, const float *d_up, long n, float *d_y,
+                   hb200_stream stream);
+
+/* a[i] += delta for n int32 counters kept on the device (positions, lengths), so a
+ * captured decode step advances without host writes.  The reference rewrites its
+ * params buffer from the host every layer (Hesper/Layers/Attention.lean:1197-1206). */
+int hb200_add_i32(hb200_ctx *ctx, int32_t *d_a, int n, int delta, hb200_stream stream);
+
+/* ---- BitNet-b1.58-shaped decode loop --------------------------------------- */
+
+/* Shape of the model (Hesper/Models/BitNet.lean:189-199 for the 2B configuration). */
+typedef struct hb200_bitnet_config {
+  int n_layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab, max_seq;
+  float rope_base, rms_eps;
+} hb200_bitnet_config;
+
+/* Device pointers of one transformer block; all borrowed.  Weights are i2_s bytes, each
+ * with its one-f32 scale buffer; norms are f32 vectors. */
+typedef struct hb200_bitnet_layer {
+  const float *attn_norm, *attn_sub_norm, *ffn_norm, *ffn_sub_norm;
+  const void *wq, *wk, *wv, *wo, *wgate, *wup, *wdown;
+  const float *sq, *sk, *sv, *so, *sgate, *sup, *sdown;
+} hb200_bitnet_layer;
+
+typedef struct hb200_bitnet hb200_bitnet;
+
+/* Allocates the activations, the f16 KV cache [layer][batch][kv_head][max_seq][head_dim]
+ * and the device-side counters for `batch` sequences decoded in lock step; nothing is
+ * allocated afterwards.  d_embed is the [vocab][hidden] table (dtype 0 = bf16, 1 = f16),
+ * also used as the tied LM head.  max_new_tokens sizes the device token log.
+ * Replaces BitNet model construction + createCachedLayerBuffers / KV cache creation
+ * (Hesper/Models/BitNet.lean:358-398). */
+int hb200_bitnet_create(hb200_ctx *ctx, const hb200_bitnet_config *cfg,
+                        const hb200_bitnet_layer *layers, const void *d_embed, int embed_dtype,
+                        const float *d_final_norm, int batch, int max_new_tokens,
+                        hb200_bitnet **out);
+int hb200_bitnet_destroy(hb200_bitnet *m);
+
+/* Positions back to 0 (the cache content is simply overwritten as decoding proceeds). */
+int hb200_bitnet_reset(hb200_bitnet *m, hb200_stream stream);
+
+/* Enqueues ONE decode step for all sequences: forwardSingleToken
+ * (Hesper/Models/BitNet.lean:403) + gpuArgmax (:456).  d_tokens [batch] int32 are the
+ * input tokens, or NULL to feed back the previous step's argmax.  The step advances the
+ * device-side positions itself and is capturable.  want_logits != 0 also stores the
+ * [batch][vocab] logits (hb200_bitnet_logits). */
+int hb200_bitnet_step(hb200_bitnet *m, const int32_t *d_tokens, int want_logits,
+                      hb200_stream stream);
+const float *hb200_bitnet_logits(const hb200_bitnet *m);
+const int32_t *hb200_bitnet_tokens(const hb200_bitnet *m);
+
+/* generate (Hesper/Models/BitNet.lean:594): prefill as single-token forwards over
+ * h_prompt [batch][prompt_len] (host), then n_new greedy tokens per sequence into h_out
+ * [batch][n_new] (host).  With use_graph the decode step is captured once and replayed.
+ * ms_prefill / ms_decode (nullable) receive device times; ms_decode covers the n_new - 1
+ * steps after the prefill (the first new token is the prefill's argmax). */
+int hb200_bitnet_generate(hb200_bitnet *m, const int32_t *h_prompt, int prompt_len, int n_new,
+                          int use_graph, int32_t *h_out, float *ms_prefill, float *ms_decode,
+                          hb200_stream stream);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

@@ -640,3 +640,90 @@ ORC_API void orc_lmhead_bf16(const uint16_t *table, long V, int K, const float *
     logits[v] = (float)acc;
   }
 }
+
+/* ------------------------------------------------------------------------- */
+/* Whole decode step of a BitNet-b1.58-shaped model                            */
+/* ------------------------------------------------------------------------- */
+
+/* Layer order of TransformerBlock.forwardWithCache (Hesper/Layers/TransformerBlock.lean:439-485)
+ * and Attention.forwardWithCache (Hesper/Layers/Attention.lean:1171-1248):
+ *   attn_norm -> wq,wk,wv -> RoPE(q,k) -> KV append -> attention -> attn_sub_norm ->
+ *   wo + residual -> ffn_norm -> relu(gate)^2*up -> ffn_sub_norm -> down + residual,
+ * then final norm, tied LM head (Hesper/Models/BitNet.lean:431-445) and greedy argmax.
+ * Linear layers follow orc_bitlinear_forward (int8 activations), the KV cache is f16,
+ * the embedding / LM-head table is bf16. */
+typedef struct orc_bitnet_layer {
+  const float *attn_norm, *attn_sub_norm, *ffn_norm, *ffn_sub_norm;
+  const uint8_t *wq, *wk, *wv, *wo, *wgate, *wup, *wdown;
+  float sq, sk, sv, so, sgate, sup, sdown;
+} orc_bitnet_layer;
+
+typedef struct orc_bitnet {
+  int n_layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab, max_seq;
+  double rope_base;
+  float eps;
+  const orc_bitnet_layer *layers;
+  const uint16_t *embed; /* bf16 [vocab][hidden] */
+  const float *final_norm;
+  uint16_t *kcache, *vcache; /* [layer][kv_head][max_seq][head_dim] f16 */
+} orc_bitnet;
+
+ORC_API orc_bitnet *orc_bitnet_create(int n_layers, int hidden, int n_heads, int n_kv_heads,
+                                      int head_dim, int ffn, int vocab, int max_seq,
+                                      double rope_base, float eps, const orc_bitnet_layer *layers,
+                                      const uint16_t *embed, const float *final_norm) {
+  orc_bitnet *m = (orc_bitnet *)calloc(1, sizeof(orc_bitnet));
+  m->n_layers = n_layers; m->hidden = hidden; m->n_heads = n_heads; m->n_kv_heads = n_kv_heads;
+  m->head_dim = head_dim; m->ffn = ffn; m->vocab = vocab; m->max_seq = max_seq;
+  m->rope_base = rope_base; m->eps = eps; m->layers = layers; m->embed = embed;
+  m->final_norm = final_norm;
+  size_t n = (size_t)n_layers * n_kv_heads * max_seq * head_dim;
+  m->kcache = (uint16_t *)calloc(n, 2);
+  m->vcache = (uint16_t *)calloc(n, 2);
+  return m;
+}
+
+ORC_API void orc_bitnet_destroy(orc_bitnet *m) {
+  if (!m) return;
+  free(m->kcache);
+  free(m->vcache);
+  free(m);
+}
+
+/* One token at position `pos`: fills logits[vocab] and returns the greedy token. */
+ORC_API int orc_bitnet_step(orc_bitnet *m, int token, int pos, float *logits) {
+  const int Hd = m->hidden, H = m->n_heads, Hkv = m->n_kv_heads, D = m->head_dim, F = m->ffn;
+  const int qdim = H * D, kvdim = Hkv * D;
+  float *x = (float *)malloc(sizeof(float) * Hd), *x1 = (float *)malloc(sizeof(float) * Hd);
+  float *q = (float *)malloc(sizeof(float) * qdim), *k = (float *)malloc(sizeof(float) * kvdim);
+  float *v = (float *)malloc(sizeof(float) * kvdim), *att = (float *)malloc(sizeof(float) * qdim);
+  float *h = (float *)malloc(sizeof(float) * F);
+  for (int i = 0; i < Hd; ++i) x[i] = orc_bf16_to_f32(m->embed[(size_t)token * Hd + i]);
+  int32_t len = pos + 1;
+  for (int l = 0; l < m->n_layers; ++l) {
+    const orc_bitnet_layer *L = &m->layers[l];
+    orc_bitlinear_forward(L->wq, L->sq, Hd, qdim, 1, x, L->attn_norm, m->eps, NULL, NULL, NULL, q);
+    orc_bitlinear_forward(L->wk, L->sk, Hd, kvdim, 1, x, L->attn_norm, m->eps, NULL, NULL, NULL, k);
+    orc_bitlinear_forward(L->wv, L->sv, Hd, kvdim, 1, x, L->attn_norm, m->eps, NULL, NULL, NULL, v);
+    for (int hh = 0; hh < H; ++hh) orc_rope_neox(q + hh * D, D, pos, m->rope_base);
+    for (int hh = 0; hh < Hkv; ++hh) orc_rope_neox(k + hh * D, D, pos, m->rope_base);
+    uint16_t *kc = m->kcache + (size_t)l * Hkv * m->max_seq * D;
+    uint16_t *vc = m->vcache + (size_t)l * Hkv * m->max_seq * D;
+    for (int hh = 0; hh < Hkv; ++hh)
+      for (int d = 0; d < D; ++d) {
+        kc[((size_t)hh * m->max_seq + pos) * D + d] = orc_f32_to_f16(k[hh * D + d]);
+        vc[((size_t)hh * m->max_seq + pos) * D + d] = orc_f32_to_f16(v[hh * D + d]);
+      }
+    orc_attn_decode(q, 0, kc, vc, &len, 1, H, Hkv, D, m->max_seq, 0,
+                    (float)(1.0 / sqrt((double)D)), att);
+    orc_bitlinear_forward(L->wo, L->so, qdim, Hd, 1, att, L->attn_sub_norm, m->eps, x, NULL, NULL, x1);
+    orc_bitlinear_gateup_relu2(L->wgate, L->sgate, L->wup, L->sup, Hd, F, 1, x1, L->ffn_norm, m->eps, h);
+    orc_bitlinear_forward(L->wdown, L->sdown, F, Hd, 1, h, L->ffn_sub_norm, m->eps, x1, NULL, NULL, x);
+  }
+  float *xn = (float *)malloc(sizeof(float) * Hd);
+  orc_rmsnorm_f32(x, m->final_norm, Hd, m->eps, xn);
+  orc_lmhead_bf16(m->embed, m->vocab, Hd, xn, logits);
+  int tok = orc_argmax(logits, m->vocab);
+  free(x); free(x1); free(q); free(k); free(v); free(att); free(h); free(xn);
+  return tok;
+}

@@ -274,3 +274,52 @@ def lmhead_bf16(table_u16, x):
 
 def gelu_tanh(x: float) -> float:
     return float(lib().orc_gelu_tanh(C.c_double(x)))
+
+
+# ---- whole-model BitNet decode ------------------------------------------------------------
+
+class _OrcLayer(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("attn_norm", "attn_sub_norm", "ffn_norm", "ffn_sub_norm",
+                                          "wq", "wk", "wv", "wo", "wgate", "wup", "wdown")] + \
+               [(n, C.c_float) for n in ("sq", "sk", "sv", "so", "sgate", "sup", "sdown")]
+
+
+class BitNetOracle:
+    """CPU model of one sequence (orc_bitnet_step); weights as produced by
+    hesper_b200.models.random_bitnet_weights."""
+
+    def __init__(self, shape, weights):
+        L = lib()
+        L.orc_bitnet_create.restype = C.c_void_p
+        L.orc_bitnet_step.restype = C.c_int
+        self.shape = shape
+        self._keep = []
+        arr = (_OrcLayer * shape.n_layers)()
+        for i, W in enumerate(weights["layers"]):
+            f = {}
+            for n in ("attn_norm", "attn_sub_norm", "ffn_norm", "ffn_sub_norm"):
+                a = _c(W[n], np.float32); self._keep.append(a); f[n] = a.ctypes.data
+            for n in ("wq", "wk", "wv", "wo", "wgate", "wup", "wdown"):
+                a = _c(W[n], np.uint8); self._keep.append(a); f[n] = a.ctypes.data
+                f["s" + n[1:]] = float(W["s" + n[1:]])
+            arr[i] = _OrcLayer(**f)
+        self._arr = arr
+        self._emb = _c(weights["embed"], np.uint16)
+        self._fn = _c(weights["final_norm"], np.float32)
+        self._h = C.c_void_p(L.orc_bitnet_create(
+            shape.n_layers, shape.hidden, shape.n_heads, shape.n_kv_heads, shape.head_dim,
+            shape.ffn, shape.vocab, shape.max_seq, C.c_double(shape.rope_base),
+            C.c_float(shape.rms_eps), arr, _p(self._emb), _p(self._fn)))
+        self.pos = 0
+
+    def step(self, token: int):
+        """Feeds one token at the next position; returns (greedy token, logits f32 [vocab])."""
+        logits = np.empty(self.shape.vocab, np.float32)
+        tok = lib().orc_bitnet_step(self._h, int(token), self.pos, _p(logits))
+        self.pos += 1
+        return int(tok), logits
+
+    def close(self):
+        if self._h:
+            lib().orc_bitnet_destroy(self._h)
+            self._h = None

@@ -1,0 +1,91 @@
+"""GPU parity of the whole decode step of a BitNet-b1.58-shaped model (random-init weights)
+against the CPU oracle model: greedy tokens over 64 steps and logits.
+
+Comparison rule (stated before measuring): the oracle runs attention in f64 while the GPU
+uses f16 tensor-core products, so two near-tied logits may swap.  Each step is teacher-forced
+with the oracle's token; a differing argmax counts as a mismatch only if the oracle's own
+top-1/top-2 margin exceeds MARGIN times the logit standard deviation."""
+import numpy as np
+import pytest
+import torch
+
+from hesper_b200 import BitNetModel, BitNetShape, random_bitnet_weights
+
+pytestmark = pytest.mark.gpu
+MARGIN = 0.02
+
+SMALL = BitNetShape(n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=384,
+                    vocab=512, max_seq=96, rope_base=500000.0, rms_eps=1e-5)
+
+
+def _forced_compare(ctx, oracle, shape, weights, prompt, n_steps, batch=1):
+    from oracle.oracle import BitNetOracle
+    model = BitNetModel(ctx, shape, weights, batch=batch, max_new_tokens=n_steps + 1)
+    oracles = [BitNetOracle(shape, weights) for _ in range(batch)]
+    toks = [list(prompt[b]) for b in range(batch)]
+    mismatches, worst = 0, 0.0
+    n_total = prompt.shape[1] + n_steps
+    for t in range(n_total):
+        cur = np.array([toks[b][t] for b in range(batch)], np.int32)
+        g_tok, g_logits = model.step(torch.from_numpy(cur).cuda(), want_logits=True)
+        for b in range(batch):
+            o_tok, o_logits = oracles[b].step(int(cur[b]))
+            sd = float(np.std(o_logits))
+            worst = max(worst, float(np.max(np.abs(g_logits[b] - o_logits))) / sd)
+            if t >= prompt.shape[1] - 1:
+                if t + 1 >= len(toks[b]):
+                    toks[b].append(o_tok)  # teacher forcing with the oracle's token
+                if int(g_tok[b]) != o_tok:
+                    top2 = np.partition(o_logits, -2)[-2:]
+                    if (top2[1] - top2[0]) > MARGIN * sd:
+                        mismatches += 1
+    for o in oracles:
+        o.close()
+    model.close()
+    return mismatches, worst
+
+
+def test_small_model_forced_64_steps(ctx, oracle):
+    w = random_bitnet_weights(SMALL, seed=1)
+    prompt = np.random.default_rng(0).integers(0, SMALL.vocab, (1, 8)).astype(np.int32)
+    mism, worst = _forced_compare(ctx, oracle, SMALL, w, prompt, 64)
+    assert mism == 0
+    assert worst < 0.05  # logits within 5 % of their spread
+
+
+def test_small_model_batch3(ctx, oracle):
+    w = random_bitnet_weights(SMALL, seed=2)
+    prompt = np.random.default_rng(1).integers(0, SMALL.vocab, (3, 5)).astype(np.int32)
+    mism, worst = _forced_compare(ctx, oracle, SMALL, w, prompt, 16, batch=3)
+    assert mism == 0 and worst < 0.05
+
+
+def test_generate_graph_equals_stepwise(ctx):
+    """The captured-graph decode loop, the uncaptured loop and explicit steps give the same tokens."""
+    w = random_bitnet_weights(SMALL, seed=3)
+    prompt = np.random.default_rng(2).integers(0, SMALL.vocab, (2, 7)).astype(np.int32)
+    model = BitNetModel(ctx, SMALL, w, batch=2, max_new_tokens=32)
+    a, _, _ = model.generate(prompt, 32, use_graph=True)
+    b, _, _ = model.generate(prompt, 32, use_graph=False)
+    assert np.array_equal(a, b)
+    model.reset()
+    cur = None
+    out = []
+    for t in range(prompt.shape[1] + 31):
+        inp = torch.from_numpy(prompt[:, t].copy()).cuda() if t < prompt.shape[1] else None
+        tok, _ = model.step(inp)
+        if t >= prompt.shape[1] - 1:
+            out.append(tok.copy())
+    assert np.array_equal(np.stack(out, 1), a)
+    model.close()
+
+
+def test_full_size_bitnet2b_forced_64_steps(ctx, oracle):
+    """BASELINE config 3 shape (30 layers, hidden 2560, 20/5 heads, FFN 6912, vocab 128256),
+    short prompt, 64 teacher-forced greedy steps against the CPU oracle."""
+    shape = BitNetShape.bitnet_2b(max_seq=128)
+    w = random_bitnet_weights(shape, seed=4)
+    prompt = np.random.default_rng(3).integers(0, shape.vocab, (1, 4)).astype(np.int32)
+    mism, worst = _forced_compare(ctx, oracle, shape, w, prompt, 64)
+    assert mism == 0
+    assert worst < 0.05
