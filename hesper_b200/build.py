@@ -61,7 +61,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 if verbose and out:
                     sys.stderr.write(out)
     if jobs or force or _stale(LIB, objs):
-        link = [nvcc, "-shared", "-o", LIB] + objs + ["-cudart", "static",
+        link = [nvcc, "-shared", "-o", LIB] + objs + ["-cudart", "static", "-ldl",
                 "-gencode", "arch=compute_100a,code=sm_100a"]
         run(link)
     return LIB
