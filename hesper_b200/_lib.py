@@ -41,6 +41,18 @@ class BitNetLayer(C.Structure):
         "sq", "sk", "sv", "so", "sgate", "sup", "sdown")]
 
 
+class GemmaConfig(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("n_layers", "hidden", "head_dim", "vocab", "max_seq", "window",
+                                       "global_every", "local_q_heads", "local_kv_heads",
+                                       "local_ffn", "local_vocab", "vocab_offset")] + \
+               [(n, C.c_float) for n in ("rope_base", "rms_eps", "attn_scale", "embed_scale")]
+
+
+class GemmaLayer(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("attn_norm", "post_attn_norm", "ffn_norm", "post_ffn_norm",
+                                          "wq", "wk", "wv", "wo", "wgate", "wup", "wdown")]
+
+
 class KQuantSeg(C.Structure):
     _fields_ = [("d_blocks", C.c_void_p), ("d_residual", C.c_void_p), ("d_y", C.c_void_p),
                 ("N", C.c_int)]
@@ -56,6 +68,7 @@ SIGNATURES = {
     "hb200_version": (_i, []),
     "hb200_ctx_sm_count": (_i, [_vp]),
     "hb200_ctx_check": (_i, [_vp, _vp, C.POINTER(C.c_uint32)]),
+    "hb200_ctx_set_attn_mode": (_i, [_vp, _i]),
     "hb200_ctx_read_status": (_i, [_vp, _vp, C.POINTER(C.c_uint32)]),
     "hb200_bitlinear_forward": (_i, [_vp, _vp, _vp, _i, _i, _vp, _i, _vp, _f, _vp, _vp, _vp, _vp, _vp]),
     "hb200_bitlinear_forward_multi": (_i, [_vp, C.POINTER(BitLinearSeg), _i, _i, _vp, _i, _vp, _f, _vp, _vp]),
@@ -80,6 +93,22 @@ SIGNATURES = {
     "hb200_bitnet_logits": (_vp, [_vp]),
     "hb200_bitnet_tokens": (_vp, [_vp]),
     "hb200_bitnet_generate": (_i, [_vp, _vp, _i, _i, _i, _vp, C.POINTER(_f), C.POINTER(_f), _vp]),
+    "hb200_tp_unique_id": (_i, [_vp]),
+    "hb200_tp_init": (_i, [_vp, _i, _i, _vp, C.POINTER(_vp)]),
+    "hb200_tp_destroy": (_i, [_vp]),
+    "hb200_tp_rank": (_i, [_vp]),
+    "hb200_tp_size": (_i, [_vp]),
+    "hb200_tp_allreduce_f32": (_i, [_vp, _vp, _sz, _vp]),
+    "hb200_tp_allreduce_max_u64": (_i, [_vp, _vp, _sz, _vp]),
+    "hb200_tp_check": (_i, [_vp]),
+    "hb200_gemma_create": (_i, [_vp, _vp, C.POINTER(GemmaConfig), C.POINTER(GemmaLayer), _vp, _vp, _vp, _i, _i, C.POINTER(_vp)]),
+    "hb200_gemma_destroy": (_i, [_vp]),
+    "hb200_gemma_reset": (_i, [_vp, _vp]),
+    "hb200_gemma_set_position": (_i, [_vp, _i, _vp]),
+    "hb200_gemma_step": (_i, [_vp, _vp, _vp]),
+    "hb200_gemma_local_logits": (_vp, [_vp]),
+    "hb200_gemma_tokens": (_vp, [_vp]),
+    "hb200_gemma_generate": (_i, [_vp, _vp, _i, _i, _i, _vp, C.POINTER(_f), C.POINTER(_f), _vp]),
     "hb200_attn_decode": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp, _vp]),
 }
 

@@ -93,13 +93,18 @@ struct AttnCfg {
   static constexpr int kRowBytes = D * 2;
   static constexpr int kTileBytes = kChunk * kRowBytes;  // one of K or V
   static constexpr int kStageBytes = 2 * kTileBytes;
-  static constexpr int kQBytes = 8 * D * 2;              // Q as f16 [8][D]
+  static constexpr int kQStride = D + 8;                 // halves per Q row (bank spread)
+  static constexpr int kQBytes = 2 * 8 * kQStride * 2;   // Q as f16 hi and lo planes [8][D+8]
   static constexpr int kSmem = kQBytes + kAttnWarps * kStages * kStageBytes;
 };
 
-template <int D>
+// PRECISE: the scaled query and the softmax weights are each split into two f16 terms
+// (hi + lo), doubling the tensor-core work and removing their rounding from the result;
+// K and V are f16 in the cache, so what remains is f32 accumulation error (~1e-6).
+template <int D, bool PRECISE>
 __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __grid_constant__ AttnParams p) {
   using Cfg = AttnCfg<D>;
+  constexpr int QS = Cfg::kQStride;
   constexpr int NS = Cfg::kStages;
   constexpr int CPR = D / 8;   // 16-byte chunks per row
   constexpr int KS = D / 16;   // k-steps of the score product = m-tiles of the output
@@ -112,7 +117,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __gr
   const int b = blockIdx.x / (p.nsplit * p.Hkv);
   const int G = p.G;
 
-  __half* qs = reinterpret_cast<__half*>(smem);  // [8][D], heads >= G are zero
+  __half* qs = reinterpret_cast<__half*>(smem);  // [8][D+8] hi plane, heads >= G are zero
+  __half* qsl = qs + 8 * QS;                       // lo plane (PRECISE only)
   uint8_t* stage0 = smem + Cfg::kQBytes + (size_t)warp * NS * Cfg::kStageBytes;
 
   pdl_trigger();
@@ -166,16 +172,28 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __gr
       if (h < G)
         v = p.q_is_f16 ? __half2float(reinterpret_cast<const __half*>(p.q)[qoff + i])
                        : reinterpret_cast<const float*>(p.q)[qoff + i];
-      qs[i] = __float2half_rn(v * p.scale_log2);
+      const float sv = v * p.scale_log2;
+      const __half hv = __float2half_rn(sv);
+      qs[h * QS + (i - h * D)] = hv;
+      if (PRECISE) qsl[h * QS + (i - h * D)] = __float2half_rn(sv - __half2float(hv));
     }
   }
   __syncthreads();
-  uint32_t qb[KS][2];  // B fragments of Q^T: head g, dims 16s+2t(+1) and 16s+2t+8(+9)
+  // B fragments of Q^T: head g, dims 16s+2t(+1) and 16s+2t+8(+9).  The fast path keeps
+  // them in registers; the precise path re-reads hi and lo from shared memory per k-step.
+  constexpr int QR = PRECISE ? 1 : KS;
+  uint32_t qb[QR][2];
+  if (!PRECISE) {
 #pragma unroll
-  for (int s = 0; s < KS; ++s) {
-    qb[s][0] = *reinterpret_cast<const uint32_t*>(qs + g * D + 16 * s + 2 * t);
-    qb[s][1] = *reinterpret_cast<const uint32_t*>(qs + g * D + 16 * s + 2 * t + 8);
+    for (int s = 0; s < KS; ++s) {
+      qb[s][0] = *reinterpret_cast<const uint32_t*>(qs + g * QS + 16 * s + 2 * t);
+      qb[s][1] = *reinterpret_cast<const uint32_t*>(qs + g * QS + 16 * s + 2 * t + 8);
+    }
   }
+  auto qfrag = [&](const __half* plane, int s, uint32_t& b0, uint32_t& b1) {
+    b0 = *reinterpret_cast<const uint32_t*>(plane + g * QS + 16 * s + 2 * t);
+    b1 = *reinterpret_cast<const uint32_t*>(plane + g * QS + 16 * s + 2 * t + 8);
+  };
 
   // online softmax state of heads 2t and 2t+1 (replicated over g), exp2 domain
   float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
@@ -202,11 +220,25 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __gr
       const uint8_t* rbase = ks + row * Cfg::kRowBytes;
 #pragma unroll
       for (int s = 0; s < KS; s += 2) {
-        uint32_t a[4];
+        uint32_t a[4], b0, b1;
         ldsm_x4(a, rbase + (((2 * s + hi) ^ (row & 7)) << 4));
-        mma16816(sa, a, qb[s][0], qb[s][1]);
+        if (PRECISE) {
+          qfrag(qs, s, b0, b1);
+          mma16816(sa, a, b0, b1);
+          qfrag(qsl, s, b0, b1);
+          mma16816(sa, a, b0, b1);
+        } else {
+          mma16816(sa, a, qb[s][0], qb[s][1]);
+        }
         ldsm_x4(a, rbase + (((2 * s + 2 + hi) ^ (row & 7)) << 4));
-        mma16816(sb, a, qb[s + 1][0], qb[s + 1][1]);
+        if (PRECISE) {
+          qfrag(qs, s + 1, b0, b1);
+          mma16816(sb, a, b0, b1);
+          qfrag(qsl, s + 1, b0, b1);
+          mma16816(sb, a, b0, b1);
+        } else {
+          mma16816(sb, a, qb[s + 1][0], qb[s + 1][1]);
+        }
       }
     }
     const int pos0 = start + c * kChunk;
@@ -241,8 +273,16 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __gr
     m1 = mn1;
 
     // P^T into the B-operand layout: (pos 2t,2t+1 | head g) and (pos 2t+8,2t+9 | head g)
-    const uint32_t pb0 = movmatrix_t(pack_h2(p00, p01));
-    const uint32_t pb1 = movmatrix_t(pack_h2(p10, p11));
+    const uint32_t ph0 = pack_h2(p00, p01), ph1 = pack_h2(p10, p11);
+    const uint32_t pb0 = movmatrix_t(ph0);
+    const uint32_t pb1 = movmatrix_t(ph1);
+    uint32_t pl0 = 0, pl1 = 0;
+    if (PRECISE) {  // what f16 rounding dropped from the softmax weights
+      const float2 r0 = __half22float2(*reinterpret_cast<const __half2*>(&ph0));
+      const float2 r1 = __half22float2(*reinterpret_cast<const __half2*>(&ph1));
+      pl0 = movmatrix_t(pack_h2(p00 - r0.x, p01 - r0.y));
+      pl1 = movmatrix_t(pack_h2(p10 - r1.x, p11 - r1.y));
+    }
 
     // ---- O^T = O^T*alpha + V^T . P^T ---------------------------------------------
     {
@@ -258,6 +298,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __gr
         o[s][2] *= al0;
         o[s][3] *= al1;
         mma16816(o[s], a, pb0, pb1);
+        if (PRECISE) mma16816(o[s], a, pl0, pl1);
       }
     }
     __syncwarp();  // the stage may be refilled by the next iteration's copies
@@ -336,6 +377,78 @@ __global__ void attn_combine_kernel(const __grid_constant__ AttnParams p, int D)
   }
 }
 
+
+// ---- bit-reproducible attention (parity mode) -------------------------------------------
+//
+// A 30-layer network that re-quantises its activations to int8 after every block is
+// chaotic at the level of its quantisation noise: one activation that rounds the other way
+// because attention differed by 1e-6 grows into per-cent logit noise a few layers later.
+// Comparing greedy tokens with a CPU model therefore needs an attention whose every f32
+// operation and its order are specified.  This kernel is that specification (a CPU
+// restatement follows it operation for operation); it is slow on purpose, never the default:
+//   one warp per (sequence, query head), positions strictly in order;
+//   lane i owns dims [i*D/32, (i+1)*D/32): partial = fma(q_d, k_d, partial), d ascending;
+//   the 32 partials are summed by the xor-butterfly 16, 8, 4, 2, 1;
+//   s = total * (scale*log2e);  online softmax with exp2_det below;
+//   acc_d = fma(p, v_d, acc_d * alpha);  l = fma(l, alpha, p);  out_d = acc_d / l.
+__host__ __device__ __forceinline__ float exp2_det(float x) {
+  // 2^x for x <= 0 from IEEE f32 operations only: x = n + f, |f| <= 1/2, degree-6 polynomial
+  if (!(x > -120.0f)) return 0.0f;
+  const float n = rintf(x);
+  const float f = x - n;
+  float p = 1.5403530e-4f;
+  p = fmaf(p, f, 1.3398874e-3f);
+  p = fmaf(p, f, 9.6184370e-3f);
+  p = fmaf(p, f, 5.5503324e-2f);
+  p = fmaf(p, f, 2.4022648e-1f);
+  p = fmaf(p, f, 6.9314720e-1f);
+  p = fmaf(p, f, 1.0f);
+  return ldexpf(p, (int)n);
+}
+
+template <int D>
+__global__ void __launch_bounds__(32) attn_exact_kernel(const __grid_constant__ AttnParams p) {
+  constexpr int DL = D / 32;
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x;
+  const int h = blockIdx.x % p.H, b = blockIdx.x / p.H;
+  const int kvh = h / p.G;
+  const int len = min(max(p.seqlens[b], 0), p.max_seq);
+  int start = 0;
+  if (p.window > 0 && len > p.window) start = len - p.window;
+  float q[DL], acc[DL];
+#pragma unroll
+  for (int j = 0; j < DL; ++j) {
+    const size_t qi = ((size_t)b * p.H + h) * D + lane * DL + j;
+    q[j] = p.q_is_f16 ? __half2float(reinterpret_cast<const __half*>(p.q)[qi])
+                      : reinterpret_cast<const float*>(p.q)[qi];
+    acc[j] = 0.f;
+  }
+  const __half* kb = p.k + ((size_t)b * p.Hkv + kvh) * (size_t)p.max_seq * D + lane * DL;
+  const __half* vb = p.v + ((size_t)b * p.Hkv + kvh) * (size_t)p.max_seq * D + lane * DL;
+  float m = -CUDART_INF_F, l = 0.f;
+  for (int s = start; s < len; ++s) {
+    float part = 0.f;
+#pragma unroll
+    for (int j = 0; j < DL; ++j) part = fmaf(q[j], __half2float(kb[(size_t)s * D + j]), part);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, o));
+    const float sc = __fmul_rn(part, p.scale_log2);
+    const float mn = fmaxf(m, sc);
+    const float alpha = exp2_det(__fsub_rn(m, mn));  // m = -inf: exp2_det(-inf) = 0
+    const float pw = exp2_det(__fsub_rn(sc, mn));
+    l = fmaf(l, alpha, pw);
+#pragma unroll
+    for (int j = 0; j < DL; ++j)
+      acc[j] = fmaf(pw, __half2float(vb[(size_t)s * D + j]), __fmul_rn(acc[j], alpha));
+    m = mn;
+  }
+#pragma unroll
+  for (int j = 0; j < DL; ++j)
+    p.out[((size_t)b * p.H + h) * D + lane * DL + j] = l > 0.f ? __fdiv_rn(acc[j], l) : 0.f;
+}
+
 // Splits per (sequence, KV head): enough CTAs for a few waves over the SMs, but
 // no split shorter than 8 chunks (128 positions) and at most kMaxSplits.
 static int attn_pick_splits(const hb200_ctx* ctx, int B, int Hkv, int max_len) {
@@ -350,10 +463,10 @@ static int attn_pick_splits(const hb200_ctx* ctx, int B, int Hkv, int max_len) {
   return (int)want;
 }
 
-template <int D>
+template <int D, bool PRECISE>
 static int attn_launch(hb200_ctx* ctx, const AttnParams& p, cudaStream_t st) {
   using Cfg = AttnCfg<D>;
-  auto kern = attn_decode_kernel<D>;
+  auto kern = attn_decode_kernel<D, PRECISE>;
   static bool configured = false;
   if (!configured) {
     HB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
@@ -420,9 +533,25 @@ extern "C" int hb200_attn_decode(hb200_ctx* ctx, const void* d_q, int q_is_f16, 
     p.part_meta = reinterpret_cast<float*>(static_cast<uint8_t*>(d_workspace) + po);
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (ctx->attn_mode == HB200_ATTN_EXACT) {
+    const dim3 grid(B * H);
+    switch (D) {
+      case 64: HB_CUDA(launch_pdl(attn_exact_kernel<64>, grid, dim3(32), 0, st, ctx->pdl, p)); break;
+      case 128: HB_CUDA(launch_pdl(attn_exact_kernel<128>, grid, dim3(32), 0, st, ctx->pdl, p)); break;
+      default: HB_CUDA(launch_pdl(attn_exact_kernel<256>, grid, dim3(32), 0, st, ctx->pdl, p)); break;
+    }
+    return HB200_OK;
+  }
+  if (ctx->attn_mode == HB200_ATTN_PRECISE) {
+    switch (D) {
+      case 64: return attn_launch<64, true>(ctx, p, st);
+      case 128: return attn_launch<128, true>(ctx, p, st);
+      default: return attn_launch<256, true>(ctx, p, st);
+    }
+  }
   switch (D) {
-    case 64: return attn_launch<64>(ctx, p, st);
-    case 128: return attn_launch<128>(ctx, p, st);
-    default: return attn_launch<256>(ctx, p, st);
+    case 64: return attn_launch<64, false>(ctx, p, st);
+    case 128: return attn_launch<128, false>(ctx, p, st);
+    default: return attn_launch<256, false>(ctx, p, st);
   }
 }

@@ -191,4 +191,5 @@ struct hb200_ctx {
   int smem_optin;      // max dynamic shared memory per block
   uint32_t* d_status;  // 16 words
   bool pdl;            // use programmatic dependent launch
+  int attn_mode;       // HB200_ATTN_FAST / PRECISE / EXACT
 };

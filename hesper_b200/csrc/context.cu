@@ -50,6 +50,7 @@ extern "C" int hb200_ctx_create(int device, hb200_ctx** out) {
   c->sm_count = prop.multiProcessorCount;
   c->smem_optin = (int)prop.sharedMemPerBlockOptin;
   c->pdl = true;
+  c->attn_mode = HB200_ATTN_FAST;
   const char* env = getenv("HB200_NO_PDL");
   if (env && env[0] == '1') c->pdl = false;
   cudaError_t e = cudaMalloc(&c->d_status, 256);
@@ -94,5 +95,12 @@ extern "C" int hb200_ctx_read_status(hb200_ctx* ctx, hb200_stream stream, uint32
   HB_REQUIRE(ctx != nullptr && words != nullptr, "ctx_read_status: null argument");
   HB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   HB_CUDA(cudaMemcpy(words, ctx->d_status, 256, cudaMemcpyDeviceToHost));
+  return HB200_OK;
+}
+
+extern "C" int hb200_ctx_set_attn_mode(hb200_ctx* ctx, int mode) {
+  HB_REQUIRE(ctx != nullptr, "ctx_set_attn_mode: null context");
+  HB_REQUIRE(mode >= HB200_ATTN_FAST && mode <= HB200_ATTN_EXACT, "ctx_set_attn_mode: mode %d", mode);
+  ctx->attn_mode = mode;
   return HB200_OK;
 }

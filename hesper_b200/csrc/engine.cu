@@ -203,6 +203,14 @@ extern "C" int hb200_bitnet_generate(hb200_bitnet* m, const int32_t* h_prompt, i
   const int B = m->B;
   int rc = hb200_bitnet_reset(m, stream);
   if (rc) return rc;
+  // The legacy default stream cannot be captured: run the loop on a stream of our own then
+  // (reset() above has synchronised with whatever the caller queued before).
+  cudaStream_t own = nullptr;
+  if (st == nullptr) {
+    HB_CUDA(cudaStreamCreateWithFlags(&own, cudaStreamNonBlocking));
+    st = own;
+    stream = own;
+  }
   m->want_logits = false;
   // prompt tokens, position-major so each step reads a contiguous [B] slice
   int32_t* d_prompt = nullptr;
@@ -221,6 +229,7 @@ extern "C" int hb200_bitnet_generate(hb200_bitnet* m, const int32_t* h_prompt, i
     if (graph) cudaGraphDestroy(graph);
     cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
     cudaFree(d_prompt);
+    if (own) cudaStreamDestroy(own);
   };
   if (e != cudaSuccess) { cleanup(); return cuda_fail(e, "prompt upload"); }
   // ---- prefill: one single-token forward per prompt position (as BitNet.generate :623-625);
@@ -269,7 +278,8 @@ extern "C" int hb200_bitnet_generate(hb200_bitnet* m, const int32_t* h_prompt, i
   if (e != cudaSuccess) { cleanup(); return cuda_fail(e, "token log download"); }
   for (int b = 0; b < B; ++b)
     for (int i = 0; i < n_new; ++i) h_out[(size_t)b * n_new + i] = log[(size_t)b * m->log_stride + i];
-  cleanup();
   uint32_t flags = 0;
-  return hb200_ctx_check(m->ctx, stream, &flags);
+  rc = hb200_ctx_check(m->ctx, stream, &flags);
+  cleanup();
+  return rc;
 }

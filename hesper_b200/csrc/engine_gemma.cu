@@ -1,0 +1,357 @@
+// engine_gemma.cu -- tensor-parallel decode loop of a Gemma-4-E4B-shaped model (Q4_K
+// weights, f16 KV cache, 5 sliding-window layers to 1 global layer, GeGLU FFN).
+//
+// Block order follows Hesper.Models.Gemma4.forwardBlock (Hesper/Models/Gemma4.lean:485):
+// fused norm + q/k/v, RoPE + f16 KV write, decode attention, o_proj, post-attention norm
+// then add, fused norm + gate/up GELU, down_proj, post-FFN norm then add; the reference's
+// per-layer embeddings, MoE, vision/audio towers and per-head q/k norms are not part of
+// the benchmark shape and are left out.
+//
+// Tensor parallelism (new: the reference is single-GPU): this rank holds a contiguous
+// range of query heads with the KV head they attend to, the matching rows of gate/up and
+// of the LM head, and the matching input columns of o_proj and down_proj.  The only
+// exchange is one f32 sum all-reduce of hidden*batch elements after o_proj and after
+// down_proj, and one u64 max all-reduce of batch argmax keys per token.
+#include <vector>
+
+#include "common.cuh"
+
+struct hb200_gemma {
+  hb200_ctx* ctx;
+  hb200_tp* tp;
+  hb200_gemma_config cfg;
+  std::vector<hb200_gemma_layer> layers;
+  const void* embed;
+  const void* lm_head;
+  const float* final_norm;
+  int B;
+  float *x, *x1, *q, *k, *v, *att, *o, *h, *logits;
+  std::vector<__half*> kc, vc;  // per layer
+  std::vector<int> slots;       // cache slots per layer (window or max_seq)
+  int32_t *pos, *len, *tok, *log_index, *token_log;
+  unsigned long long* keys;
+  void* attn_ws;
+  size_t attn_ws_bytes;
+  int log_stride;
+};
+
+namespace hb {
+
+// keys[m] = best (value, global index) of this rank's logits slice
+__global__ void argmax_keys_kernel(const float* logits, int V, int voffset,
+                                   unsigned long long* keys) {
+  __shared__ unsigned long long red[32];
+  pdl_trigger();
+  pdl_wait();
+  const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float* row = logits + (size_t)m * V;
+  unsigned long long best = 0;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = row[i];
+    if (v == v) {
+      uint32_t u = __float_as_uint(v);
+      u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+      const unsigned long long k =
+          ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)(i + voffset));
+      best = k > best ? k : best;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
+  }
+  if (lane == 0) red[warp] = best;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) best = red[i] > best ? red[i] : best;
+    keys[m] = best;
+  }
+}
+
+__global__ void keys_to_tokens_kernel(const unsigned long long* keys, int M, int32_t* tok,
+                                      int32_t* log, const int32_t* log_index, int log_stride) {
+  pdl_trigger();
+  pdl_wait();
+  const int m = blockIdx.x * blockDim.x + threadIdx.x;
+  if (m >= M) return;
+  const unsigned long long k = keys[m];
+  const int32_t t = k ? (int32_t)(0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull)) : 0;
+  tok[m] = t;
+  const int li = log_index[0];
+  if (li >= 0 && li < log_stride) log[(size_t)m * log_stride + li] = t;
+}
+
+}  // namespace hb
+
+using namespace hb;
+
+namespace {
+
+bool layer_is_global(const hb200_gemma_config& c, int l) {
+  return c.global_every > 0 && (l + 1) % c.global_every == 0;
+}
+
+int gemma_enqueue_step(hb200_gemma* m, const int32_t* d_tokens, bool lm_head, cudaStream_t st) {
+  const hb200_gemma_config& c = m->cfg;
+  hb200_ctx* ctx = m->ctx;
+  const int B = m->B, Hd = c.hidden, D = c.head_dim;
+  const int qdim = c.local_q_heads * D, kvdim = c.local_kv_heads * D;
+  const int32_t* toks = d_tokens ? d_tokens : m->tok;
+  int rc = hb200_embed_lookup(ctx, m->embed, 0, c.vocab, Hd, toks, B, c.embed_scale, m->x, st);
+  if (rc) return rc;
+  for (int l = 0; l < c.n_layers; ++l) {
+    const hb200_gemma_layer& L = m->layers[l];
+    hb200_kquant_seg segs[3] = {
+        {L.wq, nullptr, m->q, qdim}, {L.wk, nullptr, m->k, kvdim}, {L.wv, nullptr, m->v, kvdim}};
+    rc = hb200_kquant_forward_multi(ctx, HB200_FMT_Q4_K, segs, 3, Hd, m->x, B, L.attn_norm,
+                                    c.rms_eps, st);
+    if (rc) return rc;
+    const bool glob = layer_is_global(c, l);
+    rc = hb200_rope_kv_write(ctx, m->q, m->k, m->v, m->kc[l], m->vc[l], m->pos, B, c.local_q_heads,
+                             c.local_kv_heads, D, m->slots[l], glob ? 0 : 1, c.rope_base, st);
+    if (rc) return rc;
+    // a ring cache holds exactly the window: the kernel clamps the length to the slots
+    rc = hb200_attn_decode(ctx, m->q, 0, m->kc[l], m->vc[l], m->len, B, c.local_q_heads,
+                           c.local_kv_heads, D, m->slots[l], 0, c.attn_scale, m->attn_ws,
+                           m->attn_ws_bytes, m->att, st);
+    if (rc) return rc;
+    rc = hb200_kquant_forward(ctx, HB200_FMT_Q4_K, L.wo, qdim, Hd, m->att, B, nullptr, 0.f, nullptr,
+                              m->o, st);
+    if (rc) return rc;
+    rc = hb200_tp_allreduce_f32(m->tp, m->o, (size_t)B * Hd, st);
+    if (rc) return rc;
+    rc = hb200_rmsnorm(ctx, m->o, L.post_attn_norm, m->x, c.rms_eps, B, Hd, m->x1, st);
+    if (rc) return rc;
+    rc = hb200_kquant_gateup_gelu(ctx, HB200_FMT_Q4_K, L.wgate, L.wup, Hd, c.local_ffn, m->x1, B,
+                                  L.ffn_norm, c.rms_eps, m->h, st);
+    if (rc) return rc;
+    rc = hb200_kquant_forward(ctx, HB200_FMT_Q4_K, L.wdown, c.local_ffn, Hd, m->h, B, nullptr, 0.f,
+                              nullptr, m->o, st);
+    if (rc) return rc;
+    rc = hb200_tp_allreduce_f32(m->tp, m->o, (size_t)B * Hd, st);
+    if (rc) return rc;
+    rc = hb200_rmsnorm(ctx, m->o, L.post_ffn_norm, m->x1, c.rms_eps, B, Hd, m->x, st);
+    if (rc) return rc;
+  }
+  if (lm_head) {
+    rc = hb200_kquant_forward(ctx, HB200_FMT_Q4_K, m->lm_head, Hd, c.local_vocab, m->x, B,
+                              m->final_norm, c.rms_eps, nullptr, m->logits, st);
+    if (rc) return rc;
+    HB_CUDA(launch_pdl(argmax_keys_kernel, dim3(B), dim3(1024), 0, st, ctx->pdl,
+                       (const float*)m->logits, c.local_vocab, c.vocab_offset, m->keys));
+    rc = hb200_tp_allreduce_max_u64(m->tp, m->keys, (size_t)B, st);
+    if (rc) return rc;
+    HB_CUDA(launch_pdl(keys_to_tokens_kernel, dim3((B + 63) / 64), dim3(64), 0, st, ctx->pdl,
+                       (const unsigned long long*)m->keys, B, m->tok, m->token_log,
+                       (const int32_t*)m->log_index, m->log_stride));
+    rc = hb200_add_i32(ctx, m->log_index, 1, 1, st);
+    if (rc) return rc;
+  }
+  return hb200_add_i32(ctx, m->pos, 2 * B, 1, st);
+}
+
+}  // namespace
+
+extern "C" int hb200_gemma_create(hb200_ctx* ctx, hb200_tp* tp, const hb200_gemma_config* cfg,
+                                  const hb200_gemma_layer* layers, const void* d_embed_bf16,
+                                  const void* d_lm_head_q4k, const float* d_final_norm, int batch,
+                                  int max_new_tokens, hb200_gemma** out) {
+  HB_REQUIRE(ctx && cfg && layers && d_embed_bf16 && d_lm_head_q4k && d_final_norm && out,
+             "gemma_create: null argument");
+  HB_REQUIRE(batch >= 1 && batch <= 64, "gemma_create: batch %d outside 1..64", batch);
+  HB_REQUIRE(cfg->hidden % 256 == 0 && cfg->local_ffn % 256 == 0 &&
+                 (cfg->local_q_heads * cfg->head_dim) % 256 == 0 && cfg->local_kv_heads >= 1 &&
+                 cfg->local_q_heads % cfg->local_kv_heads == 0,
+             "gemma_create: local shapes must be multiples of the 256-weight super-block");
+  *out = nullptr;
+  hb200_gemma* m = new hb200_gemma();
+  m->ctx = ctx;
+  m->tp = tp;
+  m->cfg = *cfg;
+  m->layers.assign(layers, layers + cfg->n_layers);
+  m->embed = d_embed_bf16;
+  m->lm_head = d_lm_head_q4k;
+  m->final_norm = d_final_norm;
+  m->B = batch;
+  m->log_stride = max_new_tokens > 0 ? max_new_tokens : 1;
+  const int B = batch, D = cfg->head_dim, qdim = cfg->local_q_heads * D, kvdim = cfg->local_kv_heads * D;
+  cudaError_t e = cudaSuccess;
+  auto A = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
+  auto F = [&](float** p, size_t n) { A(cudaMalloc(reinterpret_cast<void**>(p), n * sizeof(float))); };
+  F(&m->x, (size_t)B * cfg->hidden);
+  F(&m->x1, (size_t)B * cfg->hidden);
+  F(&m->o, (size_t)B * cfg->hidden);
+  F(&m->q, (size_t)B * qdim);
+  F(&m->k, (size_t)B * kvdim);
+  F(&m->v, (size_t)B * kvdim);
+  F(&m->att, (size_t)B * qdim);
+  F(&m->h, (size_t)B * cfg->local_ffn);
+  F(&m->logits, (size_t)B * cfg->local_vocab);
+  m->kc.assign(cfg->n_layers, nullptr);
+  m->vc.assign(cfg->n_layers, nullptr);
+  m->slots.assign(cfg->n_layers, 0);
+  int max_slots = 1;
+  for (int l = 0; l < cfg->n_layers; ++l) {
+    const bool glob = layer_is_global(*cfg, l) || cfg->window <= 0 || cfg->window >= cfg->max_seq;
+    m->slots[l] = glob ? cfg->max_seq : cfg->window;
+    if (m->slots[l] > max_slots) max_slots = m->slots[l];
+    const size_t n = (size_t)B * cfg->local_kv_heads * m->slots[l] * D;
+    A(cudaMalloc(reinterpret_cast<void**>(&m->kc[l]), n * sizeof(__half)));
+    A(cudaMalloc(reinterpret_cast<void**>(&m->vc[l]), n * sizeof(__half)));
+    if (e == cudaSuccess) e = cudaMemset(m->kc[l], 0, n * sizeof(__half));
+    if (e == cudaSuccess) e = cudaMemset(m->vc[l], 0, n * sizeof(__half));
+  }
+  A(cudaMalloc(reinterpret_cast<void**>(&m->pos), sizeof(int32_t) * 2 * B));
+  m->len = m->pos ? m->pos + B : nullptr;
+  A(cudaMalloc(reinterpret_cast<void**>(&m->tok), sizeof(int32_t) * B));
+  A(cudaMalloc(reinterpret_cast<void**>(&m->log_index), sizeof(int32_t)));
+  A(cudaMalloc(reinterpret_cast<void**>(&m->token_log), sizeof(int32_t) * (size_t)B * m->log_stride));
+  A(cudaMalloc(reinterpret_cast<void**>(&m->keys), sizeof(unsigned long long) * B));
+  m->attn_ws_bytes = hb200_attn_workspace_bytes(ctx, B, cfg->local_q_heads, cfg->local_kv_heads, D,
+                                                max_slots);
+  A(cudaMalloc(&m->attn_ws, m->attn_ws_bytes));
+  if (e != cudaSuccess) {
+    hb200_gemma_destroy(m);
+    return cuda_fail(e, "gemma_create allocation");
+  }
+  *out = m;
+  return hb200_gemma_reset(m, nullptr);
+}
+
+extern "C" int hb200_gemma_destroy(hb200_gemma* m) {
+  if (!m) return HB200_OK;
+  cudaFree(m->x); cudaFree(m->x1); cudaFree(m->o); cudaFree(m->q); cudaFree(m->k); cudaFree(m->v);
+  cudaFree(m->att); cudaFree(m->h); cudaFree(m->logits);
+  for (auto p : m->kc) cudaFree(p);
+  for (auto p : m->vc) cudaFree(p);
+  cudaFree(m->pos); cudaFree(m->tok); cudaFree(m->log_index); cudaFree(m->token_log);
+  cudaFree(m->keys); cudaFree(m->attn_ws);
+  delete m;
+  return HB200_OK;
+}
+
+extern "C" int hb200_gemma_reset(hb200_gemma* m, hb200_stream stream) {
+  HB_REQUIRE(m != nullptr, "gemma_reset: null model");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int B = m->B;
+  std::vector<int32_t> init(2 * B, 0);
+  for (int b = 0; b < B; ++b) init[B + b] = 1;
+  HB_CUDA(cudaMemcpyAsync(m->pos, init.data(), sizeof(int32_t) * 2 * B, cudaMemcpyHostToDevice, st));
+  HB_CUDA(cudaMemsetAsync(m->tok, 0, sizeof(int32_t) * B, st));
+  HB_CUDA(cudaMemsetAsync(m->log_index, 0, sizeof(int32_t), st));
+  HB_CUDA(cudaStreamSynchronize(st));
+  return HB200_OK;
+}
+
+extern "C" int hb200_gemma_step(hb200_gemma* m, const int32_t* d_tokens, hb200_stream stream) {
+  HB_REQUIRE(m != nullptr, "gemma_step: null model");
+  return gemma_enqueue_step(m, d_tokens, true, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" const float* hb200_gemma_local_logits(const hb200_gemma* m) { return m ? m->logits : nullptr; }
+extern "C" const int32_t* hb200_gemma_tokens(const hb200_gemma* m) { return m ? m->tok : nullptr; }
+
+// Seeds every sequence's position (and length) without running the prompt: the KV cache keeps
+// whatever it holds.  For throughput measurements at a given context length.
+extern "C" int hb200_gemma_set_position(hb200_gemma* m, int pos, hb200_stream stream) {
+  HB_REQUIRE(m != nullptr && pos >= 0 && pos < m->cfg.max_seq, "gemma_set_position: bad argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  std::vector<int32_t> init(2 * m->B, pos);
+  for (int b = 0; b < m->B; ++b) init[m->B + b] = pos + 1;
+  HB_CUDA(cudaMemcpyAsync(m->pos, init.data(), sizeof(int32_t) * 2 * m->B, cudaMemcpyHostToDevice, st));
+  HB_CUDA(cudaStreamSynchronize(st));
+  return HB200_OK;
+}
+
+extern "C" int hb200_gemma_generate(hb200_gemma* m, const int32_t* h_prompt, int prompt_len,
+                                    int n_new, int use_graph, int32_t* h_out, float* ms_prefill,
+                                    float* ms_decode, hb200_stream stream) {
+  HB_REQUIRE(m && h_out, "gemma_generate: null argument");
+  HB_REQUIRE(prompt_len >= 0 && n_new >= 1 && n_new <= m->log_stride,
+             "gemma_generate: prompt_len=%d n_new=%d (log holds %d)", prompt_len, n_new, m->log_stride);
+  HB_REQUIRE(prompt_len == 0 || h_prompt != nullptr, "gemma_generate: null prompt");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int B = m->B;
+  cudaStream_t own = nullptr;
+  if (st == nullptr) {  // the legacy default stream cannot be captured
+    HB_CUDA(cudaStreamCreateWithFlags(&own, cudaStreamNonBlocking));
+    st = own;
+  }
+  int rc = HB200_OK;
+  int32_t* d_prompt = nullptr;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  cudaEvent_t e0, e1, e2;
+  cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventCreate(&e2);
+  auto cleanup = [&]() {
+    if (exec) cudaGraphExecDestroy(exec);
+    if (graph) cudaGraphDestroy(graph);
+    cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
+    if (d_prompt) cudaFree(d_prompt);
+    if (own) cudaStreamDestroy(own);
+  };
+  cudaError_t e = cudaSuccess;
+  // prompt_len == 0 continues from the current position (see hb200_gemma_set_position)
+  if (prompt_len > 0) {
+    rc = hb200_gemma_reset(m, st);
+    if (rc) { cleanup(); return rc; }
+    e = cudaMalloc(reinterpret_cast<void**>(&d_prompt), sizeof(int32_t) * (size_t)B * prompt_len);
+    if (e != cudaSuccess) { cleanup(); return cuda_fail(e, "prompt buffer"); }
+    std::vector<int32_t> pm((size_t)B * prompt_len);
+    for (int b = 0; b < B; ++b)
+      for (int p = 0; p < prompt_len; ++p) pm[(size_t)p * B + b] = h_prompt[(size_t)b * prompt_len + p];
+    e = cudaMemcpyAsync(d_prompt, pm.data(), pm.size() * sizeof(int32_t), cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) { cleanup(); return cuda_fail(e, "prompt upload"); }
+    cudaStreamSynchronize(st);
+  } else {
+    HB_CUDA(cudaMemsetAsync(m->log_index, 0, sizeof(int32_t), st));
+  }
+  cudaEventRecord(e0, st);
+  for (int p = 0; p < prompt_len; ++p) {
+    rc = gemma_enqueue_step(m, d_prompt + (size_t)p * B, p == prompt_len - 1, st);
+    if (rc) { cleanup(); return rc; }
+  }
+  cudaEventRecord(e1, st);
+  const int steps = prompt_len > 0 ? n_new - 1 : n_new;
+  if (steps > 0) {
+    if (use_graph) {
+      e = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
+      if (e == cudaSuccess) {
+        rc = gemma_enqueue_step(m, nullptr, true, st);
+        cudaError_t e2c = cudaStreamEndCapture(st, &graph);
+        if (rc) { cleanup(); return rc; }
+        e = e2c;
+      }
+      if (e == cudaSuccess) e = cudaGraphInstantiate(&exec, graph, 0);
+      if (e != cudaSuccess) { cleanup(); return cuda_fail(e, "decode graph capture"); }
+      cudaEventRecord(e1, st);
+      for (int s = 0; s < steps; ++s) {
+        e = cudaGraphLaunch(exec, st);
+        if (e != cudaSuccess) { cleanup(); return cuda_fail(e, "cudaGraphLaunch"); }
+      }
+    } else {
+      for (int s = 0; s < steps; ++s) {
+        rc = gemma_enqueue_step(m, nullptr, true, st);
+        if (rc) { cleanup(); return rc; }
+      }
+    }
+  }
+  cudaEventRecord(e2, st);
+  e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) { cleanup(); return cuda_fail(e, "decode"); }
+  float a = 0.f, b2 = 0.f;
+  cudaEventElapsedTime(&a, e0, e1);
+  cudaEventElapsedTime(&b2, e1, e2);
+  if (ms_prefill) *ms_prefill = a;
+  if (ms_decode) *ms_decode = b2;
+  std::vector<int32_t> log((size_t)B * m->log_stride);
+  e = cudaMemcpy(log.data(), m->token_log, log.size() * sizeof(int32_t), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) { cleanup(); return cuda_fail(e, "token log download"); }
+  for (int b = 0; b < B; ++b)
+    for (int i = 0; i < n_new; ++i) h_out[(size_t)b * n_new + i] = log[(size_t)b * m->log_stride + i];
+  uint32_t flags = 0;
+  rc = hb200_ctx_check(m->ctx, st, &flags);
+  cleanup();
+  return rc;
+}

@@ -60,6 +60,13 @@ class Context:
     def sm_count(self) -> int:
         return self._lib.hb200_ctx_sm_count(self._h)
 
+    ATTN_FAST, ATTN_PRECISE, ATTN_EXACT = 0, 1, 2
+
+    def set_attn_mode(self, mode: int) -> None:
+        """Decode-attention arithmetic: fast f16, hi+lo f16 split, or the bit-reproducible
+        reference-order kernel (see the header)."""
+        check(self._lib.hb200_ctx_set_attn_mode(self._h, int(mode)))
+
     def check(self, stream=None) -> int:
         """Synchronise and return the device status flags (raises on a device-side timeout)."""
         flags = C.c_uint32(0)

@@ -75,6 +75,18 @@ int hb200_ctx_sm_count(const hb200_ctx *ctx);
  * returned as well).  For tests and diagnostics; not on the hot path. */
 int hb200_ctx_check(hb200_ctx *ctx, hb200_stream stream, uint32_t *flags);
 
+/* Decode-attention arithmetic.
+ *   FAST (default): the scaled query and the softmax weights are rounded to f16 for the
+ *     tensor-core products (error ~5e-4, inside the 2e-3 bar).
+ *   PRECISE: both are split into hi + lo f16 terms, twice the MMA work, error ~1e-6.
+ *   EXACT: a slow one-warp-per-head kernel in which every f32 operation and its order are
+ *     specified, so a CPU restatement reproduces it bit for bit.  For parity runs of a whole
+ *     model only: its int8 re-quantisers amplify any 1e-6 difference into per-cent logit noise. */
+#define HB200_ATTN_FAST 0
+#define HB200_ATTN_PRECISE 1
+#define HB200_ATTN_EXACT 2
+int hb200_ctx_set_attn_mode(hb200_ctx *ctx, int mode);
+
 /* Synchronises `stream` and copies the raw 64-word status block to `words`
  * without clearing it (word 0 = flags; the rest is kernel debug scratch). */
 int hb200_ctx_read_status(hb200_ctx *ctx, hb200_stream stream, uint32_t words[64]);
@@ -296,6 +308,74 @@ const int32_t *hb200_bitnet_tokens(const hb200_bitnet *m);
 int hb200_bitnet_generate(hb200_bitnet *m, const int32_t *h_prompt, int prompt_len, int n_new,
                           int use_graph, int32_t *h_out, float *ms_prefill, float *ms_decode,
                           hb200_stream stream);
+
+/* ---- tensor parallelism (no counterpart in the reference: it is single-GPU) ------------- */
+
+typedef struct hb200_tp hb200_tp;
+
+/* One process per GPU.  Rank 0 makes the 128-byte id (ncclGetUniqueId), the host program
+ * carries it to the other ranks by any means, then every rank calls hb200_tp_init.  NCCL is
+ * loaded at run time (dlopen), so a single-GPU process needs no NCCL at all. */
+int hb200_tp_unique_id(unsigned char out[128]);
+int hb200_tp_init(hb200_ctx *ctx, int rank, int nranks, const unsigned char id[128],
+                  hb200_tp **out);
+int hb200_tp_destroy(hb200_tp *tp);
+int hb200_tp_rank(const hb200_tp *tp);
+int hb200_tp_size(const hb200_tp *tp);
+
+/* In-place sum of n f32 over the ranks (the exchange after a row-split o_proj / down_proj)
+ * and in-place max of n u64 (argmax keys after a column-split LM head), enqueued on `stream`
+ * (capturable).  A NULL tp or a 1-rank communicator is a no-op. */
+int hb200_tp_allreduce_f32(hb200_tp *tp, float *d_buf, size_t n, hb200_stream stream);
+int hb200_tp_allreduce_max_u64(hb200_tp *tp, unsigned long long *d_buf, size_t n,
+                               hb200_stream stream);
+
+/* Host-side health check of the communicator (ncclCommGetAsyncError): a peer that died or
+ * never joined shows up here or as an error of the next collective, not as a GPU fault. */
+int hb200_tp_check(hb200_tp *tp);
+
+/* ---- Gemma-4-E4B-shaped tensor-parallel decode loop (BASELINE config 4) ----------------- */
+
+/* Global shape plus this rank's share.  Layer l is a global-attention layer when
+ * (l+1) % global_every == 0, else a sliding-window layer whose cache is a ring of `window`
+ * slots.  Shape source: Hesper/Models/Gemma4/Config.lean:19-45, simplified as BASELINE.json
+ * config 4 states it (no per-layer embeddings, MoE, towers or per-head q/k norms). */
+typedef struct hb200_gemma_config {
+  int n_layers, hidden, head_dim, vocab, max_seq, window, global_every;
+  int local_q_heads, local_kv_heads, local_ffn, local_vocab, vocab_offset;
+  float rope_base, rms_eps, attn_scale, embed_scale;
+} hb200_gemma_config;
+
+/* This rank's shards, all Q4_K, device pointers, borrowed.  wq/wk/wv/wgate/wup/lm_head are
+ * row ranges of the full tensors (contiguous bytes); wo and wdown are column ranges, i.e.
+ * for every output row the super-blocks of this rank's input slice, stored contiguously. */
+typedef struct hb200_gemma_layer {
+  const float *attn_norm, *post_attn_norm, *ffn_norm, *post_ffn_norm;
+  const void *wq, *wk, *wv, *wo, *wgate, *wup, *wdown;
+} hb200_gemma_layer;
+
+typedef struct hb200_gemma hb200_gemma;
+
+/* Replaces Gemma4 model construction (Hesper/Models/Gemma4.lean:78-123) for the benchmark
+ * shape.  tp may be NULL on one GPU.  d_embed_bf16 is the full [vocab][hidden] table. */
+int hb200_gemma_create(hb200_ctx *ctx, hb200_tp *tp, const hb200_gemma_config *cfg,
+                       const hb200_gemma_layer *layers, const void *d_embed_bf16,
+                       const void *d_lm_head_q4k, const float *d_final_norm, int batch,
+                       int max_new_tokens, hb200_gemma **out);
+int hb200_gemma_destroy(hb200_gemma *m);
+int hb200_gemma_reset(hb200_gemma *m, hb200_stream stream);
+/* Positions of all sequences := pos without running a prompt (cache content stays as is);
+ * for throughput measurements at a given context length. */
+int hb200_gemma_set_position(hb200_gemma *m, int pos, hb200_stream stream);
+/* One decode step on every rank: Gemma4.forwardSingleToken (Hesper/Models/Gemma4.lean:2558). */
+int hb200_gemma_step(hb200_gemma *m, const int32_t *d_tokens, hb200_stream stream);
+const float *hb200_gemma_local_logits(const hb200_gemma *m);
+const int32_t *hb200_gemma_tokens(const hb200_gemma *m);
+/* Gemma4.generate (Hesper/Models/Gemma4.lean:3212).  prompt_len = 0 continues from the
+ * current position and decodes n_new tokens. */
+int hb200_gemma_generate(hb200_gemma *m, const int32_t *h_prompt, int prompt_len, int n_new,
+                         int use_graph, int32_t *h_out, float *ms_prefill, float *ms_decode,
+                         hb200_stream stream);
 
 #if defined(__GNUC__)
 #pragma GCC visibility pop

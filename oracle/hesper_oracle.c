@@ -666,7 +666,15 @@ typedef struct orc_bitnet {
   const uint16_t *embed; /* bf16 [vocab][hidden] */
   const float *final_norm;
   uint16_t *kcache, *vcache; /* [layer][kv_head][max_seq][head_dim] f16 */
+  int exact_attention;       /* 1: attention by orc_attn_decode_exact (mirror of the library) */
 } orc_bitnet;
+
+ORC_API void orc_attn_decode_exact(const void *q, int q_is_f16, const uint16_t *k,
+                                   const uint16_t *v, const int32_t *seqlens, int B, int H,
+                                   int Hkv, int D, int max_seq, int window, float scale_log2,
+                                   float *out);
+
+ORC_API void orc_bitnet_set_exact_attention(orc_bitnet *m, int on) { m->exact_attention = on; }
 
 ORC_API orc_bitnet *orc_bitnet_create(int n_layers, int hidden, int n_heads, int n_kv_heads,
                                       int head_dim, int ffn, int vocab, int max_seq,
@@ -714,8 +722,15 @@ ORC_API int orc_bitnet_step(orc_bitnet *m, int token, int pos, float *logits) {
         kc[((size_t)hh * m->max_seq + pos) * D + d] = orc_f32_to_f16(k[hh * D + d]);
         vc[((size_t)hh * m->max_seq + pos) * D + d] = orc_f32_to_f16(v[hh * D + d]);
       }
-    orc_attn_decode(q, 0, kc, vc, &len, 1, H, Hkv, D, m->max_seq, 0,
-                    (float)(1.0 / sqrt((double)D)), att);
+    {
+      /* scale exactly as the decode engine forms it: f32 operations */
+      const float scale = 1.0f / sqrtf((float)D);
+      if (m->exact_attention)
+        orc_attn_decode_exact(q, 0, kc, vc, &len, 1, H, Hkv, D, m->max_seq, 0,
+                              scale * 1.4426950408889634f, att);
+      else
+        orc_attn_decode(q, 0, kc, vc, &len, 1, H, Hkv, D, m->max_seq, 0, scale, att);
+    }
     orc_bitlinear_forward(L->wo, L->so, qdim, Hd, 1, att, L->attn_sub_norm, m->eps, x, NULL, NULL, x1);
     orc_bitlinear_gateup_relu2(L->wgate, L->sgate, L->wup, L->sup, Hd, F, 1, x1, L->ffn_norm, m->eps, h);
     orc_bitlinear_forward(L->wdown, L->sdown, F, Hd, 1, h, L->ffn_sub_norm, m->eps, x1, NULL, NULL, x);
@@ -726,4 +741,82 @@ ORC_API int orc_bitnet_step(orc_bitnet *m, int token, int pos, float *logits) {
   int tok = orc_argmax(logits, m->vocab);
   free(x); free(x1); free(q); free(k); free(v); free(att); free(h); free(xn);
   return tok;
+}
+
+/* ------------------------------------------------------------------------- */
+/* Operation-for-operation mirror of the CUDA library's EXACT attention mode   */
+/* ------------------------------------------------------------------------- */
+
+/* 2^x for x <= 0 from IEEE f32 operations only; same constants and order as the kernel. */
+static float orc_exp2_det(float x) {
+  if (!(x > -120.0f)) return 0.0f;
+  const float n = rintf(x);
+  const float f = x - n;
+  float p = 1.5403530e-4f;
+  p = fmaf(p, f, 1.3398874e-3f);
+  p = fmaf(p, f, 9.6184370e-3f);
+  p = fmaf(p, f, 5.5503324e-2f);
+  p = fmaf(p, f, 2.4022648e-1f);
+  p = fmaf(p, f, 6.9314720e-1f);
+  p = fmaf(p, f, 1.0f);
+  return ldexpf(p, (int)n);
+}
+
+/* Same inputs, outputs and head mapping as orc_attn_decode, but every f32 operation in
+ * the order the library's bit-reproducible kernel fixes: 32 "lanes" each own D/32
+ * consecutive dims, partial dot products by fma with d ascending, the 32 partials combined
+ * by the xor-butterfly 16,8,4,2,1, online softmax in the exp2 domain with orc_exp2_det,
+ * acc = fma(p, v, acc*alpha), l = fma(l, alpha, p), out = acc / l.  Not a restatement of a
+ * reference function: it exists so that a whole-model run can be compared token for token
+ * (see orc_bitnet_step with exact_attention = 1); orc_attn_decode remains the definition. */
+ORC_API void orc_attn_decode_exact(const void *q, int q_is_f16, const uint16_t *k,
+                                   const uint16_t *v, const int32_t *seqlens, int B, int H,
+                                   int Hkv, int D, int max_seq, int window, float scale_log2,
+                                   float *out) {
+  const int G = H / Hkv, DL = D / 32;
+#pragma omp parallel for collapse(2) schedule(dynamic)
+  for (int b = 0; b < B; ++b) {
+    for (int h = 0; h < H; ++h) {
+      int len = seqlens[b];
+      if (len < 0) len = 0;
+      if (len > max_seq) len = max_seq;
+      int start = 0;
+      if (window > 0 && len > window) start = len - window;
+      const int kvh = h / G;
+      float qf[256], acc[256];
+      for (int d = 0; d < D; ++d) {
+        long qi = ((long)b * H + h) * D + d;
+        qf[d] = q_is_f16 ? orc_f16_to_f32(((const uint16_t *)q)[qi]) : ((const float *)q)[qi];
+        acc[d] = 0.0f;
+      }
+      const uint16_t *kb = k + ((long)b * Hkv + kvh) * (long)max_seq * D;
+      const uint16_t *vb = v + ((long)b * Hkv + kvh) * (long)max_seq * D;
+      float m = -INFINITY, l = 0.0f;
+      for (int s = start; s < len; ++s) {
+        float part[32], tmp[32];
+        for (int lane = 0; lane < 32; ++lane) {
+          float pp = 0.0f;
+          for (int j = 0; j < DL; ++j) {
+            int d = lane * DL + j;
+            pp = fmaf(qf[d], orc_f16_to_f32(kb[(long)s * D + d]), pp);
+          }
+          part[lane] = pp;
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+          for (int lane = 0; lane < 32; ++lane) tmp[lane] = part[lane] + part[lane ^ o];
+          memcpy(part, tmp, sizeof(part));
+        }
+        const float sc = part[0] * scale_log2;
+        const float mn = (m > sc) ? m : sc;
+        const float alpha = orc_exp2_det(m - mn);
+        const float pw = orc_exp2_det(sc - mn);
+        l = fmaf(l, alpha, pw);
+        for (int d = 0; d < D; ++d)
+          acc[d] = fmaf(pw, orc_f16_to_f32(vb[(long)s * D + d]), acc[d] * alpha);
+        m = mn;
+      }
+      float *o = out + ((long)b * H + h) * D;
+      for (int d = 0; d < D; ++d) o[d] = l > 0.0f ? acc[d] / l : 0.0f;
+    }
+  }
 }

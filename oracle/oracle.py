@@ -250,6 +250,22 @@ def attn_decode(q, k_f16, v_f16, seqlens, H, Hkv, D, max_seq, scale, window=0):
     return out
 
 
+def attn_decode_exact(q, k_f16, v_f16, seqlens, H, Hkv, D, max_seq, scale, window=0):
+    """Mirror of the library's EXACT attention mode (same f32 operations in the same order)."""
+    q_is_f16 = q.dtype == np.float16
+    qq = np.ascontiguousarray(q)
+    kk = np.ascontiguousarray(k_f16, dtype=np.float16).view(np.uint16)
+    vv = np.ascontiguousarray(v_f16, dtype=np.float16).view(np.uint16)
+    sl = _c(seqlens, np.int32)
+    B = sl.size
+    out = np.empty((B, H, D), np.float32)
+    qptr = qq.view(np.uint16) if q_is_f16 else qq.astype(np.float32, copy=False)
+    scale_log2 = np.float32(scale) * np.float32(1.4426950408889634)
+    lib().orc_attn_decode_exact(_p(qptr), int(q_is_f16), _p(kk), _p(vv), _p(sl), B, H, Hkv, D,
+                                max_seq, window, C.c_float(scale_log2), _p(out))
+    return out
+
+
 # ---- glue -----------------------------------------------------------------------
 
 def rope_neox(x, pos, base):
@@ -311,6 +327,9 @@ class BitNetOracle:
             shape.ffn, shape.vocab, shape.max_seq, C.c_double(shape.rope_base),
             C.c_float(shape.rms_eps), arr, _p(self._emb), _p(self._fn)))
         self.pos = 0
+
+    def set_exact_attention(self, on: bool):
+        lib().orc_bitnet_set_exact_attention(self._h, int(bool(on)))
 
     def step(self, token: int):
         """Feeds one token at the next position; returns (greedy token, logits f32 [vocab])."""

@@ -127,3 +127,43 @@ def test_long_context_properties(ctx):
     b = execute_flash_attention_v11(ctx, q, k, v2, lens, **kw)
     assert torch.equal(a, b)
     ctx.check()
+
+
+@pytest.mark.parametrize("B,H,Hkv,D,L", [(2, 8, 2, 256, 3000), (1, 20, 5, 128, 777), (3, 8, 8, 64, 50)])
+def test_precise_mode(ctx, oracle, B, H, Hkv, D, L):
+    """hi+lo f16 split of q and the softmax weights: only f32 accumulation error remains."""
+    rng = np.random.default_rng(L)
+    q = rng.standard_normal((B, H, D)).astype(np.float32)
+    k = rng.standard_normal((B, Hkv, L, D)).astype(np.float16)
+    v = rng.standard_normal((B, Hkv, L, D)).astype(np.float16)
+    lens = np.full(B, L, np.int32)
+    ref = oracle.attn_decode(q, k, v, lens, H, Hkv, D, L, 1.0 / np.sqrt(D))
+    ctx.set_attn_mode(ctx.ATTN_PRECISE)
+    try:
+        out = _run(ctx, q, k, v, lens, H, Hkv, D, L, 1.0 / np.sqrt(D))
+    finally:
+        ctx.set_attn_mode(ctx.ATTN_FAST)
+    ctx.check()
+    _check(out, ref, tol=2e-5)
+
+
+@pytest.mark.parametrize("B,H,Hkv,D,L,window", [(2, 8, 2, 256, 300, 0), (1, 20, 5, 128, 777, 0),
+                                                (3, 8, 8, 64, 50, 20), (2, 4, 2, 128, 1, 0)])
+def test_exact_mode_is_bit_reproducible(ctx, oracle, B, H, Hkv, D, L, window):
+    """EXACT mode equals its CPU mirror bit for bit and the f64 definition to ~1e-6."""
+    rng = np.random.default_rng(L + D)
+    q = rng.standard_normal((B, H, D)).astype(np.float32)
+    k = rng.standard_normal((B, Hkv, L, D)).astype(np.float16)
+    v = rng.standard_normal((B, Hkv, L, D)).astype(np.float16)
+    lens = rng.integers(max(1, L // 2), L + 1, B).astype(np.int32)
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(D)))
+    mirror = oracle.attn_decode_exact(q, k, v, lens, H, Hkv, D, L, scale, window)
+    ref = oracle.attn_decode(q, k, v, lens, H, Hkv, D, L, scale, window)
+    ctx.set_attn_mode(ctx.ATTN_EXACT)
+    try:
+        out = _run(ctx, q, k, v, lens, H, Hkv, D, L, scale, window)
+    finally:
+        ctx.set_attn_mode(ctx.ATTN_FAST)
+    ctx.check()
+    assert np.array_equal(out, mirror)
+    _check(out, ref, tol=2e-5)

@@ -1,10 +1,17 @@
 """GPU parity of the whole decode step of a BitNet-b1.58-shaped model (random-init weights)
 against the CPU oracle model: greedy tokens over 64 steps and logits.
 
-Comparison rule (stated before measuring): the oracle runs attention in f64 while the GPU
-uses f16 tensor-core products, so two near-tied logits may swap.  Each step is teacher-forced
-with the oracle's token; a differing argmax counts as a mismatch only if the oracle's own
-top-1/top-2 margin exceeds MARGIN times the logit standard deviation."""
+Why the attention runs in its EXACT mode here: the model re-quantises its activations to int8
+after every block, so it is chaotic at the level of its quantisation noise -- one activation
+rounding the other way because attention differed by 1e-6 becomes per-cent logit noise a few
+layers later, and a 30-layer random-init model then swaps near-tied tokens every few steps.
+With the bit-reproducible attention kernel (mirrored operation for operation by the oracle)
+every quantiser sees identical inputs on both sides; what is left is the LM head's f32 versus
+f64 accumulation (~1e-6).
+
+Comparison rule (stated before measuring): each step is teacher-forced with the oracle's
+token; a differing argmax counts as a mismatch only if the oracle's own top-1/top-2 margin
+exceeds MARGIN times the logit standard deviation."""
 import numpy as np
 import pytest
 import torch
@@ -12,18 +19,27 @@ import torch
 from hesper_b200 import BitNetModel, BitNetShape, random_bitnet_weights
 
 pytestmark = pytest.mark.gpu
-MARGIN = 0.02
+MARGIN = 1e-4
 
 SMALL = BitNetShape(n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=384,
                     vocab=512, max_seq=96, rope_base=500000.0, rms_eps=1e-5)
+
+
+@pytest.fixture(autouse=True)
+def _exact_attention(ctx):
+    ctx.set_attn_mode(ctx.ATTN_EXACT)
+    yield
+    ctx.set_attn_mode(ctx.ATTN_FAST)
 
 
 def _forced_compare(ctx, oracle, shape, weights, prompt, n_steps, batch=1):
     from oracle.oracle import BitNetOracle
     model = BitNetModel(ctx, shape, weights, batch=batch, max_new_tokens=n_steps + 1)
     oracles = [BitNetOracle(shape, weights) for _ in range(batch)]
+    for o in oracles:
+        o.set_exact_attention(True)
     toks = [list(prompt[b]) for b in range(batch)]
-    mismatches, worst = 0, 0.0
+    mismatches, devs = 0, []
     n_total = prompt.shape[1] + n_steps
     for t in range(n_total):
         cur = np.array([toks[b][t] for b in range(batch)], np.int32)
@@ -31,7 +47,7 @@ def _forced_compare(ctx, oracle, shape, weights, prompt, n_steps, batch=1):
         for b in range(batch):
             o_tok, o_logits = oracles[b].step(int(cur[b]))
             sd = float(np.std(o_logits))
-            worst = max(worst, float(np.max(np.abs(g_logits[b] - o_logits))) / sd)
+            devs.append(float(np.max(np.abs(g_logits[b] - o_logits))) / sd)
             if t >= prompt.shape[1] - 1:
                 if t + 1 >= len(toks[b]):
                     toks[b].append(o_tok)  # teacher forcing with the oracle's token
@@ -42,22 +58,29 @@ def _forced_compare(ctx, oracle, shape, weights, prompt, n_steps, batch=1):
     for o in oracles:
         o.close()
     model.close()
-    return mismatches, worst
+    return mismatches, np.array(devs)
+
+
+def _check_devs(devs):
+    """Logit agreement per step: max |gpu - oracle| over the vocabulary in units of the logit
+    spread.  Only the LM head's accumulation order differs between the two sides."""
+    assert np.max(devs) < 1e-4
 
 
 def test_small_model_forced_64_steps(ctx, oracle):
     w = random_bitnet_weights(SMALL, seed=1)
     prompt = np.random.default_rng(0).integers(0, SMALL.vocab, (1, 8)).astype(np.int32)
-    mism, worst = _forced_compare(ctx, oracle, SMALL, w, prompt, 64)
+    mism, devs = _forced_compare(ctx, oracle, SMALL, w, prompt, 64)
     assert mism == 0
-    assert worst < 0.05  # logits within 5 % of their spread
+    _check_devs(devs)
 
 
 def test_small_model_batch3(ctx, oracle):
     w = random_bitnet_weights(SMALL, seed=2)
     prompt = np.random.default_rng(1).integers(0, SMALL.vocab, (3, 5)).astype(np.int32)
-    mism, worst = _forced_compare(ctx, oracle, SMALL, w, prompt, 16, batch=3)
-    assert mism == 0 and worst < 0.05
+    mism, devs = _forced_compare(ctx, oracle, SMALL, w, prompt, 16, batch=3)
+    assert mism == 0
+    _check_devs(devs)
 
 
 def test_generate_graph_equals_stepwise(ctx):
@@ -86,6 +109,6 @@ def test_full_size_bitnet2b_forced_64_steps(ctx, oracle):
     shape = BitNetShape.bitnet_2b(max_seq=128)
     w = random_bitnet_weights(shape, seed=4)
     prompt = np.random.default_rng(3).integers(0, shape.vocab, (1, 4)).astype(np.int32)
-    mism, worst = _forced_compare(ctx, oracle, shape, w, prompt, 64)
+    mism, devs = _forced_compare(ctx, oracle, shape, w, prompt, 64)
     assert mism == 0
-    assert worst < 0.05
+    _check_devs(devs)

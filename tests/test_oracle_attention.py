@@ -106,3 +106,17 @@ def test_golden_q4k_and_bitlinear(oracle):
     yk = oracle.bitlinear_spec(np.full(a["K"] // 4, a["byte"], np.uint8), 1.0, a["K"], 1,
                                np.ones((1, a["K"]), np.float32))
     assert yk[0, 0] == a["y"]
+
+
+def test_exact_order_mirror_agrees_with_definition(oracle):
+    """The f32 fixed-order attention (mirror of the library's EXACT mode) stays within 1e-5
+    of the f64 definition, so using it for whole-model parity does not change what is tested."""
+    rng = np.random.default_rng(5)
+    B, H, Hkv, D, L = 2, 8, 2, 128, 400
+    q = rng.standard_normal((B, H, D)).astype(np.float32)
+    k = rng.standard_normal((B, Hkv, L, D)).astype(np.float16)
+    v = rng.standard_normal((B, Hkv, L, D)).astype(np.float16)
+    for window in (0, 100):
+        a = oracle.attn_decode(q, k, v, [L, 37], H, Hkv, D, L, 0.09, window)
+        b = oracle.attn_decode_exact(q, k, v, [L, 37], H, Hkv, D, L, 0.09, window)
+        assert np.max(np.abs(a - b)) < 1e-5 * np.max(np.abs(a))
