@@ -555,3 +555,52 @@ extern "C" int hb200_attn_decode(hb200_ctx* ctx, const void* d_q, int q_is_f16, 
     default: return attn_launch<256, false>(ctx, p, st);
   }
 }
+
+// ---- the same operator for callers that must not allocate -----------------------------
+//
+// Split-K partials need scratch memory.  hb200_attn_decode takes it from the caller; this
+// variant keeps it inside the library image instead, as one fixed array in device global
+// memory.  Every GPU that loads the library carries those 8 MiB until the process exits.
+static __device__ __align__(256) unsigned char g_attn_static_scratch[HB200_ATTN_STATIC_SCRATCH_BYTES];
+
+// Device address of the array, looked up once per device.  In host code the array's name
+// is only a handle for the runtime, never a pointer a kernel could use.
+static void* g_attn_static_scratch_addr[64] = {};
+
+extern "C" int hb200_attn_decode_static(hb200_ctx* ctx, const void* d_q, int q_is_f16,
+                                        const void* d_k, const void* d_v,
+                                        const int32_t* d_seqlens, int B, int H, int Hkv, int D,
+                                        int max_seq, int window, float scale, float* d_out,
+                                        hb200_stream stream) {
+  HB_REQUIRE(ctx != nullptr, "attn (static scratch): null context");
+  HB_REQUIRE(B >= 1 && H >= 1 && Hkv >= 1 && H % Hkv == 0 && max_seq >= 1 && window >= 0 && D >= 1,
+             "attn (static scratch): B=%d H=%d Hkv=%d D=%d max_seq=%d window=%d", B, H, Hkv, D,
+             max_seq, window);
+  HB_REQUIRE(ctx->device >= 0 && ctx->device < 64, "attn (static scratch): device %d", ctx->device);
+  // the split count the launch below will choose, hence the scratch it will touch
+  const int eff_len = (window > 0 && window < max_seq) ? window : max_seq;
+  const int nsplit = attn_pick_splits(ctx, B, Hkv, eff_len);
+  const size_t need =
+      nsplit > 1 ? (size_t)B * Hkv * nsplit * 8 * ((size_t)D + 2) * sizeof(float) : 0;
+  if (need > (size_t)HB200_ATTN_STATIC_SCRATCH_BYTES) {
+    set_error("attn (static scratch): this shape needs %zu bytes of split-K scratch but the "
+              "built-in array holds %zu; call hb200_attn_decode with a workspace of your own",
+              need, (size_t)HB200_ATTN_STATIC_SCRATCH_BYTES);
+    return HB200_ERR_UNSUPPORTED;
+  }
+  int cur = -1;
+  HB_CUDA(cudaGetDevice(&cur));
+  HB_REQUIRE(cur == ctx->device,
+             "attn (static scratch): device %d is current but the context belongs to device %d",
+             cur, ctx->device);
+  void*& addr = g_attn_static_scratch_addr[ctx->device];
+  if (addr == nullptr) {  // first call on this device
+    void* p = nullptr;
+    HB_CUDA(cudaGetSymbolAddress(&p, g_attn_static_scratch));
+    addr = p;
+  }
+  // Nothing in the array has to be cleared: the decode kernel writes every partial
+  // (max, sum, output row) that the combine kernel of the same call reads.
+  return hb200_attn_decode(ctx, d_q, q_is_f16, d_k, d_v, d_seqlens, B, H, Hkv, D, max_seq, window,
+                           scale, addr, (size_t)HB200_ATTN_STATIC_SCRATCH_BYTES, d_out, stream);
+}

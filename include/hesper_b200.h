@@ -199,6 +199,34 @@ int hb200_attn_decode(hb200_ctx *ctx, const void *d_q, int q_is_f16, const void 
                       size_t workspace_bytes, float *d_out, hb200_stream stream);
 
 
+/* Decode attention for callers that cannot hand over scratch memory.  No counterpart in
+ * the reference (there the Lean side allocates the V11 partial buffers with the model).
+ *
+ * Same operator, arguments and results as hb200_attn_decode, minus the workspace: the
+ * split-K partials go to a fixed HB200_ATTN_STATIC_SCRATCH_BYTES array that is part of
+ * the library image, so the call never allocates or frees device memory, neither directly
+ * nor through a library.  It is meant for hosts where a device allocation at this point is
+ * not an option: a runtime that has already handed the whole GPU to its own buffer pool
+ * (Hesper's pooled CUDABuffer allocator works that way), a thread that may not stall on the
+ * device-wide synchronisation cudaMalloc can imply, or code running in a host callback,
+ * where CUDA API calls are not allowed at all.
+ *
+ *   - Shapes whose partials exceed the array are refused with HB200_ERR_UNSUPPORTED and
+ *     a message naming both sizes (the BASELINE sweeps up to batch 64 x 32768 positions
+ *     at 8/2 heads, D = 256, fit); use hb200_attn_decode for larger ones.
+ *   - The first call on a device looks up the array's device address.  Make that first
+ *     call before any stream capture is started on the thread.
+ *   - All calls on a device share the one array and find the previous call's partials in
+ *     it; that is harmless (every value read is written first within the same call), but
+ *     two calls that overlap on the GPU, e.g. on different streams, race on it.  Keep calls
+ *     to this entry point ordered on one stream per device.
+ *   - Every GPU that loads the library holds the array for the lifetime of the process. */
+#define HB200_ATTN_STATIC_SCRATCH_BYTES (8u << 20)
+int hb200_attn_decode_static(hb200_ctx *ctx, const void *d_q, int q_is_f16, const void *d_k,
+                             const void *d_v, const int32_t *d_seqlens, int B, int H, int Hkv,
+                             int D, int max_seq, int window, float scale, float *d_out,
+                             hb200_stream stream);
+
 /* ---- decode-step glue ------------------------------------------------------- */
 
 /* y[m] = table[ids[m]] * scale as f32.  dtype: 0 = bf16, 1 = f16, 2 = f32.
