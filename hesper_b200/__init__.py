@@ -12,5 +12,6 @@ from .layers import (  # noqa: F401
 )
 
 from .models import BitNetModel, BitNetShape, random_bitnet_weights  # noqa: F401
+from .tp import GemmaModel, GemmaShape, TensorParallel  # noqa: F401
 
 __version__ = "0.1.0"

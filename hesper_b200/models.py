@@ -64,6 +64,35 @@ def random_bitnet_weights(shape: BitNetShape, seed: int = 0x1337C0DE, device=Non
     return {"layers": layers, "embed": emb_bf16, "final_norm": final_norm}
 
 
+def random_bitnet_weights_device(shape: BitNetShape, seed: int = 0x1337C0DE, device="cuda"):
+    """Same distributions as random_bitnet_weights, generated on the GPU (seconds instead of
+    minutes at the 2B size).  Values differ from the host generator; use it where no CPU
+    comparison is needed (benchmarks)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    dims = {"hidden": shape.hidden, "qdim": shape.n_heads * shape.head_dim,
+            "kvdim": shape.n_kv_heads * shape.head_dim, "ffn": shape.ffn}
+
+    def ternary_packed(N, K):
+        u = torch.randint(0, 4, (N, K // 128, 4, 32), device=device, generator=g, dtype=torch.uint8)
+        c = (u + 1) // 2  # codes 0,1,1,2 -> P(-1,0,+1) = 1/4,1/2,1/4
+        b = (c[:, :, 0] << 6) | (c[:, :, 1] << 4) | (c[:, :, 2] << 2) | c[:, :, 3]
+        return b.reshape(-1).contiguous()
+
+    layers = []
+    for _ in range(shape.n_layers):
+        L = {}
+        for name, kin, nout in LAYER_TENSORS:
+            L[name] = ternary_packed(dims[nout], dims[kin])
+            L["s" + name[1:]] = float(torch.empty(1).uniform_(0.01, 0.1).item())
+        for nm, d in (("attn_norm", shape.hidden), ("attn_sub_norm", dims["qdim"]),
+                      ("ffn_norm", shape.hidden), ("ffn_sub_norm", shape.ffn)):
+            L[nm] = 1.0 + 0.05 * torch.randn(d, device=device, generator=g)
+        layers.append(L)
+    emb = (0.02 * torch.randn(shape.vocab, shape.hidden, device=device, generator=g)).to(torch.bfloat16)
+    final_norm = 1.0 + 0.05 * torch.randn(shape.hidden, device=device, generator=g)
+    return {"layers": layers, "embed": emb.view(torch.int16), "final_norm": final_norm}
+
+
 class BitNetModel:
     """BitNet-b1.58-shaped model resident on one GPU."""
 
@@ -75,7 +104,10 @@ class BitNetModel:
         self._keep: List[torch.Tensor] = []
 
         def up(a, dt=None):
-            t = torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+            if isinstance(a, torch.Tensor):
+                t = a.to(dev).contiguous()
+            else:
+                t = torch.from_numpy(np.ascontiguousarray(a)).to(dev)
             self._keep.append(t)
             return t
 
@@ -88,7 +120,8 @@ class BitNetModel:
                 f[name] = up(L[name]).data_ptr()
                 f["s" + name[1:]] = up(np.array([L["s" + name[1:]]], np.float32)).data_ptr()
             arr[i] = BitNetLayer(**f)
-        self.embed = up(weights["embed"].view(np.int16))
+        emb = weights["embed"]
+        self.embed = up(emb if isinstance(emb, torch.Tensor) else emb.view(np.int16))
         self.final_norm = up(weights["final_norm"])
         cfg = BitNetConfig(shape.n_layers, shape.hidden, shape.n_heads, shape.n_kv_heads,
                            shape.head_dim, shape.ffn, shape.vocab, shape.max_seq,

@@ -820,3 +820,99 @@ ORC_API void orc_attn_decode_exact(const void *q, int q_is_f16, const uint16_t *
     }
   }
 }
+
+/* ------------------------------------------------------------------------- */
+/* Whole decode step of a Gemma-4-E4B-shaped model (Q4_K weights)              */
+/* ------------------------------------------------------------------------- */
+
+/* Block order of Gemma4.forwardBlock (Hesper/Models/Gemma4.lean:485): norm -> q/k/v ->
+ * RoPE -> f16 KV append -> attention -> o_proj -> post-attention norm then add -> norm ->
+ * gelu_tanh(gate)*up -> down_proj -> post-FFN norm then add (forwardNormThenAdd); final norm,
+ * Q4_K LM head, greedy argmax.  Sliding-window layers attend to the last `window` positions
+ * (the rule of flashAttentionSWAKernel, Hesper/WGSL/FlashAttention.lean:1621-1624); layer l is
+ * global when (l+1) % global_every == 0.  Unsharded: the tensor-parallel run must reproduce it. */
+typedef struct orc_gemma_layer {
+  const float *attn_norm, *post_attn_norm, *ffn_norm, *post_ffn_norm;
+  const uint8_t *wq, *wk, *wv, *wo, *wgate, *wup, *wdown;
+} orc_gemma_layer;
+
+typedef struct orc_gemma {
+  int n_layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab, max_seq, window, global_every;
+  double rope_base;
+  float eps, attn_scale, embed_scale;
+  const orc_gemma_layer *layers;
+  const uint16_t *embed; /* bf16 */
+  const uint8_t *lm_head;
+  const float *final_norm;
+  uint16_t *kcache, *vcache;
+} orc_gemma;
+
+ORC_API orc_gemma *orc_gemma_create(int n_layers, int hidden, int n_heads, int n_kv_heads,
+                                    int head_dim, int ffn, int vocab, int max_seq, int window,
+                                    int global_every, double rope_base, float eps,
+                                    float attn_scale, float embed_scale,
+                                    const orc_gemma_layer *layers, const uint16_t *embed,
+                                    const uint8_t *lm_head, const float *final_norm) {
+  orc_gemma *m = (orc_gemma *)calloc(1, sizeof(orc_gemma));
+  m->n_layers = n_layers; m->hidden = hidden; m->n_heads = n_heads; m->n_kv_heads = n_kv_heads;
+  m->head_dim = head_dim; m->ffn = ffn; m->vocab = vocab; m->max_seq = max_seq;
+  m->window = window; m->global_every = global_every; m->rope_base = rope_base; m->eps = eps;
+  m->attn_scale = attn_scale; m->embed_scale = embed_scale; m->layers = layers;
+  m->embed = embed; m->lm_head = lm_head; m->final_norm = final_norm;
+  size_t n = (size_t)n_layers * n_kv_heads * max_seq * head_dim;
+  m->kcache = (uint16_t *)calloc(n, 2);
+  m->vcache = (uint16_t *)calloc(n, 2);
+  return m;
+}
+
+ORC_API void orc_gemma_destroy(orc_gemma *m) {
+  if (!m) return;
+  free(m->kcache);
+  free(m->vcache);
+  free(m);
+}
+
+ORC_API int orc_gemma_step(orc_gemma *m, int token, int pos, float *logits) {
+  const int Hd = m->hidden, H = m->n_heads, Hkv = m->n_kv_heads, D = m->head_dim, F = m->ffn;
+  const int qdim = H * D, kvdim = Hkv * D;
+  float *x = (float *)malloc(sizeof(float) * Hd), *x1 = (float *)malloc(sizeof(float) * Hd);
+  float *xn = (float *)malloc(sizeof(float) * Hd), *o = (float *)malloc(sizeof(float) * Hd);
+  float *q = (float *)malloc(sizeof(float) * qdim), *k = (float *)malloc(sizeof(float) * kvdim);
+  float *v = (float *)malloc(sizeof(float) * kvdim), *att = (float *)malloc(sizeof(float) * qdim);
+  float *h = (float *)malloc(sizeof(float) * F);
+  for (int i = 0; i < Hd; ++i)
+    x[i] = orc_bf16_to_f32(m->embed[(size_t)token * Hd + i]) * m->embed_scale;
+  int32_t len = pos + 1;
+  for (int l = 0; l < m->n_layers; ++l) {
+    const orc_gemma_layer *L = &m->layers[l];
+    const int global = m->global_every > 0 && (l + 1) % m->global_every == 0;
+    orc_rmsnorm_f32(x, L->attn_norm, Hd, m->eps, xn);
+    orc_q4k_matvec(L->wq, Hd, qdim, 1, xn, NULL, q);
+    orc_q4k_matvec(L->wk, Hd, kvdim, 1, xn, NULL, k);
+    orc_q4k_matvec(L->wv, Hd, kvdim, 1, xn, NULL, v);
+    for (int hh = 0; hh < H; ++hh) orc_rope_neox(q + hh * D, D, pos, m->rope_base);
+    for (int hh = 0; hh < Hkv; ++hh) orc_rope_neox(k + hh * D, D, pos, m->rope_base);
+    uint16_t *kc = m->kcache + (size_t)l * Hkv * m->max_seq * D;
+    uint16_t *vc = m->vcache + (size_t)l * Hkv * m->max_seq * D;
+    for (int hh = 0; hh < Hkv; ++hh)
+      for (int d = 0; d < D; ++d) {
+        kc[((size_t)hh * m->max_seq + pos) * D + d] = orc_f32_to_f16(k[hh * D + d]);
+        vc[((size_t)hh * m->max_seq + pos) * D + d] = orc_f32_to_f16(v[hh * D + d]);
+      }
+    orc_attn_decode(q, 0, kc, vc, &len, 1, H, Hkv, D, m->max_seq, global ? 0 : m->window,
+                    m->attn_scale, att);
+    orc_q4k_matvec(L->wo, qdim, Hd, 1, att, NULL, o);
+    orc_rmsnorm_f32(o, L->post_attn_norm, Hd, m->eps, xn);
+    for (int i = 0; i < Hd; ++i) x1[i] = x[i] + xn[i];
+    orc_rmsnorm_f32(x1, L->ffn_norm, Hd, m->eps, xn);
+    orc_kquant_gateup_gelu(L->wgate, L->wup, 12, Hd, F, 1, xn, h);
+    orc_q4k_matvec(L->wdown, F, Hd, 1, h, NULL, o);
+    orc_rmsnorm_f32(o, L->post_ffn_norm, Hd, m->eps, xn);
+    for (int i = 0; i < Hd; ++i) x[i] = x1[i] + xn[i];
+  }
+  orc_rmsnorm_f32(x, m->final_norm, Hd, m->eps, xn);
+  orc_q4k_matvec(m->lm_head, Hd, m->vocab, 1, xn, NULL, logits);
+  int tok = orc_argmax(logits, m->vocab);
+  free(x); free(x1); free(xn); free(o); free(q); free(k); free(v); free(att); free(h);
+  return tok;
+}

@@ -342,3 +342,48 @@ class BitNetOracle:
         if self._h:
             lib().orc_bitnet_destroy(self._h)
             self._h = None
+
+
+class _OrcGemmaLayer(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("attn_norm", "post_attn_norm", "ffn_norm", "post_ffn_norm",
+                                          "wq", "wk", "wv", "wo", "wgate", "wup", "wdown")]
+
+
+class GemmaOracle:
+    """Unsharded CPU model of one sequence (orc_gemma_step); weights as produced by
+    hesper_b200.tp.random_gemma_weights."""
+
+    def __init__(self, shape, weights):
+        L = lib()
+        L.orc_gemma_create.restype = C.c_void_p
+        self.shape = shape
+        self._keep = []
+        arr = (_OrcGemmaLayer * shape.n_layers)()
+        for i, W in enumerate(weights["layers"]):
+            f = {}
+            for n in ("attn_norm", "post_attn_norm", "ffn_norm", "post_ffn_norm"):
+                a = _c(W[n], np.float32); self._keep.append(a); f[n] = a.ctypes.data
+            for n in ("wq", "wk", "wv", "wo", "wgate", "wup", "wdown"):
+                a = _c(W[n], np.uint8); self._keep.append(a); f[n] = a.ctypes.data
+            arr[i] = _OrcGemmaLayer(**f)
+        self._arr = arr
+        self._emb = _c(weights["embed"], np.uint16)
+        self._lm = _c(weights["lm_head"], np.uint8)
+        self._fn = _c(weights["final_norm"], np.float32)
+        self._h = C.c_void_p(L.orc_gemma_create(
+            shape.n_layers, shape.hidden, shape.n_heads, shape.n_kv_heads, shape.head_dim,
+            shape.ffn, shape.vocab, shape.max_seq, shape.window, shape.global_every,
+            C.c_double(shape.rope_base), C.c_float(shape.rms_eps), C.c_float(shape.attn_scale),
+            C.c_float(shape.embed_scale), arr, _p(self._emb), _p(self._lm), _p(self._fn)))
+        self.pos = 0
+
+    def step(self, token: int):
+        logits = np.empty(self.shape.vocab, np.float32)
+        tok = lib().orc_gemma_step(self._h, int(token), self.pos, _p(logits))
+        self.pos += 1
+        return int(tok), logits
+
+    def close(self):
+        if self._h:
+            lib().orc_gemma_destroy(self._h)
+            self._h = None
