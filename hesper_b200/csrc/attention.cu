@@ -45,6 +45,7 @@ struct AttnParams {
   int q_is_f16;
   int B, H, Hkv, G, max_seq, window, nsplit;
   float scale_log2;  // scale * log2(e)
+  int* tickets;      // nullable: per (sequence, kv head) arrival counters, zero between calls
 };
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -350,6 +351,63 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __gr
       }
     }
   }
+  if (p.nsplit == 1 || p.tickets == nullptr) return;
+
+  // ---- the last split to finish merges all splits of its (sequence, kv head) ------------
+  // Each CTA publishes its partials, then takes a ticket; whoever draws the last one knows
+  // every other CTA's partials are visible (fence before the ticket, fence after) and does
+  // the work the separate combine kernel would do, saving that launch.
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int t = atomicAdd(&p.tickets[b * p.Hkv + kvh], 1);
+    s_last = (t == p.nsplit - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  float* cw = reinterpret_cast<float*>(smem + Cfg::kQBytes);  // [nsplit][8] weights, then [8] sums
+  float* cl = cw + kMaxSplits * 8;
+  const size_t base = ((size_t)b * p.Hkv + kvh) * p.nsplit;
+  for (int i = tid; i < p.nsplit * 8; i += kAttnThreads) {  // stage (max, sum) of every split
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_meta) + base * 8 + i);
+    cw[i] = ml.x;
+    cw[kMaxSplits * 8 + 8 + i] = ml.y;
+  }
+  __syncthreads();
+  if (tid < 8) {
+    float mstar = -CUDART_INF_F;
+    for (int sidx = 0; sidx < p.nsplit; ++sidx) mstar = fmaxf(mstar, cw[sidx * 8 + tid]);
+    float lsum = 0.f;
+    for (int sidx = 0; sidx < p.nsplit; ++sidx) {
+      const float wgt = mstar == -CUDART_INF_F ? 0.f : exp2f(cw[sidx * 8 + tid] - mstar);
+      lsum += wgt * cw[kMaxSplits * 8 + 8 + sidx * 8 + tid];
+      cw[sidx * 8 + tid] = wgt;
+    }
+    cl[tid] = lsum;
+  }
+  __syncthreads();
+  // 4 consecutive dims per thread, 8 splits' loads in flight at a time
+  for (int i = tid; i < G * D / 4; i += kAttnThreads) {
+    const int h = (i * 4) / D, d = (i * 4) % D;
+    const float4* src = reinterpret_cast<const float4*>(p.part_out + (base * 8 + h) * D + d);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int sidx = 0; sidx < p.nsplit; ++sidx) {
+      const float4 v = __ldcg(src + (size_t)sidx * 2 * D);  // next split: 8*D floats further
+      const float wgt = cw[sidx * 8 + h];
+      acc.x = fmaf(wgt, v.x, acc.x);
+      acc.y = fmaf(wgt, v.y, acc.y);
+      acc.z = fmaf(wgt, v.z, acc.z);
+      acc.w = fmaf(wgt, v.w, acc.w);
+    }
+    const float lsum = cl[h];
+    const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
+    float4* dst = reinterpret_cast<float4*>(p.out + ((size_t)b * p.H + (size_t)kvh * G + h) * D + d);
+    *dst = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+  }
+  if (tid == 0) p.tickets[b * p.Hkv + kvh] = 0;  // ready for the next call
 }
 
 // Merges the split partials: out = sum_s 2^(m_s - m*) O_s / sum_s 2^(m_s - m*) l_s.
@@ -474,7 +532,7 @@ static int attn_launch(hb200_ctx* ctx, const AttnParams& p, cudaStream_t st) {
   }
   const int grid = p.B * p.Hkv * p.nsplit;
   HB_CUDA(launch_pdl(kern, dim3(grid), dim3(kAttnThreads), (size_t)Cfg::kSmem, st, ctx->pdl, p));
-  if (p.nsplit > 1) {
+  if (p.nsplit > 1 && p.tickets == nullptr) {
     HB_CUDA(launch_pdl(attn_combine_kernel, dim3(p.B * p.H), dim3(D >= 128 ? 128 : 64), 0, st,
                        ctx->pdl, p, D));
   }
@@ -531,6 +589,9 @@ extern "C" int hb200_attn_decode(hb200_ctx* ctx, const void* d_q, int q_is_f16, 
                "attn: workspace must be 16-byte aligned");
     p.part_out = static_cast<float*>(d_workspace);
     p.part_meta = reinterpret_cast<float*>(static_cast<uint8_t*>(d_workspace) + po);
+    // arrival counters live in the context (zeroed at creation, left zero by every call);
+    // beyond their capacity the separate combine kernel is used instead
+    p.tickets = (B * Hkv <= hb::kCtxTickets) ? ctx->d_tickets : nullptr;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (ctx->attn_mode == HB200_ATTN_EXACT) {

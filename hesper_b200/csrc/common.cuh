@@ -17,6 +17,7 @@ constexpr int kWarp = 32;
 // bit when a bounded wait gives up; word 1 keeps the id of the first reporter.
 constexpr uint32_t kStatusMbarTimeout = 1u;
 constexpr uint32_t kStatusFlagTimeout = 2u;
+constexpr int kCtxTickets = 4096;  // arrival counters kept by a context
 
 // ---- PTX wrappers -----------------------------------------------------------
 
@@ -189,7 +190,8 @@ struct hb200_ctx {
   int device;
   int sm_count;
   int smem_optin;      // max dynamic shared memory per block
-  uint32_t* d_status;  // 16 words
+  uint32_t* d_status;  // 64 words
+  int* d_tickets;      // kCtxTickets zero-initialised arrival counters
   bool pdl;            // use programmatic dependent launch
   int attn_mode;       // HB200_ATTN_FAST / PRECISE / EXACT
 };

@@ -46,6 +46,7 @@ extern "C" int hb200_ctx_create(int device, hb200_ctx** out) {
     return HB200_ERR_UNSUPPORTED;
   }
   hb200_ctx* c = new hb200_ctx();
+  c->d_tickets = nullptr;
   c->device = device;
   c->sm_count = prop.multiProcessorCount;
   c->smem_optin = (int)prop.sharedMemPerBlockOptin;
@@ -59,10 +60,13 @@ extern "C" int hb200_ctx_create(int device, hb200_ctx** out) {
     return cuda_fail(e, "cudaMalloc(status)");
   }
   e = cudaMemset(c->d_status, 0, 256);
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_tickets, sizeof(int) * kCtxTickets);
+  if (e == cudaSuccess) e = cudaMemset(c->d_tickets, 0, sizeof(int) * kCtxTickets);
   if (e != cudaSuccess) {
     cudaFree(c->d_status);
+    cudaFree(c->d_tickets);
     delete c;
-    return cuda_fail(e, "cudaMemset(status)");
+    return cuda_fail(e, "context buffers");
   }
   *out = c;
   return HB200_OK;
@@ -71,6 +75,7 @@ extern "C" int hb200_ctx_create(int device, hb200_ctx** out) {
 extern "C" int hb200_ctx_destroy(hb200_ctx* ctx) {
   if (!ctx) return HB200_OK;
   cudaFree(ctx->d_status);
+  cudaFree(ctx->d_tickets);
   delete ctx;
   return HB200_OK;
 }

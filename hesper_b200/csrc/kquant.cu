@@ -28,6 +28,21 @@
 
 namespace hb {
 
+#ifdef HB_PROFILE
+__device__ __forceinline__ unsigned long long kq_gtimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define HB_STAMP(i)                                                           \
+  do {                                                                        \
+    if (blockIdx.x == 0 && threadIdx.x == 0)                                  \
+      reinterpret_cast<unsigned long long*>(p.status)[1 + (i)] = kq_gtimer(); \
+  } while (0)
+#else
+#define HB_STAMP(i) ((void)0)
+#endif
+
 constexpr int kKQMaxSeg = 4;
 constexpr int kKQThreads = 384;
 constexpr int kKQWarps = kKQThreads / 32;
@@ -46,7 +61,8 @@ struct KQParams {
   int ntiles;
   int K;
   int M;
-  int stages;
+  int stages;   // tiles a warp keeps in flight
+  int nslots;   // stage slots of the CTA: min(warps*stages, most tiles any CTA owns)
   const float* x;
   const float* gamma;
   float eps;
@@ -75,14 +91,44 @@ __device__ __forceinline__ float transpose_reduce_f(const float (&a)[NS], int la
   return v[0];
 }
 
-__device__ __forceinline__ float u8_to_f(uint32_t v) { return (float)(v & 0xffu); }
+// The two low bytes of v as floats (I2F with a byte selector, no masking).
+__device__ __forceinline__ void u8x2_to_f(uint32_t v, float& a, float& b) {
+  asm("{\n\t.reg .b8 t0, t1, t2, t3;\n\t"
+      "mov.b32 {t0, t1, t2, t3}, %2;\n\t"
+      "cvt.rn.f32.u8 %0, t0;\n\t"
+      "cvt.rn.f32.u8 %1, t1;\n\t}"
+      : "=f"(a), "=f"(b)
+      : "r"(v));
+}
+
+// Lane-constant selectors for the 6-bit scale / min pair of chunk c (sub-blocks 2c, 2c+1)
+// out of the 12 packed bytes w0..w2 (Hesper/Quantization/Q4_K_M.lean:120-144):
+//   c < 2 : sc = (w0 >> sh) & 0x3F3F                         m = (w1 >> sh) & 0x3F3F
+//   c >= 2: sc = ((w2 >> sh) & 0x0F0F) | ((w0 >> sh+2) & 0x3030)
+//           m  = ((w2 >> sh+4) & 0x0F0F) | ((w1 >> sh+2) & 0x3030)      with sh = 16*(c&1)
+// Written with masks and shift counts that depend only on c, so every lane runs the same
+// instructions whatever its chunk.
+struct Q4KSel {
+  uint32_t sh, mask_lo, mask_hi, m_extra;  // m_extra: extra right shift of w2 for the mins
+  bool upper;                              // c >= 2
+};
+__device__ __forceinline__ Q4KSel q4k_sel(int c) {
+  Q4KSel s;
+  s.upper = c >= 2;
+  s.sh = (uint32_t)(c & 1) * 16u;
+  s.mask_lo = s.upper ? 0x0F0Fu : 0x3F3Fu;
+  s.mask_hi = s.upper ? 0x3030u : 0u;
+  s.m_extra = s.upper ? 4u : 0u;
+  return s;
+}
 
 // One 64-weight Q4_K chunk (sub-blocks 2c and 2c+1 of a super-block) against its
 // 64 activations.  blk = super-block base in shared memory; xh/xl = the 16+16
 // words of the hi/lo activation planes of the chunk; tab = {dx_lo, dx_hi/16,
 // sumx_lo, sumx_hi} of the two sub-blocks.
-__device__ __forceinline__ float q4k_chunk(const uint8_t* blk, int c, const uint32_t (&xh)[16],
-                                           const uint32_t (&xl)[16], float4 tab) {
+__device__ __forceinline__ float q4k_chunk(const uint8_t* blk, int c, const Q4KSel& sel,
+                                           const uint32_t (&xh)[16], const uint32_t (&xl)[16],
+                                           float4 tab) {
   const uint4 hdr = *reinterpret_cast<const uint4*>(blk);  // d|dmin, scales[0..11]
   const uint4 qa = *reinterpret_cast<const uint4*>(blk + 16 + 32 * c);
   const uint4 qb = *reinterpret_cast<const uint4*>(blk + 32 + 32 * c);
@@ -98,18 +144,18 @@ __device__ __forceinline__ float q4k_chunk(const uint8_t* blk, int c, const uint
   }
   const float fL = (float)(lh * 256 + ll);
   const float fH = (float)(hh * 256 + hl);  // carries the factor 16 of the high nibble
-  // four packed 6-bit scales / mins at a time: j = 0..3 and j = 4..7
-  const uint32_t scA = hdr.y & 0x3F3F3F3Fu;
-  const uint32_t scB = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
-  const uint32_t mA = hdr.z & 0x3F3F3F3Fu;
-  const uint32_t mB = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
-  const uint32_t sh = (c & 1) * 16;
-  const uint32_t sc2 = (c < 2 ? scA : scB) >> sh;
-  const uint32_t m2 = (c < 2 ? mA : mB) >> sh;
+  const uint32_t wa = sel.upper ? hdr.w : hdr.y;   // low bits of the scales
+  const uint32_t wm = sel.upper ? hdr.w : hdr.z;   // low bits of the mins
+  const uint32_t sc2 = ((wa >> sel.sh) & sel.mask_lo) | ((hdr.y >> (sel.sh + 2)) & sel.mask_hi);
+  const uint32_t m2 =
+      ((wm >> (sel.sh + sel.m_extra)) & sel.mask_lo) | ((hdr.z >> (sel.sh + 2)) & sel.mask_hi);
+  float scl, sch, ml, mh;
+  u8x2_to_f(sc2, scl, sch);
+  u8x2_to_f(m2, ml, mh);
   const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));
-  const float main = u8_to_f(sc2) * tab.x * fL + u8_to_f(sc2 >> 8) * tab.y * fH;
-  const float mins = u8_to_f(m2) * tab.z + u8_to_f(m2 >> 8) * tab.w;
-  return dd.x * main - dd.y * mins;
+  const float main = fmaf(sch * tab.y, fH, (scl * tab.x) * fL);
+  const float mins = fmaf(mh, tab.w, ml * tab.z);
+  return fmaf(dd.x, main, -(dd.y * mins));
 }
 
 // Two consecutive Q8_0 blocks (68 bytes, 4-byte aligned) against 64 activations.
@@ -145,7 +191,7 @@ __device__ __forceinline__ float gelu_tanh_f(float x) {
 // FMT: 12 = Q4_K, 8 = Q8_0 (GGUF type ids).  RT rows per tile (a gate/up tile
 // holds RT gate rows and RT up rows).  GU: fused gelu_tanh(gate)*up.
 template <int FMT, int RT, bool GU>
-__global__ void __launch_bounds__(kKQThreads, 2) kquant_kernel(const __grid_constant__ KQParams p) {
+__global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_constant__ KQParams p) {
   constexpr int kRows = GU ? 2 * RT : RT;      // rows held by one stage
   constexpr int kNS = kRows <= 2 ? 2 : (kRows <= 4 ? 4 : 8);  // reduction width
   extern __shared__ __align__(128) uint8_t smem[];
@@ -157,8 +203,11 @@ __global__ void __launch_bounds__(kKQThreads, 2) kquant_kernel(const __grid_cons
   const int stage_bytes = kRows * rowbytes;
 
   // shared memory carve-up (kq_smem_bytes mirrors it)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // [warps][S]
-  size_t off = ((size_t)kKQWarps * S * sizeof(uint64_t) + 127) & ~size_t(127);
+  // Stage slots are interleaved over the warps: the warp's k-th tile sits in slot
+  // warp + (k % S) * warps.  When every tile of the CTA is resident at once this makes the
+  // slot simply the tile's index in the CTA, so no slot is wasted on a warp with fewer tiles.
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // [nslots]
+  size_t off = ((size_t)p.nslots * sizeof(uint64_t) + 127) & ~size_t(127);
   double* red_f64 = reinterpret_cast<double*>(smem + off);  // [16]
   off += 16 * sizeof(double);
   uint32_t* xhi = reinterpret_cast<uint32_t*>(smem + off);  // [K] int8 hi plane
@@ -168,15 +217,17 @@ __global__ void __launch_bounds__(kKQThreads, 2) kquant_kernel(const __grid_cons
   float4* xtab = reinterpret_cast<float4*>(smem + off);  // [K/64] chunk scales and sums
   off += (size_t)nchunk * sizeof(float4);
   off = (off + 127) & ~size_t(127);
-  uint8_t* wstage = smem + off + (size_t)warp * S * stage_bytes;
-  uint64_t* mybar = bars + warp * S;
+  uint8_t* wstage = smem + off;
+  auto slot_of = [&](int k) { return warp + (k % S) * kKQWarps; };
 
   const int G = gridDim.x;
   const int t0 = (int)(((long long)blockIdx.x * p.ntiles) / G);
   const int t1 = (int)(((long long)(blockIdx.x + 1) * p.ntiles) / G);
 
+  HB_STAMP(0);
   if (lane == 0) {
-    for (int s = 0; s < S; ++s) mbar_init(&mybar[s], 1);
+    for (int s = 0; s < S; ++s)
+      if (slot_of(s) < p.nslots) mbar_init(&bars[slot_of(s)], 1);
     fence_mbar_init();
   }
   if (tid < 16) red_f64[tid] = 0.0;
@@ -199,17 +250,17 @@ __global__ void __launch_bounds__(kKQThreads, 2) kquant_kernel(const __grid_cons
     int seg, row, nr;
     tile_at(tprod, seg, row, nr);
     if (lane == 0) {
-      const int stage = issued % S;
-      uint8_t* dst = wstage + (size_t)stage * stage_bytes;
+      const int slot = slot_of(issued);
+      uint8_t* dst = wstage + (size_t)slot * stage_bytes;
       const uint32_t bytes = (uint32_t)nr * rowbytes;
       if (!GU) {
-        mbar_arrive_expect_tx(&mybar[stage], bytes);
-        bulk_g2s_stream(dst, p.seg[seg].w + (size_t)row * rowbytes, bytes, &mybar[stage], pol);
+        mbar_arrive_expect_tx(&bars[slot], bytes);
+        bulk_g2s_stream(dst, p.seg[seg].w + (size_t)row * rowbytes, bytes, &bars[slot], pol);
       } else {
-        mbar_arrive_expect_tx(&mybar[stage], 2 * bytes);
-        bulk_g2s_stream(dst, p.seg[0].w + (size_t)row * rowbytes, bytes, &mybar[stage], pol);
+        mbar_arrive_expect_tx(&bars[slot], 2 * bytes);
+        bulk_g2s_stream(dst, p.seg[0].w + (size_t)row * rowbytes, bytes, &bars[slot], pol);
         bulk_g2s_stream(dst + (size_t)RT * rowbytes, p.seg[1].w + (size_t)row * rowbytes, bytes,
-                        &mybar[stage], pol);
+                        &bars[slot], pol);
       }
     }
     tprod += kKQWarps;
@@ -221,13 +272,17 @@ __global__ void __launch_bounds__(kKQThreads, 2) kquant_kernel(const __grid_cons
   const int M = p.M;
   const float* const xbase = p.x;
   const float* const gamma = p.gamma;
+  HB_STAMP(1);
   pdl_trigger();
   pdl_wait();
+  HB_STAMP(2);
 
   const int nvec = K >> 2;
+  const Q4KSel sel_main = q4k_sel(lane & 3);  // in whole passes a lane's chunk index is lane & 3
   const int npass = nchunk >> 5;   // whole passes: lane l owns chunk pass*32 + l
   const int rem = nchunk & 31;     // chunks left per row; rem*kRows tasks per tile
   const int nrem_iter = (rem * kRows + 31) >> 5;
+  const uint32_t rem_magic = rem ? 0xFFFFFFFFu / (uint32_t)rem + 1u : 0u;  // idx / rem by multiply
 
   for (int m = 0; m < M; ++m) {
     // ---- activation prologue: (RMSNorm), per-32 block 16-bit quantisation ------
@@ -296,6 +351,7 @@ __global__ void __launch_bounds__(kKQThreads, 2) kquant_kernel(const __grid_cons
       }
     }
     __syncthreads();
+    HB_STAMP(3);
 
     if (m > 0) {  // later tokens stream the weights again (from L2)
       tprod = t0 + warp;
@@ -304,12 +360,13 @@ __global__ void __launch_bounds__(kKQThreads, 2) kquant_kernel(const __grid_cons
 
     // ---- streaming main loop (per warp) ---------------------------------------
     for (int t = t0 + warp; t < t1; t += kKQWarps) {
-      const int stage = consumed % S;
+      const int sslot = slot_of(consumed);
       const uint32_t parity = (uint32_t)((consumed / S) & 1);
       int seg, row, nr;
       tile_at(t, seg, row, nr);
-      mbar_wait(&mybar[stage], parity, p.status);
-      const uint8_t* ws = wstage + (size_t)stage * stage_bytes;
+      mbar_wait(&bars[sslot], parity, p.status);
+      HB_STAMP(4 + 2 * (consumed & 1));
+      const uint8_t* ws = wstage + (size_t)sslot * stage_bytes;
 
       float acc[kNS];
 #pragma unroll
@@ -333,7 +390,7 @@ __global__ void __launch_bounds__(kKQThreads, 2) kquant_kernel(const __grid_cons
 #pragma unroll
         for (int r = 0; r < kRows; ++r) {
           const uint8_t* base = ws + r * rowbytes + boff;
-          acc[r] += FMT == 12 ? q4k_chunk(base, bc & 3, xh, xl, tab) : q80_pair(base, xh, xl, tab);
+          acc[r] += FMT == 12 ? q4k_chunk(base, bc & 3, sel_main, xh, xl, tab) : q80_pair(base, xh, xl, tab);
         }
       }
       // leftover chunks: task index -> (row of the tile, chunk), no register reuse
@@ -341,7 +398,7 @@ __global__ void __launch_bounds__(kKQThreads, 2) kquant_kernel(const __grid_cons
       for (int u = 0; u < nrem_iter; ++u) {
         const int idx = u * 32 + lane;
         const bool ok = idx < rem * kRows;
-        const int r = ok ? idx / rem : 0;
+        const int r = ok ? (int)__umulhi((uint32_t)idx, rem_magic) : 0;
         const int bc = npass * 32 + (ok ? idx - r * rem : 0);
         uint32_t xh[16], xl[16];
 #pragma unroll
@@ -355,12 +412,13 @@ __global__ void __launch_bounds__(kKQThreads, 2) kquant_kernel(const __grid_cons
         const float4 tab = xtab[bc];
         const int boff = FMT == 12 ? (bc >> 2) * 144 : bc * 68;
         const uint8_t* base = ws + r * rowbytes + boff;
-        float v = FMT == 12 ? q4k_chunk(base, bc & 3, xh, xl, tab) : q80_pair(base, xh, xl, tab);
+        float v = FMT == 12 ? q4k_chunk(base, bc & 3, q4k_sel(bc & 3), xh, xl, tab) : q80_pair(base, xh, xl, tab);
         v = ok ? v : 0.f;
 #pragma unroll
         for (int rr = 0; rr < kRows; ++rr) acc[rr] += (r == rr) ? v : 0.f;
       }
       __syncwarp();
+      HB_STAMP(5 + 2 * (consumed & 1));
       if (tprod < t1) produce();
 
       // ---- reduce and store -----------------------------------------------------
@@ -388,20 +446,21 @@ __global__ void __launch_bounds__(kKQThreads, 2) kquant_kernel(const __grid_cons
       ++consumed;
     }
   }
+  HB_STAMP(8);
 }
 
 // ---- host side --------------------------------------------------------------------
 
-static size_t kq_smem_bytes(int stages, int rows, int K, int rowbytes) {
+static size_t kq_smem_bytes(int nslots, int rows, int K, int rowbytes) {
   auto up128 = [](size_t v) { return (v + 127) & ~size_t(127); };
-  size_t off = up128((size_t)kKQWarps * stages * 8);
+  size_t off = up128((size_t)nslots * 8);
   off += 16 * 8 + 2 * (size_t)K + (size_t)(K / 64) * 16;
   off = up128(off);
-  return off + (size_t)kKQWarps * stages * rows * (size_t)rowbytes;
+  return off + (size_t)nslots * rows * (size_t)rowbytes;
 }
 
 struct KQPlan {
-  int rt, stages;
+  int rt, stages, nslots;
   size_t smem;
 };
 
@@ -412,8 +471,11 @@ struct KQPlan {
 //  (b) a ring of >= 2 stages inside half of the shared memory, most bytes in flight;
 //  (c) the same inside the whole shared memory;  (d) whatever fits.
 static bool kq_plan(const hb200_ctx* ctx, long rows, int K, int rowbytes, bool gu, KQPlan* out) {
-  const size_t half = (size_t)ctx->smem_optin / 2 - 1024, full = (size_t)ctx->smem_optin;
-  KQPlan best = {0, 0, 0};
+  // One CTA per SM (the kernel wants ~166 registers per thread; capping it at the 80 that
+  // would let two launches share an SM made it re-derive addresses and constants inside
+  // the chunk loop for no net gain), so "half" below only keeps headroom for the L1.
+  const size_t half = (size_t)ctx->smem_optin * 3 / 4, full = (size_t)ctx->smem_optin;
+  KQPlan best = {0, 0, 0, 0};
   long best_bytes = -1;
   for (int pass = 0; pass < 4 && best.rt == 0; ++pass) {
     for (int rt = 4; rt >= 1; --rt) {
@@ -423,16 +485,17 @@ static bool kq_plan(const hb200_ctx* ctx, long rows, int K, int rowbytes, bool g
       const int tpw = (tpc + kKQWarps - 1) / kKQWarps;
       const int srows = gu ? 2 * rt : rt;
       for (int st = (tpw < 4 ? tpw : 4); st >= 1; --st) {
-        const size_t sm = kq_smem_bytes(st, srows, K, rowbytes);
+        const int nslots = kKQWarps * st < tpc ? kKQWarps * st : tpc;
+        const size_t sm = kq_smem_bytes(nslots, srows, K, rowbytes);
         bool ok = false;
         if (pass == 0) ok = st == tpw && sm <= half;
         if (pass == 1) ok = st >= 2 && sm <= half;
         if (pass == 2) ok = (st >= 2 || st == tpw) && sm <= full;
         if (pass == 3) ok = sm <= full;
-        const long inflight = (long)st * srows * rowbytes;
+        const long inflight = (long)nslots * srows * rowbytes;
         if (ok && inflight > best_bytes) {
           best_bytes = inflight;
-          best = {rt, st, sm};
+          best = {rt, st, nslots, sm};
         }
       }
       if (pass == 0 && best.rt) break;  // tallest fully resident tile
@@ -517,6 +580,7 @@ extern "C" int hb200_kquant_forward_multi(hb200_ctx* ctx, int fmt, const hb200_k
   p.K = K;
   p.M = M;
   p.stages = plan.stages;
+  p.nslots = plan.nslots;
   p.x = d_x;
   p.gamma = d_rms_gamma;
   p.eps = rms_eps;
@@ -558,6 +622,7 @@ extern "C" int hb200_kquant_gateup_gelu(hb200_ctx* ctx, int fmt, const void* d_b
   p.K = K;
   p.M = M;
   p.stages = plan.stages;
+  p.nslots = plan.nslots;
   p.x = d_x;
   p.gamma = d_rms_gamma;
   p.eps = rms_eps;
