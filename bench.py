@@ -272,6 +272,11 @@ def run_ours(args):
     extra = {}
     if rank == 0 and not args.no_extra:
         extra = run_extra(torch, ctx, st, hesper_b200, args)
+    if not args.no_extra:
+        # config 4 is tensor-parallel over all ranks of the job: every rank takes part
+        tpd = run_tp_decode(torch, dist, ctx, hesper_b200, rank, world)
+        if rank == 0:
+            extra["cfg4_gemma_tp_decode"] = tpd
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_baseline()
@@ -360,6 +365,78 @@ def run_extra(torch, ctx, st, hb, args):
         att[f"B{B}_L{L}"] = {"us": sec * 1e6, "GBs": B * (2048 * L + 12288) / sec / 1e9}
         del q, k, v
     out["cfg2_attention"] = att
+    out["cfg3_bitnet2b_decode"] = run_bitnet_decode(torch, ctx, hb)
+    return out
+
+
+def run_tp_decode(torch, dist, ctx, hb, rank, world):
+    """BASELINE config 4: Gemma-4-E4B-shaped Q4_K model, tensor-parallel over `world` GPUs,
+    random-init shards generated on each GPU, decode at context ~8000 of 8192."""
+    from hesper_b200 import tp
+    S = tp.GemmaShape()
+    out = {"tp": world}
+    comm = None
+    try:
+        if world > 1:
+            comm = tp.TensorParallel.from_torch_distributed(ctx)
+        plan = tp.plan(S, rank, world)
+        shard = tp.random_gemma_shard_device(S, plan, seed=7)
+        # algorithmic bytes per token per the whole job: Q4_K layers + LM head + bf16 embedding
+        # row + f16 KV (35 sliding-window layers x 512 positions, 7 global layers x ctx)
+        wbytes = 42 * 51_609_600 + 377_487_360
+        for B, steps in ((1, 64), (32, 16)):
+            model = tp.GemmaModel(ctx, S, shard, plan, comm, batch=B, max_new_tokens=steps)
+            model.set_position(8000)
+            model.generate(None, 4, use_graph=True)       # warm-up (also captures once)
+            model.set_position(8000)
+            if world > 1:
+                dist.barrier()
+            _, _, ms = model.generate(None, steps, use_graph=True)
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+            kv = B * (35 * 512 + 7 * 8000) * 2048
+            us = ms / steps * 1e3
+            out[f"B{B}"] = {"tok_s": B * steps / ms * 1e3, "us_per_step": us,
+                            "roofline_us_at_measured_peak": (wbytes + kv) / world / measured_peak()[0] / 1e3,
+                            "allreduces_per_step": 84 if world > 1 else 0}
+            model.close()
+            del model
+    except Exception as e:  # keep the headline line alive if a side measurement fails
+        out["error"] = repr(e)[:300]
+    finally:
+        if comm is not None:
+            comm.close()
+    return out
+
+
+def run_bitnet_decode(torch, ctx, hb):
+    """BASELINE config 3: BitNet-b1.58-2B-shaped model, random-init, 2048-token random prompt
+    then 128 greedy tokens at batch 1 (graph replay); batch 64 with a short prompt."""
+    from hesper_b200.models import BitNetShape, BitNetModel, random_bitnet_weights_device
+    shape = BitNetShape.bitnet_2b(max_seq=2304)
+    w = random_bitnet_weights_device(shape)
+    out = {}
+    peak = measured_peak()[0]
+    for B, P, n_new in ((1, 2048, 128), (64, 16, 32)):
+        try:
+            model = BitNetModel(ctx, shape, w, batch=B, max_new_tokens=n_new)
+            prompt = np.random.default_rng(0).integers(0, shape.vocab, (B, P)).astype(np.int32)
+            _, ms_p, ms_d = model.generate(prompt, n_new, use_graph=True)
+            steps = n_new - 1
+            us = ms_d / steps * 1e3
+            # bytes per step: ternary layers + bf16 LM head + f16 KV at the mean decode position
+            kv = B * 30 * 2 * 5 * 128 * 2 * (P + n_new // 2)
+            byts = 521_011_200 + 656_670_720 + kv
+            out[f"B{B}"] = {"tok_s": B * steps / ms_d * 1e3, "us_per_step": us,
+                            "prompt_len": P, "new_tokens": n_new, "prefill_ms": ms_p,
+                            "roofline_us_at_measured_peak": byts / peak / 1e3,
+                            "frac_of_roofline": byts / peak / 1e3 / us}
+            model.close()
+            del model
+        except Exception as e:
+            out[f"B{B}"] = {"error": repr(e)[:300]}
     return out
 
 

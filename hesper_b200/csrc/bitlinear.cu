@@ -546,6 +546,10 @@ extern "C" int hb200_bitlinear_forward_multi(hb200_ctx* ctx, const hb200_bitline
                "bitlinear: segment %d weights must be 16-byte aligned", s);
     rows += segs[s].N;
   }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // 16 or more tokens: a real contraction -> tensor cores (weights still streamed once)
+  if (M >= 16 && K <= 12288 && !ctx->no_mma)
+    return hb_bitlinear_mma_run(ctx, segs, nseg, K, d_x, M, d_rms_gamma, rms_eps, d_act_scale, st);
   const int rt = bl_pick_rt(ctx, rows);
   BLParams p = {};
   int t = 0;
@@ -564,7 +568,6 @@ extern "C" int hb200_bitlinear_forward_multi(hb200_ctx* ctx, const hb200_bitline
   p.eps = rms_eps;
   p.act_scale = d_act_scale;
   p.status = ctx->d_status;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   return rt == 4 ? bl_dispatch_wpl<4, false>(ctx, p, st) : bl_dispatch_wpl<2, false>(ctx, p, st);
 }
 
@@ -591,6 +594,18 @@ extern "C" int hb200_bitlinear_gateup_relu2(hb200_ctx* ctx, const void* d_packed
   HB_REQUIRE(((reinterpret_cast<uintptr_t>(d_packed_gate) |
                reinterpret_cast<uintptr_t>(d_packed_up)) & 15) == 0,
              "bitlinear gate/up: weights must be 16-byte aligned");
+  if (M >= 16 && K <= 12288 && !ctx->no_mma &&
+      (size_t)2 * M * N * sizeof(float) + ((size_t)2 << 20) <= ctx->scratch_bytes) {
+    // batched: both products on the tensor cores into scratch, then the GLU epilogue
+    float* g = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->d_scratch) + ((size_t)2 << 20));
+    float* u = g + (size_t)M * N;
+    hb200_bitlinear_seg segs[2] = {{d_packed_gate, d_scale_gate, nullptr, g, nullptr, N},
+                                   {d_packed_up, d_scale_up, nullptr, u, nullptr, N}};
+    rc = hb_bitlinear_mma_run(ctx, segs, 2, K, d_x, M, d_rms_gamma, rms_eps, nullptr,
+                              static_cast<cudaStream_t>(stream));
+    if (rc) return rc;
+    return hb200_relu2_mul(ctx, g, u, (long)M * N, d_y, stream);
+  }
   // a gate/up tile streams 2*RT rows, so the row count that matters doubles
   const int rt = bl_pick_rt(ctx, 2L * N) == 4 ? 4 : 2;
   BLParams p = {};

@@ -186,12 +186,20 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 
 }  // namespace hb
 
+// batched (16..64 token) ternary path on the tensor cores, bitlinear_mma.cu
+int hb_bitlinear_mma_run(struct hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int nseg, int K,
+                         const float* d_x, int M, const float* d_rms_gamma, float rms_eps,
+                         float* d_act_scale, cudaStream_t st);
+
 struct hb200_ctx {
   int device;
   int sm_count;
   int smem_optin;      // max dynamic shared memory per block
   uint32_t* d_status;  // 64 words
   int* d_tickets;      // kCtxTickets zero-initialised arrival counters
+  void* d_scratch;     // batched paths: quantised activations, gate/up temporaries
+  size_t scratch_bytes;
   bool pdl;            // use programmatic dependent launch
   int attn_mode;       // HB200_ATTN_FAST / PRECISE / EXACT
+  bool no_mma;         // HB200_NO_MMA=1: keep batched ternary products on the dp4a kernel
 };

@@ -1,6 +1,7 @@
 // context.cu -- context object, error strings and status block of the C ABI.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -47,11 +48,14 @@ extern "C" int hb200_ctx_create(int device, hb200_ctx** out) {
   }
   hb200_ctx* c = new hb200_ctx();
   c->d_tickets = nullptr;
+  c->d_scratch = nullptr;
   c->device = device;
   c->sm_count = prop.multiProcessorCount;
   c->smem_optin = (int)prop.sharedMemPerBlockOptin;
   c->pdl = true;
   c->attn_mode = HB200_ATTN_FAST;
+  c->no_mma = false;
+  if (const char* e2 = getenv("HB200_NO_MMA")) c->no_mma = e2[0] == '1';
   const char* env = getenv("HB200_NO_PDL");
   if (env && env[0] == '1') c->pdl = false;
   cudaError_t e = cudaMalloc(&c->d_status, 256);
@@ -62,9 +66,12 @@ extern "C" int hb200_ctx_create(int device, hb200_ctx** out) {
   e = cudaMemset(c->d_status, 0, 256);
   if (e == cudaSuccess) e = cudaMalloc(&c->d_tickets, sizeof(int) * kCtxTickets);
   if (e == cudaSuccess) e = cudaMemset(c->d_tickets, 0, sizeof(int) * kCtxTickets);
+  c->scratch_bytes = (size_t)8 << 20;
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_scratch, c->scratch_bytes);
   if (e != cudaSuccess) {
     cudaFree(c->d_status);
     cudaFree(c->d_tickets);
+    cudaFree(c->d_scratch);
     delete c;
     return cuda_fail(e, "context buffers");
   }
@@ -76,6 +83,7 @@ extern "C" int hb200_ctx_destroy(hb200_ctx* ctx) {
   if (!ctx) return HB200_OK;
   cudaFree(ctx->d_status);
   cudaFree(ctx->d_tickets);
+  cudaFree(ctx->d_scratch);
   delete ctx;
   return HB200_OK;
 }

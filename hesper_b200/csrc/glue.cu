@@ -164,7 +164,7 @@ __global__ void argmax_kernel(const float* logits, long V, int32_t* out) {
 
 constexpr int kLMThreads = 256;
 constexpr int kLMWarps = kLMThreads / 32;
-constexpr int kLMRows = 4;  // rows per tile
+constexpr int kLMRows = 2;  // rows per tile
 
 struct LMParams {
   const uint16_t* table;  // [V][K] bf16 (dtype 0) or f16 (dtype 1)

@@ -81,7 +81,8 @@ def test_residual_and_rmsnorm_prologue(ctx, oracle, M):
     assert np.array_equal(y.cpu().numpy(), y_ref)
 
 
-@pytest.mark.parametrize("K,N,M", [(2560, 6912, 1), (256, 5, 1), (2560, 100, 3), (1024, 64, 8)])
+@pytest.mark.parametrize("K,N,M", [(2560, 6912, 1), (256, 5, 1), (2560, 100, 3), (1024, 64, 8),
+                                   (2560, 300, 32), (2560, 6912, 64), (6912, 130, 17)])
 def test_gate_up_relu2(ctx, oracle, K, N, M):
     rng = np.random.default_rng(K + N + M)
     pg = formats.i2s_pack(formats.random_ternary(rng, N, K))
@@ -113,6 +114,25 @@ def test_fused_qkv_multi(ctx, oracle):
         y_ref, acc_ref, _ = oracle.bitlinear_forward(p, s, K, n, x, gamma=gamma)
         assert np.array_equal(a.cpu().numpy(), acc_ref)
         assert np.array_equal(y.cpu().numpy(), y_ref)
+
+
+@pytest.mark.parametrize("K,N,M", [(2560, 6912, 64), (6912, 2560, 64), (2560, 2560, 33),
+                                   (128, 1, 16), (1152, 129, 20), (8192, 257, 48)])
+def test_batched_tensor_core_path_bit_exact(ctx, oracle, K, N, M):
+    """16 or more tokens run on tcgen05 (kind::i8, accumulators in tensor memory): the int32
+    results must still be bit-exact, including ragged row tiles and partial K chunks."""
+    rng = np.random.default_rng(K + N + M)
+    packed = formats.i2s_pack(formats.random_ternary(rng, N, K))
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    gamma = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    res = rng.standard_normal((M, N)).astype(np.float32)
+    layer = BitLinear.create_from_bytes(ctx, packed, 0.043, K, N)
+    y_ref, acc_ref, d_ref = oracle.bitlinear_forward(packed, 0.043, K, N, x, gamma=gamma, residual=res)
+    y, acc, d = layer.forward_fused_rmsnorm_residual(_dev(x), _dev(gamma), _dev(res), return_acc=True)
+    ctx.check()
+    assert np.array_equal(d.cpu().numpy(), d_ref)
+    assert np.array_equal(acc.cpu().numpy(), acc_ref)
+    assert np.array_equal(y.cpu().numpy(), y_ref)
 
 
 def test_zero_input_and_determinism(ctx, oracle):
