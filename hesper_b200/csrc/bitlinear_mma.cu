@@ -11,19 +11,26 @@
 //                      int8 activations are written straight in the shared-memory operand
 //                      layout (K-major, 8x16-byte core matrices), one 8 KB block per
 //                      128-wide K group, so the GEMM kernel fetches a B tile with ONE bulk copy
-//   bitlinear_mma_kernel  one CTA per 128 weight rows:
-//     * packed rows arrive by per-row TMA bulk copies in chunks of 8 groups (1024 weights)
-//       on a 3-deep ring;
-//     * warps 0-7 expand one 128-wide group per step from 2-bit codes to unsigned bytes
-//       (0,1,2) directly into the A-operand layout (16 ALU pairs and 4 x 16-byte stores per
-//       thread and step) -- the expansion is the only per-weight work left on the SM; they
-//       hand stages over through mbarriers only, there is no CTA-wide barrier in the loop;
-//     * warp 8 drives the copies and issues 4 tcgen05.mma (M=128, N=64 tokens, K=32 each) per
-//       step from one thread, operands described by shared-memory matrix descriptors (no
-//       swizzle), D[128x64] int32 in 64 TMEM columns; tcgen05.commit releases the stage;
-//     * epilogue: 4 warps read their 32 TMEM lanes (tcgen05.ld 32x32b), subtract sum(q) per
-//       token (value = code - 1), scale and store.
+//   bitlinear_mma_kernel  one CTA per 128 weight rows, 11 warps with fixed roles:
+//     * warp 9 issues every copy: the packed weights as boxes of 128 rows x 128 bytes
+//       (4 groups) through a 2-D tensor map with the 128-byte swizzle, ONE instruction per
+//       16 KB on a 4-deep ring (per-row 1-D bulk copies cost ~35 ns each at the TMA unit and
+//       throttled the stream), and each step's activations with one 16 KB bulk copy;
+//     * warps 0-7 expand two 128-wide groups per step from 2-bit codes to unsigned bytes
+//       (0,1,2) and store them with tcgen05.st straight into TENSOR MEMORY as the A operand
+//       (lane = weight row, 4 K-bytes per column): the expanded weights never touch shared
+//       memory, whose bandwidth bounded the earlier shared-memory-A version of this kernel;
+//     * warps 8 and 10 each issue the MMAs of every other step from one thread into their own
+//       accumulator (tcgen05.mma kind::i8, A from tensor memory, B by a shared-memory
+//       descriptor, M=128, N=64 tokens, K=32 per instruction; 2 x 64 columns of int32): one
+//       thread alone spends ~45 ns per MMA, two keep the tensor pipe busy.  One barrier per
+//       step gathers the 8 expander arrivals and the activation bytes; one tcgen05.commit
+//       per step releases the stage (6 stages = 384 columns of A);
+//     * epilogue: 8 warps read 32 lanes x 32 columns of both accumulators (tcgen05.ld
+//       32x32b), add them, subtract sum(q) per token (value = code - 1), scale and store.
 // Every mbarrier wait is bounded; on expiry the kernel still releases its tensor memory.
+#include <cuda.h>  // CUtensorMap and its enums only; the encoder comes from the runtime
+
 #include "common.cuh"
 
 namespace hb {
@@ -31,13 +38,16 @@ namespace hb {
 constexpr int kMmaThreads = 256;
 constexpr int kMmaRows = 128;    // weight rows per CTA = MMA M
 constexpr int kMmaTokens = 64;   // MMA N
-constexpr int kChunkGroups = 8;  // 128-weight groups per packed chunk
-constexpr int kPkStages = 3, kExStages = 4;
-constexpr int kPkRowBytes = kChunkGroups * 32;          // 256 packed bytes per row and chunk
-constexpr int kPkBytes = kMmaRows * kPkRowBytes;        // 32 KB
-constexpr int kABytes = kMmaRows * 128;                 // 16 KB expanded A stage
-constexpr int kBBytes = kMmaTokens * 128;               // 8 KB B stage
-constexpr int kMmaSmem = 1024 + kPkStages * kPkBytes + kExStages * (kABytes + kBBytes);
+constexpr int kChunkGroups = 4;  // 128-weight groups per packed box: 128 bytes of every row
+constexpr int kPkStages = 4;     // packed ring
+constexpr int kPkBytes = kMmaRows * kChunkGroups * 32;  // 16 KB box
+constexpr int kStepGroups = 2;   // groups per pipeline step: one barrier round trip per 8 MMAs
+constexpr int kStages = 6;       // operand stages (A in tensor memory, B in shared memory)
+constexpr int kBBytes = kMmaTokens * 128;               // 8 KB activation tile of one group
+constexpr int kAccCols = 64;     // TMEM columns of the 128 x 64 int32 accumulator
+constexpr int kAGroupCols = 32;  // TMEM columns of one expanded group: 128 K-bytes per row
+static_assert(kAccCols + kStages * kStepGroups * kAGroupCols <= 512, "tensor memory columns");
+constexpr int kMmaSmem = 1024 + kPkStages * kPkBytes + kStages * kStepGroups * kBBytes;
 
 struct MmaSeg {
   const uint8_t* w;
@@ -50,6 +60,7 @@ struct MmaSeg {
 };
 
 struct MmaParams {
+  CUtensorMap tmap[4];  // per segment: packed weights as [N rows][K/4 bytes], 128 x 128 boxes
   MmaSeg seg[4];
   int nseg, K, M;
   const uint8_t* xq;   // [K/128][64 tokens x 128 bytes, core-matrix layout]
@@ -160,6 +171,39 @@ __global__ void __launch_bounds__(256) quant_act_kernel(const __grid_constant__ 
   }
 }
 
+#ifdef HB_PROFILE
+__device__ int g_mma_dbg = 0;  // bit0: skip MMAs, bit1: skip expansion stores, bit2: skip B copies
+extern "C" __attribute__((visibility("default"))) void hb200_prof_set_mma_dbg(int v) {
+  cudaMemcpyToSymbol(g_mma_dbg, &v, sizeof(int));
+}
+__device__ __forceinline__ unsigned long long gtimer2() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define MMA_STAMP(i, cond)                                                    \
+  do {                                                                        \
+    if (blockIdx.x == 0 && (cond))                                            \
+      reinterpret_cast<unsigned long long*>(p.status)[1 + (i)] = gtimer2();   \
+  } while (0)
+#define MMA_DBG(bit) ((g_mma_dbg >> (bit)) & 1)
+// fine-grained stamps go to the 512 bytes after d[] and sumq[] in the context scratch
+#define MMA_FINE(i, cond)                                                              \
+  do {                                                                                 \
+    if (blockIdx.x == 0 && (cond))                                                     \
+      reinterpret_cast<unsigned long long*>(const_cast<float*>(p.d))[64 + (i)] = gtimer2(); \
+  } while (0)
+extern "C" __attribute__((visibility("default"))) void hb200_prof_read_fine(hb200_ctx* ctx,
+                                                                            unsigned long long* out) {
+  cudaDeviceSynchronize();
+  cudaMemcpy(out, (char*)ctx->d_scratch + 512, 512, cudaMemcpyDeviceToHost);
+}
+#else
+#define MMA_FINE(i, cond) ((void)0)
+#define MMA_STAMP(i, cond) ((void)0)
+#define MMA_DBG(bit) 0
+#endif
+
 // ---- tcgen05 helpers --------------------------------------------------------------------
 
 // Shared-memory matrix descriptor, K-major, no swizzle: core matrices of 8 rows x 16 bytes,
@@ -209,51 +253,73 @@ __device__ __forceinline__ bool mma_wait(bool ok, uint64_t* bar, uint32_t parity
   return false;
 }
 
-__global__ void __launch_bounds__(kMmaThreads + 32, 1)
+// A operand from tensor memory (lane = weight row, 4 K-bytes per 32-bit column).
+__device__ __forceinline__ void umma_i8_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(kIdescI8), "r"(accumulate)
+      : "memory");
+}
+
+// One box of the packed-weight tensor map: 128 rows x 128 bytes (4 groups) -> 16 KB of shared
+// memory in the 128-byte swizzle (16-byte unit u of row r lands at unit u ^ (r & 7)).
+__device__ __forceinline__ void tma_box_2d(void* dst, const CUtensorMap* tm, int x, int y,
+                                           uint64_t* bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kMmaThreads + 96, 1)
     bitlinear_mma_kernel(const __grid_constant__ MmaParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int K = p.K, rowbytes = K >> 2, ngroups = K >> 7;
+  const int ngroups = p.K >> 7;
   const int nchunks = (ngroups + kChunkGroups - 1) / kChunkGroups;
-  constexpr int kExpWarps = kMmaThreads / 32;  // warps 0..7 expand, warp 8 drives TMA and MMA
+  const int nsteps = (ngroups + kStepGroups - 1) / kStepGroups;
+  constexpr int kExpWarps = kMmaThreads / 32;  // warps 0..7 expand, warp 8 issues MMAs, warp 9 copies
+  constexpr int kMmaWarp = kExpWarps, kCopyWarp = kExpWarps + 1;
 
-  // control block, then packed ring, then expanded stages (1 KB aligned for the descriptors)
-  uint64_t* pk_full = reinterpret_cast<uint64_t*>(smem);  // [3] packed chunk landed (tx bytes)
-  uint64_t* pk_free = pk_full + kPkStages;                 // [3] all expander warps done with it
-  uint64_t* a_full = pk_free + kPkStages;                  // [4] A stage written by all expanders
-  uint64_t* b_full = a_full + kExStages;                   // [4] B stage landed (tx bytes)
-  uint64_t* st_free = b_full + kExStages;                  // [4] MMAs that read the stage finished
-  uint64_t* done = st_free + kExStages;                    // [1]
+  // control block, then the packed ring and the activation stages (1 KB aligned)
+  uint64_t* pk_full = reinterpret_cast<uint64_t*>(smem);  // [kPkStages] box landed (tx bytes)
+  uint64_t* pk_free = pk_full + kPkStages;                 // [kPkStages] every expander warp left it
+  uint64_t* full = pk_free + kPkStages;   // [kStages] A stored by 8 warps + B landed (tx bytes)
+  uint64_t* mma_done = full + kStages;    // [kStages] the MMAs that read the stage have retired
+  uint64_t* done = mma_done + kStages;    // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
-  float* sd = reinterpret_cast<float*>(smem + 256);        // [64]
-  int* ssum = reinterpret_cast<int*>(smem + 512);          // [64]
+  float* sd = reinterpret_cast<float*>(smem + 512);        // [64]
+  int* ssum = reinterpret_cast<int*>(smem + 768);          // [64]
   uint8_t* pk = smem + 1024;
-  uint8_t* ex = pk + kPkStages * kPkBytes;
+  uint8_t* bstg = pk + kPkStages * kPkBytes;  // [kStages][kStepGroups] activation tiles
 
   // tile -> (segment, first row)
   int seg = 0;
 #pragma unroll
   for (int s = 1; s < 4; ++s)
     if (s < p.nseg && (int)blockIdx.x >= p.seg[s].tile0) seg = s;
-  const MmaSeg& sg = p.seg[seg];
-  const int row0 = ((int)blockIdx.x - sg.tile0) * kMmaRows;
-  const int nrows = min(kMmaRows, sg.N - row0);
+  const int seg_N = p.seg[seg].N;
+  const int row0 = ((int)blockIdx.x - p.seg[seg].tile0) * kMmaRows;
+  const int nrows = min(kMmaRows, seg_N - row0);
+  MMA_STAMP(0, tid == 0);
 
   if (tid == 0) {
     for (int i = 0; i < kPkStages; ++i) {
       mbar_init(&pk_full[i], 1);
       mbar_init(&pk_free[i], kExpWarps);
     }
-    for (int i = 0; i < kExStages; ++i) {
-      mbar_init(&a_full[i], kExpWarps);
-      mbar_init(&b_full[i], 1);
-      mbar_init(&st_free[i], 1);
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&full[i], kExpWarps + 1);
+      mbar_init(&mma_done[i], 1);
     }
-    mbar_init(done, 1);
+    mbar_init(done, 2);
     fence_mbar_init();
   }
-  if (warp == kExpWarps) {  // 64 TMEM columns: the 128 x 64 int32 accumulator
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 64;" ::"r"(
+  if (warp == kMmaWarp) {  // all 512 columns: 64 for the accumulator, the rest A stages
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(
         smem_u32(tmem_slot)));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
@@ -263,160 +329,261 @@ __global__ void __launch_bounds__(kMmaThreads + 32, 1)
   const uint32_t tmem = *tmem_slot;
   bool ok = true;
 
-  if (warp == kExpWarps) {
-    // ================= control warp: TMA producer and MMA issuer =========================
+  if (warp == kCopyWarp) {
+    // ================= copy warp: packed weight boxes and activation tiles ==================
     const uint64_t pol = policy_evict_first();
-    // packed chunk c: one bulk copy per row (rows past the tensor's end repeat its last row)
-    auto issue_chunk = [&](int c) {
-      const int st = c % kPkStages;
-      const int g0 = c * kChunkGroups;
-      const uint32_t bytes = (uint32_t)min(kChunkGroups, ngroups - g0) * 32u;
-      if (lane == 0) mbar_arrive_expect_tx(&pk_full[st], bytes * kMmaRows);
-      __syncwarp();
-#pragma unroll
-      for (int i = 0; i < kMmaRows / 32; ++i) {
-        const int r = lane + 32 * i;
-        const int gr = min(row0 + r, sg.N - 1);
-        bulk_g2s_stream(pk + (size_t)st * kPkBytes + (size_t)r * kPkRowBytes,
-                        sg.w + (size_t)gr * rowbytes + (size_t)g0 * 32, bytes, &pk_full[st], pol);
-      }
-    };
-    auto issue_b = [&](int g) {  // activations of group g: one 8 KB block in operand layout
-      if (lane == 0) {
-        const int st = g % kExStages;
-        mbar_arrive_expect_tx(&b_full[st], kBBytes);
-        bulk_g2s(ex + (size_t)st * (kABytes + kBBytes) + kABytes, p.xq + (size_t)g * kBBytes,
-                 kBBytes, &b_full[st]);
-      }
-    };
-    for (int c = 0; c < kPkStages && c < nchunks; ++c) issue_chunk(c);  // weights: no dependency
-    pdl_trigger();
-    pdl_wait();  // the quantised activations come from the kernel before this one
-    constexpr int kAhead = 3;  // activation tiles kept in flight
-    for (int g = 0; g < kAhead && g < ngroups; ++g) issue_b(g);
-    for (int g = 0; g < ngroups; ++g) {
-      const int c = g / kChunkGroups, gi = g % kChunkGroups;
-      const int st = g % kExStages;
-      // refill the packed ring: chunk c+2 goes where chunk c-1 was, once every expander left it
-      if (gi == 0 && c >= 1 && c + kPkStages - 1 < nchunks) {
-        ok = mma_wait(ok, &pk_free[(c - 1) % kPkStages], (uint32_t)(((c - 1) / kPkStages) & 1),
-                      p.status);
-        issue_chunk(c + kPkStages - 1);
-      }
-      ok = mma_wait(ok, &a_full[st], (uint32_t)((g / kExStages) & 1), p.status);
-      ok = mma_wait(ok, &b_full[st], (uint32_t)((g / kExStages) & 1), p.status);
-      if (lane == 0) {
-        tc_fence_after();
-        const uint32_t abase = smem_u32(ex + (size_t)st * (kABytes + kBBytes));
-        const uint32_t bbase = abase + kABytes;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)  // K = 32 bytes per instruction = 2 core matrices
-          umma_i8(tmem, umma_desc(abase + j * 256, 128, 1024),
-                  umma_desc(bbase + j * 256, 128, 1024), (g > 0 || j > 0) ? 1u : 0u);
-        umma_commit(&st_free[st]);  // arrives once these (and all earlier) MMAs read the stage
-      }
-      __syncwarp();
-      // activations kAhead groups ahead, into a stage whose previous MMAs are done
-      const int g2 = g + kAhead;
-      if (g2 < ngroups) {
-        if (g2 >= kExStages)
-          ok = mma_wait(ok, &st_free[g2 % kExStages], (uint32_t)(((g2 / kExStages) - 1) & 1),
-                        p.status);
-        issue_b(g2);
+    const CUtensorMap* tm = &p.tmap[seg];
+    int cnext = 0;
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm)) : "memory");
+      for (; cnext < kPkStages && cnext < nchunks; ++cnext) {  // weights: no dependency
+        mbar_arrive_expect_tx(&pk_full[cnext], kPkBytes);
+        tma_box_2d(pk + (size_t)cnext * kPkBytes, tm, cnext * kChunkGroups * 32, row0,
+                   &pk_full[cnext], pol);
       }
     }
+    cnext = min(kPkStages, nchunks);
+    pdl_trigger();
+    pdl_wait();  // the quantised activations come from the kernel before this one
+    MMA_STAMP(1, lane == 0);
+    for (int s = 0; s < nsteps; ++s) {
+      const int st = s % kStages;
+      if (s >= kStages)  // the MMAs that read this stage kStages steps ago must have retired
+        ok = mma_wait(ok, &mma_done[st], (uint32_t)(((s / kStages) - 1) & 1), p.status);
+      if (lane == 0) {  // activations of the step's groups: contiguous in the operand layout
+        const int g0 = s * kStepGroups;
+        const uint32_t bytes = (uint32_t)min(kStepGroups, ngroups - g0) * kBBytes;
+        mbar_arrive_expect_tx(&full[st], bytes);
+        bulk_g2s(bstg + (size_t)st * kStepGroups * kBBytes, p.xq + (size_t)g0 * kBBytes, bytes,
+                 &full[st]);
+      }
+      // refill the packed ring as soon as every expander warp has left the oldest box
+      if (cnext < nchunks && mbar_try_wait(&pk_free[cnext % kPkStages],
+                                           (uint32_t)(((cnext / kPkStages) - 1) & 1))) {
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&pk_full[cnext % kPkStages], kPkBytes);
+          tma_box_2d(pk + (size_t)(cnext % kPkStages) * kPkBytes, tm, cnext * kChunkGroups * 32,
+                     row0, &pk_full[cnext % kPkStages], pol);
+        }
+        ++cnext;
+      }
+    }
+    while (cnext < nchunks) {  // boxes still owed (their slot frees up as the expanders go)
+      ok = mma_wait(ok, &pk_free[cnext % kPkStages], (uint32_t)(((cnext / kPkStages) - 1) & 1),
+                    p.status);
+      if (!ok) break;
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&pk_full[cnext % kPkStages], kPkBytes);
+        tma_box_2d(pk + (size_t)(cnext % kPkStages) * kPkBytes, tm, cnext * kChunkGroups * 32,
+                   row0, &pk_full[cnext % kPkStages], pol);
+      }
+      ++cnext;
+    }
+  } else if (warp == kMmaWarp || warp == kMmaWarp + 2) {
+    // ================= two MMA warps: even steps -> accumulator 0, odd steps -> accumulator 1
+    const int which = warp == kMmaWarp ? 0 : 1;
+    const uint32_t tmem_d = tmem + (which ? 448u : 0u);
+    for (int s = which; s < nsteps; s += 2) {
+      const int st = s % kStages;
+      ok = mma_wait(ok, &full[st], (uint32_t)((s / kStages) & 1), p.status);
+      if (s < 10) MMA_FINE(2 * s, lane == 0);
+      if (lane == 0) {
+        tc_fence_after();
+        const uint32_t a_t = tmem + kAccCols + (uint32_t)st * (kStepGroups * kAGroupCols);
+        const uint32_t bbase = smem_u32(bstg + (size_t)st * kStepGroups * kBBytes);
+        const int ng = min(kStepGroups, ngroups - s * kStepGroups);
+#pragma unroll
+        for (int gg = 0; gg < kStepGroups; ++gg)
+          if (gg < ng) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)  // K = 32 bytes per instruction: 8 columns of A
+              umma_i8_ta(tmem_d, a_t + gg * kAGroupCols + j * 8,
+                         umma_desc(bbase + gg * kBBytes + j * 256, 128, 1024),
+                         (s > 1 || gg > 0 || j > 0) ? 1u : 0u);
+          }
+        umma_commit(&mma_done[st]);  // arrives once these (and all earlier) MMAs have retired
+      }
+      __syncwarp();
+      if (s < 10) MMA_FINE(2 * s + 1, lane == 0);
+    }
+    MMA_STAMP(3, lane == 0);
     if (lane == 0) umma_commit(done);
   } else {
     // ================= expander warps ========================================================
-    pdl_wait();
+    // warp w owns TMEM lanes (= weight rows) 32*(w&3).., and K-half h = w>>2 of every group:
+    // planes 2h and 2h+1 of the packed bytes = K bytes 64h..64h+63 = 16 columns.
+    const int q = warp & 3, h = warp >> 2;
+    const int erow = q * 32 + lane;
+    const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16) + kAccCols + 16u * h;
+    MMA_STAMP(5, tid == 0);
+    for (int s = 0; s < nsteps; ++s) {
+      const int st = s % kStages;
+      if (s >= kStages) {
+        ok = mma_wait(ok, &mma_done[st], (uint32_t)(((s / kStages) - 1) & 1), p.status);
+        tc_fence_after();
+      }
+      const int ng = min(kStepGroups, ngroups - s * kStepGroups);
+      if (s < 10) MMA_FINE(20 + 2 * s, tid == 0);
+#pragma unroll
+      for (int gg = 0; gg < kStepGroups; ++gg) {
+        if (gg >= ng) break;
+        const int g = s * kStepGroups + gg;
+        const int c = g / kChunkGroups, gi = g % kChunkGroups;
+        if (gi == 0)
+          ok = mma_wait(ok, &pk_full[c % kPkStages], (uint32_t)((c / kPkStages) & 1), p.status);
+        // the row's 32 packed bytes of this group: units 2gi and 2gi+1 of its swizzled 128 bytes
+        const uint8_t* rowp = pk + (size_t)(c % kPkStages) * kPkBytes + (size_t)erow * 128;
+        const uint4 w0 = *reinterpret_cast<const uint4*>(rowp + (((2 * gi) ^ (erow & 7)) << 4));
+        const uint4 w1 = *reinterpret_cast<const uint4*>(rowp + (((2 * gi + 1) ^ (erow & 7)) << 4));
+        const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        uint32_t o[16];
+#pragma unroll
+        for (int pp = 0; pp < 2; ++pp) {
+          // plane pl holds elements 32*pl + j in byte j: word i -> K bytes 32*pl + 4i .. +3
+          const int sh = h ? (2 - 2 * pp) : (6 - 2 * pp);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[8 * pp + i] = (w[i] >> sh) & 0x03030303u;
+        }
+        const uint32_t taddr = lane_addr + (uint32_t)st * (kStepGroups * kAGroupCols) +
+                               (uint32_t)gg * kAGroupCols;
+        asm volatile(
+            "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+            "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+            "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]),
+            "r"(o[8]), "r"(o[9]), "r"(o[10]), "r"(o[11]), "r"(o[12]), "r"(o[13]), "r"(o[14]),
+            "r"(o[15])
+            : "memory");
+        if (gi == kChunkGroups - 1 || g == ngroups - 1) {  // last read of this packed box
+          __syncwarp();
+          if (lane == 0)
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(
+                             smem_u32(&pk_free[c % kPkStages]))
+                         : "memory");
+        }
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full[st]))
+                     : "memory");
+      if (s < 10) MMA_FINE(21 + 2 * s, tid == 0);
+    }
+    MMA_STAMP(7, tid == 0);
+    pdl_wait();  // d and sum(q) come from the quantiser
     if (tid < kMmaTokens) {
       sd[tid] = p.d[tid];
       ssum[tid] = p.sumq[tid];
     }
-    const int erow = tid >> 1, ehalf = tid & 1;
-    for (int g = 0; g < ngroups; ++g) {
-      const int c = g / kChunkGroups, gi = g % kChunkGroups;
-      const int st = g % kExStages;
-      if (gi == 0)
-        ok = mma_wait(ok, &pk_full[c % kPkStages], (uint32_t)((c / kPkStages) & 1), p.status);
-      if (g >= kExStages)  // the MMAs that read this stage four groups ago must be done
-        ok = mma_wait(ok, &st_free[st], (uint32_t)(((g / kExStages) - 1) & 1), p.status);
-      // this thread's 16 packed bytes (64 weights of one row) -> 4 x 16 bytes of the A operand
-      const uint4 w = *reinterpret_cast<const uint4*>(pk + (size_t)(c % kPkStages) * kPkBytes +
-                                                      (size_t)erow * kPkRowBytes + gi * 32 +
-                                                      ehalf * 16);
-      uint8_t* a = ex + (size_t)st * (kABytes + kBBytes) + (size_t)(erow >> 3) * 1024 +
-                   (size_t)(erow & 7) * 16;
-#pragma unroll
-      for (int pl = 0; pl < 4; ++pl) {
-        const int sh = 6 - 2 * pl;
-        uint4 o;
-        o.x = (w.x >> sh) & 0x03030303u;
-        o.y = (w.y >> sh) & 0x03030303u;
-        o.z = (w.z >> sh) & 0x03030303u;
-        o.w = (w.w >> sh) & 0x03030303u;
-        // plane pl holds elements 32*pl + j: K bytes 32*pl + 16*half .. +15 = one core-matrix row
-        *reinterpret_cast<uint4*>(a + (size_t)(2 * pl + ehalf) * 128) = o;
-      }
-      fence_proxy_async();  // generic-proxy stores -> visible to the tensor core's async reads
-      __syncwarp();
-      if (lane == 0) {
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&a_full[st]))
-                     : "memory");
-        if (gi == kChunkGroups - 1 || g == ngroups - 1)
-          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(
-                           smem_u32(&pk_free[c % kPkStages]))
-                       : "memory");
-      }
-    }
   }
   ok = mma_wait(true, done, 0, p.status) && ok;
   tc_fence_after();
+  __syncthreads();  // sd / ssum visible; every warp past its loop
+  MMA_STAMP(4, tid == 0);
 
-  // ---- epilogue: TMEM lane = weight row, column = token -------------------------------
-  if (warp < 4) {
-    const int r = warp * 32 + lane;
-    const float ws = __ldg(sg.scale);
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      uint32_t v[32];
-      const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(half * 32);
+  // ---- epilogue: TMEM lane = weight row, column = token; warps w and w+4 share lanes ------
+  if (warp < kExpWarps) {
+    const int q = warp & 3, half = warp >> 2;  // lane quarter, token half
+    const int r = q * 32 + lane;
+    const float ws = __ldg(p.seg[seg].scale);
+    uint32_t v[32];
+    const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 32);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
+          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
+          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    if (nsteps > 1) {
+      uint32_t u[32];
       asm volatile(
           "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
           "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
           "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-          : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-            "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-            "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
-            "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
-            "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-          : "r"(taddr));
+          : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]),
+            "=r"(u[7]), "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]),
+            "=r"(u[13]), "=r"(u[14]), "=r"(u[15]), "=r"(u[16]), "=r"(u[17]), "=r"(u[18]),
+            "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]),
+            "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]),
+            "=r"(u[31])
+          : "r"(taddr + 448u));
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (r < nrows && ok) {
 #pragma unroll
-        for (int t = 0; t < 32; ++t) {
-          const int m = half * 32 + t;
-          if (m < p.M) {
-            const int total = (int)v[t] - ssum[m];
-            const size_t o = (size_t)m * sg.N + row0 + r;
-            if (sg.acc) sg.acc[o] = total;
-            float y = __fmul_rn(__fmul_rn((float)total, sd[m]), ws);
-            if (sg.residual) y = __fadd_rn(y, sg.residual[o]);
-            sg.y[o] = y;
-          }
-        }
-      }
+      for (int t = 0; t < 32; ++t) v[t] += u[t];
+    } else {
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
     }
+    MMA_STAMP(13, tid == 0);
+    if (r < nrows && ok) {
+      const int m0 = half * 32;
+      const int mcount = min(32, p.M - m0);
+      const size_t o0 = (size_t)m0 * seg_N + row0 + r;
+      float* yp = p.seg[seg].y + o0;
+      const float* rp = p.seg[seg].residual ? p.seg[seg].residual + o0 : nullptr;
+      int32_t* ap = p.seg[seg].acc ? p.seg[seg].acc + o0 : nullptr;
+      // all shared-memory reads first (v[t] becomes the integer total), so that the stores
+      // below, whose target the compiler cannot tell from shared memory, do not serialise them
+      float dsc[32];
+#pragma unroll
+      for (int t = 0; t < 32; ++t) {
+        v[t] = (uint32_t)((int)v[t] - ssum[m0 + t]);
+        dsc[t] = sd[m0 + t];
+      }
+      if (ap) {
+#pragma unroll
+        for (int t = 0; t < 32; ++t)
+          if (t < mcount) ap[(size_t)t * seg_N] = (int)v[t];
+      }
+      float res[32];
+      if (rp) {
+#pragma unroll
+        for (int t = 0; t < 32; ++t) res[t] = t < mcount ? rp[(size_t)t * seg_N] : 0.f;
+      }
+#pragma unroll
+      for (int t = 0; t < 32; ++t)
+        if (t < mcount) {
+          float y = __fmul_rn(__fmul_rn((float)(int)v[t], dsc[t]), ws);
+          if (rp) y = __fadd_rn(y, res[t]);
+          yp[(size_t)t * seg_N] = y;
+        }
+    }
+    MMA_STAMP(14, tid == 0);
   }
+  MMA_STAMP(8, tid == 0);
   tc_fence_before();
   __syncthreads();
-  if (warp == kExpWarps)
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 64;" ::"r"(tmem));
+  if (warp == kMmaWarp)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem));
 }
 
 }  // namespace hb
 
 using namespace hb;
+
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// The tensor-map encoder is a driver entry point; it is looked up through the runtime so
+// that the library does not link against the driver library.
+EncodeTiledFn tensor_map_encoder() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) !=
+            cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+}  // namespace
 
 // Batched path of hb200_bitlinear_forward_multi (16 <= M <= 64).  Scratch in the context:
 // quantised activations in operand layout, their scales and sums.
@@ -435,10 +602,25 @@ int hb_bitlinear_mma_run(hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int ns
                      ctx->pdl, q));
   MmaParams p = {};
   int t = 0;
+  EncodeTiledFn encode = tensor_map_encoder();
+  HB_REQUIRE(encode != nullptr, "bitlinear (batched): the driver has no cuTensorMapEncodeTiled");
   for (int s = 0; s < nseg; ++s) {
     p.seg[s] = {static_cast<const uint8_t*>(segs[s].d_packed), segs[s].d_scale,
                 segs[s].d_residual, segs[s].d_y, segs[s].d_acc, segs[s].N, t};
     t += (segs[s].N + kMmaRows - 1) / kMmaRows;
+    HB_REQUIRE((reinterpret_cast<uintptr_t>(segs[s].d_packed) & 15) == 0,
+               "bitlinear (batched): packed weights must be 16-byte aligned");
+    const cuuint64_t dims[2] = {(cuuint64_t)(K / 4), (cuuint64_t)segs[s].N};
+    const cuuint64_t strides[1] = {(cuuint64_t)(K / 4)};  // bytes between rows
+    const cuuint32_t box[2] = {(cuuint32_t)(kChunkGroups * 32), (cuuint32_t)kMmaRows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult rc = encode(&p.tmap[s], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                               const_cast<void*>(segs[s].d_packed), dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    HB_REQUIRE(rc == CUDA_SUCCESS, "bitlinear (batched): cuTensorMapEncodeTiled failed (%d)",
+               (int)rc);
   }
   p.nseg = nseg;
   p.K = K;
@@ -453,7 +635,7 @@ int hb_bitlinear_mma_run(hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int ns
                                  kMmaSmem));
     configured = true;
   }
-  HB_CUDA(launch_pdl(bitlinear_mma_kernel, dim3(t), dim3(kMmaThreads + 32), (size_t)kMmaSmem, st,
+  HB_CUDA(launch_pdl(bitlinear_mma_kernel, dim3(t), dim3(kMmaThreads + 96), (size_t)kMmaSmem, st,
                      ctx->pdl, p));
   return HB200_OK;
 }
