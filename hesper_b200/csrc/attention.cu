@@ -34,6 +34,17 @@ constexpr int kAttnThreads = kAttnWarps * 32;
 constexpr int kChunk = 16;       // positions per warp step
 constexpr int kMaxSplits = 64;
 
+constexpr int kMinSplitChunks = 8;  // no split shorter than 128 positions
+
+// Splits of one (sequence, KV head) that have work at its CURRENT length: the grid is sized
+// on the host for the longest sequence the cache can hold, the sequence may be much shorter.
+// Returns chunks per split in `cps`; splits >= the result exit at once and are not waited for.
+__device__ __forceinline__ int attn_active_splits(int nch, int nsplit, int& cps) {
+  cps = (nch + nsplit - 1) / nsplit;
+  if (cps < kMinSplitChunks) cps = kMinSplitChunks;
+  return nch > 0 ? (nch + cps - 1) / cps : 1;
+}
+
 struct AttnParams {
   const void* q;
   const __half* k;
@@ -47,6 +58,20 @@ struct AttnParams {
   float scale_log2;  // scale * log2(e)
   int* tickets;      // nullable: per (sequence, kv head) arrival counters, zero between calls
 };
+
+#ifdef HB_PROFILE
+__device__ unsigned long long g_attn_stamps[16];
+#define AT_STAMP(i)                                                                        \
+  do {                                                                                     \
+    if (blockIdx.x == 0 && threadIdx.x == 0) {                                             \
+      unsigned long long t_;                                                               \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                               \
+      g_attn_stamps[i] = t_;                                                               \
+    }                                                                                      \
+  } while (0)
+#else
+#define AT_STAMP(i) ((void)0)
+#endif
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
   const uint32_t n = valid ? 16u : 0u;  // src-size 0: the 16 bytes are zero-filled
@@ -122,15 +147,20 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __gr
   __half* qsl = qs + 8 * QS;                       // lo plane (PRECISE only)
   uint8_t* stage0 = smem + Cfg::kQBytes + (size_t)warp * NS * Cfg::kStageBytes;
 
+  AT_STAMP(0);
   pdl_trigger();
   pdl_wait();  // q, the cache and seqlens come from earlier kernels of the step
+  AT_STAMP(1);
 
   // a length outside [0, max_seq] can only come from a corrupt input: clamp, never overrun
   const int len = min(max(p.seqlens[b], 0), p.max_seq);
   int start = 0;
   if (p.window > 0 && len > p.window) start = len - p.window;
+  AT_STAMP(2);
   const int nch = (len - start + kChunk - 1) / kChunk;  // chunks of this sequence (<= 0 if empty)
-  const int cps = (nch + p.nsplit - 1) / p.nsplit;      // chunks per split
+  int cps;                                              // chunks per split
+  const int nact = attn_active_splits(nch, p.nsplit, cps);
+  if (split >= nact) return;  // an idle split of a short sequence
   const int c_begin = split * cps;
   const int c_end = min(nch, c_begin + cps);
 
@@ -167,19 +197,30 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __gr
   // Q -> f16, pre-multiplied by scale*log2(e), heads >= G zero
   {
     const size_t qoff = ((size_t)b * p.H + (size_t)kvh * G) * D;
-    for (int i = tid; i < 8 * D; i += kAttnThreads) {
+    // all global loads first: interleaved with the shared-memory stores below they would
+    // be issued one at a time (the compiler cannot tell the two address spaces apart)
+    constexpr int QI = 8 * D / kAttnThreads;
+    float qv[QI];
+#pragma unroll
+    for (int j = 0; j < QI; ++j) {
+      const int i = tid + j * kAttnThreads;
+      qv[j] = 0.f;
+      if (i / D < G)
+        qv[j] = p.q_is_f16 ? __half2float(reinterpret_cast<const __half*>(p.q)[qoff + i])
+                           : reinterpret_cast<const float*>(p.q)[qoff + i];
+    }
+#pragma unroll
+    for (int j = 0; j < QI; ++j) {
+      const int i = tid + j * kAttnThreads;
       const int h = i / D;
-      float v = 0.f;
-      if (h < G)
-        v = p.q_is_f16 ? __half2float(reinterpret_cast<const __half*>(p.q)[qoff + i])
-                       : reinterpret_cast<const float*>(p.q)[qoff + i];
-      const float sv = v * p.scale_log2;
+      const float sv = qv[j] * p.scale_log2;
       const __half hv = __float2half_rn(sv);
       qs[h * QS + (i - h * D)] = hv;
       if (PRECISE) qsl[h * QS + (i - h * D)] = __float2half_rn(sv - __half2float(hv));
     }
   }
   __syncthreads();
+  AT_STAMP(3);
   // B fragments of Q^T: head g, dims 16s+2t(+1) and 16s+2t+8(+9).  The fast path keeps
   // them in registers; the precise path re-reads hi and lo from shared memory per k-step.
   constexpr int QR = PRECISE ? 1 : KS;
@@ -306,6 +347,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __gr
   }
   cp_async_wait<0>();
   __syncthreads();  // every warp is done with its stages: reuse them for the merge
+  AT_STAMP(4);
 
   // ---- merge the 4 warps ---------------------------------------------------------
   float* mo = reinterpret_cast<float*>(smem + Cfg::kQBytes);  // [warps][8 heads][D]
@@ -340,7 +382,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __gr
         lsum += wgt * mm[w * 16 + h * 2 + 1];
       }
     }
-    if (p.nsplit == 1) {
+    if (nact == 1) {
       p.out[((size_t)b * p.H + (size_t)kvh * G + h) * D + d] = lsum > 0.f ? acc / lsum : 0.f;
     } else {
       const size_t pi = (((size_t)b * p.Hkv + kvh) * p.nsplit + split) * 8 + h;
@@ -351,7 +393,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __gr
       }
     }
   }
-  if (p.nsplit == 1 || p.tickets == nullptr) return;
+  AT_STAMP(5);
+  if (nact == 1 || p.tickets == nullptr) return;
 
   // ---- the last split to finish merges all splits of its (sequence, kv head) ------------
   // Each CTA publishes its partials, then takes a ticket; whoever draws the last one knows
@@ -362,15 +405,16 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __gr
   __syncthreads();
   if (tid == 0) {
     const int t = atomicAdd(&p.tickets[b * p.Hkv + kvh], 1);
-    s_last = (t == p.nsplit - 1);
+    s_last = (t == nact - 1);
   }
   __syncthreads();
+  AT_STAMP(6);
   if (!s_last) return;
   __threadfence();
   float* cw = reinterpret_cast<float*>(smem + Cfg::kQBytes);  // [nsplit][8] weights, then [8] sums
   float* cl = cw + kMaxSplits * 8;
   const size_t base = ((size_t)b * p.Hkv + kvh) * p.nsplit;
-  for (int i = tid; i < p.nsplit * 8; i += kAttnThreads) {  // stage (max, sum) of every split
+  for (int i = tid; i < nact * 8; i += kAttnThreads) {  // stage (max, sum) of every split
     const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_meta) + base * 8 + i);
     cw[i] = ml.x;
     cw[kMaxSplits * 8 + 8 + i] = ml.y;
@@ -378,9 +422,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __gr
   __syncthreads();
   if (tid < 8) {
     float mstar = -CUDART_INF_F;
-    for (int sidx = 0; sidx < p.nsplit; ++sidx) mstar = fmaxf(mstar, cw[sidx * 8 + tid]);
+    for (int sidx = 0; sidx < nact; ++sidx) mstar = fmaxf(mstar, cw[sidx * 8 + tid]);
     float lsum = 0.f;
-    for (int sidx = 0; sidx < p.nsplit; ++sidx) {
+    for (int sidx = 0; sidx < nact; ++sidx) {
       const float wgt = mstar == -CUDART_INF_F ? 0.f : exp2f(cw[sidx * 8 + tid] - mstar);
       lsum += wgt * cw[kMaxSplits * 8 + 8 + sidx * 8 + tid];
       cw[sidx * 8 + tid] = wgt;
@@ -394,7 +438,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __gr
     const float4* src = reinterpret_cast<const float4*>(p.part_out + (base * 8 + h) * D + d);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 8
-    for (int sidx = 0; sidx < p.nsplit; ++sidx) {
+    for (int sidx = 0; sidx < nact; ++sidx) {
       const float4 v = __ldcg(src + (size_t)sidx * 2 * D);  // next split: 8*D floats further
       const float wgt = cw[sidx * 8 + h];
       acc.x = fmaf(wgt, v.x, acc.x);
@@ -419,12 +463,20 @@ __global__ void attn_combine_kernel(const __grid_constant__ AttnParams p, int D)
   const int kvh = (blockIdx.x / p.G) % p.Hkv;
   const int b = blockIdx.x / (p.G * p.Hkv);
   const size_t base = ((size_t)b * p.Hkv + kvh) * p.nsplit;
+  // the same active-split count as the main kernel derived; a single active split wrote
+  // its result straight to `out`
+  const int len = min(max(p.seqlens[b], 0), p.max_seq);
+  int start = 0;
+  if (p.window > 0 && len > p.window) start = len - p.window;
+  int cps;
+  const int nact = attn_active_splits((len - start + kChunk - 1) / kChunk, p.nsplit, cps);
+  if (nact == 1) return;
   float mstar = -CUDART_INF_F;
-  for (int s = 0; s < p.nsplit; ++s) mstar = fmaxf(mstar, p.part_meta[((base + s) * 8 + h) * 2]);
+  for (int s = 0; s < nact; ++s) mstar = fmaxf(mstar, p.part_meta[((base + s) * 8 + h) * 2]);
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float acc = 0.f, lsum = 0.f;
     if (mstar != -CUDART_INF_F) {
-      for (int s = 0; s < p.nsplit; ++s) {
+      for (int s = 0; s < nact; ++s) {
         const size_t pi = (base + s) * 8 + h;
         const float wgt = exp2f(p.part_meta[pi * 2] - mstar);
         acc += wgt * p.part_out[pi * D + d];
@@ -542,6 +594,13 @@ static int attn_launch(hb200_ctx* ctx, const AttnParams& p, cudaStream_t st) {
 }  // namespace hb
 
 using namespace hb;
+
+#ifdef HB_PROFILE
+extern "C" __attribute__((visibility("default"))) void hb200_prof_read_attn(unsigned long long* out) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, g_attn_stamps, sizeof(unsigned long long) * 16);
+}
+#endif
 
 extern "C" size_t hb200_attn_workspace_bytes(const hb200_ctx* ctx, int B, int H, int Hkv, int D,
                                              int max_seq) {

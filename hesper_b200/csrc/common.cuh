@@ -191,6 +191,11 @@ int hb_bitlinear_mma_run(struct hb200_ctx* ctx, const hb200_bitlinear_seg* segs,
                          const float* d_x, int M, const float* d_rms_gamma, float rms_eps,
                          float* d_act_scale, cudaStream_t st);
 
+// batched (16..64 token) LM head on the tensor cores, lmhead_mma.cu
+int hb_lmhead_mma_run(struct hb200_ctx* ctx, const void* d_table, int dtype, long V, int K,
+                      const float* d_x, int M, const float* d_rms_gamma, float rms_eps,
+                      float* d_logits, unsigned long long* d_keys, cudaStream_t st);
+
 struct hb200_ctx {
   int device;
   int sm_count;

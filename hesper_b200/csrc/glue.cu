@@ -452,6 +452,16 @@ extern "C" int hb200_lmhead_argmax(hb200_ctx* ctx, const void* d_table, int dtyp
   HB_REQUIRE((reinterpret_cast<uintptr_t>(d_table) & 15) == 0 &&
                  (reinterpret_cast<uintptr_t>(d_x) & 15) == 0,
              "lmhead: table and x must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M >= 16 && K % 64 == 0 && !ctx->no_mma) {  // a real contraction: tensor-core path
+    const int rc = hb_lmhead_mma_run(ctx, d_table, dtype, V, K, d_x, M, d_rms_gamma, rms_eps,
+                                     d_logits, static_cast<unsigned long long*>(d_scratch), st);
+    if (rc != HB200_OK) return rc;
+    HB_CUDA(launch_pdl(argmax_finish_kernel, dim3((M + 63) / 64), dim3(64), 0, st, ctx->pdl,
+                       static_cast<unsigned long long*>(d_scratch), M, d_argmax, d_token_log,
+                       d_log_index, log_stride));
+    return HB200_OK;
+  }
   LMParams p = {};
   p.table = static_cast<const uint16_t*>(d_table);
   p.x = d_x;
@@ -474,7 +484,6 @@ extern "C" int hb200_lmhead_argmax(hb200_ctx* ctx, const void* d_table, int dtyp
   p.stages = stages;
   const long ntiles = (V + kLMRows - 1) / kLMRows;
   const int grid = ntiles < ctx->sm_count ? (int)ntiles : ctx->sm_count;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e = MT == 1 ? lm_launch<1>(ctx, p, grid, smem, st)
                           : (MT == 4 ? lm_launch<4>(ctx, p, grid, smem, st)
                                      : lm_launch<8>(ctx, p, grid, smem, st));

@@ -1,0 +1,414 @@
+// lmhead_mma.cu -- batched (16..64 tokens) LM head on the 5th-generation tensor cores.
+//
+// logits[m][v] = sum_k table[v][k] * xn[m][k] with the 16-bit table (bf16 or f16, [V][K], the
+// tied embedding of Hesper/Models/BitNet.lean:456) and f32 activations, optional final RMSNorm
+// in front and the greedy argmax (first strict maximum, Hesper/Inference/Sampling.lean:74)
+// behind.  The batch-1 kernel streams the table once per 8 tokens and is FMA-bound from 16
+// tokens on; here the table is streamed ONCE and the contraction runs as tcgen05.mma
+// kind::f16 with f32 accumulators in tensor memory.
+//
+// Keeping f32-activation accuracy on a 16-bit tensor-core path: each activation is split as
+// x = hi + lo with hi = round16(x), lo = round16(x - hi).  Products of 16-bit values are exact
+// in the f32 accumulator, so the logit error is that of dropping x - hi - lo (2^-17 relative
+// for bf16, 2^-22 for f16) plus the accumulation order.  hi and lo occupy token rows 0..63
+// and 64..127 of one N=128 operand; the epilogue adds the two halves.
+//
+//   lm_split_kernel     one CTA per token: optional RMSNorm, split, and store in the
+//                       shared-memory operand layout (K-major 8x16-byte core matrices), one
+//                       16 KB block per 64-wide K step
+//   lmhead_mma_kernel   one CTA per 128 vocabulary rows, two CTAs per SM so that one tile's
+//                       epilogue overlaps the other's main loop:
+//     warp 0  producer: table tile [128 rows x 64 el] per step by ONE 2-D tensor-map TMA
+//             (128-byte swizzle, consumed by the tensor core as it lands) + one bulk copy of
+//             the 16 KB activation block;
+//     warp 1  one thread issues 4 MMAs (M=128, N=128, K=16) per step; tcgen05.commit frees
+//             the stage;
+//     warps 2-5  epilogue: tcgen05.ld of hi and lo columns, add, optional logits store,
+//             per-token argmax over the tile's 128 rows (redux + ballot), then one
+//             atomicMax of the ordered (value,row) key per token.
+// Every mbarrier wait is bounded; on expiry the kernel still releases its tensor memory.
+#include <cuda.h>  // CUtensorMap and its enums only; the encoder comes from the runtime
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace hb {
+
+constexpr int kLmRows = 128;      // vocabulary rows per CTA = MMA M
+constexpr int kLmTokens = 64;     // token slots; the operand holds 2 x 64 rows (hi, lo)
+constexpr int kLmN = 2 * kLmTokens;
+constexpr int kLmKStep = 64;      // elements per pipeline step = 128 bytes of a table row
+constexpr int kLmStages = 3;
+constexpr int kLmABytes = kLmRows * kLmKStep * 2;  // 16 KB
+constexpr int kLmBBytes = kLmN * kLmKStep * 2;     // 16 KB
+constexpr int kLmCtrl = 4096;     // barriers, tensor-memory slot, per-warp argmax keys
+constexpr int kLmSmem = kLmCtrl + kLmStages * (kLmABytes + kLmBBytes);
+constexpr int kLmThreads = 192;
+
+struct LmSplitParams {
+  const float* x;      // [M][K]
+  const float* gamma;  // nullable
+  float eps;
+  int K, M, dtype;     // dtype 0 = bf16, 1 = f16
+  uint8_t* xb;         // [K/64][16 KB] operand blocks
+};
+
+struct LmMmaParams {
+  CUtensorMap tmap;    // table as [V rows][K elements of 2 bytes], boxes of 128 rows x 64
+  const uint8_t* xb;
+  float* logits;       // nullable [M][V]
+  unsigned long long* keys;  // [M]
+  long V;
+  int K, M;
+  uint32_t idesc;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ uint16_t round16(float v, int dtype) {
+  return dtype == 0 ? __bfloat16_as_ushort(__float2bfloat16_rn(v))
+                    : __half_as_ushort(__float2half_rn(v));
+}
+__device__ __forceinline__ float widen16(uint16_t h, int dtype) {
+  return dtype == 0 ? __uint_as_float((uint32_t)h << 16) : __half2float(__ushort_as_half(h));
+}
+
+__global__ void __launch_bounds__(256) lm_split_kernel(const __grid_constant__ LmSplitParams p) {
+  __shared__ double red[8];
+  pdl_trigger();
+  pdl_wait();
+  const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int K = p.K;
+  // 8 consecutive k of token row `row` -> their 16 bytes in the operand block
+  auto dst = [&](int row, int k) {
+    return p.xb + (size_t)(k >> 6) * kLmBBytes + (size_t)(row >> 3) * 1024 +
+           (size_t)((k & 63) >> 3) * 128 + (size_t)(row & 7) * 16;
+  };
+  if (m >= p.M) {
+    for (int k = tid * 8; k < K; k += 256 * 8) {
+      *reinterpret_cast<uint4*>(dst(m, k)) = make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(dst(kLmTokens + m, k)) = make_uint4(0, 0, 0, 0);
+    }
+    return;
+  }
+  const float* xg = p.x + (size_t)m * K;
+  float rinv = 1.f;
+  if (p.gamma) {
+    double ss = 0.0;
+    for (int k = tid; k < K; k += 256) {
+      const float v = xg[k];
+      ss += (double)v * v;
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    ss = 0.0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += red[i];
+    rinv = (float)(1.0 / sqrt(ss / (double)K + (double)p.eps));
+  }
+  for (int k = tid * 8; k < K; k += 256 * 8) {
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint16_t h[2], l[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int kk = k + 2 * j + e;
+        const float v = p.gamma ? __fmul_rn(__fmul_rn(xg[kk], rinv), p.gamma[kk]) : xg[kk];
+        h[e] = round16(v, p.dtype);
+        l[e] = round16(__fsub_rn(v, widen16(h[e], p.dtype)), p.dtype);
+      }
+      hi[j] = (uint32_t)h[0] | ((uint32_t)h[1] << 16);
+      lo[j] = (uint32_t)l[0] | ((uint32_t)l[1] << 16);
+    }
+    *reinterpret_cast<uint4*>(dst(m, k)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    *reinterpret_cast<uint4*>(dst(kLmTokens + m, k)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+  }
+}
+
+// ---- tcgen05 helpers -----------------------------------------------------------------
+
+// K-major shared-memory matrix descriptor.  layout 0: no swizzle, core matrices of 8 rows x
+// 16 bytes, LBO = distance between core matrices adjacent in K, SBO = between 8-row groups.
+// layout 2: 128-byte swizzle, rows of 128 bytes in 1 KB atoms of 8 rows, SBO = 1024.
+__device__ __forceinline__ uint64_t lm_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo,
+                                            uint32_t layout) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version of this architecture
+  d |= (uint64_t)layout << 61;
+  return d;
+}
+__device__ __forceinline__ void lm_umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void lm_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void lm_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void lm_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void lm_tma_box(void* dst, const CUtensorMap* tm, int x, int y,
+                                           uint64_t* bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+// Bounded wait (about a tenth of a second at worst); later waits are skipped after a failure.
+__device__ __forceinline__ bool lm_wait(bool ok, uint64_t* bar, uint32_t parity,
+                                        uint32_t* status) {
+  if (!ok) return false;
+#pragma unroll 1
+  for (uint32_t it = 0; it < (1u << 18); ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+  atomicOr(status, kStatusMbarTimeout);
+  return false;
+}
+
+#define LM_TMEM_LD32(v, addr)                                                                  \
+  asm volatile(                                                                                \
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                \
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"                                \
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"               \
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),    \
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]),             \
+        "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),          \
+        "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),          \
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),          \
+        "=r"(v[31])                                                                            \
+      : "r"(addr))
+
+__global__ void __launch_bounds__(kLmThreads, 2)
+    lmhead_mma_kernel(const __grid_constant__ LmMmaParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nsteps = p.K / kLmKStep;
+  const long row0 = (long)blockIdx.x * kLmRows;
+
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);   // [kLmStages] table box + activations
+  uint64_t* empty = full + kLmStages;                    // [kLmStages] MMAs of the stage retired
+  uint64_t* done = empty + kLmStages;                    // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
+  unsigned long long* wkeys = reinterpret_cast<unsigned long long*>(smem + 1024);  // [4][64]
+  uint8_t* stg = smem + kLmCtrl;  // per stage: A (16 KB, swizzled) then B (16 KB)
+
+  if (tid == 0) {
+    for (int i = 0; i < kLmStages; ++i) {
+      mbar_init(&full[i], 2);  // one arrival with the table bytes, one with the activation bytes
+      mbar_init(&empty[i], 1);
+    }
+    mbar_init(done, 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) {  // 128 columns: the 128 x 128 f32 accumulator
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 128;" ::"r"(
+        smem_u32(tmem_slot)));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  lm_fence_before();
+  __syncthreads();
+  lm_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  bool ok = true;
+
+  if (warp == 0) {
+    // ================= producer =============================================================
+    const uint64_t pol = policy_evict_first();
+    auto issue_a = [&](int ks) {
+      const int st = ks % kLmStages;
+      mbar_arrive_expect_tx(&full[st], kLmABytes);
+      lm_tma_box(stg + (size_t)st * (kLmABytes + kLmBBytes), &p.tmap, ks * kLmKStep, (int)row0,
+                 &full[st], pol);
+    };
+    auto issue_b = [&](int ks) {
+      const int st = ks % kLmStages;
+      mbar_arrive_expect_tx(&full[st], kLmBBytes);
+      bulk_g2s(stg + (size_t)st * (kLmABytes + kLmBBytes) + kLmABytes,
+               p.xb + (size_t)ks * kLmBBytes, kLmBBytes, &full[st]);
+    };
+    const int pre = min(kLmStages, nsteps);
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&p.tmap))
+                   : "memory");
+      for (int ks = 0; ks < pre; ++ks) issue_a(ks);  // the table does not depend on anything
+    }
+    pdl_trigger();
+    pdl_wait();  // the split activations come from the kernel before this one
+    if (lane == 0)
+      for (int ks = 0; ks < pre; ++ks) issue_b(ks);
+    for (int ks = pre; ks < nsteps; ++ks) {
+      ok = lm_wait(ok, &empty[ks % kLmStages], (uint32_t)(((ks / kLmStages) - 1) & 1), p.status);
+      if (lane == 0 && ok) {
+        issue_a(ks);
+        issue_b(ks);
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer ===========================================================
+    for (int ks = 0; ks < nsteps; ++ks) {
+      const int st = ks % kLmStages;
+      ok = lm_wait(ok, &full[st], (uint32_t)((ks / kLmStages) & 1), p.status);
+      if (lane == 0) {
+        lm_fence_after();
+        const uint32_t abase = smem_u32(stg + (size_t)st * (kLmABytes + kLmBBytes));
+        const uint32_t bbase = abase + kLmABytes;
+#pragma unroll
+        for (int j = 0; j < kLmKStep / 16; ++j)  // K = 16 elements = 32 bytes per instruction
+          lm_umma_f16(tmem, lm_desc(abase + j * 32, 0, 1024, 2),
+                      lm_desc(bbase + j * 256, 128, 1024, 0), p.idesc,
+                      (ks > 0 || j > 0) ? 1u : 0u);
+        lm_commit(&empty[st]);
+      }
+      __syncwarp();
+    }
+    if (lane == 0) lm_commit(done);
+  }
+  // ================= epilogue (warps 2..5) ====================================================
+  if (warp >= 2) {
+    ok = lm_wait(true, done, 0, p.status);
+    lm_fence_after();
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const long row = row0 + q * 32 + lane;
+    const bool row_ok = row < p.V;
+    const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
+    unsigned long long* mykeys = wkeys + (warp - 2) * kLmTokens;
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {
+      if (half * 32 >= p.M) {
+        if (lane < 32) mykeys[half * 32 + lane] = 0ull;
+        continue;
+      }
+      uint32_t hi[32], lo[32];
+      LM_TMEM_LD32(hi, lane_addr + (uint32_t)(half * 32));
+      LM_TMEM_LD32(lo, lane_addr + (uint32_t)(kLmTokens + half * 32));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      unsigned long long mine = 0ull;  // lane t keeps the key of token half*32 + t
+#pragma unroll
+      for (int t = 0; t < 32; ++t) {
+        const int m = half * 32 + t;
+        const float v = __fadd_rn(__uint_as_float(hi[t]), __uint_as_float(lo[t]));
+        if (m < p.M && row_ok && p.logits && ok) p.logits[(size_t)m * p.V + row] = v;
+        uint32_t u = __float_as_uint(v);
+        u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);  // monotone map float -> uint
+        if (!(v == v) || !row_ok) u = 0u;                  // NaN and padding rows never win
+        const uint32_t best = __reduce_max_sync(0xffffffffu, u);
+        const uint32_t who = __ballot_sync(0xffffffffu, u == best);
+        if (lane == t) {
+          const uint32_t first_row = (uint32_t)(row0 + q * 32) + (uint32_t)(__ffs(who) - 1);
+          mine = best ? (((unsigned long long)best << 32) |
+                         (unsigned long long)(0xFFFFFFFFu - first_row))
+                      : 0ull;
+        }
+      }
+      mykeys[half * 32 + lane] = mine;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+    if (warp == 2 && p.keys && ok) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int m = lane + 32 * i;
+        if (m < p.M) {
+          unsigned long long k = wkeys[m];
+#pragma unroll
+          for (int w = 1; w < 4; ++w) {
+            const unsigned long long o = wkeys[w * kLmTokens + m];
+            k = o > k ? o : k;
+          }
+          if (k) atomicMax(&p.keys[m], k);
+        }
+      }
+    }
+  }
+  lm_fence_before();
+  __syncthreads();
+  if (warp == 1)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 128;" ::"r"(tmem));
+}
+
+}  // namespace hb
+
+using namespace hb;
+
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn lm_tensor_map_encoder() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) !=
+            cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+}  // namespace
+
+// Batched LM head (16 <= M <= 64, K a multiple of 64).  The split activations live in the
+// context scratch at kLmScratchOffset; keys are accumulated with atomicMax like the batch-1
+// kernel does, so the caller's finishing kernel is shared.
+int hb_lmhead_mma_run(hb200_ctx* ctx, const void* d_table, int dtype, long V, int K,
+                      const float* d_x, int M, const float* d_rms_gamma, float rms_eps,
+                      float* d_logits, unsigned long long* d_keys, cudaStream_t st) {
+  constexpr size_t kLmScratchOffset = (size_t)6 << 20;
+  const size_t xb_bytes = (size_t)(K / kLmKStep) * kLmBBytes;
+  HB_REQUIRE(kLmScratchOffset + xb_bytes <= ctx->scratch_bytes,
+             "lmhead (batched): K=%d needs %zu bytes of activation scratch", K, xb_bytes);
+  HB_REQUIRE(V < (1l << 31), "lmhead (batched): V too large");
+  uint8_t* xb = static_cast<uint8_t*>(ctx->d_scratch) + kLmScratchOffset;
+  LmSplitParams sp = {d_x, d_rms_gamma, rms_eps, K, M, dtype, xb};
+  HB_CUDA(launch_pdl(lm_split_kernel, dim3(kLmTokens), dim3(256), 0, st, ctx->pdl, sp));
+
+  LmMmaParams p = {};
+  EncodeTiledFn encode = lm_tensor_map_encoder();
+  HB_REQUIRE(encode != nullptr, "lmhead (batched): the driver has no cuTensorMapEncodeTiled");
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)V};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kLmKStep, (cuuint32_t)kLmRows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult rc =
+      encode(&p.tmap, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(d_table), dims, strides,
+             box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  HB_REQUIRE(rc == CUDA_SUCCESS, "lmhead (batched): cuTensorMapEncodeTiled failed (%d)", (int)rc);
+  p.xb = xb;
+  p.logits = d_logits;
+  p.keys = d_keys;
+  p.V = V;
+  p.K = K;
+  p.M = M;
+  // instruction descriptor of kind::f16: D = f32, A and B of the table's type, both K-major
+  const uint32_t fmt = dtype == 0 ? 1u : 0u;  // 1 = bf16, 0 = f16
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kLmN >> 3) << 17) |
+            ((uint32_t)(kLmRows >> 4) << 24);
+  p.status = ctx->d_status;
+  static bool configured = false;
+  if (!configured) {
+    HB_CUDA(cudaFuncSetAttribute(lmhead_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kLmSmem));
+    configured = true;
+  }
+  const long ntiles = (V + kLmRows - 1) / kLmRows;
+  HB_CUDA(launch_pdl(lmhead_mma_kernel, dim3((unsigned)ntiles), dim3(kLmThreads), (size_t)kLmSmem,
+                     st, ctx->pdl, p));
+  return HB200_OK;
+}
