@@ -595,9 +595,9 @@ extern "C" int hb200_bitlinear_gateup_relu2(hb200_ctx* ctx, const void* d_packed
                reinterpret_cast<uintptr_t>(d_packed_up)) & 15) == 0,
              "bitlinear gate/up: weights must be 16-byte aligned");
   if (M >= 16 && K <= 12288 && !ctx->no_mma &&
-      (size_t)2 * M * N * sizeof(float) + ((size_t)2 << 20) <= ctx->scratch_bytes) {
+      kScratchGlu + (size_t)2 * M * N * sizeof(float) <= kScratchLmSplit) {
     // batched: both products on the tensor cores into scratch, then the GLU epilogue
-    float* g = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->d_scratch) + ((size_t)2 << 20));
+    float* g = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->d_scratch) + kScratchGlu);
     float* u = g + (size_t)M * N;
     hb200_bitlinear_seg segs[2] = {{d_packed_gate, d_scale_gate, nullptr, g, nullptr, N},
                                    {d_packed_up, d_scale_up, nullptr, u, nullptr, N}};

@@ -27,7 +27,10 @@
 //       step gathers the 8 expander arrivals and the activation bytes; one tcgen05.commit
 //       per step releases the stage (6 stages = 384 columns of A);
 //     * epilogue: 8 warps read 32 lanes x 32 columns of both accumulators (tcgen05.ld
-//       32x32b), add them, subtract sum(q) per token (value = code - 1), scale and store.
+//       32x32b), add them, subtract sum(q) per token (value = code - 1), scale and store;
+//     * split-K: a launch with few tiles (o_proj and down_proj have 20) splits K over several
+//       CTAs per tile; each publishes its int32 partial, the last to arrive (a ticket per
+//       tile) adds the others' and runs the epilogue -- exact, since integers commute.
 // Every mbarrier wait is bounded; on expiry the kernel still releases its tensor memory.
 #include <cuda.h>  // CUtensorMap and its enums only; the encoder comes from the runtime
 
@@ -63,6 +66,9 @@ struct MmaParams {
   CUtensorMap tmap[4];  // per segment: packed weights as [N rows][K/4 bytes], 128 x 128 boxes
   MmaSeg seg[4];
   int nseg, K, M;
+  int nsplit, gps;     // split-K: CTAs per tile, groups per split
+  int32_t* part;       // [tile][split][64 tokens][128 rows] partial accumulators (nsplit > 1)
+  int* tickets;        // [tile] arrival counters, zero between launches
   const uint8_t* xq;   // [K/128][64 tokens x 128 bytes, core-matrix layout]
   const float* d;      // [64] activation scales
   const int32_t* sumq; // [64]
@@ -278,7 +284,10 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
     bitlinear_mma_kernel(const __grid_constant__ MmaParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int ngroups = p.K >> 7;
+  // this CTA's K range (split-K over 128-wide groups; a whole row when nsplit == 1)
+  const int tile = (int)blockIdx.x / p.nsplit, split = (int)blockIdx.x % p.nsplit;
+  const int gbase = split * p.gps;
+  const int ngroups = min(p.gps, (p.K >> 7) - gbase);
   const int nchunks = (ngroups + kChunkGroups - 1) / kChunkGroups;
   const int nsteps = (ngroups + kStepGroups - 1) / kStepGroups;
   constexpr int kExpWarps = kMmaThreads / 32;  // warps 0..7 expand, warp 8 issues MMAs, warp 9 copies
@@ -300,9 +309,9 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
   int seg = 0;
 #pragma unroll
   for (int s = 1; s < 4; ++s)
-    if (s < p.nseg && (int)blockIdx.x >= p.seg[s].tile0) seg = s;
+    if (s < p.nseg && tile >= p.seg[s].tile0) seg = s;
   const int seg_N = p.seg[seg].N;
-  const int row0 = ((int)blockIdx.x - p.seg[seg].tile0) * kMmaRows;
+  const int row0 = (tile - p.seg[seg].tile0) * kMmaRows;
   const int nrows = min(kMmaRows, seg_N - row0);
   MMA_STAMP(0, tid == 0);
 
@@ -338,7 +347,7 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm)) : "memory");
       for (; cnext < kPkStages && cnext < nchunks; ++cnext) {  // weights: no dependency
         mbar_arrive_expect_tx(&pk_full[cnext], kPkBytes);
-        tma_box_2d(pk + (size_t)cnext * kPkBytes, tm, cnext * kChunkGroups * 32, row0,
+        tma_box_2d(pk + (size_t)cnext * kPkBytes, tm, (gbase + cnext * kChunkGroups) * 32, row0,
                    &pk_full[cnext], pol);
       }
     }
@@ -354,7 +363,7 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
         const int g0 = s * kStepGroups;
         const uint32_t bytes = (uint32_t)min(kStepGroups, ngroups - g0) * kBBytes;
         mbar_arrive_expect_tx(&full[st], bytes);
-        bulk_g2s(bstg + (size_t)st * kStepGroups * kBBytes, p.xq + (size_t)g0 * kBBytes, bytes,
+        bulk_g2s(bstg + (size_t)st * kStepGroups * kBBytes, p.xq + (size_t)(gbase + g0) * kBBytes, bytes,
                  &full[st]);
       }
       // refill the packed ring as soon as every expander warp has left the oldest box
@@ -362,8 +371,8 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
                                            (uint32_t)(((cnext / kPkStages) - 1) & 1))) {
         if (lane == 0) {
           mbar_arrive_expect_tx(&pk_full[cnext % kPkStages], kPkBytes);
-          tma_box_2d(pk + (size_t)(cnext % kPkStages) * kPkBytes, tm, cnext * kChunkGroups * 32,
-                     row0, &pk_full[cnext % kPkStages], pol);
+          tma_box_2d(pk + (size_t)(cnext % kPkStages) * kPkBytes, tm,
+                     (gbase + cnext * kChunkGroups) * 32, row0, &pk_full[cnext % kPkStages], pol);
         }
         ++cnext;
       }
@@ -374,8 +383,8 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
       if (!ok) break;
       if (lane == 0) {
         mbar_arrive_expect_tx(&pk_full[cnext % kPkStages], kPkBytes);
-        tma_box_2d(pk + (size_t)(cnext % kPkStages) * kPkBytes, tm, cnext * kChunkGroups * 32,
-                   row0, &pk_full[cnext % kPkStages], pol);
+        tma_box_2d(pk + (size_t)(cnext % kPkStages) * kPkBytes, tm,
+                   (gbase + cnext * kChunkGroups) * 32, row0, &pk_full[cnext % kPkStages], pol);
       }
       ++cnext;
     }
@@ -482,11 +491,11 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
   MMA_STAMP(4, tid == 0);
 
   // ---- epilogue: TMEM lane = weight row, column = token; warps w and w+4 share lanes ------
+  const int q = warp & 3, half = warp >> 2;  // lane quarter, token half (expander warps only)
+  const int r = q * 32 + lane;
+  const int m0 = half * 32;
+  uint32_t v[32];
   if (warp < kExpWarps) {
-    const int q = warp & 3, half = warp >> 2;  // lane quarter, token half
-    const int r = q * 32 + lane;
-    const float ws = __ldg(p.seg[seg].scale);
-    uint32_t v[32];
     const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 32);
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -498,7 +507,7 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
           "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
           "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
         : "r"(taddr));
-    if (nsteps > 1) {
+    if (nsteps > 1) {  // the second MMA warp's accumulator
       uint32_t u[32];
       asm volatile(
           "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -517,9 +526,43 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
     } else {
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
     }
-    MMA_STAMP(13, tid == 0);
+  }
+  MMA_STAMP(13, tid == 0);
+
+  // ---- split-K: publish the int32 partial, the last split of the tile to arrive adds them ---
+  // Integer addition commutes, so the result is bit-identical to the unsplit product.
+  bool finish = true;
+  if (p.nsplit > 1) {
+    __shared__ int s_last;
+    int32_t* mine = p.part + ((size_t)(tile * p.nsplit + split) * kMmaTokens) * kMmaRows;
+    if (warp < kExpWarps) {
+#pragma unroll
+      for (int t = 0; t < 32; ++t) mine[(size_t)(m0 + t) * kMmaRows + r] = (int32_t)v[t];
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const int t = atomicAdd(&p.tickets[tile], 1);
+      s_last = (t == p.nsplit - 1);
+      if (s_last) p.tickets[tile] = 0;  // every split has arrived: ready for the next launch
+    }
+    __syncthreads();
+    finish = s_last != 0;
+    if (finish && warp < kExpWarps) {
+      __threadfence();
+      for (int s2 = 0; s2 < p.nsplit; ++s2) {
+        if (s2 == split) continue;
+        const int32_t* other =
+            p.part + ((size_t)(tile * p.nsplit + s2) * kMmaTokens + m0) * kMmaRows + r;
+#pragma unroll
+        for (int t = 0; t < 32; ++t) v[t] += (uint32_t)__ldcg(other + (size_t)t * kMmaRows);
+      }
+    }
+  }
+
+  if (finish && warp < kExpWarps) {
+    const float ws = __ldg(p.seg[seg].scale);
     if (r < nrows && ok) {
-      const int m0 = half * 32;
       const int mcount = min(32, p.M - m0);
       const size_t o0 = (size_t)m0 * seg_N + row0 + r;
       float* yp = p.seg[seg].y + o0;
@@ -591,7 +634,7 @@ int hb_bitlinear_mma_run(hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int ns
                          const float* d_x, int M, const float* d_rms_gamma, float rms_eps,
                          float* d_act_scale, cudaStream_t st) {
   const size_t xq_bytes = (size_t)(K / 128) * kBBytes;
-  HB_REQUIRE(xq_bytes + 1024 <= ctx->scratch_bytes,
+  HB_REQUIRE(xq_bytes + 1024 <= kScratchGlu,
              "bitlinear (batched): K=%d needs %zu bytes of activation scratch", K, xq_bytes);
   uint8_t* base = static_cast<uint8_t*>(ctx->d_scratch);
   float* d = reinterpret_cast<float*>(base);
@@ -625,6 +668,19 @@ int hb_bitlinear_mma_run(hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int ns
   p.nseg = nseg;
   p.K = K;
   p.M = M;
+  // split-K when the tiles alone leave most SMs idle: as many splits as fit the SMs, each at
+  // least 4 groups (two pipeline steps) long, partials within their scratch region
+  const int ngroups = K / 128;
+  int nsplit = ctx->sm_count / t;
+  if (nsplit > ngroups / 4) nsplit = ngroups / 4;
+  while (nsplit > 1 && (size_t)t * nsplit * kMmaTokens * kMmaRows * 4 >
+                           kScratchBytes - kScratchSplitK)
+    --nsplit;
+  if (nsplit < 1 || t > kCtxTickets) nsplit = 1;
+  p.gps = (ngroups + nsplit - 1) / nsplit;
+  p.nsplit = (ngroups + p.gps - 1) / p.gps;  // no empty split
+  p.part = reinterpret_cast<int32_t*>(base + kScratchSplitK);
+  p.tickets = ctx->d_tickets;
   p.xq = xq;
   p.d = d;
   p.sumq = sumq;
@@ -635,7 +691,7 @@ int hb_bitlinear_mma_run(hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int ns
                                  kMmaSmem));
     configured = true;
   }
-  HB_CUDA(launch_pdl(bitlinear_mma_kernel, dim3(t), dim3(kMmaThreads + 96), (size_t)kMmaSmem, st,
+  HB_CUDA(launch_pdl(bitlinear_mma_kernel, dim3(t * p.nsplit), dim3(kMmaThreads + 96), (size_t)kMmaSmem, st,
                      ctx->pdl, p));
   return HB200_OK;
 }

@@ -196,6 +196,14 @@ int hb_lmhead_mma_run(struct hb200_ctx* ctx, const void* d_table, int dtype, lon
                       const float* d_x, int M, const float* d_rms_gamma, float rms_eps,
                       float* d_logits, unsigned long long* d_keys, cudaStream_t st);
 
+// Layout of the context's device scratch (one stream at a time uses it; regions of ops that
+// never overlap in time may overlap in space):
+constexpr size_t kScratchBytes = (size_t)16 << 20;
+constexpr size_t kScratchActs = 0;                     // batched ternary: d[64], sumq[64], int8 tiles
+constexpr size_t kScratchGlu = (size_t)2 << 20;       // batched gate/up products before the GLU
+constexpr size_t kScratchLmSplit = (size_t)8 << 20;   // batched LM head: hi/lo activation tiles
+constexpr size_t kScratchSplitK = (size_t)10 << 20;   // batched ternary: split-K int32 partials
+
 struct hb200_ctx {
   int device;
   int sm_count;

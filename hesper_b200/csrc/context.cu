@@ -66,7 +66,7 @@ extern "C" int hb200_ctx_create(int device, hb200_ctx** out) {
   e = cudaMemset(c->d_status, 0, 256);
   if (e == cudaSuccess) e = cudaMalloc(&c->d_tickets, sizeof(int) * kCtxTickets);
   if (e == cudaSuccess) e = cudaMemset(c->d_tickets, 0, sizeof(int) * kCtxTickets);
-  c->scratch_bytes = (size_t)8 << 20;
+  c->scratch_bytes = kScratchBytes;
   if (e == cudaSuccess) e = cudaMalloc(&c->d_scratch, c->scratch_bytes);
   if (e != cudaSuccess) {
     cudaFree(c->d_status);

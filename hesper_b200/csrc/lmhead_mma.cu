@@ -364,14 +364,14 @@ EncodeTiledFn lm_tensor_map_encoder() {
 }  // namespace
 
 // Batched LM head (16 <= M <= 64, K a multiple of 64).  The split activations live in the
-// context scratch at kLmScratchOffset; keys are accumulated with atomicMax like the batch-1
+// context scratch; keys are accumulated with atomicMax like the batch-1
 // kernel does, so the caller's finishing kernel is shared.
 int hb_lmhead_mma_run(hb200_ctx* ctx, const void* d_table, int dtype, long V, int K,
                       const float* d_x, int M, const float* d_rms_gamma, float rms_eps,
                       float* d_logits, unsigned long long* d_keys, cudaStream_t st) {
-  constexpr size_t kLmScratchOffset = (size_t)6 << 20;
+  constexpr size_t kLmScratchOffset = kScratchLmSplit;
   const size_t xb_bytes = (size_t)(K / kLmKStep) * kLmBBytes;
-  HB_REQUIRE(kLmScratchOffset + xb_bytes <= ctx->scratch_bytes,
+  HB_REQUIRE(kLmScratchOffset + xb_bytes <= kScratchSplitK,
              "lmhead (batched): K=%d needs %zu bytes of activation scratch", K, xb_bytes);
   HB_REQUIRE(V < (1l << 31), "lmhead (batched): V too large");
   uint8_t* xb = static_cast<uint8_t*>(ctx->d_scratch) + kLmScratchOffset;
