@@ -294,7 +294,7 @@ def run_ours(args):
                                    "programmatic dependent launch between matvecs",
                        "pct_of_8TBs": value / world / 8000.0 * 100.0},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": args.traffic, "peak_source": peak_src,
+                         "frac": achieved / peak, "traffic": (None if args.traffic != args.traffic else args.traffic), "peak_source": peak_src,
                          "kernel": "kquant_kernel<12,RT,false>",
                          "algorithmic_bytes_per_launch": Q4K_BYTES,
                          "us_per_launch": per_launch * 1e6},
@@ -365,7 +365,54 @@ def run_extra(torch, ctx, st, hb, args):
         att[f"B{B}_L{L}"] = {"us": sec * 1e6, "GBs": B * (2048 * L + 12288) / sec / 1e9}
         del q, k, v
     out["cfg2_attention"] = att
+    out["batched_64_tokens"] = run_batched(torch, ctx, st, steps, warm)
     out["cfg3_bitnet2b_decode"] = run_bitnet_decode(torch, ctx, hb)
+    return out
+
+
+def run_batched(torch, ctx, st, steps, warm):
+    """The tensor-core paths at 64 tokens: ternary product (tcgen05 kind::i8, activation
+    quantiser included) and the LM head (tcgen05 kind::f16), cold rings."""
+    from hesper_b200 import BitLinear, formats, _lib
+    out = {}
+    rng = np.random.default_rng(3)
+    M = 64
+    sc = torch.tensor([0.05], device="cuda")
+    for K, N in ((2560, 6912), (6912, 2560)):
+        R = 64
+        base = torch.from_numpy(formats.i2s_pack(formats.random_ternary(rng, N, K))).cuda()
+        bl = [BitLinear(ctx, base if r == 0 else torch.roll(base, r * 640 * 3), sc, K, N)
+              for r in range(R)]
+        x = torch.randn(M, K, device="cuda")
+        y = torch.empty(M, N, device="cuda")
+
+        def pb():
+            for l in bl:
+                l.forward(x, out=y, stream=st)
+        sec, _ = time_graph(torch, st, pb, steps, warm)
+        t = sec / R
+        out[f"i2s_K{K}_N{N}"] = {"us": t * 1e6, "weight_GBs": N * K / 4 / t / 1e9,
+                                 "int8_TOPs": 2.0 * M * K * N / t / 1e12}
+        del bl, base
+    lib = _lib.load()
+    V, K = 128256, 2560
+    tabs = [(torch.randn(V, K, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(2)]
+    x = torch.randn(M, K, device="cuda")
+    arg = torch.zeros(M, dtype=torch.int32, device="cuda")
+    scr = torch.zeros(M, dtype=torch.int64, device="cuda")
+
+    def pl():
+        for t_ in tabs:
+            rc = lib.hb200_lmhead_argmax(ctx.handle, t_.data_ptr(), 0, V, K, x.data_ptr(), M, None,
+                                         0.0, None, arg.data_ptr(), scr.data_ptr(), None, None, 0,
+                                         st.cuda_stream)
+            assert rc == 0
+    sec, _ = time_graph(torch, st, pl, steps, warm)
+    t = sec / len(tabs)
+    peak = measured_peak()[0]
+    out["lmhead_V128256_K2560"] = {"us": t * 1e6, "table_GBs": V * K * 2 / t / 1e9,
+                                   "frac_of_hbm_peak": V * K * 2 / t / 1e9 / peak,
+                                   "bf16_TFLOPs": 2.0 * 2 * M * V * K / t / 1e12}
     return out
 
 
@@ -413,13 +460,14 @@ def run_tp_decode(torch, dist, ctx, hb, rank, world):
 
 def run_bitnet_decode(torch, ctx, hb):
     """BASELINE config 3: BitNet-b1.58-2B-shaped model, random-init, 2048-token random prompt
-    then 128 greedy tokens at batch 1 (graph replay); batch 64 with a short prompt."""
+    then 128 greedy tokens at batch 1 and at batch 64 (graph replay; the prompt is consumed
+    one position per step through the same decode path)."""
     from hesper_b200.models import BitNetShape, BitNetModel, random_bitnet_weights_device
     shape = BitNetShape.bitnet_2b(max_seq=2304)
     w = random_bitnet_weights_device(shape)
     out = {}
     peak = measured_peak()[0]
-    for B, P, n_new in ((1, 2048, 128), (64, 16, 32)):
+    for B, P, n_new in ((1, 2048, 128), (64, 2048, 128)):
         try:
             model = BitNetModel(ctx, shape, w, batch=B, max_new_tokens=n_new)
             prompt = np.random.default_rng(0).integers(0, shape.vocab, (B, P)).astype(np.int32)
@@ -449,8 +497,9 @@ def main():
     ap.add_argument("--ring", type=int, default=40, help="distinct weight matrices per pass")
     ap.add_argument("--no-extra", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--traffic", type=float, default=None,
-                    help="dram bytes per launch from an ncu capture, if known")
+    ap.add_argument("--traffic", type=float, default=14_790_000.0,
+                    help="dram bytes per launch of the Q4_K kernel from the committed ncu capture "
+                         "(profiles/kquant_q4k_K2560_N10240.md); null it with --traffic nan")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

@@ -6,6 +6,11 @@ under a few GB, so that a full-metric capture of one to three launches ends in a
   q80      ring of 8 Q8_0 matrices (223 MB), 3 passes
   i2s      ring of 40 ternary matrices K=2560 N=6912 (177 MB), 3 passes
   attn     decode attention B=16 L=4096, 8q/2kv heads, D=256 (268 MB of KV), 6 calls
+  i2s_mma  64-token ternary product on the tensor cores, ring of 40 matrices K=2560 N=6912
+           (177 MB), 2 passes
+  lmhead64 64-token LM head on the tensor cores, one bf16 table V=128256 K=2560 (657 MB), 3 calls
+  bitnet1 / bitnet64   BitNet-2B-shaped decode loop at batch 1 / 64: 2 prompt positions and
+           3 new tokens, launched one by one (no graph) so that a launch list sees each kernel
 """
 from __future__ import annotations
 
@@ -44,6 +49,40 @@ def main(name: str) -> None:
         for _ in range(3):
             for l in layers:
                 l.forward(x, out=y)
+    elif name == "i2s_mma":
+        K, N, R, M = 2560, 6912, 40, 64
+        base = torch.from_numpy(formats.i2s_pack(formats.random_ternary(rng, N, K))).cuda()
+        sc = torch.tensor([0.05], device="cuda")
+        layers = [hb.BitLinear(ctx, torch.roll(base, r * 640), sc, K, N) for r in range(R)]
+        x = torch.randn(M, K, device="cuda")
+        y = torch.empty(M, N, device="cuda")
+        torch.cuda.synchronize()
+        for _ in range(2):
+            for l in layers:
+                l.forward(x, out=y)
+    elif name == "lmhead64":
+        from hesper_b200 import _lib
+        lib = _lib.load()
+        V, K, M = 128256, 2560, 64
+        table = (torch.randn(V, K, device="cuda") * 0.02).to(torch.bfloat16)
+        x = torch.randn(M, K, device="cuda")
+        arg = torch.zeros(M, dtype=torch.int32, device="cuda")
+        scr = torch.zeros(M, dtype=torch.int64, device="cuda")
+        torch.cuda.synchronize()
+        for _ in range(3):
+            rc = lib.hb200_lmhead_argmax(ctx.handle, table.data_ptr(), 0, V, K, x.data_ptr(), M,
+                                         None, 0.0, None, arg.data_ptr(), scr.data_ptr(), None,
+                                         None, 0, None)
+            assert rc == 0
+    elif name in ("bitnet1", "bitnet64"):
+        from hesper_b200.models import BitNetModel, BitNetShape, random_bitnet_weights_device
+        B = 1 if name == "bitnet1" else 64
+        shape = BitNetShape.bitnet_2b(max_seq=2304)
+        w = random_bitnet_weights_device(shape)
+        m = BitNetModel(ctx, shape, w, batch=B, max_new_tokens=8)
+        prompt = rng.integers(0, shape.vocab, (B, 2)).astype(np.int32)
+        m.generate(prompt, 3, use_graph=False)
+        m.close()
     elif name == "attn":
         B, H, Hkv, D, L = 16, 8, 2, 256, 4096
         q = torch.randn(B, H, D, device="cuda").half()

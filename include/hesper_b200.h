@@ -55,8 +55,12 @@ typedef void *hb200_stream;
 
 /* Replaces CUDAContext.init (Hesper/Backend/CUDA.lean:46; native/cuda_bridge.cpp:78-82)
  * for this path only: binds to `device` (its primary context), reads the SM
- * count, raises the kernels' dynamic shared-memory limits and allocates one
- * 256-byte device status block.  No other allocation happens later. */
+ * count, raises the kernels' dynamic shared-memory limits and allocates what the
+ * operators need later: a 256-byte status block, 4096 arrival counters and 16 MB of
+ * scratch (activation tiles, split-K partials of the batched paths).  No operator
+ * allocates afterwards; a context serves one stream at a time.
+ * Environment: HB200_NO_PDL=1 launches without programmatic dependent launch,
+ * HB200_NO_MMA=1 keeps the batched (>= 16 token) operators off the tensor-core kernels. */
 int hb200_ctx_create(int device, hb200_ctx **out);
 int hb200_ctx_destroy(hb200_ctx *ctx);
 
@@ -115,7 +119,9 @@ typedef struct hb200_bitlinear_seg {
  *   d_x          [M][K] f32 activations
  *   d_rms_gamma  nullable [K]; when set x is replaced by RMSNorm(x)*gamma, eps = rms_eps
  *   d_act_scale  nullable [M]; receives d[m]
- * K must be a multiple of 128, 1 <= M <= 64. */
+ * K must be a multiple of 128, 1 <= M <= 64.  From 16 tokens on (and K <= 12288) the
+ * product runs on the tensor cores (tcgen05 kind::i8, accumulators in tensor memory,
+ * the M>1 role of Hesper/Layers/BitLinear.lean:122,869,994) with identical results. */
 int hb200_bitlinear_forward(hb200_ctx *ctx, const void *d_packed, const float *d_scale,
                             int K, int N, const float *d_x, int M,
                             const float *d_rms_gamma, float rms_eps,
@@ -260,6 +266,9 @@ int hb200_argmax(hb200_ctx *ctx, const float *d_logits, long V, int M, int32_t *
 /* LM head over a 16-bit table [V][K] (dtype 0 = bf16, 1 = f16) with the final RMSNorm
  * fused in front (d_rms_gamma nullable) and the greedy argmax fused behind.
  * Replaces executeMatMulTransposeF16Shared + gpuArgmax (Hesper/Models/BitNet.lean:437-521).
+ * 1 <= M <= 64; from 16 tokens on (K a multiple of 64) the table is streamed once through
+ * the tensor cores (tcgen05 kind::f16, activations split into two 16-bit terms so that
+ * f32-activation accuracy is kept).
  *   d_logits   nullable [M][V]
  *   d_argmax   [M] token ids
  *   d_scratch  hb200_lmhead_scratch_bytes(M) bytes, zero before the first call (the
