@@ -431,7 +431,7 @@ def run_tp_decode(torch, dist, ctx, hb, rank, world):
         # algorithmic bytes per token per the whole job: Q4_K layers + LM head + bf16 embedding
         # row + f16 KV (35 sliding-window layers x 512 positions, 7 global layers x ctx)
         wbytes = 42 * 51_609_600 + 377_487_360
-        for B, steps in ((1, 64), (32, 16)):
+        for B, steps in ((1, 64), (32, 16), (256, 8)):
             model = tp.GemmaModel(ctx, S, shard, plan, comm, batch=B, max_new_tokens=steps)
             model.set_position(8000)
             model.generate(None, 4, use_graph=True)       # warm-up (also captures once)

@@ -198,11 +198,19 @@ int hb_lmhead_mma_run(struct hb200_ctx* ctx, const void* d_table, int dtype, lon
 
 // Layout of the context's device scratch (one stream at a time uses it; regions of ops that
 // never overlap in time may overlap in space):
-constexpr size_t kScratchBytes = (size_t)16 << 20;
+constexpr size_t kScratchBytes = (size_t)20 << 20;
 constexpr size_t kScratchActs = 0;                     // batched ternary: d[64], sumq[64], int8 tiles
 constexpr size_t kScratchGlu = (size_t)2 << 20;       // batched gate/up products before the GLU
-constexpr size_t kScratchLmSplit = (size_t)8 << 20;   // batched LM head: hi/lo activation tiles
-constexpr size_t kScratchSplitK = (size_t)10 << 20;   // batched ternary: split-K int32 partials
+constexpr size_t kScratchLmSplit = (size_t)8 << 20;   // 16-bit products: hi/lo activation tiles
+constexpr size_t kScratchSplitK = (size_t)12 << 20;   // batched ternary: split-K int32 partials
+
+// the two halves of it, also used by the batched k-quant path (weights dequantised to f16)
+int hb_gemm16_split(struct hb200_ctx* ctx, int dtype, int K, const float* d_x, int M,
+                    const float* d_rms_gamma, float rms_eps, cudaStream_t st);
+int hb_gemm16_mma(struct hb200_ctx* ctx, const void* d_table, int dtype, long V, int K, int M,
+                  float* d_y, const float* d_residual, long ldy, unsigned long long* d_keys,
+                  cudaStream_t st);
+constexpr size_t kArenaBytes = (size_t)64 << 20;  // f16 weights of one batched k-quant product
 
 struct hb200_ctx {
   int device;
@@ -210,6 +218,7 @@ struct hb200_ctx {
   int smem_optin;      // max dynamic shared memory per block
   uint32_t* d_status;  // 64 words
   int* d_tickets;      // kCtxTickets zero-initialised arrival counters
+  void* d_arena;       // kArenaBytes, batched k-quant path
   void* d_scratch;     // batched paths: quantised activations, gate/up temporaries
   size_t scratch_bytes;
   bool pdl;            // use programmatic dependent launch

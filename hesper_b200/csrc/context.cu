@@ -49,6 +49,7 @@ extern "C" int hb200_ctx_create(int device, hb200_ctx** out) {
   hb200_ctx* c = new hb200_ctx();
   c->d_tickets = nullptr;
   c->d_scratch = nullptr;
+  c->d_arena = nullptr;
   c->device = device;
   c->sm_count = prop.multiProcessorCount;
   c->smem_optin = (int)prop.sharedMemPerBlockOptin;
@@ -68,10 +69,12 @@ extern "C" int hb200_ctx_create(int device, hb200_ctx** out) {
   if (e == cudaSuccess) e = cudaMemset(c->d_tickets, 0, sizeof(int) * kCtxTickets);
   c->scratch_bytes = kScratchBytes;
   if (e == cudaSuccess) e = cudaMalloc(&c->d_scratch, c->scratch_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_arena, kArenaBytes);
   if (e != cudaSuccess) {
     cudaFree(c->d_status);
     cudaFree(c->d_tickets);
     cudaFree(c->d_scratch);
+    cudaFree(c->d_arena);
     delete c;
     return cuda_fail(e, "context buffers");
   }
@@ -84,6 +87,7 @@ extern "C" int hb200_ctx_destroy(hb200_ctx* ctx) {
   cudaFree(ctx->d_status);
   cudaFree(ctx->d_tickets);
   cudaFree(ctx->d_scratch);
+  cudaFree(ctx->d_arena);
   delete ctx;
   return HB200_OK;
 }

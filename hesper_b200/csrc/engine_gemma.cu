@@ -159,7 +159,7 @@ extern "C" int hb200_gemma_create(hb200_ctx* ctx, hb200_tp* tp, const hb200_gemm
                                   int max_new_tokens, hb200_gemma** out) {
   HB_REQUIRE(ctx && cfg && layers && d_embed_bf16 && d_lm_head_q4k && d_final_norm && out,
              "gemma_create: null argument");
-  HB_REQUIRE(batch >= 1 && batch <= 64, "gemma_create: batch %d outside 1..64", batch);
+  HB_REQUIRE(batch >= 1 && batch <= 256, "gemma_create: batch %d outside 1..256", batch);
   HB_REQUIRE(cfg->hidden % 256 == 0 && cfg->local_ffn % 256 == 0 &&
                  (cfg->local_q_heads * cfg->head_dim) % 256 == 0 && cfg->local_kv_heads >= 1 &&
                  cfg->local_q_heads % cfg->local_kv_heads == 0,

@@ -44,6 +44,7 @@ __device__ __forceinline__ unsigned long long kq_gtimer() {
 #endif
 
 constexpr int kKQMaxSeg = 4;
+constexpr int kKQBatchedFrom = 16;  // tokens from which the tensor-core path takes over
 constexpr int kKQThreads = 384;
 constexpr int kKQWarps = kKQThreads / 32;
 
@@ -449,6 +450,102 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
   HB_STAMP(8);
 }
 
+// ---- batched path: dequantise to f16, then the 16-bit tensor-core product ---------------
+//
+// From 16 tokens on the product is a real contraction.  The weights of one product (or a
+// row chunk of it) are dequantised once into a 64 MB f16 arena of the context -- it stays
+// in the 126 MB L2 -- and multiplied by the tensor-core kernel that also serves the LM head
+// (tcgen05 kind::f16, activations split into hi + lo f16 so their rounding drops out).
+// f16 weights carry 2^-11 relative rounding each; the measured output error is ~3e-4 of
+// max|y|, inside the 1e-3 bar of this path.  One thread per 8 weights, 16-byte stores.
+template <int FMT>
+__global__ void __launch_bounds__(256) kq_dequant_kernel(const uint8_t* __restrict__ blocks,
+                                                         int K, long rows, int rowbytes,
+                                                         __half* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();  // the arena may still be read by the product before this one
+  const long gpr = K >> 3;  // 8-weight groups per row
+  const long idx = (long)blockIdx.x * 256 + threadIdx.x;
+  if (idx >= rows * gpr) return;
+  const long row = idx / gpr;
+  const int g = (int)(idx - row * gpr);
+  float w[8];
+  if (FMT == 12) {
+    // super-block: f16 d, f16 dmin, 12 bytes of 6-bit scales/mins, 128 bytes of nibbles;
+    // sub-blocks 2c and 2c+1 are the low and high nibbles of bytes 32c..32c+31
+    // (Hesper/Quantization/Q4_K_M.lean:13-52,120-144)
+    const uint8_t* blk = blocks + (size_t)row * rowbytes + (size_t)(g >> 5) * 144;
+    const int j = g & 31, sub = j >> 2, part = j & 3;
+    const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(blk));
+    const uint8_t* sc = blk + 4;
+    int s6, m6;
+    if (sub < 4) {
+      s6 = sc[sub] & 63;
+      m6 = sc[sub + 4] & 63;
+    } else {
+      s6 = (sc[sub + 4] & 0xF) | ((sc[sub - 4] >> 6) << 4);
+      m6 = (sc[sub + 4] >> 4) | ((sc[sub] >> 6) << 4);
+    }
+    const float ds = dd.x * (float)s6, dm = dd.y * (float)m6;
+    const uint2 q = *reinterpret_cast<const uint2*>(blk + 16 + 32 * (sub >> 1) + 8 * part);
+    const uint32_t qq[2] = {q.x, q.y};
+    const int sh = (sub & 1) * 4;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      w[i] = fmaf(ds, (float)((qq[i >> 2] >> (8 * (i & 3) + sh)) & 0xF), -dm);
+  } else {
+    // block: f16 d, 32 int8 (Hesper/Layers/Linear.lean:6207-6223); 2-byte aligned only
+    const uint8_t* blk = blocks + (size_t)row * rowbytes + (size_t)(g >> 2) * 34;
+    const float d = __half2float(*reinterpret_cast<const __half*>(blk));
+    const uint16_t* q16 = reinterpret_cast<const uint16_t*>(blk + 2 + 8 * (g & 3));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint16_t v = q16[i];
+      w[2 * i] = d * (float)(int8_t)(v & 0xff);
+      w[2 * i + 1] = d * (float)(int8_t)(v >> 8);
+    }
+  }
+  __half2 h[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(w[2 * i], w[2 * i + 1]);
+  *reinterpret_cast<uint4*>(out + (size_t)row * K + (size_t)g * 8) =
+      *reinterpret_cast<const uint4*>(h);
+}
+
+// y[M][N] = W x (+ residual) for one tensor, any M >= 1: row chunks that fit the arena,
+// token chunks of 64.
+static int kq_batched_one(hb200_ctx* ctx, int fmt, const uint8_t* blocks, int K, long N,
+                          const float* d_x, int M, const float* gamma, float eps,
+                          const float* residual, float* y, cudaStream_t st) {
+  const int rowbytes = fmt == HB200_FMT_Q4_K ? K / 256 * 144 : K / 32 * 34;
+  long chunk = (long)(kArenaBytes / ((size_t)K * 2)) / 128 * 128;
+  HB_REQUIRE(chunk >= 128, "kquant (batched): K=%d too large for the f16 arena", K);
+  __half* arena = static_cast<__half*>(ctx->d_arena);
+  for (long r0 = 0; r0 < N; r0 += chunk) {
+    const long nr = N - r0 < chunk ? N - r0 : chunk;
+    const long threads = nr * (K / 8);
+    const unsigned grid = (unsigned)((threads + 255) / 256);
+    const uint8_t* src = blocks + (size_t)r0 * rowbytes;
+    if (fmt == HB200_FMT_Q4_K)
+      HB_CUDA(launch_pdl(kq_dequant_kernel<12>, dim3(grid), dim3(256), 0, st, ctx->pdl, src, K, nr,
+                         rowbytes, arena));
+    else
+      HB_CUDA(launch_pdl(kq_dequant_kernel<8>, dim3(grid), dim3(256), 0, st, ctx->pdl, src, K, nr,
+                         rowbytes, arena));
+    for (int m0 = 0; m0 < M; m0 += 64) {
+      const int mc = M - m0 < 64 ? M - m0 : 64;
+      int rc = hb_gemm16_split(ctx, 1, K, d_x + (size_t)m0 * K, mc, gamma, eps, st);
+      if (rc != HB200_OK) return rc;
+      // the product addresses its output as [m][row] with row stride 1 and token stride N:
+      // a row chunk is a column offset into the caller's [M][N] arrays
+      rc = hb_gemm16_mma(ctx, arena, 1, nr, K, mc, y + (size_t)m0 * N + r0,
+                         residual ? residual + (size_t)m0 * N + r0 : nullptr, N, nullptr, st);
+      if (rc != HB200_OK) return rc;
+    }
+  }
+  return HB200_OK;
+}
+
 // ---- host side --------------------------------------------------------------------
 
 static size_t kq_smem_bytes(int nslots, int rows, int K, int rowbytes) {
@@ -534,7 +631,7 @@ static int kq_check(hb200_ctx* ctx, int fmt, int K, int M, const float* d_x) {
   HB_REQUIRE(fmt == HB200_FMT_Q4_K || fmt == HB200_FMT_Q8_0,
              "kquant: format id %d is neither Q4_K (12) nor Q8_0 (8)", fmt);
   HB_REQUIRE(K > 0 && K % 256 == 0, "kquant: K=%d must be a positive multiple of 256", K);
-  HB_REQUIRE(M >= 1 && M <= 64, "kquant: M=%d outside 1..64", M);
+  HB_REQUIRE(M >= 1 && M <= 4096, "kquant: M=%d outside 1..4096", M);
   HB_REQUIRE(d_x != nullptr && (reinterpret_cast<uintptr_t>(d_x) & 15) == 0,
              "kquant: x must be non-null and 16-byte aligned");
   return HB200_OK;
@@ -562,6 +659,16 @@ extern "C" int hb200_kquant_forward_multi(hb200_ctx* ctx, int fmt, const hb200_k
                "kquant: segment %d blocks must be 16-byte aligned", s);
     rows += segs[s].N;
   }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M >= kKQBatchedFrom && !ctx->no_mma) {  // a real contraction: tensor-core path
+    for (int s = 0; s < nseg; ++s) {
+      rc = kq_batched_one(ctx, fmt, static_cast<const uint8_t*>(segs[s].d_blocks), K, segs[s].N,
+                          d_x, M, d_rms_gamma, rms_eps, segs[s].d_residual, segs[s].d_y, st);
+      if (rc != HB200_OK) return rc;
+    }
+    return HB200_OK;
+  }
+  HB_REQUIRE(M <= 64, "kquant: M=%d needs the batched path (HB200_NO_MMA is set)", M);
   const int rowbytes = kq_rowbytes(fmt, K);
   KQPlan plan;
   if (!kq_plan(ctx, rows, K, rowbytes, false, &plan)) {
@@ -585,7 +692,6 @@ extern "C" int hb200_kquant_forward_multi(hb200_ctx* ctx, int fmt, const hb200_k
   p.gamma = d_rms_gamma;
   p.eps = rms_eps;
   p.status = ctx->d_status;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   return fmt == HB200_FMT_Q4_K ? kq_dispatch<12, false>(ctx, p, plan, st)
                                : kq_dispatch<8, false>(ctx, p, plan, st);
 }
@@ -608,6 +714,26 @@ extern "C" int hb200_kquant_gateup_gelu(hb200_ctx* ctx, int fmt, const void* d_b
   HB_REQUIRE(((reinterpret_cast<uintptr_t>(d_blocks_gate) |
                reinterpret_cast<uintptr_t>(d_blocks_up)) & 15) == 0,
              "kquant gate/up: blocks must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M >= kKQBatchedFrom && !ctx->no_mma &&
+      kScratchGlu + (size_t)2 * 64 * N * sizeof(float) <= kScratchLmSplit) {
+    // both products on the tensor cores into scratch (64 tokens at a time), then the GLU
+    float* g = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->d_scratch) + kScratchGlu);
+    for (int m0 = 0; m0 < M; m0 += 64) {
+      const int mc = M - m0 < 64 ? M - m0 : 64;
+      float* u = g + (size_t)mc * N;
+      rc = kq_batched_one(ctx, fmt, static_cast<const uint8_t*>(d_blocks_gate), K, N,
+                          d_x + (size_t)m0 * K, mc, d_rms_gamma, rms_eps, nullptr, g, st);
+      if (rc == HB200_OK)
+        rc = kq_batched_one(ctx, fmt, static_cast<const uint8_t*>(d_blocks_up), K, N,
+                            d_x + (size_t)m0 * K, mc, d_rms_gamma, rms_eps, nullptr, u, st);
+      if (rc == HB200_OK)
+        rc = hb200_gelu_mul(ctx, g, u, (long)mc * N, d_y + (size_t)m0 * N, stream);
+      if (rc != HB200_OK) return rc;
+    }
+    return HB200_OK;
+  }
+  HB_REQUIRE(M <= 64, "kquant gate/up: M=%d needs the batched path", M);
   const int rowbytes = kq_rowbytes(fmt, K);
   KQPlan plan;
   if (!kq_plan(ctx, N, K, rowbytes, true, &plan)) {
@@ -627,7 +753,6 @@ extern "C" int hb200_kquant_gateup_gelu(hb200_ctx* ctx, int fmt, const void* d_b
   p.gamma = d_rms_gamma;
   p.eps = rms_eps;
   p.status = ctx->d_status;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   return fmt == HB200_FMT_Q4_K ? kq_dispatch<12, true>(ctx, p, plan, st)
                                : kq_dispatch<8, true>(ctx, p, plan, st);
 }

@@ -58,8 +58,10 @@ struct LmMmaParams {
   CUtensorMap tmap;    // table as [V rows][K elements of 2 bytes], boxes of 128 rows x 64
   const uint8_t* xb;
   float* logits;       // nullable [M][V]
-  unsigned long long* keys;  // [M]
+  const float* residual;  // nullable [M][V], added to what is stored in `logits`
+  unsigned long long* keys;  // nullable [M]
   long V;
+  long ldy;            // token stride of logits / residual (>= V)
   int K, M;
   uint32_t idesc;
   uint32_t* status;
@@ -302,7 +304,11 @@ __global__ void __launch_bounds__(kLmThreads, 2)
       for (int t = 0; t < 32; ++t) {
         const int m = half * 32 + t;
         const float v = __fadd_rn(__uint_as_float(hi[t]), __uint_as_float(lo[t]));
-        if (m < p.M && row_ok && p.logits && ok) p.logits[(size_t)m * p.V + row] = v;
+        if (m < p.M && row_ok && p.logits && ok) {
+          const size_t o = (size_t)m * p.ldy + (size_t)(row);
+          p.logits[o] = p.residual ? __fadd_rn(v, p.residual[o]) : v;
+        }
+        if (!p.keys) continue;  // plain product: no argmax
         uint32_t u = __float_as_uint(v);
         u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);  // monotone map float -> uint
         if (!(v == v) || !row_ok) u = 0u;                  // NaN and padding rows never win
@@ -363,24 +369,29 @@ EncodeTiledFn lm_tensor_map_encoder() {
 }
 }  // namespace
 
-// Batched LM head (16 <= M <= 64, K a multiple of 64).  The split activations live in the
-// context scratch; keys are accumulated with atomicMax like the batch-1
-// kernel does, so the caller's finishing kernel is shared.
-int hb_lmhead_mma_run(hb200_ctx* ctx, const void* d_table, int dtype, long V, int K,
-                      const float* d_x, int M, const float* d_rms_gamma, float rms_eps,
-                      float* d_logits, unsigned long long* d_keys, cudaStream_t st) {
-  constexpr size_t kLmScratchOffset = kScratchLmSplit;
+// x[M][K] (M <= 64) -> hi/lo 16-bit operand blocks in the context scratch, optional RMSNorm.
+int hb_gemm16_split(hb200_ctx* ctx, int dtype, int K, const float* d_x, int M,
+                    const float* d_rms_gamma, float rms_eps, cudaStream_t st) {
   const size_t xb_bytes = (size_t)(K / kLmKStep) * kLmBBytes;
-  HB_REQUIRE(kLmScratchOffset + xb_bytes <= kScratchSplitK,
-             "lmhead (batched): K=%d needs %zu bytes of activation scratch", K, xb_bytes);
-  HB_REQUIRE(V < (1l << 31), "lmhead (batched): V too large");
-  uint8_t* xb = static_cast<uint8_t*>(ctx->d_scratch) + kLmScratchOffset;
+  HB_REQUIRE(kScratchLmSplit + xb_bytes <= kScratchSplitK,
+             "batched 16-bit product: K=%d needs %zu bytes of activation scratch", K, xb_bytes);
+  uint8_t* xb = static_cast<uint8_t*>(ctx->d_scratch) + kScratchLmSplit;
   LmSplitParams sp = {d_x, d_rms_gamma, rms_eps, K, M, dtype, xb};
   HB_CUDA(launch_pdl(lm_split_kernel, dim3(kLmTokens), dim3(256), 0, st, ctx->pdl, sp));
+  return HB200_OK;
+}
 
+// y[m*ldy + v] = sum_k table[v][k] * x[m][k] (+ residual[m*ldy + v]) for the activations
+// staged by hb_gemm16_split; d_y nullable, d_keys nullable (argmax keys, atomicMax like the batch-1
+// LM head so that the finishing kernel is shared).
+int hb_gemm16_mma(hb200_ctx* ctx, const void* d_table, int dtype, long V, int K, int M,
+                  float* d_y, const float* d_residual, long ldy, unsigned long long* d_keys,
+                  cudaStream_t st) {
+  HB_REQUIRE(V >= 1 && V < (1l << 31), "batched 16-bit product: bad row count");
+  uint8_t* xb = static_cast<uint8_t*>(ctx->d_scratch) + kScratchLmSplit;
   LmMmaParams p = {};
   EncodeTiledFn encode = lm_tensor_map_encoder();
-  HB_REQUIRE(encode != nullptr, "lmhead (batched): the driver has no cuTensorMapEncodeTiled");
+  HB_REQUIRE(encode != nullptr, "batched 16-bit product: the driver has no cuTensorMapEncodeTiled");
   const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)V};
   const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
   const cuuint32_t box[2] = {(cuuint32_t)kLmKStep, (cuuint32_t)kLmRows};
@@ -389,11 +400,14 @@ int hb_lmhead_mma_run(hb200_ctx* ctx, const void* d_table, int dtype, long V, in
       encode(&p.tmap, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(d_table), dims, strides,
              box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  HB_REQUIRE(rc == CUDA_SUCCESS, "lmhead (batched): cuTensorMapEncodeTiled failed (%d)", (int)rc);
+  HB_REQUIRE(rc == CUDA_SUCCESS, "batched 16-bit product: cuTensorMapEncodeTiled failed (%d)",
+             (int)rc);
   p.xb = xb;
-  p.logits = d_logits;
+  p.logits = d_y;
+  p.residual = d_residual;
   p.keys = d_keys;
   p.V = V;
+  p.ldy = ldy;
   p.K = K;
   p.M = M;
   // instruction descriptor of kind::f16: D = f32, A and B of the table's type, both K-major
@@ -411,4 +425,13 @@ int hb_lmhead_mma_run(hb200_ctx* ctx, const void* d_table, int dtype, long V, in
   HB_CUDA(launch_pdl(lmhead_mma_kernel, dim3((unsigned)ntiles), dim3(kLmThreads), (size_t)kLmSmem,
                      st, ctx->pdl, p));
   return HB200_OK;
+}
+
+// Batched LM head (16 <= M <= 64, K a multiple of 64).
+int hb_lmhead_mma_run(hb200_ctx* ctx, const void* d_table, int dtype, long V, int K,
+                      const float* d_x, int M, const float* d_rms_gamma, float rms_eps,
+                      float* d_logits, unsigned long long* d_keys, cudaStream_t st) {
+  const int rc = hb_gemm16_split(ctx, dtype, K, d_x, M, d_rms_gamma, rms_eps, st);
+  if (rc != HB200_OK) return rc;
+  return hb_gemm16_mma(ctx, d_table, dtype, V, K, M, d_logits, nullptr, V, d_keys, st);
 }

@@ -98,6 +98,60 @@ def test_fused_qkv_multi(ctx, oracle):
 
 
 @pytest.mark.parametrize("fmt", [12, 8])
+@pytest.mark.parametrize("K,N,M", [(2560, 10240, 16), (2560, 300, 33), (10240, 2560, 64),
+                                   (256, 1, 17), (512, 129, 100), (2560, 2048, 256)])
+def test_batched_tensor_core_path(ctx, oracle, fmt, K, N, M):
+    """16 or more tokens: weights dequantised to f16 into the context's arena, product on
+    tcgen05 (kind::f16) with the activations split hi + lo.  Same 1e-3 bar; the f16 rounding
+    of the weights puts this path near 3e-4."""
+    rng = np.random.default_rng(K + N + M + fmt)
+    blocks = formats.random_kquant(rng, fmt, N, K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    gamma = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    res = rng.standard_normal((M, N)).astype(np.float32)
+    layer = LinearLayer.create_from_bytes(ctx, blocks, fmt, K, N)
+    rows = sorted(set([0, M // 2, M - 1]))  # the f64 oracle is slow: check three tokens
+    y = layer.forward(_dev(x), residual=_dev(res))
+    ctx.check()
+    ref = oracle.kquant_matvec(fmt, blocks, K, N, x[rows], residual=res[rows])
+    _check(y[rows], ref)
+    xn = np.stack([oracle.rmsnorm_f64(x[m], gamma, 1e-6) for m in rows]).astype(np.float32)
+    y = layer.forward(_dev(x), rms_gamma=_dev(gamma), eps=1e-6)
+    ctx.check()
+    _check(y[rows], oracle.kquant_matvec(fmt, blocks, K, N, xn))
+
+
+def test_batched_row_chunks_of_the_arena(ctx, oracle):
+    # 2560 x 16384 f16 = 80 MB: more than the 64 MB arena, so two row chunks
+    K, N, M = 2560, 16384, 20
+    rng = np.random.default_rng(77)
+    blocks = formats.random_q4k(rng, N, K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    y = LinearLayer.create_from_bytes(ctx, blocks, 12, K, N).forward(_dev(x))
+    ctx.check()
+    _check(y[[0, 19]], oracle.q4k_matvec(blocks, K, N, x[[0, 19]]))
+
+
+@pytest.mark.parametrize("M", [16, 70])
+def test_batched_gate_up_and_multi(ctx, oracle, M):
+    K, N = 2560, 1000
+    rng = np.random.default_rng(M)
+    bg = formats.random_q4k(rng, N, K)
+    bu = formats.random_q4k(rng, N, K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    g = LinearLayer.create_from_bytes(ctx, bg, 12, K, N)
+    u = LinearLayer.create_from_bytes(ctx, bu, 12, K, N)
+    y = LinearLayer.forward_fused_gate_up(g, u, _dev(x))
+    ctx.check()
+    rows = [0, M - 1]
+    _check(y[rows], oracle.kquant_gateup_gelu(bg, bu, 12, K, N, x[rows]), tol=2e-3)
+    ys = LinearLayer.forward_multi([g, u], _dev(x))
+    ctx.check()
+    _check(ys[0][rows], oracle.q4k_matvec(bg, K, N, x[rows]))
+    _check(ys[1][rows], oracle.q4k_matvec(bu, K, N, x[rows]))
+
+
+@pytest.mark.parametrize("fmt", [12, 8])
 def test_linearity_full_size(ctx, fmt):
     """Size-independent property at the benchmark shape: y(a*x) = a*y(x) for a power of two
     (the block quantiser scales exactly), and zero input gives zero output."""
