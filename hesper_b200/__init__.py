@@ -8,7 +8,7 @@ flash-attention decode); it only marshals device pointers into that ABI.
 from ._lib import HesperB200Error, load, LIB_PATH, FMT_Q4_K, FMT_Q8_0, FMT_I2_S  # noqa: F401
 from .layers import (  # noqa: F401
     Context, BitLinear, LinearLayer, QuantFormat,
-    execute_flash_attention_v11, flash_attention_workspace,
+    execute_flash_attention_v11, flash_attention_workspace, flash_attention_prefill,
 )
 
 from .models import BitNetModel, BitNetShape, random_bitnet_weights  # noqa: F401

@@ -111,6 +111,9 @@ SIGNATURES = {
     "hb200_gemma_tokens": (_vp, [_vp]),
     "hb200_gemma_generate": (_i, [_vp, _vp, _i, _i, _i, _vp, C.POINTER(_f), C.POINTER(_f), _vp]),
     "hb200_attn_decode": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp, _vp]),
+    "hb200_attn_prefill_workspace_bytes": (_sz, [_vp, _i, _i, _i, _i, _i, _i]),
+    "hb200_attn_prefill": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp, _vp]),
+    "hb200_rope_kv_write_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
 }
 
 _lib = None

@@ -55,6 +55,7 @@ struct AttnParams {
   float* part_meta;  // [B][Hkv][nsplit][8][2]  (max in the exp2 domain, sum)
   int q_is_f16;
   int B, H, Hkv, G, max_seq, window, nsplit;
+  int T;             // query tokens per sequence (1 = decode); B counts query tokens, B/T caches
   float scale_log2;  // scale * log2(e)
   int* tickets;      // nullable: per (sequence, kv head) arrival counters, zero between calls
 };
@@ -72,6 +73,15 @@ __device__ unsigned long long g_attn_stamps[16];
 #else
 #define AT_STAMP(i) ((void)0)
 #endif
+
+// Query token b of a launch with T tokens per sequence: its cache index and how many
+// positions it sees (causal: token t of the T appended ones sees all but the T-1-t last).
+__device__ __forceinline__ int attn_visible_len(const AttnParams& p, int b, int& cache) {
+  cache = b / p.T;
+  const int t = b - cache * p.T;
+  const int len = min(max(p.seqlens[cache], 0), p.max_seq) - (p.T - 1 - t);
+  return max(len, 0);
+}
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
   const uint32_t n = valid ? 16u : 0u;  // src-size 0: the 16 bytes are zero-filled
@@ -153,7 +163,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __gr
   AT_STAMP(1);
 
   // a length outside [0, max_seq] can only come from a corrupt input: clamp, never overrun
-  const int len = min(max(p.seqlens[b], 0), p.max_seq);
+  int cb;  // which sequence's cache
+  const int len = attn_visible_len(p, b, cb);
   int start = 0;
   if (p.window > 0 && len > p.window) start = len - p.window;
   AT_STAMP(2);
@@ -164,8 +175,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __gr
   const int c_begin = split * cps;
   const int c_end = min(nch, c_begin + cps);
 
-  const __half* kbase = p.k + ((size_t)b * p.Hkv + kvh) * (size_t)p.max_seq * D;
-  const __half* vbase = p.v + ((size_t)b * p.Hkv + kvh) * (size_t)p.max_seq * D;
+  const __half* kbase = p.k + ((size_t)cb * p.Hkv + kvh) * (size_t)p.max_seq * D;
+  const __half* vbase = p.v + ((size_t)cb * p.Hkv + kvh) * (size_t)p.max_seq * D;
 
   // chunk c -> stage: rows of 16 positions, 16-byte units XOR-swizzled by (row & 7)
   auto issue = [&](int c, int st) {
@@ -465,7 +476,8 @@ __global__ void attn_combine_kernel(const __grid_constant__ AttnParams p, int D)
   const size_t base = ((size_t)b * p.Hkv + kvh) * p.nsplit;
   // the same active-split count as the main kernel derived; a single active split wrote
   // its result straight to `out`
-  const int len = min(max(p.seqlens[b], 0), p.max_seq);
+  int cb;
+  const int len = attn_visible_len(p, b, cb);
   int start = 0;
   if (p.window > 0 && len > p.window) start = len - p.window;
   int cps;
@@ -524,7 +536,8 @@ __global__ void __launch_bounds__(32) attn_exact_kernel(const __grid_constant__ 
   const int lane = threadIdx.x;
   const int h = blockIdx.x % p.H, b = blockIdx.x / p.H;
   const int kvh = h / p.G;
-  const int len = min(max(p.seqlens[b], 0), p.max_seq);
+  int cb;
+  const int len = attn_visible_len(p, b, cb);
   int start = 0;
   if (p.window > 0 && len > p.window) start = len - p.window;
   float q[DL], acc[DL];
@@ -535,8 +548,8 @@ __global__ void __launch_bounds__(32) attn_exact_kernel(const __grid_constant__ 
                       : reinterpret_cast<const float*>(p.q)[qi];
     acc[j] = 0.f;
   }
-  const __half* kb = p.k + ((size_t)b * p.Hkv + kvh) * (size_t)p.max_seq * D + lane * DL;
-  const __half* vb = p.v + ((size_t)b * p.Hkv + kvh) * (size_t)p.max_seq * D + lane * DL;
+  const __half* kb = p.k + ((size_t)cb * p.Hkv + kvh) * (size_t)p.max_seq * D + lane * DL;
+  const __half* vb = p.v + ((size_t)cb * p.Hkv + kvh) * (size_t)p.max_seq * D + lane * DL;
   float m = -CUDART_INF_F, l = 0.f;
   for (int s = start; s < len; ++s) {
     float part = 0.f;
@@ -610,12 +623,16 @@ extern "C" size_t hb200_attn_workspace_bytes(const hb200_ctx* ctx, int B, int H,
   return (size_t)B * Hkv * ns * 8 * ((size_t)D + 2) * sizeof(float) + 256;
 }
 
-extern "C" int hb200_attn_decode(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d_k,
-                                 const void* d_v, const int32_t* d_seqlens, int B, int H, int Hkv,
-                                 int D, int max_seq, int window, float scale, void* d_workspace,
-                                 size_t workspace_bytes, float* d_out, hb200_stream stream) {
+// Decode (T = 1) and causal prefill (T > 1) share everything: a prefill token is a query with
+// its own visible length over its sequence's cache.  nseq sequences, T query tokens each.
+static int attn_run(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d_k,
+                    const void* d_v, const int32_t* d_seqlens, int nseq, int T, int H, int Hkv,
+                    int D, int max_seq, int window, float scale, void* d_workspace,
+                    size_t workspace_bytes, float* d_out, hb200_stream stream) {
   HB_REQUIRE(ctx != nullptr, "attn: null context");
   HB_REQUIRE(d_q && d_k && d_v && d_seqlens && d_out, "attn: null pointer");
+  HB_REQUIRE(nseq >= 1 && T >= 1 && (long)nseq * T < (1l << 24), "attn: B=%d T=%d", nseq, T);
+  const int B = nseq * T;  // query tokens
   HB_REQUIRE(B >= 1 && H >= 1 && Hkv >= 1 && H % Hkv == 0, "attn: B=%d H=%d Hkv=%d", B, H, Hkv);
   const int G = H / Hkv;
   HB_REQUIRE(G <= 8, "attn: %d query heads per KV head (at most 8)", G);
@@ -636,6 +653,7 @@ extern "C" int hb200_attn_decode(hb200_ctx* ctx, const void* d_q, int q_is_f16, 
   p.G = G;
   p.max_seq = max_seq;
   p.window = window;
+  p.T = T;
   p.scale_log2 = scale * 1.4426950408889634f;
   const int eff_len = (window > 0 && window < max_seq) ? window : max_seq;
   p.nsplit = attn_pick_splits(ctx, B, Hkv, eff_len);
@@ -674,6 +692,29 @@ extern "C" int hb200_attn_decode(hb200_ctx* ctx, const void* d_q, int q_is_f16, 
     case 128: return attn_launch<128, false>(ctx, p, st);
     default: return attn_launch<256, false>(ctx, p, st);
   }
+}
+
+extern "C" int hb200_attn_decode(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d_k,
+                                 const void* d_v, const int32_t* d_seqlens, int B, int H, int Hkv,
+                                 int D, int max_seq, int window, float scale, void* d_workspace,
+                                 size_t workspace_bytes, float* d_out, hb200_stream stream) {
+  return attn_run(ctx, d_q, q_is_f16, d_k, d_v, d_seqlens, B, 1, H, Hkv, D, max_seq, window, scale,
+                  d_workspace, workspace_bytes, d_out, stream);
+}
+
+extern "C" size_t hb200_attn_prefill_workspace_bytes(const hb200_ctx* ctx, int B, int T, int H,
+                                                     int Hkv, int D, int max_seq) {
+  if (T < 1 || B < 1 || (long)B * T >= (1l << 24)) return 0;
+  return hb200_attn_workspace_bytes(ctx, B * T, H, Hkv, D, max_seq);
+}
+
+extern "C" int hb200_attn_prefill(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d_k,
+                                  const void* d_v, const int32_t* d_seqlens, int B, int T, int H,
+                                  int Hkv, int D, int max_seq, int window, float scale,
+                                  void* d_workspace, size_t workspace_bytes, float* d_out,
+                                  hb200_stream stream) {
+  return attn_run(ctx, d_q, q_is_f16, d_k, d_v, d_seqlens, B, T, H, Hkv, D, max_seq, window, scale,
+                  d_workspace, workspace_bytes, d_out, stream);
 }
 
 // ---- the same operator for callers that must not allocate -----------------------------

@@ -76,8 +76,9 @@ struct RopeParams {
   const float* v;    // [B][Hkv][D]
   __half* k_cache;   // [B][Hkv][slots][D]
   __half* v_cache;
-  const int32_t* pos;  // [B] position of the new token
+  const int32_t* pos;  // [B/T] position of each sequence's first new token
   int B, H, Hkv, D, slots, ring;
+  int T;               // new tokens per sequence (1 = decode); B counts tokens
   double base;
 };
 
@@ -93,7 +94,8 @@ __global__ void rope_kv_kernel(const __grid_constant__ RopeParams p) {
   const int b = (int)(idx / per_seq);
   const int r = (int)(idx % per_seq);
   const int head = r / half, i = r % half;
-  const int pos = p.pos[b];
+  const int cb = b / p.T;  // which sequence's cache
+  const int pos = p.pos[cb] + (b - cb * p.T);
   int slot = p.ring ? pos % p.slots : pos;
   slot = slot < 0 ? 0 : (slot >= p.slots ? p.slots - 1 : slot);
   if (head < p.H + p.Hkv) {
@@ -111,14 +113,14 @@ __global__ void rope_kv_kernel(const __grid_constant__ RopeParams p) {
       const int kh = head - p.H;
       const float* kk = p.k + ((size_t)b * p.Hkv + kh) * p.D;
       const double x0 = kk[i], x1 = kk[i + half];
-      __half* dst = p.k_cache + (((size_t)b * p.Hkv + kh) * p.slots + slot) * p.D;
+      __half* dst = p.k_cache + (((size_t)cb * p.Hkv + kh) * p.slots + slot) * p.D;
       dst[i] = __float2half_rn((float)(x0 * cs - x1 * sn));
       dst[i + half] = __float2half_rn((float)(x0 * sn + x1 * cs));
     }
   } else {
     const int vh = head - p.H - p.Hkv;
     const float* vv = p.v + ((size_t)b * p.Hkv + vh) * p.D;
-    __half* dst = p.v_cache + (((size_t)b * p.Hkv + vh) * p.slots + slot) * p.D;
+    __half* dst = p.v_cache + (((size_t)cb * p.Hkv + vh) * p.slots + slot) * p.D;
     dst[i] = __float2half_rn(vv[i]);
     dst[i + half] = __float2half_rn(vv[i + half]);
   }
@@ -415,19 +417,39 @@ extern "C" int hb200_rmsnorm(hb200_ctx* ctx, const float* d_x, const float* d_ga
   return HB200_OK;
 }
 
-extern "C" int hb200_rope_kv_write(hb200_ctx* ctx, float* d_q, const float* d_k, const float* d_v,
-                                   void* d_k_cache, void* d_v_cache, const int32_t* d_pos, int B,
-                                   int H, int Hkv, int D, int cache_slots, int ring,
-                                   float rope_base, hb200_stream stream) {
+static int rope_run(hb200_ctx* ctx, float* d_q, const float* d_k, const float* d_v,
+                    void* d_k_cache, void* d_v_cache, const int32_t* d_pos, int nseq, int T, int H,
+                    int Hkv, int D, int cache_slots, int ring, float rope_base,
+                    hb200_stream stream) {
   HB_REQUIRE(ctx && d_q && d_k && d_v && d_k_cache && d_v_cache && d_pos, "rope: null pointer");
-  HB_REQUIRE(B >= 1 && H >= 1 && Hkv >= 1 && D >= 2 && D % 2 == 0 && cache_slots >= 1,
+  HB_REQUIRE(nseq >= 1 && T >= 1 && (long)nseq * T < (1l << 24) && H >= 1 && Hkv >= 1 && D >= 2 &&
+                 D % 2 == 0 && cache_slots >= 1,
              "rope: bad shape");
+  HB_REQUIRE(!(ring && T > 1), "rope: a ring cache takes one token per call");
+  const int B = nseq * T;
   RopeParams p = {d_q, d_k, d_v, static_cast<__half*>(d_k_cache), static_cast<__half*>(d_v_cache),
-                  d_pos, B, H, Hkv, D, cache_slots, ring, (double)rope_base};
+                  d_pos, B, H, Hkv, D, cache_slots, ring, T, (double)rope_base};
   const long n = (long)B * (H + 2 * Hkv) * (D / 2);
   HB_CUDA(launch_pdl(rope_kv_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0,
                      static_cast<cudaStream_t>(stream), ctx->pdl, p));
   return HB200_OK;
+}
+
+extern "C" int hb200_rope_kv_write(hb200_ctx* ctx, float* d_q, const float* d_k, const float* d_v,
+                                   void* d_k_cache, void* d_v_cache, const int32_t* d_pos, int B,
+                                   int H, int Hkv, int D, int cache_slots, int ring,
+                                   float rope_base, hb200_stream stream) {
+  return rope_run(ctx, d_q, d_k, d_v, d_k_cache, d_v_cache, d_pos, B, 1, H, Hkv, D, cache_slots,
+                  ring, rope_base, stream);
+}
+
+extern "C" int hb200_rope_kv_write_prefill(hb200_ctx* ctx, float* d_q, const float* d_k,
+                                           const float* d_v, void* d_k_cache, void* d_v_cache,
+                                           const int32_t* d_pos0, int B, int T, int H, int Hkv,
+                                           int D, int cache_slots, float rope_base,
+                                           hb200_stream stream) {
+  return rope_run(ctx, d_q, d_k, d_v, d_k_cache, d_v_cache, d_pos0, B, T, H, Hkv, D, cache_slots, 0,
+                  rope_base, stream);
 }
 
 extern "C" int hb200_argmax(hb200_ctx* ctx, const float* d_logits, long V, int M, int32_t* d_out,

@@ -276,6 +276,31 @@ def flash_attention_workspace(ctx: Context, B: int, H: int, Hkv: int, D: int, ma
     return torch.empty((max(int(n), 16),), dtype=torch.uint8, device=dev)
 
 
+def flash_attention_prefill(ctx: Context, q: torch.Tensor, k_cache: torch.Tensor,
+                            v_cache: torch.Tensor, seqlens: torch.Tensor, *, num_heads: int,
+                            num_kv_heads: int, head_dim: int, max_seq_len: int, scale: float,
+                            window: int = 0, stream=None) -> torch.Tensor:
+    """Causal prefill attention (the prefill kernels of Hesper/WGSL/FlashAttention.lean:495-715).
+
+    q [B, T, H, D] f32 or f16: T new tokens per sequence whose K/V already sit at positions
+    seqlens[b]-T .. seqlens[b]-1 of the f16 caches [B, Hkv, max_seq_len, D]; returns [B, T, H, D].
+    """
+    _need(q, q.dtype, "q")
+    _need(k_cache, torch.float16, "k_cache")
+    _need(v_cache, torch.float16, "v_cache")
+    _need(seqlens, torch.int32, "seqlens")
+    B, T = int(q.shape[0]), int(q.shape[1])
+    n = ctx._lib.hb200_attn_prefill_workspace_bytes(ctx.handle, B, T, num_heads, num_kv_heads,
+                                                    head_dim, max_seq_len)
+    ws = torch.empty((max(int(n), 16),), dtype=torch.uint8, device=q.device)
+    o = torch.empty((B, T, num_heads, head_dim), dtype=torch.float32, device=q.device)
+    check(ctx._lib.hb200_attn_prefill(
+        ctx.handle, _ptr(q), int(q.dtype == torch.float16), _ptr(k_cache), _ptr(v_cache),
+        _ptr(seqlens), B, T, num_heads, num_kv_heads, head_dim, max_seq_len, int(window),
+        C.c_float(scale), _ptr(ws), C.c_size_t(ws.numel()), _ptr(o), _stream_handle(stream)))
+    return o
+
+
 def execute_flash_attention_v11(ctx: Context, q: torch.Tensor, k_cache: torch.Tensor,
                                 v_cache: torch.Tensor, seqlens: torch.Tensor, *, num_heads: int,
                                 num_kv_heads: int, head_dim: int, max_seq_len: int, scale: float,

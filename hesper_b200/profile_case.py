@@ -9,6 +9,8 @@ under a few GB, so that a full-metric capture of one to three launches ends in a
   i2s_mma  64-token ternary product on the tensor cores, ring of 40 matrices K=2560 N=6912
            (177 MB), 2 passes
   lmhead64 64-token LM head on the tensor cores, one bf16 table V=128256 K=2560 (657 MB), 3 calls
+  q4k_b32  32-token Q4_K product on the tensor cores (dequantise to f16 + 16-bit product),
+           ring of 12 matrices K=2560 N=10240, 2 passes
   bitnet1 / bitnet64   BitNet-2B-shaped decode loop at batch 1 / 64: 2 prompt positions and
            3 new tokens, launched one by one (no graph) so that a launch list sees each kernel
 """
@@ -47,6 +49,17 @@ def main(name: str) -> None:
         y = torch.empty(1, N, device="cuda")
         torch.cuda.synchronize()
         for _ in range(3):
+            for l in layers:
+                l.forward(x, out=y)
+    elif name == "q4k_b32":
+        K, N, R, M = 2560, 10240, 12, 32
+        base = torch.from_numpy(formats.random_kquant(rng, 12, N, K)).cuda()
+        rb = formats.kquant_row_bytes(12, K)
+        layers = [hb.LinearLayer(ctx, torch.roll(base, r * rb), 12, K, N) for r in range(R)]
+        x = torch.randn(M, K, device="cuda")
+        y = torch.empty(M, N, device="cuda")
+        torch.cuda.synchronize()
+        for _ in range(2):
             for l in layers:
                 l.forward(x, out=y)
     elif name == "i2s_mma":

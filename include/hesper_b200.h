@@ -206,6 +206,23 @@ int hb200_attn_decode(hb200_ctx *ctx, const void *d_q, int q_is_f16, const void 
                       size_t workspace_bytes, float *d_out, hb200_stream stream);
 
 
+/* Causal prefill attention: T new query tokens per sequence against the same f16 cache,
+ * which already holds them at positions seqlens[b]-T .. seqlens[b]-1 (written by
+ * hb200_rope_kv_write_prefill).  Token t sees the positions before and including its own:
+ * seqlens[b] - (T-1-t) of them (and of those only the last `window`, if set).
+ * Replaces the prefill FlashAttention kernels (Hesper/WGSL/FlashAttention.lean:495-715).
+ *   d_q, d_out  [B][T][H][D];  d_seqlens [B] lengths AFTER the T tokens were appended
+ * Every query token runs as one decode query over its sequence's cache (the K/V of a
+ * sequence are shared through the L2, not through shared memory), so this is a correct
+ * prefill for prompt chunks, not a tuned long-prompt kernel.  Linear caches only.
+ * T = 1 is hb200_attn_decode. */
+size_t hb200_attn_prefill_workspace_bytes(const hb200_ctx *ctx, int B, int T, int H, int Hkv,
+                                          int D, int max_seq);
+int hb200_attn_prefill(hb200_ctx *ctx, const void *d_q, int q_is_f16, const void *d_k,
+                       const void *d_v, const int32_t *d_seqlens, int B, int T, int H, int Hkv,
+                       int D, int max_seq, int window, float scale, void *d_workspace,
+                       size_t workspace_bytes, float *d_out, hb200_stream stream);
+
 /* Decode attention for callers that cannot hand over scratch memory.  No counterpart in
  * the reference (there the Lean side allocates the V11 partial buffers with the model).
  *
@@ -258,6 +275,15 @@ int hb200_rope_kv_write(hb200_ctx *ctx, float *d_q, const float *d_k, const floa
                         void *d_k_cache, void *d_v_cache, const int32_t *d_pos, int B, int H,
                         int Hkv, int D, int cache_slots, int ring, float rope_base,
                         hb200_stream stream);
+
+/* The same for T new tokens per sequence (prompt chunk): d_q [B][T][H][D], d_k / d_v
+ * [B][T][Hkv][D], token t of sequence b is at position d_pos0[b] + t.  Linear caches only.
+ * Replaces the batched RoPE + kvWriteBatchKernelF16 of the prefill path
+ * (Hesper/Layers/Attention.lean:809-945). */
+int hb200_rope_kv_write_prefill(hb200_ctx *ctx, float *d_q, const float *d_k, const float *d_v,
+                                void *d_k_cache, void *d_v_cache, const int32_t *d_pos0, int B,
+                                int T, int H, int Hkv, int D, int cache_slots, float rope_base,
+                                hb200_stream stream);
 
 /* Greedy argmax over [M][V] logits, first strict maximum.  Replaces argmaxKernel
  * (Hesper/Models/BitNet.lean:456-479). */
