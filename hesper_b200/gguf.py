@@ -198,3 +198,100 @@ def write_gguf(path: str, metadata: Dict[str, object], tensors: List[Tuple[str, 
 def i2s_payload(packed: np.ndarray, scale: float) -> bytes:
     """numel/4 packed bytes + f32 scale + 28 bytes of padding (the i2_s blob of a GGUF file)."""
     return bytes(np.asarray(packed, np.uint8)) + struct.pack("<f", scale) + b"\0" * 28
+
+
+# ---- BitNet-shaped checkpoints -------------------------------------------------------------
+#
+# Tensor names and types as BitNetModel.fromGGUFObject reads them
+# (Hesper/Models/BitNet.lean:788-941): token_embd.weight (F16, or BF16 here as well),
+# blk.N.{attn_norm,attn_sub_norm,ffn_norm,ffn_sub_norm}.weight (F32),
+# blk.N.{attn_q,attn_k,attn_v,attn_output,ffn_gate,ffn_up,ffn_down}.weight (i2_s),
+# output_norm.weight (F32).  The reference takes its dimensions from a fixed configuration
+# (extractConfig, :773-777); this loader reads the standard `<arch>.*` metadata keys
+# (Hesper/GGUF/Reader.lean:186-202) and falls back to the tensor shapes.
+
+_BITNET_LINEARS = (("wq", "attn_q"), ("wk", "attn_k"), ("wv", "attn_v"), ("wo", "attn_output"),
+                   ("wgate", "ffn_gate"), ("wup", "ffn_up"), ("wdown", "ffn_down"))
+_BITNET_NORMS = ("attn_norm", "attn_sub_norm", "ffn_norm", "ffn_sub_norm")
+
+
+def save_bitnet_gguf(path: str, shape, weights: dict, arch: str = "bitnet-b1.58") -> None:
+    """Write a weights dict in the layout of hesper_b200.models.random_bitnet_weights (host
+    arrays) as a GGUF file; the embedding is stored as BF16 bits unless
+    weights['embed_dtype'] == 1 (F16)."""
+    dims = {"hidden": shape.hidden, "qdim": shape.n_heads * shape.head_dim,
+            "kvdim": shape.n_kv_heads * shape.head_dim, "ffn": shape.ffn}
+    io = {"wq": ("hidden", "qdim"), "wk": ("hidden", "kvdim"), "wv": ("hidden", "kvdim"),
+          "wo": ("qdim", "hidden"), "wgate": ("hidden", "ffn"), "wup": ("hidden", "ffn"),
+          "wdown": ("ffn", "hidden")}
+    meta = {"general.architecture": arch, f"{arch}.block_count": int(shape.n_layers),
+            f"{arch}.embedding_length": int(shape.hidden),
+            f"{arch}.attention.head_count": int(shape.n_heads),
+            f"{arch}.attention.head_count_kv": int(shape.n_kv_heads),
+            f"{arch}.attention.key_length": int(shape.head_dim),
+            f"{arch}.feed_forward_length": int(shape.ffn),
+            f"{arch}.context_length": int(shape.max_seq),
+            f"{arch}.vocab_size": int(shape.vocab),
+            f"{arch}.rope.freq_base": float(shape.rope_base),
+            f"{arch}.attention.layer_norm_rms_epsilon": float(shape.rms_eps)}
+    emb = np.ascontiguousarray(weights["embed"]).view(np.uint16).reshape(shape.vocab, shape.hidden)
+    emb_type = T_F16 if int(weights.get("embed_dtype", 0)) == 1 else T_BF16
+    tensors = [("token_embd.weight", (shape.hidden, shape.vocab), emb_type, emb.tobytes())]
+    for i, L in enumerate(weights["layers"]):
+        for nm in _BITNET_NORMS:
+            a = np.ascontiguousarray(L[nm], np.float32)
+            tensors.append((f"blk.{i}.{nm}.weight", (a.size,), T_F32, a.tobytes()))
+        for key, gname in _BITNET_LINEARS:
+            K, N = dims[io[key][0]], dims[io[key][1]]
+            tensors.append((f"blk.{i}.{gname}.weight", (K, N), T_I2_S,
+                            i2s_payload(np.ascontiguousarray(L[key], np.uint8),
+                                        float(L["s" + key[1:]]))))
+    fn = np.ascontiguousarray(weights["final_norm"], np.float32)
+    tensors.append(("output_norm.weight", (fn.size,), T_F32, fn.tobytes()))
+    write_gguf(path, meta, tensors)
+
+
+def load_bitnet_gguf(path: str, max_seq: int = 0):
+    """(BitNetShape, weights dict) from a GGUF file: the payloads are views of the mapped
+    file in exactly the bytes the kernels consume (packed i2_s + one f32 scale per tensor)."""
+    from .models import BitNetShape
+    g = GGUFFile(path)
+    arch = g.metadata.get("general.architecture", "bitnet-b1.58")
+
+    def md(key, default=None):
+        return g.metadata.get(f"{arch}.{key}", default)
+
+    emb_t = g.tensors["token_embd.weight"]
+    hidden = int(md("embedding_length", emb_t.shape[0]))
+    vocab = int(md("vocab_size", emb_t.shape[1]))
+    n_layers = int(md("block_count", 0))
+    if not n_layers:
+        while f"blk.{n_layers}.attn_q.weight" in g.tensors:
+            n_layers += 1
+    n_heads = int(md("attention.head_count", 0))
+    qdim = g.tensors["blk.0.attn_q.weight"].shape[1]
+    kvdim = g.tensors["blk.0.attn_k.weight"].shape[1]
+    head_dim = int(md("attention.key_length", qdim // n_heads if n_heads else 128))
+    n_heads = n_heads or qdim // head_dim
+    n_kv = int(md("attention.head_count_kv", kvdim // head_dim))
+    ffn = int(md("feed_forward_length", g.tensors["blk.0.ffn_gate.weight"].shape[1]))
+    ctx_len = int(md("context_length", 2304))
+    shape = BitNetShape(n_layers=n_layers, hidden=hidden, n_heads=n_heads, n_kv_heads=n_kv,
+                        head_dim=head_dim, ffn=ffn, vocab=vocab, max_seq=max_seq or ctx_len,
+                        rope_base=float(md("rope.freq_base", 500000.0)),
+                        rms_eps=float(md("attention.layer_norm_rms_epsilon", 1e-5)))
+    if emb_t.ggml_type not in (T_F16, T_BF16):
+        raise ValueError(f"token_embd.weight has type id {emb_t.ggml_type}; F16 or BF16 expected")
+    layers = []
+    for i in range(n_layers):
+        L = {nm: g.get_f32(f"blk.{i}.{nm}.weight") for nm in _BITNET_NORMS}
+        for key, gname in _BITNET_LINEARS:
+            packed, scale, _ = g.get_i2s(f"blk.{i}.{gname}.weight")
+            L[key] = packed
+            L["s" + key[1:]] = np.float32(scale)
+        layers.append(L)
+    weights = {"layers": layers,
+               "embed": g.raw("token_embd.weight").view(np.uint16).reshape(vocab, hidden),
+               "embed_dtype": 1 if emb_t.ggml_type == T_F16 else 0,
+               "final_norm": g.get_f32("output_norm.weight"), "_file": g}
+    return shape, weights

@@ -127,7 +127,8 @@ class BitNetModel:
                            shape.head_dim, shape.ffn, shape.vocab, shape.max_seq,
                            shape.rope_base, shape.rms_eps)
         h = C.c_void_p()
-        check(ctx._lib.hb200_bitnet_create(ctx.handle, C.byref(cfg), arr, self.embed.data_ptr(), 0,
+        check(ctx._lib.hb200_bitnet_create(ctx.handle, C.byref(cfg), arr, self.embed.data_ptr(),
+                                           int(weights.get("embed_dtype", 0)),
                                            self.final_norm.data_ptr(), batch, max_new_tokens,
                                            C.byref(h)))
         self._h = h

@@ -45,3 +45,51 @@ def test_bad_magic(tmp_path):
     p.write_bytes(b"NOPE" + b"\0" * 64)
     with pytest.raises(ValueError, match="Invalid GGUF magic"):
         gguf.GGUFFile(str(p))
+
+
+def _tiny_shape():
+    from hesper_b200.models import BitNetShape
+    return BitNetShape(n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=384,
+                       vocab=512, max_seq=64)
+
+
+def test_bitnet_checkpoint_roundtrip(tmp_path):
+    """A whole BitNet-shaped checkpoint under the reference's tensor names
+    (Hesper/Models/BitNet.lean:788-941) comes back byte for byte, dimensions from metadata."""
+    from hesper_b200.models import random_bitnet_weights
+    shape = _tiny_shape()
+    w = random_bitnet_weights(shape, seed=5)
+    path = str(tmp_path / "tiny.gguf")
+    gguf.save_bitnet_gguf(path, shape, w)
+    shape2, w2 = gguf.load_bitnet_gguf(path)
+    for f in ("n_layers", "hidden", "n_heads", "n_kv_heads", "head_dim", "ffn", "vocab", "max_seq"):
+        assert getattr(shape2, f) == getattr(shape, f)
+    assert shape2.rope_base == shape.rope_base
+    assert np.float32(shape2.rms_eps) == np.float32(shape.rms_eps)
+    assert np.array_equal(w2["embed"], w["embed"]) and w2["embed_dtype"] == 0
+    assert np.array_equal(w2["final_norm"], w["final_norm"])
+    for L, L2 in zip(w["layers"], w2["layers"]):
+        for k in L:
+            assert np.array_equal(np.asarray(L2[k]), np.asarray(L[k])), k
+    assert set(w2["_file"].tensors) >= {"token_embd.weight", "output_norm.weight",
+                                        "blk.1.attn_output.weight", "blk.0.ffn_sub_norm.weight"}
+
+
+@pytest.mark.gpu
+def test_bitnet_checkpoint_decodes_like_the_arrays_it_was_written_from(tmp_path, ctx):
+    from hesper_b200 import BitNetModel
+    from hesper_b200.models import random_bitnet_weights
+    shape = _tiny_shape()
+    w = random_bitnet_weights(shape, seed=6)
+    path = str(tmp_path / "tiny.gguf")
+    gguf.save_bitnet_gguf(path, shape, w)
+    shape2, w2 = gguf.load_bitnet_gguf(path)
+    prompt = np.random.default_rng(1).integers(0, shape.vocab, (2, 5)).astype(np.int32)
+    outs = []
+    for s_, w_ in ((shape, w), (shape2, w2)):
+        m = BitNetModel(ctx, s_, w_, batch=2, max_new_tokens=12)
+        toks, _, _ = m.generate(prompt, 12, use_graph=False)
+        outs.append(np.array(toks))
+        m.close()
+    ctx.check()
+    assert np.array_equal(outs[0], outs[1])
