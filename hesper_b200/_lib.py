@@ -102,6 +102,11 @@ SIGNATURES = {
     "hb200_tp_allreduce_f32": (_i, [_vp, _vp, _sz, _vp]),
     "hb200_tp_allreduce_max_u64": (_i, [_vp, _vp, _sz, _vp]),
     "hb200_tp_check": (_i, [_vp]),
+    "hb200_tp_allreduce_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _i, _i, _vp, _vp]),
+    "hb200_tp_peer_handle_bytes": (_sz, []),
+    "hb200_tp_peer_export": (_i, [_vp, _vp]),
+    "hb200_tp_peer_attach": (_i, [_vp, _vp]),
+    "hb200_tp_peer_attached": (_i, [_vp]),
     "hb200_gemma_create": (_i, [_vp, _vp, C.POINTER(GemmaConfig), C.POINTER(GemmaLayer), _vp, _vp, _vp, _i, _i, C.POINTER(_vp)]),
     "hb200_gemma_destroy": (_i, [_vp]),
     "hb200_gemma_reset": (_i, [_vp, _vp]),

@@ -119,9 +119,8 @@ int gemma_enqueue_step(hb200_gemma* m, const int32_t* d_tokens, bool lm_head, cu
     rc = hb200_kquant_forward(ctx, HB200_FMT_Q4_K, L.wo, qdim, Hd, m->att, B, nullptr, 0.f, nullptr,
                               m->o, st);
     if (rc) return rc;
-    rc = hb200_tp_allreduce_f32(m->tp, m->o, (size_t)B * Hd, st);
-    if (rc) return rc;
-    rc = hb200_rmsnorm(ctx, m->o, L.post_attn_norm, m->x, c.rms_eps, B, Hd, m->x1, st);
+    rc = hb200_tp_allreduce_rmsnorm(m->tp, ctx, m->o, L.post_attn_norm, m->x, c.rms_eps, B, Hd,
+                                    m->x1, st);
     if (rc) return rc;
     rc = hb200_kquant_gateup_gelu(ctx, HB200_FMT_Q4_K, L.wgate, L.wup, Hd, c.local_ffn, m->x1, B,
                                   L.ffn_norm, c.rms_eps, m->h, st);
@@ -129,9 +128,8 @@ int gemma_enqueue_step(hb200_gemma* m, const int32_t* d_tokens, bool lm_head, cu
     rc = hb200_kquant_forward(ctx, HB200_FMT_Q4_K, L.wdown, c.local_ffn, Hd, m->h, B, nullptr, 0.f,
                               nullptr, m->o, st);
     if (rc) return rc;
-    rc = hb200_tp_allreduce_f32(m->tp, m->o, (size_t)B * Hd, st);
-    if (rc) return rc;
-    rc = hb200_rmsnorm(ctx, m->o, L.post_ffn_norm, m->x1, c.rms_eps, B, Hd, m->x, st);
+    rc = hb200_tp_allreduce_rmsnorm(m->tp, ctx, m->o, L.post_ffn_norm, m->x1, c.rms_eps, B, Hd,
+                                    m->x, st);
     if (rc) return rc;
   }
   if (lm_head) {

@@ -76,6 +76,220 @@ static int nccl_fail(int r, const char* what) {
 
 constexpr int kNcclSum = 0, kNcclMax = 2, kNcclUint64 = 5, kNcclFloat32 = 7;
 
+// ---- one-shot all-reduce over peer memory ----------------------------------------------
+//
+// The exchanges of tensor-parallel decode are tiny (hidden x batch floats: 10 KB at batch 1)
+// and there are 84 of them per token, so their cost is latency, not bandwidth.  Every rank
+// owns an exchange buffer that all peers map (CUDA IPC); an all-reduce is ONE kernel:
+//   push   each CTA stores its chunk of the input into slot [epoch][my rank] of EVERY
+//          rank's buffer (plain peer stores over NVLink), fences, then writes the call's
+//          sequence number into flag [epoch][my rank][cta] on every rank;
+//   wait   the CTA polls its own W flags (its own memory) until they carry the number;
+//   reduce it adds the W slots in rank order -- the same order on every rank, so all ranks
+//          hold bit-identical results -- and writes the chunk back.
+// Two epochs alternate, so a rank that runs ahead never overwrites a slot a slower peer is
+// still reading (it cannot be two calls ahead: the call in between needs that peer's flags).
+// The sequence number lives in device memory and is advanced by the kernel itself, so a
+// captured graph replays correctly.  Every wait is bounded; on expiry the kernel raises the
+// status flag and returns.  No multicast, no NVLS: plain loads and stores.
+constexpr int kPeerMaxRanks = 8;
+constexpr int kPeerMaxCtas = 64;
+constexpr size_t kPeerSlotBytes = (size_t)2560 * 64 * 4;  // hidden 2560 x 64 tokens of f32
+constexpr size_t kPeerFlagBytes = (size_t)2 * kPeerMaxRanks * kPeerMaxCtas * sizeof(uint32_t);
+constexpr size_t kPeerBufBytes = 2 * kPeerMaxRanks * kPeerSlotBytes + kPeerFlagBytes;
+
+struct PeerParams {
+  unsigned char* buf[kPeerMaxRanks];  // every rank's exchange buffer (own one included)
+  void* io;                           // local vector, reduced in place
+  size_t n;                           // elements
+  int rank, nranks;
+  uint32_t* seq;                      // [0] last finished call, [1] finishing ticket
+  uint32_t* status;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// T = float with sum, or unsigned long long with max.  Elements are moved as 16-byte words.
+template <typename T, bool kMax>
+__global__ void __launch_bounds__(256) peer_allreduce_kernel(const __grid_constant__ PeerParams p) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int kPer16 = 16 / (int)sizeof(T);
+  const int tid = threadIdx.x, cta = blockIdx.x, W = p.nranks;
+  const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(p.seq) + 1u;
+  const int epoch = (int)(seq & 1u);
+  const size_t nvec = (p.n + kPer16 - 1) / kPer16;             // 16-byte words (buffers are padded)
+  const size_t per = (nvec + gridDim.x - 1) / gridDim.x;
+  const size_t v0 = (size_t)cta * per, v1 = v0 + per < nvec ? v0 + per : nvec;
+  uint4* io = reinterpret_cast<uint4*>(p.io);
+  const size_t slot_off = ((size_t)epoch * kPeerMaxRanks + p.rank) * kPeerSlotBytes;
+  // ---- push -------------------------------------------------------------------------
+  for (size_t v = v0 + tid; v < v1; v += 256) {
+    const uint4 x = io[v];
+    for (int r = 0; r < W; ++r) reinterpret_cast<uint4*>(p.buf[r] + slot_off)[v] = x;
+  }
+  __threadfence_system();
+  __syncthreads();
+  const size_t flag_base = 2 * kPeerMaxRanks * kPeerSlotBytes;
+  if (tid < W) {
+    uint32_t* f = reinterpret_cast<uint32_t*>(p.buf[tid] + flag_base) +
+                  ((size_t)epoch * kPeerMaxRanks + p.rank) * kPeerMaxCtas + cta;
+    st_release_sys(f, seq);
+  }
+  // ---- wait for every rank's chunk (flags in this rank's own buffer) ------------------------
+  __shared__ int s_ok;
+  if (tid == 0) s_ok = 1;
+  __syncthreads();
+  if (tid < W) {
+    const uint32_t* f = reinterpret_cast<const uint32_t*>(p.buf[p.rank] + flag_base) +
+                        ((size_t)epoch * kPeerMaxRanks + tid) * kPeerMaxCtas + cta;
+    bool got = false;
+#pragma unroll 1
+    for (uint32_t it = 0; it < (1u << 21); ++it) {  // about a second at worst
+      if (ld_acquire_sys(f) == seq) {
+        got = true;
+        break;
+      }
+    }
+    if (!got) {
+      s_ok = 0;
+      atomicOr(p.status, kStatusMbarTimeout);
+    }
+  }
+  __syncthreads();
+  // ---- reduce in rank order -----------------------------------------------------------
+  if (s_ok) {
+    const unsigned char* mine = p.buf[p.rank] + (size_t)epoch * kPeerMaxRanks * kPeerSlotBytes;
+    for (size_t v = v0 + tid; v < v1; v += 256) {
+      uint4 a = __ldcg(reinterpret_cast<const uint4*>(mine) + v);
+      T* av = reinterpret_cast<T*>(&a);
+      for (int r = 1; r < W; ++r) {
+        const uint4 b = __ldcg(reinterpret_cast<const uint4*>(mine + (size_t)r * kPeerSlotBytes) + v);
+        const T* bv = reinterpret_cast<const T*>(&b);
+#pragma unroll
+        for (int i = 0; i < kPer16; ++i) {
+          if (kMax)
+            av[i] = bv[i] > av[i] ? bv[i] : av[i];
+          else
+            av[i] = av[i] + bv[i];
+        }
+      }
+      io[v] = a;
+    }
+  }
+  // ---- the last CTA to finish advances the sequence number -----------------------------
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const uint32_t t = atomicAdd(&p.seq[1], 1u);
+    if (t == gridDim.x - 1) {
+      p.seq[1] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(p.seq) = seq;
+    }
+  }
+}
+
+// The same exchange with the RMSNorm that follows it in the decode loop folded in: one CTA
+// per token pushes the token's row of partial sums, waits, adds the W rows in rank order
+// (bit-identical to the plain all-reduce) and writes y = add + RMSNorm(sum) * gamma with the
+// arithmetic of the stand-alone RMSNorm kernel (f64 sum of squares in the same order).
+struct PeerNormParams {
+  unsigned char* buf[kPeerMaxRanks];
+  const float* x;      // [M][K] this rank's partial sums
+  const float* gamma;  // [K]
+  const float* add;    // nullable [M][K]
+  float* y;            // [M][K]
+  float eps;
+  int K, rank, nranks;
+  uint32_t* seq;
+  uint32_t* status;
+};
+
+__global__ void __launch_bounds__(256) peer_allreduce_rmsnorm_kernel(
+    const __grid_constant__ PeerNormParams p) {
+  extern __shared__ __align__(16) float row[];  // [K] the reduced row
+  __shared__ double red[8];
+  __shared__ int s_ok;
+  pdl_trigger();
+  pdl_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, m = blockIdx.x, W = p.nranks;
+  const int K = p.K;
+  const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(p.seq) + 1u;
+  const int epoch = (int)(seq & 1u);
+  const size_t slot_off = ((size_t)epoch * kPeerMaxRanks + p.rank) * kPeerSlotBytes;
+  const uint4* xin = reinterpret_cast<const uint4*>(p.x + (size_t)m * K);
+  for (int v = tid; v < (K >> 2); v += 256) {
+    const uint4 x = xin[v];
+    for (int r = 0; r < W; ++r)
+      reinterpret_cast<uint4*>(p.buf[r] + slot_off + (size_t)m * K * 4)[v] = x;
+  }
+  __threadfence_system();
+  if (tid == 0) s_ok = 1;
+  __syncthreads();
+  const size_t flag_base = 2 * kPeerMaxRanks * kPeerSlotBytes;
+  if (tid < W) {
+    uint32_t* f = reinterpret_cast<uint32_t*>(p.buf[tid] + flag_base) +
+                  ((size_t)epoch * kPeerMaxRanks + p.rank) * kPeerMaxCtas + m;
+    st_release_sys(f, seq);
+    const uint32_t* g = reinterpret_cast<const uint32_t*>(p.buf[p.rank] + flag_base) +
+                        ((size_t)epoch * kPeerMaxRanks + tid) * kPeerMaxCtas + m;
+    bool got = false;
+#pragma unroll 1
+    for (uint32_t it = 0; it < (1u << 21); ++it) {
+      if (ld_acquire_sys(g) == seq) {
+        got = true;
+        break;
+      }
+    }
+    if (!got) {
+      s_ok = 0;
+      atomicOr(p.status, kStatusMbarTimeout);
+    }
+  }
+  __syncthreads();
+  if (s_ok) {
+    const unsigned char* mine = p.buf[p.rank] + (size_t)epoch * kPeerMaxRanks * kPeerSlotBytes +
+                                (size_t)m * K * 4;
+    double ss = 0.0;
+    for (int k = tid; k < K; k += 256) {
+      float a = __ldcg(reinterpret_cast<const float*>(mine) + k);
+      for (int r = 1; r < W; ++r)
+        a = __fadd_rn(a, __ldcg(reinterpret_cast<const float*>(mine + (size_t)r * kPeerSlotBytes) + k));
+      row[k] = a;
+      ss += (double)a * a;
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    double tot = 0.0;
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float rinv = (float)(1.0 / sqrt(tot / (double)K + (double)p.eps));
+    for (int k = tid; k < K; k += 256) {
+      float v = __fmul_rn(__fmul_rn(row[k], rinv), p.gamma[k]);
+      if (p.add) v = __fadd_rn(p.add[(size_t)m * K + k], v);
+      p.y[(size_t)m * K + k] = v;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const uint32_t t = atomicAdd(&p.seq[1], 1u);
+    if (t == gridDim.x - 1) {
+      p.seq[1] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(p.seq) = seq;
+    }
+  }
+}
+
 }  // namespace hb
 
 using namespace hb;
@@ -83,7 +297,35 @@ using namespace hb;
 struct hb200_tp {
   ncclComm_t comm;
   int rank, nranks;
+  hb200_ctx* ctx;
+  unsigned char* peer_buf[kPeerMaxRanks];  // mapped exchange buffers, [rank] is the local one
+  bool peer_ready;
+  uint32_t* d_seq;   // sequence number and finishing ticket of the peer all-reduce
 };
+
+// In-place reduction of n elements through the peer buffers, or HB200_ERR_UNSUPPORTED when
+// this call does not qualify (not attached, too large, unaligned).
+template <typename T, bool kMax>
+static int peer_allreduce(hb200_tp* tp, T* d_buf, size_t n, cudaStream_t st) {
+  if (!tp->peer_ready || n * sizeof(T) > kPeerSlotBytes ||
+      (reinterpret_cast<uintptr_t>(d_buf) & 15) != 0 || (n * sizeof(T)) % 16 != 0)
+    return HB200_ERR_UNSUPPORTED;
+  PeerParams p = {};
+  for (int r = 0; r < tp->nranks; ++r) p.buf[r] = tp->peer_buf[r];
+  p.io = d_buf;
+  p.n = n;
+  p.rank = tp->rank;
+  p.nranks = tp->nranks;
+  p.seq = tp->d_seq;
+  p.status = tp->ctx->d_status;
+  // one CTA per 16 KB, the same count on every rank (it depends on n only)
+  size_t ctas = (n * sizeof(T) + 16383) / 16384;
+  if (ctas > kPeerMaxCtas) ctas = kPeerMaxCtas;
+  if (ctas < 1) ctas = 1;
+  HB_CUDA(launch_pdl(peer_allreduce_kernel<T, kMax>, dim3((unsigned)ctas), dim3(256), 0, st,
+                     tp->ctx->pdl, p));
+  return HB200_OK;
+}
 
 extern "C" int hb200_tp_unique_id(unsigned char out[128]) {
   HB_REQUIRE(out != nullptr, "tp_unique_id: null output");
@@ -109,13 +351,64 @@ extern "C" int hb200_tp_init(hb200_ctx* ctx, int rank, int nranks, const unsigne
   ncclComm_t comm = nullptr;
   int r = g_nccl.comm_init_rank(&comm, nranks, nid, rank);
   if (r != 0) return nccl_fail(r, "ncclCommInitRank");
-  hb200_tp* tp = new hb200_tp{comm, rank, nranks};
+  hb200_tp* tp = new hb200_tp();
+  tp->comm = comm;
+  tp->rank = rank;
+  tp->nranks = nranks;
+  tp->ctx = ctx;
   *out = tp;
   return HB200_OK;
 }
 
+extern "C" size_t hb200_tp_peer_handle_bytes(void) { return sizeof(cudaIpcMemHandle_t); }
+
+extern "C" int hb200_tp_peer_export(hb200_tp* tp, unsigned char* out_handle) {
+  HB_REQUIRE(tp && out_handle, "tp_peer_export: null argument");
+  HB_REQUIRE(tp->nranks <= kPeerMaxRanks, "tp_peer_export: at most %d ranks", kPeerMaxRanks);
+  HB_CUDA(cudaSetDevice(tp->ctx->device));
+  if (!tp->peer_buf[tp->rank]) {
+    void* b = nullptr;
+    HB_CUDA(cudaMalloc(&b, kPeerBufBytes));
+    HB_CUDA(cudaMemset(b, 0, kPeerBufBytes));
+    tp->peer_buf[tp->rank] = static_cast<unsigned char*>(b);
+    HB_CUDA(cudaMalloc(&tp->d_seq, 2 * sizeof(uint32_t)));
+    HB_CUDA(cudaMemset(tp->d_seq, 0, 2 * sizeof(uint32_t)));
+    HB_CUDA(cudaDeviceSynchronize());
+  }
+  cudaIpcMemHandle_t h;
+  HB_CUDA(cudaIpcGetMemHandle(&h, tp->peer_buf[tp->rank]));
+  memcpy(out_handle, &h, sizeof(h));
+  return HB200_OK;
+}
+
+extern "C" int hb200_tp_peer_attach(hb200_tp* tp, const unsigned char* all_handles) {
+  HB_REQUIRE(tp && all_handles, "tp_peer_attach: null argument");
+  HB_REQUIRE(tp->peer_buf[tp->rank] != nullptr, "tp_peer_attach: call hb200_tp_peer_export first");
+  HB_CUDA(cudaSetDevice(tp->ctx->device));
+  for (int r = 0; r < tp->nranks; ++r) {
+    if (r == tp->rank || tp->peer_buf[r]) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, all_handles + (size_t)r * sizeof(h), sizeof(h));
+    void* ptr = nullptr;
+    HB_CUDA(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    tp->peer_buf[r] = static_cast<unsigned char*>(ptr);
+  }
+  tp->peer_ready = true;
+  return HB200_OK;
+}
+
+extern "C" int hb200_tp_peer_attached(const hb200_tp* tp) { return tp && tp->peer_ready ? 1 : 0; }
+
 extern "C" int hb200_tp_destroy(hb200_tp* tp) {
   if (!tp) return HB200_OK;
+  for (int r = 0; r < kPeerMaxRanks; ++r) {
+    if (!tp->peer_buf[r]) continue;
+    if (r == tp->rank)
+      cudaFree(tp->peer_buf[r]);
+    else
+      cudaIpcCloseMemHandle(tp->peer_buf[r]);
+  }
+  if (tp->d_seq) cudaFree(tp->d_seq);
   if (tp->comm && g_nccl.comm_destroy) g_nccl.comm_destroy(tp->comm);
   delete tp;
   return HB200_OK;
@@ -127,6 +420,8 @@ extern "C" int hb200_tp_size(const hb200_tp* tp) { return tp ? tp->nranks : 1; }
 extern "C" int hb200_tp_allreduce_f32(hb200_tp* tp, float* d_buf, size_t n, hb200_stream stream) {
   if (!tp || tp->nranks == 1) return HB200_OK;  // nothing to exchange
   HB_REQUIRE(d_buf != nullptr && n >= 1, "tp_allreduce_f32: bad argument");
+  const int pr = peer_allreduce<float, false>(tp, d_buf, n, static_cast<cudaStream_t>(stream));
+  if (pr != HB200_ERR_UNSUPPORTED) return pr;
   int r = g_nccl.all_reduce(d_buf, d_buf, n, kNcclFloat32, kNcclSum, tp->comm,
                             static_cast<cudaStream_t>(stream));
   if (r != 0) return nccl_fail(r, "ncclAllReduce(f32, sum)");
@@ -137,10 +432,43 @@ extern "C" int hb200_tp_allreduce_max_u64(hb200_tp* tp, unsigned long long* d_bu
                                           hb200_stream stream) {
   if (!tp || tp->nranks == 1) return HB200_OK;
   HB_REQUIRE(d_buf != nullptr && n >= 1, "tp_allreduce_max_u64: bad argument");
+  const int pr = peer_allreduce<unsigned long long, true>(tp, d_buf, n,
+                                                          static_cast<cudaStream_t>(stream));
+  if (pr != HB200_ERR_UNSUPPORTED) return pr;
   int r = g_nccl.all_reduce(d_buf, d_buf, n, kNcclUint64, kNcclMax, tp->comm,
                             static_cast<cudaStream_t>(stream));
   if (r != 0) return nccl_fail(r, "ncclAllReduce(u64, max)");
   return HB200_OK;
+}
+
+extern "C" int hb200_tp_allreduce_rmsnorm(hb200_tp* tp, hb200_ctx* ctx, float* d_x,
+                                          const float* d_gamma, const float* d_add, float eps,
+                                          int M, int K, float* d_y, hb200_stream stream) {
+  HB_REQUIRE(ctx && d_x && d_gamma && d_y && M >= 1 && K >= 1, "tp_allreduce_rmsnorm: bad argument");
+  if (tp && tp->nranks > 1) {
+    if (tp->peer_ready && M <= kPeerMaxCtas && K % 4 == 0 &&
+        (size_t)M * K * 4 <= kPeerSlotBytes && (size_t)K * 4 <= 48 * 1024 &&
+        (reinterpret_cast<uintptr_t>(d_x) & 15) == 0) {
+      PeerNormParams p = {};
+      for (int r = 0; r < tp->nranks; ++r) p.buf[r] = tp->peer_buf[r];
+      p.x = d_x;
+      p.gamma = d_gamma;
+      p.add = d_add;
+      p.y = d_y;
+      p.eps = eps;
+      p.K = K;
+      p.rank = tp->rank;
+      p.nranks = tp->nranks;
+      p.seq = tp->d_seq;
+      p.status = ctx->d_status;
+      HB_CUDA(launch_pdl(peer_allreduce_rmsnorm_kernel, dim3(M), dim3(256), (size_t)K * 4,
+                         static_cast<cudaStream_t>(stream), ctx->pdl, p));
+      return HB200_OK;
+    }
+    const int rc = hb200_tp_allreduce_f32(tp, d_x, (size_t)M * K, stream);
+    if (rc != HB200_OK) return rc;
+  }
+  return hb200_rmsnorm(ctx, d_x, d_gamma, d_add, eps, M, K, d_y, stream);
 }
 
 // Host-side health check of the communicator: 0 = healthy.  A peer that died or never

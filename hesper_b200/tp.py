@@ -12,6 +12,8 @@ The reference is single-GPU; this module is new.  Sharding rules (one process pe
 """
 from __future__ import annotations
 
+import os
+
 import ctypes as C
 import dataclasses
 
@@ -19,7 +21,7 @@ import numpy as np
 import torch
 
 from . import formats
-from ._lib import GemmaConfig, GemmaLayer, check
+from ._lib import GemmaConfig, GemmaLayer, HesperB200Error, check
 from .layers import Context, _stream_handle
 
 Q4K = formats.Q4K_BLOCK_BYTES
@@ -193,7 +195,34 @@ class TensorParallel:
         rank, size = dist.get_rank(), dist.get_world_size()
         box = [cls.make_id(ctx) if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
-        return cls(ctx, rank, size, box[0])
+        tp = cls(ctx, rank, size, box[0])
+        if size > 1 and size <= 8 and os.environ.get("HB200_TP_NO_PEER", "0") != "1":
+            tp.attach_peers(dist)
+        return tp
+
+    def attach_peers(self, dist) -> bool:
+        """Map every rank's exchange buffer (CUDA IPC) so that the small all-reduces of decode
+        run as one push kernel per rank instead of an NCCL call.  All ranks attach or none:
+        a rank that cannot export or open a handle makes every rank stay on NCCL."""
+        lib = self.ctx._lib
+        nb = int(lib.hb200_tp_peer_handle_bytes())
+        mine = (C.c_ubyte * nb)()
+        ok = lib.hb200_tp_peer_export(self._h, mine) == 0
+        gathered = [None] * self.size
+        dist.all_gather_object(gathered, bytes(mine) if ok else None)
+        if any(g is None for g in gathered):
+            return False
+        blob = (C.c_ubyte * (nb * self.size)).from_buffer_copy(b"".join(gathered))
+        ok = lib.hb200_tp_peer_attach(self._h, blob) == 0
+        flags = [None] * self.size
+        dist.all_gather_object(flags, bool(ok))
+        if not all(flags):
+            raise HesperB200Error(-1, "tp: some ranks attached the peer buffers and some did not")
+        return True
+
+    @property
+    def peer_attached(self) -> bool:
+        return bool(self.ctx._lib.hb200_tp_peer_attached(self._h))
 
     @property
     def handle(self):

@@ -394,6 +394,29 @@ int hb200_tp_allreduce_f32(hb200_tp *tp, float *d_buf, size_t n, hb200_stream st
 int hb200_tp_allreduce_max_u64(hb200_tp *tp, unsigned long long *d_buf, size_t n,
                                hb200_stream stream);
 
+/* One-shot all-reduce over peer memory for the small exchanges of decode (optional; without
+ * it every exchange goes through NCCL).  Each rank exports the handle of its exchange
+ * buffer (hb200_tp_peer_handle_bytes() bytes, a CUDA IPC handle), the host program gathers
+ * the handles of all ranks in rank order, every rank attaches.  From then on
+ * hb200_tp_allreduce_* of up to 2560 x 64 floats run as ONE kernel per rank: push the
+ * vector into every rank's buffer over NVLink, wait for the peers' flags (bounded; expiry
+ * shows as HB200_ERR_TIMEOUT in hb200_ctx_check), add in rank order -- so all ranks hold
+ * bit-identical sums.  Plain peer loads and stores only.  At most 8 ranks of one node, one
+ * process per GPU.  All ranks must attach, or none. */
+size_t hb200_tp_peer_handle_bytes(void);
+int hb200_tp_peer_export(hb200_tp *tp, unsigned char *out_handle);
+int hb200_tp_peer_attach(hb200_tp *tp, const unsigned char *all_handles);
+int hb200_tp_peer_attached(const hb200_tp *tp);
+
+/* The exchange and the RMSNorm that follows it in the decode loop as one operator:
+ * y = d_add + RMSNorm(sum over ranks of d_x) * gamma.  With the peer buffers attached
+ * (M <= 64) it is ONE kernel: a CTA per token pushes its row, waits for the peers, adds in
+ * rank order and normalises; otherwise it is hb200_tp_allreduce_f32 + hb200_rmsnorm (d_x
+ * then holds the sum).  tp NULL or one rank: hb200_rmsnorm alone. */
+int hb200_tp_allreduce_rmsnorm(hb200_tp *tp, hb200_ctx *ctx, float *d_x, const float *d_gamma,
+                               const float *d_add, float eps, int M, int K, float *d_y,
+                               hb200_stream stream);
+
 /* Host-side health check of the communicator (ncclCommGetAsyncError): a peer that died or
  * never joined shows up here or as an error of the next collective, not as a GPU fault. */
 int hb200_tp_check(hb200_tp *tp);

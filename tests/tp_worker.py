@@ -14,6 +14,53 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 
+def check_allreduce(hb, ctx, comm, rank, world):
+    """The exchange step on its own: the one-shot peer all-reduce must give, on every rank,
+    exactly the f32 sum taken in rank order (and the u64 maximum), call after call and when
+    replayed from a CUDA graph."""
+    import ctypes as C
+    ok = comm.peer_attached or os.environ.get("HB200_TP_NO_PEER", "0") == "1"
+    st = torch.cuda.Stream()
+    for it, n in enumerate([2560, 2560 * 2, 2560 * 64, 4, 2560 * 7] * 4):
+        parts = [np.random.default_rng(1000 * it + r).standard_normal(n).astype(np.float32)
+                 for r in range(world)]
+        want = parts[0].copy()
+        for r in range(1, world):
+            want = (want + parts[r]).astype(np.float32)
+        x = torch.from_numpy(parts[rank].copy()).cuda()
+        torch.cuda.synchronize()
+        comm.allreduce_f32(x, stream=st)
+        st.synchronize()
+        got = x.cpu().numpy()
+        if comm.peer_attached:
+            ok = ok and np.array_equal(got, want)          # rank-order sum, bit for bit
+        else:
+            ok = ok and np.allclose(got, want, rtol=1e-5, atol=1e-5)
+    # u64 maximum (argmax keys)
+    keys = torch.from_numpy(np.random.default_rng(7 + rank).integers(0, 2**62, 8)).cuda()
+    allk = [np.random.default_rng(7 + r).integers(0, 2**62, 8) for r in range(world)]
+    hb.load().hb200_tp_allreduce_max_u64(comm.handle, C.c_void_p(keys.data_ptr()), C.c_size_t(8),
+                                         C.c_void_p(st.cuda_stream))
+    st.synchronize()
+    ok = ok and np.array_equal(keys.cpu().numpy(), np.max(np.stack(allk), axis=0))
+    # graph replay: the sequence number advances on the device
+    x = torch.full((2560,), float(rank + 1), device="cuda")
+    torch.cuda.synchronize()
+    with torch.cuda.stream(st):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            for _ in range(3):
+                comm.allreduce_f32(x, stream=st)
+        for _ in range(4):
+            g.replay()
+        st.synchronize()
+    tot = float(sum(range(1, world + 1)))
+    expect = tot * float(world) ** 11  # 12 all-reduces: the first sums the ranks, 11 multiply by W
+    ok = ok and bool(torch.all(x == expect).item())
+    ctx.check()
+    return ok
+
+
 def main():
     rank = int(os.environ["RANK"])
     world = int(os.environ["WORLD_SIZE"])
@@ -25,6 +72,7 @@ def main():
     from tp_common import SMALL_GEMMA as S
     ctx = hb.Context(local)
     comm = tp.TensorParallel.from_torch_distributed(ctx)
+    ok_ar = check_allreduce(hb, ctx, comm, rank, world)
     w = tp.random_gemma_weights(S, seed=31)
     p = tp.plan(S, rank, world)
     model = hb.GemmaModel(ctx, S, tp.shard_weights(S, w, p), p, comm, batch=2, max_new_tokens=8)
@@ -56,7 +104,9 @@ def main():
         toks = box[0]
     comm.check()
     ctx.check()
-    flag = [ok]
+    oks = [None] * world
+    dist.all_gather_object(oks, bool(ok_ar))
+    flag = [ok and all(oks)]
     dist.broadcast_object_list(flag, src=0)
     model.close()
     comm.close()
