@@ -209,7 +209,7 @@ int hb_gemm16_split(struct hb200_ctx* ctx, int dtype, int K, const float* d_x, i
                     const float* d_rms_gamma, float rms_eps, cudaStream_t st);
 int hb_gemm16_mma(struct hb200_ctx* ctx, const void* d_table, int dtype, long V, int K, int M,
                   float* d_y, const float* d_residual, long ldy, unsigned long long* d_keys,
-                  cudaStream_t st);
+                  int table_constant, cudaStream_t st);
 constexpr size_t kArenaBytes = (size_t)64 << 20;  // f16 weights of one batched k-quant product
 
 struct hb200_ctx {

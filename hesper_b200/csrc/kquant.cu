@@ -461,55 +461,65 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
 template <int FMT>
 __global__ void __launch_bounds__(256) kq_dequant_kernel(const uint8_t* __restrict__ blocks,
                                                          int K, long rows, int rowbytes,
+                                                         int rows_per_cta,
                                                          __half* __restrict__ out) {
+  extern __shared__ __align__(16) uint8_t raw[];  // the CTA's rows, verbatim
+  const long r0 = (long)blockIdx.x * rows_per_cta;
+  const int nr = (int)min((long)rows_per_cta, rows - r0);
+  // the quantised rows do not depend on the kernel before this one: stage them first
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(blocks + (size_t)r0 * rowbytes);
+    const int nv = nr * rowbytes / 16;  // rowbytes is a multiple of 16 for both formats
+    for (int i = threadIdx.x; i < nv; i += 256) reinterpret_cast<uint4*>(raw)[i] = __ldg(src + i);
+  }
   pdl_trigger();
   pdl_wait();  // the arena may still be read by the product before this one
-  const long gpr = K >> 3;  // 8-weight groups per row
-  const long idx = (long)blockIdx.x * 256 + threadIdx.x;
-  if (idx >= rows * gpr) return;
-  const long row = idx / gpr;
-  const int g = (int)(idx - row * gpr);
-  float w[8];
-  if (FMT == 12) {
-    // super-block: f16 d, f16 dmin, 12 bytes of 6-bit scales/mins, 128 bytes of nibbles;
-    // sub-blocks 2c and 2c+1 are the low and high nibbles of bytes 32c..32c+31
-    // (Hesper/Quantization/Q4_K_M.lean:13-52,120-144)
-    const uint8_t* blk = blocks + (size_t)row * rowbytes + (size_t)(g >> 5) * 144;
-    const int j = g & 31, sub = j >> 2, part = j & 3;
-    const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(blk));
-    const uint8_t* sc = blk + 4;
-    int s6, m6;
-    if (sub < 4) {
-      s6 = sc[sub] & 63;
-      m6 = sc[sub + 4] & 63;
+  __syncthreads();
+  const int gpr = K >> 3;  // 8-weight groups per row
+  for (int idx = threadIdx.x; idx < nr * gpr; idx += 256) {
+    const int row = idx / gpr, g = idx - row * gpr;
+    float w[8];
+    if (FMT == 12) {
+      // super-block: f16 d, f16 dmin, 12 bytes of 6-bit scales/mins, 128 bytes of nibbles;
+      // sub-blocks 2c and 2c+1 are the low and high nibbles of bytes 32c..32c+31
+      // (Hesper/Quantization/Q4_K_M.lean:13-52,120-144)
+      const uint8_t* blk = raw + (size_t)row * rowbytes + (size_t)(g >> 5) * 144;
+      const int j = g & 31, sub = j >> 2, part = j & 3;
+      const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(blk));
+      const uint8_t* sc = blk + 4;
+      int s6, m6;
+      if (sub < 4) {
+        s6 = sc[sub] & 63;
+        m6 = sc[sub + 4] & 63;
+      } else {
+        s6 = (sc[sub + 4] & 0xF) | ((sc[sub - 4] >> 6) << 4);
+        m6 = (sc[sub + 4] >> 4) | ((sc[sub] >> 6) << 4);
+      }
+      const float ds = dd.x * (float)s6, dm = dd.y * (float)m6;
+      const uint2 q = *reinterpret_cast<const uint2*>(blk + 16 + 32 * (sub >> 1) + 8 * part);
+      const uint32_t qq[2] = {q.x, q.y};
+      const int sh = (sub & 1) * 4;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        w[i] = fmaf(ds, (float)((qq[i >> 2] >> (8 * (i & 3) + sh)) & 0xF), -dm);
     } else {
-      s6 = (sc[sub + 4] & 0xF) | ((sc[sub - 4] >> 6) << 4);
-      m6 = (sc[sub + 4] >> 4) | ((sc[sub] >> 6) << 4);
-    }
-    const float ds = dd.x * (float)s6, dm = dd.y * (float)m6;
-    const uint2 q = *reinterpret_cast<const uint2*>(blk + 16 + 32 * (sub >> 1) + 8 * part);
-    const uint32_t qq[2] = {q.x, q.y};
-    const int sh = (sub & 1) * 4;
+      // block: f16 d, 32 int8 (Hesper/Layers/Linear.lean:6207-6223); 2-byte aligned only
+      const uint8_t* blk = raw + (size_t)row * rowbytes + (size_t)(g >> 2) * 34;
+      const float d = __half2float(*reinterpret_cast<const __half*>(blk));
+      const uint16_t* q16 = reinterpret_cast<const uint16_t*>(blk + 2 + 8 * (g & 3));
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-      w[i] = fmaf(ds, (float)((qq[i >> 2] >> (8 * (i & 3) + sh)) & 0xF), -dm);
-  } else {
-    // block: f16 d, 32 int8 (Hesper/Layers/Linear.lean:6207-6223); 2-byte aligned only
-    const uint8_t* blk = blocks + (size_t)row * rowbytes + (size_t)(g >> 2) * 34;
-    const float d = __half2float(*reinterpret_cast<const __half*>(blk));
-    const uint16_t* q16 = reinterpret_cast<const uint16_t*>(blk + 2 + 8 * (g & 3));
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint16_t v = q16[i];
-      w[2 * i] = d * (float)(int8_t)(v & 0xff);
-      w[2 * i + 1] = d * (float)(int8_t)(v >> 8);
+      for (int i = 0; i < 4; ++i) {
+        const uint16_t v = q16[i];
+        w[2 * i] = d * (float)(int8_t)(v & 0xff);
+        w[2 * i + 1] = d * (float)(int8_t)(v >> 8);
+      }
     }
+    __half2 h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(w[2 * i], w[2 * i + 1]);
+    *reinterpret_cast<uint4*>(out + (size_t)(r0 + row) * K + (size_t)g * 8) =
+        *reinterpret_cast<const uint4*>(h);
   }
-  __half2 h[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(w[2 * i], w[2 * i + 1]);
-  *reinterpret_cast<uint4*>(out + (size_t)row * K + (size_t)g * 8) =
-      *reinterpret_cast<const uint4*>(h);
 }
 
 // y[M][N] = W x (+ residual) for one tensor, any M >= 1: row chunks that fit the arena,
@@ -519,19 +529,26 @@ static int kq_batched_one(hb200_ctx* ctx, int fmt, const uint8_t* blocks, int K,
                           const float* residual, float* y, cudaStream_t st) {
   const int rowbytes = fmt == HB200_FMT_Q4_K ? K / 256 * 144 : K / 32 * 34;
   long chunk = (long)(kArenaBytes / ((size_t)K * 2)) / 128 * 128;
-  HB_REQUIRE(chunk >= 128, "kquant (batched): K=%d too large for the f16 arena", K);
+  HB_REQUIRE(chunk >= 128 && rowbytes <= 48 * 1024,
+             "kquant (batched): K=%d too large for the f16 arena or the staging buffer", K);
   __half* arena = static_cast<__half*>(ctx->d_arena);
   for (long r0 = 0; r0 < N; r0 += chunk) {
     const long nr = N - r0 < chunk ? N - r0 : chunk;
-    const long threads = nr * (K / 8);
-    const unsigned grid = (unsigned)((threads + 255) / 256);
+    // rows per CTA: up to 32 KB of raw bytes, but no fewer CTAs than ~4 per SM when the
+    // tensor is small
+    int rpc = 32768 / rowbytes;
+    const long want = (nr + 4L * ctx->sm_count - 1) / (4L * ctx->sm_count);
+    if (rpc > want) rpc = (int)want;
+    if (rpc < 1) rpc = 1;
+    const unsigned grid = (unsigned)((nr + rpc - 1) / rpc);
+    const size_t dsm = (size_t)rpc * rowbytes;
     const uint8_t* src = blocks + (size_t)r0 * rowbytes;
     if (fmt == HB200_FMT_Q4_K)
-      HB_CUDA(launch_pdl(kq_dequant_kernel<12>, dim3(grid), dim3(256), 0, st, ctx->pdl, src, K, nr,
-                         rowbytes, arena));
+      HB_CUDA(launch_pdl(kq_dequant_kernel<12>, dim3(grid), dim3(256), dsm, st, ctx->pdl, src, K,
+                         nr, rowbytes, rpc, arena));
     else
-      HB_CUDA(launch_pdl(kq_dequant_kernel<8>, dim3(grid), dim3(256), 0, st, ctx->pdl, src, K, nr,
-                         rowbytes, arena));
+      HB_CUDA(launch_pdl(kq_dequant_kernel<8>, dim3(grid), dim3(256), dsm, st, ctx->pdl, src, K,
+                         nr, rowbytes, rpc, arena));
     for (int m0 = 0; m0 < M; m0 += 64) {
       const int mc = M - m0 < 64 ? M - m0 : 64;
       int rc = hb_gemm16_split(ctx, 1, K, d_x + (size_t)m0 * K, mc, gamma, eps, st);
@@ -539,7 +556,7 @@ static int kq_batched_one(hb200_ctx* ctx, int fmt, const uint8_t* blocks, int K,
       // the product addresses its output as [m][row] with row stride 1 and token stride N:
       // a row chunk is a column offset into the caller's [M][N] arrays
       rc = hb_gemm16_mma(ctx, arena, 1, nr, K, mc, y + (size_t)m0 * N + r0,
-                         residual ? residual + (size_t)m0 * N + r0 : nullptr, N, nullptr, st);
+                         residual ? residual + (size_t)m0 * N + r0 : nullptr, N, nullptr, 0, st);
       if (rc != HB200_OK) return rc;
     }
   }

@@ -39,7 +39,8 @@ constexpr int kLmRows = 128;      // vocabulary rows per CTA = MMA M
 constexpr int kLmTokens = 64;     // token slots; the operand holds 2 x 64 rows (hi, lo)
 constexpr int kLmN = 2 * kLmTokens;
 constexpr int kLmKStep = 64;      // elements per pipeline step = 128 bytes of a table row
-constexpr int kLmStages = 3;
+constexpr int kLmStages = 3;      // stages of a CTA that shares its SM with a second one
+constexpr int kLmMaxStages = 6;   // stages of a CTA alone on its SM (few row tiles)
 constexpr int kLmABytes = kLmRows * kLmKStep * 2;  // 16 KB
 constexpr int kLmBBytes = kLmN * kLmKStep * 2;     // 16 KB
 constexpr int kLmCtrl = 4096;     // barriers, tensor-memory slot, per-warp argmax keys
@@ -63,6 +64,8 @@ struct LmMmaParams {
   long V;
   long ldy;            // token stride of logits / residual (>= V)
   int K, M;
+  int stages;          // kLmStages or kLmMaxStages
+  int table_constant;  // the table is not written by kernels of this stream (weights proper)
   uint32_t idesc;
   uint32_t* status;
 };
@@ -200,17 +203,18 @@ __global__ void __launch_bounds__(kLmThreads, 2)
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nsteps = p.K / kLmKStep;
+  const int S = p.stages;
   const long row0 = (long)blockIdx.x * kLmRows;
 
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);   // [kLmStages] table box + activations
-  uint64_t* empty = full + kLmStages;                    // [kLmStages] MMAs of the stage retired
-  uint64_t* done = empty + kLmStages;                    // [1]
+  uint64_t* empty = full + kLmMaxStages;                 // [stages] MMAs of the stage retired
+  uint64_t* done = empty + kLmMaxStages;                 // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
   unsigned long long* wkeys = reinterpret_cast<unsigned long long*>(smem + 1024);  // [4][64]
   uint8_t* stg = smem + kLmCtrl;  // per stage: A (16 KB, swizzled) then B (16 KB)
 
   if (tid == 0) {
-    for (int i = 0; i < kLmStages; ++i) {
+    for (int i = 0; i < S; ++i) {
       mbar_init(&full[i], 2);  // one arrival with the table bytes, one with the activation bytes
       mbar_init(&empty[i], 1);
     }
@@ -232,29 +236,35 @@ __global__ void __launch_bounds__(kLmThreads, 2)
     // ================= producer =============================================================
     const uint64_t pol = policy_evict_first();
     auto issue_a = [&](int ks) {
-      const int st = ks % kLmStages;
+      const int st = ks % S;
       mbar_arrive_expect_tx(&full[st], kLmABytes);
       lm_tma_box(stg + (size_t)st * (kLmABytes + kLmBBytes), &p.tmap, ks * kLmKStep, (int)row0,
                  &full[st], pol);
     };
     auto issue_b = [&](int ks) {
-      const int st = ks % kLmStages;
+      const int st = ks % S;
       mbar_arrive_expect_tx(&full[st], kLmBBytes);
       bulk_g2s(stg + (size_t)st * (kLmABytes + kLmBBytes) + kLmABytes,
                p.xb + (size_t)ks * kLmBBytes, kLmBBytes, &full[st]);
     };
-    const int pre = min(kLmStages, nsteps);
+    const int pre = min(S, nsteps);
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&p.tmap))
                    : "memory");
-      for (int ks = 0; ks < pre; ++ks) issue_a(ks);  // the table does not depend on anything
+      // a constant table (the LM head) can be fetched before the dependency resolves; the
+      // f16 arena of the k-quant path is written by the kernels just before this one
+      if (p.table_constant)
+        for (int ks = 0; ks < pre; ++ks) issue_a(ks);
     }
     pdl_trigger();
     pdl_wait();  // the split activations come from the kernel before this one
     if (lane == 0)
-      for (int ks = 0; ks < pre; ++ks) issue_b(ks);
+      for (int ks = 0; ks < pre; ++ks) {
+        if (!p.table_constant) issue_a(ks);
+        issue_b(ks);
+      }
     for (int ks = pre; ks < nsteps; ++ks) {
-      ok = lm_wait(ok, &empty[ks % kLmStages], (uint32_t)(((ks / kLmStages) - 1) & 1), p.status);
+      ok = lm_wait(ok, &empty[ks % S], (uint32_t)(((ks / S) - 1) & 1), p.status);
       if (lane == 0 && ok) {
         issue_a(ks);
         issue_b(ks);
@@ -263,8 +273,8 @@ __global__ void __launch_bounds__(kLmThreads, 2)
   } else if (warp == 1) {
     // ================= MMA issuer ===========================================================
     for (int ks = 0; ks < nsteps; ++ks) {
-      const int st = ks % kLmStages;
-      ok = lm_wait(ok, &full[st], (uint32_t)((ks / kLmStages) & 1), p.status);
+      const int st = ks % S;
+      ok = lm_wait(ok, &full[st], (uint32_t)((ks / S) & 1), p.status);
       if (lane == 0) {
         lm_fence_after();
         const uint32_t abase = smem_u32(stg + (size_t)st * (kLmABytes + kLmBBytes));
@@ -386,7 +396,7 @@ int hb_gemm16_split(hb200_ctx* ctx, int dtype, int K, const float* d_x, int M,
 // LM head so that the finishing kernel is shared).
 int hb_gemm16_mma(hb200_ctx* ctx, const void* d_table, int dtype, long V, int K, int M,
                   float* d_y, const float* d_residual, long ldy, unsigned long long* d_keys,
-                  cudaStream_t st) {
+                  int table_constant, cudaStream_t st) {
   HB_REQUIRE(V >= 1 && V < (1l << 31), "batched 16-bit product: bad row count");
   uint8_t* xb = static_cast<uint8_t*>(ctx->d_scratch) + kScratchLmSplit;
   LmMmaParams p = {};
@@ -410,6 +420,7 @@ int hb_gemm16_mma(hb200_ctx* ctx, const void* d_table, int dtype, long V, int K,
   p.ldy = ldy;
   p.K = K;
   p.M = M;
+  p.table_constant = table_constant;
   // instruction descriptor of kind::f16: D = f32, A and B of the table's type, both K-major
   const uint32_t fmt = dtype == 0 ? 1u : 0u;  // 1 = bf16, 0 = f16
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kLmN >> 3) << 17) |
@@ -418,12 +429,16 @@ int hb_gemm16_mma(hb200_ctx* ctx, const void* d_table, int dtype, long V, int K,
   static bool configured = false;
   if (!configured) {
     HB_CUDA(cudaFuncSetAttribute(lmhead_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kLmSmem));
+                                 kLmCtrl + kLmMaxStages * (kLmABytes + kLmBBytes)));
     configured = true;
   }
   const long ntiles = (V + kLmRows - 1) / kLmRows;
-  HB_CUDA(launch_pdl(lmhead_mma_kernel, dim3((unsigned)ntiles), dim3(kLmThreads), (size_t)kLmSmem,
-                     st, ctx->pdl, p));
+  // few row tiles: every CTA has an SM to itself, so it takes the deeper ring (192 KB in
+  // flight) instead of sharing the SM with a CTA that does not exist
+  p.stages = ntiles <= ctx->sm_count ? kLmMaxStages : kLmStages;
+  const size_t smem = kLmCtrl + (size_t)p.stages * (kLmABytes + kLmBBytes);
+  HB_CUDA(launch_pdl(lmhead_mma_kernel, dim3((unsigned)ntiles), dim3(kLmThreads), smem, st,
+                     ctx->pdl, p));
   return HB200_OK;
 }
 
@@ -433,5 +448,5 @@ int hb_lmhead_mma_run(hb200_ctx* ctx, const void* d_table, int dtype, long V, in
                       float* d_logits, unsigned long long* d_keys, cudaStream_t st) {
   const int rc = hb_gemm16_split(ctx, dtype, K, d_x, M, d_rms_gamma, rms_eps, st);
   if (rc != HB200_OK) return rc;
-  return hb_gemm16_mma(ctx, d_table, dtype, V, K, M, d_logits, nullptr, V, d_keys, st);
+  return hb_gemm16_mma(ctx, d_table, dtype, V, K, M, d_logits, nullptr, V, d_keys, 1, st);
 }
