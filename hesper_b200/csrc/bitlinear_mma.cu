@@ -32,9 +32,7 @@
 //       CTAs per tile; each publishes its int32 partial, the last to arrive (a ticket per
 //       tile) adds the others' and runs the epilogue -- exact, since integers commute.
 // Every mbarrier wait is bounded; on expiry the kernel still releases its tensor memory.
-#include <cuda.h>  // CUtensorMap and its enums only; the encoder comes from the runtime
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace hb {
 
@@ -212,52 +210,9 @@ extern "C" __attribute__((visibility("default"))) void hb200_prof_read_fine(hb20
 
 // ---- tcgen05 helpers --------------------------------------------------------------------
 
-// Shared-memory matrix descriptor, K-major, no swizzle: core matrices of 8 rows x 16 bytes,
-// LBO = byte distance between core matrices adjacent in K, SBO = between 8-row groups.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
-  d |= (uint64_t)1 << 46;  // descriptor version of this architecture
-  return d;                // base offset 0, layout type 0 (no swizzle)
-}
-
 // Instruction descriptor for kind::i8: D = s32, A = u8, B = s8, both K-major, N = 64, M = 128.
 constexpr uint32_t kIdescI8 = (2u << 4) | (0u << 7) | (1u << 10) | ((kMmaTokens >> 3) << 17) |
                               ((kMmaRows >> 4) << 24);
-
-__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                        uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "l"(adesc), "l"(bdesc), "r"(kIdescI8), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-
-// Bounded wait with a tighter cap than the streaming kernels use: a tile's whole life is a
-// few microseconds, so ~1e5 polls already means something is broken.  Once a wait has
-// failed the later ones are skipped, so a broken launch ends quickly.
-__device__ __forceinline__ bool mma_wait(bool ok, uint64_t* bar, uint32_t parity, uint32_t* status) {
-  if (!ok) return false;
-#pragma unroll 1
-  for (uint32_t it = 0; it < (1u << 17); ++it)
-    if (mbar_try_wait(bar, parity)) return true;
-  atomicOr(status, kStatusMbarTimeout);
-  return false;
-}
 
 // A operand from tensor memory (lane = weight row, 4 K-bytes per 32-bit column).
 __device__ __forceinline__ void umma_i8_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
@@ -266,17 +221,6 @@ __device__ __forceinline__ void umma_i8_ta(uint32_t tmem_d, uint32_t tmem_a, uin
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
       "r"(tmem_a), "l"(bdesc), "r"(kIdescI8), "r"(accumulate)
-      : "memory");
-}
-
-// One box of the packed-weight tensor map: 128 rows x 128 bytes (4 groups) -> 16 KB of shared
-// memory in the 128-byte swizzle (16-byte unit u of row r lands at unit u ^ (r & 7)).
-__device__ __forceinline__ void tma_box_2d(void* dst, const CUtensorMap* tm, int x, int y,
-                                           uint64_t* bar, uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
-      ".L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(dst)),
-      "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
       : "memory");
 }
 
@@ -332,9 +276,9 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
         smem_u32(tmem_slot)));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
-  tc_fence_before();
+  tc_before_sync();
   __syncthreads();
-  tc_fence_after();
+  tc_after_sync();
   const uint32_t tmem = *tmem_slot;
   bool ok = true;
 
@@ -347,7 +291,7 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm)) : "memory");
       for (; cnext < kPkStages && cnext < nchunks; ++cnext) {  // weights: no dependency
         mbar_arrive_expect_tx(&pk_full[cnext], kPkBytes);
-        tma_box_2d(pk + (size_t)cnext * kPkBytes, tm, (gbase + cnext * kChunkGroups) * 32, row0,
+        tc_tma_box_2d(pk + (size_t)cnext * kPkBytes, tm, (gbase + cnext * kChunkGroups) * 32, row0,
                    &pk_full[cnext], pol);
       }
     }
@@ -358,7 +302,7 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
     for (int s = 0; s < nsteps; ++s) {
       const int st = s % kStages;
       if (s >= kStages)  // the MMAs that read this stage kStages steps ago must have retired
-        ok = mma_wait(ok, &mma_done[st], (uint32_t)(((s / kStages) - 1) & 1), p.status);
+        ok = tc_wait(ok, &mma_done[st], (uint32_t)(((s / kStages) - 1) & 1), p.status);
       if (lane == 0) {  // activations of the step's groups: contiguous in the operand layout
         const int g0 = s * kStepGroups;
         const uint32_t bytes = (uint32_t)min(kStepGroups, ngroups - g0) * kBBytes;
@@ -371,19 +315,19 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
                                            (uint32_t)(((cnext / kPkStages) - 1) & 1))) {
         if (lane == 0) {
           mbar_arrive_expect_tx(&pk_full[cnext % kPkStages], kPkBytes);
-          tma_box_2d(pk + (size_t)(cnext % kPkStages) * kPkBytes, tm,
+          tc_tma_box_2d(pk + (size_t)(cnext % kPkStages) * kPkBytes, tm,
                      (gbase + cnext * kChunkGroups) * 32, row0, &pk_full[cnext % kPkStages], pol);
         }
         ++cnext;
       }
     }
     while (cnext < nchunks) {  // boxes still owed (their slot frees up as the expanders go)
-      ok = mma_wait(ok, &pk_free[cnext % kPkStages], (uint32_t)(((cnext / kPkStages) - 1) & 1),
+      ok = tc_wait(ok, &pk_free[cnext % kPkStages], (uint32_t)(((cnext / kPkStages) - 1) & 1),
                     p.status);
       if (!ok) break;
       if (lane == 0) {
         mbar_arrive_expect_tx(&pk_full[cnext % kPkStages], kPkBytes);
-        tma_box_2d(pk + (size_t)(cnext % kPkStages) * kPkBytes, tm,
+        tc_tma_box_2d(pk + (size_t)(cnext % kPkStages) * kPkBytes, tm,
                    (gbase + cnext * kChunkGroups) * 32, row0, &pk_full[cnext % kPkStages], pol);
       }
       ++cnext;
@@ -394,10 +338,10 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
     const uint32_t tmem_d = tmem + (which ? 448u : 0u);
     for (int s = which; s < nsteps; s += 2) {
       const int st = s % kStages;
-      ok = mma_wait(ok, &full[st], (uint32_t)((s / kStages) & 1), p.status);
+      ok = tc_wait(ok, &full[st], (uint32_t)((s / kStages) & 1), p.status);
       if (s < 10) MMA_FINE(2 * s, lane == 0);
       if (lane == 0) {
-        tc_fence_after();
+        tc_after_sync();
         const uint32_t a_t = tmem + kAccCols + (uint32_t)st * (kStepGroups * kAGroupCols);
         const uint32_t bbase = smem_u32(bstg + (size_t)st * kStepGroups * kBBytes);
         const int ng = min(kStepGroups, ngroups - s * kStepGroups);
@@ -407,16 +351,16 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
 #pragma unroll
             for (int j = 0; j < 4; ++j)  // K = 32 bytes per instruction: 8 columns of A
               umma_i8_ta(tmem_d, a_t + gg * kAGroupCols + j * 8,
-                         umma_desc(bbase + gg * kBBytes + j * 256, 128, 1024),
+                         tc_smem_desc(bbase + gg * kBBytes + j * 256, 128, 1024, 0),
                          (s > 1 || gg > 0 || j > 0) ? 1u : 0u);
           }
-        umma_commit(&mma_done[st]);  // arrives once these (and all earlier) MMAs have retired
+        tc_commit(&mma_done[st]);  // arrives once these (and all earlier) MMAs have retired
       }
       __syncwarp();
       if (s < 10) MMA_FINE(2 * s + 1, lane == 0);
     }
     MMA_STAMP(3, lane == 0);
-    if (lane == 0) umma_commit(done);
+    if (lane == 0) tc_commit(done);
   } else {
     // ================= expander warps ========================================================
     // warp w owns TMEM lanes (= weight rows) 32*(w&3).., and K-half h = w>>2 of every group:
@@ -428,8 +372,8 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
     for (int s = 0; s < nsteps; ++s) {
       const int st = s % kStages;
       if (s >= kStages) {
-        ok = mma_wait(ok, &mma_done[st], (uint32_t)(((s / kStages) - 1) & 1), p.status);
-        tc_fence_after();
+        ok = tc_wait(ok, &mma_done[st], (uint32_t)(((s / kStages) - 1) & 1), p.status);
+        tc_after_sync();
       }
       const int ng = min(kStepGroups, ngroups - s * kStepGroups);
       if (s < 10) MMA_FINE(20 + 2 * s, tid == 0);
@@ -439,7 +383,7 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
         const int g = s * kStepGroups + gg;
         const int c = g / kChunkGroups, gi = g % kChunkGroups;
         if (gi == 0)
-          ok = mma_wait(ok, &pk_full[c % kPkStages], (uint32_t)((c / kPkStages) & 1), p.status);
+          ok = tc_wait(ok, &pk_full[c % kPkStages], (uint32_t)((c / kPkStages) & 1), p.status);
         // the row's 32 packed bytes of this group: units 2gi and 2gi+1 of its swizzled 128 bytes
         const uint8_t* rowp = pk + (size_t)(c % kPkStages) * kPkBytes + (size_t)erow * 128;
         const uint4 w0 = *reinterpret_cast<const uint4*>(rowp + (((2 * gi) ^ (erow & 7)) << 4));
@@ -471,7 +415,7 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
         }
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      tc_fence_before();
+      tc_before_sync();
       __syncwarp();
       if (lane == 0)
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full[st]))
@@ -485,8 +429,8 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
       ssum[tid] = p.sumq[tid];
     }
   }
-  ok = mma_wait(true, done, 0, p.status) && ok;
-  tc_fence_after();
+  ok = tc_wait(true, done, 0, p.status) && ok;
+  tc_after_sync();
   __syncthreads();  // sd / ssum visible; every warp past its loop
   MMA_STAMP(4, tid == 0);
 
@@ -597,7 +541,7 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
     MMA_STAMP(14, tid == 0);
   }
   MMA_STAMP(8, tid == 0);
-  tc_fence_before();
+  tc_before_sync();
   __syncthreads();
   if (warp == kMmaWarp)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem));
@@ -606,27 +550,6 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
 }  // namespace hb
 
 using namespace hb;
-
-namespace {
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-// The tensor-map encoder is a driver entry point; it is looked up through the runtime so
-// that the library does not link against the driver library.
-EncodeTiledFn tensor_map_encoder() {
-  static EncodeTiledFn fn = [] {
-    void* f = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) !=
-            cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      f = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(f);
-  }();
-  return fn;
-}
-}  // namespace
 
 // Batched path of hb200_bitlinear_forward_multi (16 <= M <= 64).  Scratch in the context:
 // quantised activations in operand layout, their scales and sums.
@@ -645,7 +568,7 @@ int hb_bitlinear_mma_run(hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int ns
                      ctx->pdl, q));
   MmaParams p = {};
   int t = 0;
-  EncodeTiledFn encode = tensor_map_encoder();
+  TcEncodeTiledFn encode = tc_tensor_map_encoder();
   HB_REQUIRE(encode != nullptr, "bitlinear (batched): the driver has no cuTensorMapEncodeTiled");
   for (int s = 0; s < nseg; ++s) {
     p.seg[s] = {static_cast<const uint8_t*>(segs[s].d_packed), segs[s].d_scale,

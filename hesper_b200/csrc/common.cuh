@@ -206,10 +206,13 @@ constexpr size_t kScratchSplitK = (size_t)12 << 20;   // batched ternary: split-
 
 // the two halves of it, also used by the batched k-quant path (weights dequantised to f16)
 int hb_gemm16_split(struct hb200_ctx* ctx, int dtype, int K, const float* d_x, int M,
-                    const float* d_rms_gamma, float rms_eps, cudaStream_t st);
+                    const float* d_rms_gamma, float rms_eps, int single, cudaStream_t st);
 int hb_gemm16_mma(struct hb200_ctx* ctx, const void* d_table, int dtype, long V, int K, int M,
                   float* d_y, const float* d_residual, long ldy, unsigned long long* d_keys,
                   int table_constant, cudaStream_t st);
+// batched Q4_K with the dequantiser fused into the tensor-core kernel, kquant_mma.cu
+int hb_kq_mma_run(struct hb200_ctx* ctx, const uint8_t* d_blocks, int K, long N, int M,
+                  float* d_y, const float* d_residual, long ldy, cudaStream_t st);
 constexpr size_t kArenaBytes = (size_t)64 << 20;  // f16 weights of one batched k-quant product
 
 struct hb200_ctx {

@@ -452,9 +452,11 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
 
 // ---- batched path: dequantise to f16, then the 16-bit tensor-core product ---------------
 //
-// From 16 tokens on the product is a real contraction.  The weights of one product (or a
-// row chunk of it) are dequantised once into a 64 MB f16 arena of the context -- it stays
-// in the 126 MB L2 -- and multiplied by the tensor-core kernel that also serves the LM head
+// From 16 tokens on the product is a real contraction.  Q4_K goes through the kernel of
+// kquant_mma.cu, which dequantises inside the tensor-core pipeline.  Q8_0 takes two kernels:
+// the weights of one product (or a row chunk of it) are dequantised once into a 64 MB f16
+// arena of the context -- it stays in the 126 MB L2 -- and multiplied by the tensor-core
+// kernel that also serves the LM head
 // (tcgen05 kind::f16, activations split into hi + lo f16 so their rounding drops out).
 // f16 weights carry 2^-11 relative rounding each; the measured output error is ~3e-4 of
 // max|y|, inside the 1e-3 bar of this path.  One thread per 8 weights, 16-byte stores.
@@ -527,6 +529,19 @@ __global__ void __launch_bounds__(256) kq_dequant_kernel(const uint8_t* __restri
 static int kq_batched_one(hb200_ctx* ctx, int fmt, const uint8_t* blocks, int K, long N,
                           const float* d_x, int M, const float* gamma, float eps,
                           const float* residual, float* y, cudaStream_t st) {
+  // Q4_K: dequantiser fused into the product kernel (kquant_mma.cu; split-K when there are
+  // few row tiles).  Q8_0 takes the two-kernel route below.
+  if (fmt == HB200_FMT_Q4_K) {
+    for (int m0 = 0; m0 < M; m0 += 64) {
+      const int mc = M - m0 < 64 ? M - m0 : 64;
+      int rc = hb_gemm16_split(ctx, 1, K, d_x + (size_t)m0 * K, mc, gamma, eps, 1, st);
+      if (rc != HB200_OK) return rc;
+      rc = hb_kq_mma_run(ctx, blocks, K, N, mc, y + (size_t)m0 * N,
+                         residual ? residual + (size_t)m0 * N : nullptr, N, st);
+      if (rc != HB200_OK) return rc;
+    }
+    return HB200_OK;
+  }
   const int rowbytes = fmt == HB200_FMT_Q4_K ? K / 256 * 144 : K / 32 * 34;
   long chunk = (long)(kArenaBytes / ((size_t)K * 2)) / 128 * 128;
   HB_REQUIRE(chunk >= 128 && rowbytes <= 48 * 1024,
@@ -551,7 +566,7 @@ static int kq_batched_one(hb200_ctx* ctx, int fmt, const uint8_t* blocks, int K,
                          nr, rowbytes, rpc, arena));
     for (int m0 = 0; m0 < M; m0 += 64) {
       const int mc = M - m0 < 64 ? M - m0 : 64;
-      int rc = hb_gemm16_split(ctx, 1, K, d_x + (size_t)m0 * K, mc, gamma, eps, st);
+      int rc = hb_gemm16_split(ctx, 1, K, d_x + (size_t)m0 * K, mc, gamma, eps, 0, st);
       if (rc != HB200_OK) return rc;
       // the product addresses its output as [m][row] with row stride 1 and token stride N:
       // a row chunk is a column offset into the caller's [M][N] arrays

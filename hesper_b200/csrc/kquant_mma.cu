@@ -1,0 +1,375 @@
+// kquant_mma.cu -- batched (16..64 tokens per pass) Q4_K product with the dequantiser fused
+// into the tensor-core kernel: the weights go from their 4.5-bit blocks to f16 in registers
+// and from there straight into TENSOR MEMORY as the A operand of tcgen05.mma kind::f16; the
+// f16 image of the tensor never exists in global memory.
+//
+// Same contract as the streaming Q4_K kernel (w = d*sc*q - dmin*m, f32 activations in, f32
+// out; the reference's batched counterparts are the M>1 paths of Hesper/Layers/Linear.lean:
+// 1152-1760,5973-6177).  Weights AND activations are rounded to f16 here (2^-11 each; the
+// hi + lo activation split of the LM head would double the activation bytes every CTA pulls
+// from L2, which is what bounds this kernel): measured error ~4e-4 of max|y|, bar 1e-3.
+//
+// One CTA per 128 weight rows, 11 warps with fixed roles:
+//   warp 9     copies: one 2-D tensor-map TMA per super-block column of the tile (128 rows x
+//              144 bytes, a 3-deep ring) and one 16 KB bulk copy of the step's activation
+//              tiles (f16, operand layout written by the split kernel);
+//   warps 0-7  dequantise: per step of 128 weights a thread owns one row and one 64-weight
+//              chunk (two sub-blocks: 6-bit scale and min, 32 low and 32 high nibbles),
+//              computes fma(d*sc, q, -dmin*m) in f32, packs f16 pairs and stores 32 columns
+//              with one tcgen05.st;
+//   warps 8,10 issue the 8 MMAs (M=128, N=64 tokens, K=16) of every other step into their
+//              own f32 accumulator; tcgen05.commit releases the stage.
+// Tensor memory: 2 x 64 accumulator columns + 6 stages x 64 columns of A.  Every wait is
+// bounded; on expiry the kernel still releases its tensor memory.
+#include <cuda_fp16.h>
+
+#include "tcgen05.cuh"
+
+namespace hb {
+
+constexpr int kQmRows = 128;          // weight rows per CTA = MMA M
+constexpr int kQmTokens = 64;         // tokens per pass
+constexpr int kQmN = kQmTokens;       // MMA N
+constexpr int kQmStepK = 128;         // weights per pipeline step (half a super-block)
+constexpr int kQmStages = 6;          // operand stages
+constexpr int kQmACols = kQmStepK / 2;           // 64 TMEM columns of f16 pairs per stage
+constexpr int kQmBBytes = kQmN * kQmStepK * 2;   // 16 KB of activations per step
+constexpr int kQmPkStages = 3;
+constexpr int kQmPkBytes = kQmRows * 144;        // one super-block of every row: 18 KB
+constexpr int kQmAcc0 = 0, kQmAcc1 = 64, kQmA0 = 128;   // TMEM column map
+constexpr int kQmSmem = 1024 + kQmPkStages * kQmPkBytes + kQmStages * kQmBBytes;
+constexpr int kQmThreads = 352;
+static_assert(kQmA0 + kQmStages * kQmACols <= 512, "tensor memory columns");
+static_assert(kQmSmem <= 232448, "shared memory budget of one CTA");
+
+struct QmParams {
+  CUtensorMap tmap;      // blocks as [N rows][rowbytes], boxes of 128 rows x 144 bytes
+  const uint8_t* xb;     // f16 activations: [K/64][64 rows x 64 f16, operand layout]
+  const float* residual; // nullable
+  float* y;              // y[m * ldy + row]
+  long ldy;
+  int K, N, M;
+  int nsplit, bps;       // split-K: CTAs per row tile, super-block boxes per split
+  float* part;           // [tile][split][64 tokens][128 rows] partial sums (nsplit > 1)
+  int* tickets;          // [tile] arrival counters, zero between launches
+  uint32_t idesc;
+  uint32_t* status;
+};
+
+#ifdef HB_PROFILE
+#define QM_STAMP(i, cond)                                                                 \
+  do {                                                                                    \
+    if (blockIdx.x == 0 && (cond)) {                                                      \
+      unsigned long long t_;                                                              \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
+      reinterpret_cast<unsigned long long*>(p.status)[1 + (i)] = t_;                      \
+    }                                                                                     \
+  } while (0)
+#else
+#define QM_STAMP(i, cond) ((void)0)
+#endif
+
+__device__ __forceinline__ uint32_t pack_f16(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_constant__ QmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // this CTA's K range: whole super-blocks (boxes of 256 weights = 2 steps)
+  const int tile = (int)blockIdx.x / p.nsplit, split = (int)blockIdx.x % p.nsplit;
+  const int b0 = split * p.bps;
+  const int nboxes = min(p.bps, p.K / 256 - b0);
+  const int nsteps = 2 * nboxes;
+  const int s0 = 2 * b0;  // first step, in units of the whole row
+  const int row0 = tile * kQmRows;
+  constexpr int kExpWarps = 8, kMmaWarpA = 8, kCopyWarp = 9, kMmaWarpB = 10;
+
+  uint64_t* pk_full = reinterpret_cast<uint64_t*>(smem);  // [3] box landed (tx bytes)
+  uint64_t* pk_free = pk_full + kQmPkStages;               // [3] every expander warp left it
+  uint64_t* full = pk_free + kQmPkStages;   // [6] A stored by 8 warps + activations landed
+  uint64_t* mma_done = full + kQmStages;    // [6] the MMAs that read the stage have retired
+  uint64_t* done = mma_done + kQmStages;    // [1] both issuers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
+  uint8_t* pk = smem + 1024;
+  uint8_t* bstg = pk + kQmPkStages * kQmPkBytes;
+
+  if (tid == 0) {
+    for (int i = 0; i < kQmPkStages; ++i) {
+      mbar_init(&pk_full[i], 1);
+      mbar_init(&pk_free[i], kExpWarps);
+    }
+    for (int i = 0; i < kQmStages; ++i) {
+      mbar_init(&full[i], kExpWarps + 1);
+      mbar_init(&mma_done[i], 1);
+    }
+    mbar_init(done, 2);
+    fence_mbar_init();
+  }
+  if (warp == kMmaWarpA) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(
+        smem_u32(tmem_slot)));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  tc_before_sync();
+  __syncthreads();
+  tc_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  bool ok = true;
+
+  if (warp == kCopyWarp) {
+    // ================= copies ==================================================================
+    const uint64_t pol = policy_evict_first();
+    auto issue_box = [&](int b) {
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&pk_full[b % kQmPkStages], kQmPkBytes);
+        tc_tma_box_2d(pk + (size_t)(b % kQmPkStages) * kQmPkBytes, &p.tmap, (b0 + b) * 144, row0,
+                      &pk_full[b % kQmPkStages], pol);
+      }
+    };
+    int bnext = 0;
+    if (lane == 0)
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&p.tmap)) : "memory");
+    for (; bnext < kQmPkStages && bnext < nboxes; ++bnext) issue_box(bnext);  // weights: constant
+    pdl_trigger();
+    pdl_wait();  // the split activations come from the kernel before this one
+    for (int s = 0; s < nsteps; ++s) {
+      const int st = s % kQmStages;
+      if (s >= kQmStages)
+        ok = tc_wait(ok, &mma_done[st], (uint32_t)(((s / kQmStages) - 1) & 1), p.status);
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&full[st], kQmBBytes);
+        bulk_g2s(bstg + (size_t)st * kQmBBytes, p.xb + (size_t)(s0 + s) * kQmBBytes, kQmBBytes,
+                 &full[st]);
+      }
+      if (bnext < nboxes && mbar_try_wait(&pk_free[bnext % kQmPkStages],
+                                          (uint32_t)(((bnext / kQmPkStages) - 1) & 1))) {
+        issue_box(bnext);
+        ++bnext;
+      }
+    }
+    while (bnext < nboxes) {
+      ok = tc_wait(ok, &pk_free[bnext % kQmPkStages], (uint32_t)(((bnext / kQmPkStages) - 1) & 1),
+                   p.status);
+      if (!ok) break;
+      issue_box(bnext);
+      ++bnext;
+    }
+  } else if (warp == kMmaWarpA || warp == kMmaWarpB) {
+    // ================= MMA issue: even steps -> accumulator 0, odd steps -> accumulator 1 =====
+    const int which = warp == kMmaWarpA ? 0 : 1;
+    const uint32_t tmem_d = tmem + (which ? kQmAcc1 : kQmAcc0);
+    for (int s = which; s < nsteps; s += 2) {
+      const int st = s % kQmStages;
+      ok = tc_wait(ok, &full[st], (uint32_t)((s / kQmStages) & 1), p.status);
+      if (s >= 8 && s < 12) QM_STAMP(12 + 2 * (s - 8), lane == 0);
+      if (lane == 0) {
+        tc_after_sync();
+        const uint32_t a_t = tmem + kQmA0 + (uint32_t)st * kQmACols;
+        const uint32_t bbase = smem_u32(bstg + (size_t)st * kQmBBytes);
+#pragma unroll
+        for (int j = 0; j < kQmStepK / 16; ++j)  // K = 16 per instruction: 8 columns of A
+          tc_mma_f16_ta(tmem_d, a_t + j * 8,
+                        tc_smem_desc(bbase + (j >> 2) * (kQmBBytes / 2) + (j & 3) * 256, 128, 1024, 0),
+                        p.idesc, (s > 1 || j > 0) ? 1u : 0u);
+        tc_commit(&mma_done[st]);
+      }
+      __syncwarp();
+      if (s >= 8 && s < 12) QM_STAMP(13 + 2 * (s - 8), lane == 0);
+    }
+    if (lane == 0) tc_commit(done);
+  } else {
+    // ================= dequantise into tensor memory ==========================================
+    const int q = warp & 3, h = warp >> 2;       // lane quarter, which 64-weight chunk of the step
+    const int erow = q * 32 + lane;
+    const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16) + kQmA0 + 32u * h;
+    for (int s = 0; s < nsteps; ++s) {
+      const int st = s % kQmStages;
+      const int box = s >> 1;
+      const int c = ((s & 1) << 1) + h;          // chunk of the super-block: sub-blocks 2c, 2c+1
+      if ((s & 1) == 0)
+        ok = tc_wait(ok, &pk_full[box % kQmPkStages], (uint32_t)((box / kQmPkStages) & 1), p.status);
+      if (s >= kQmStages) {
+        ok = tc_wait(ok, &mma_done[st], (uint32_t)(((s / kQmStages) - 1) & 1), p.status);
+        tc_after_sync();
+      }
+      // super-block of this row: f16 d, f16 dmin, 12 bytes of 6-bit scales and mins, 128 bytes
+      // of nibbles (Hesper/Quantization/Q4_K_M.lean:13-52,120-144)
+      if (s >= 8 && s < 11) QM_STAMP(4 * (s - 8), tid == 0);
+      const uint8_t* blk = pk + (size_t)(box % kQmPkStages) * kQmPkBytes + (size_t)erow * 144;
+      const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
+      const uint4 qa = *reinterpret_cast<const uint4*>(blk + 16 + 32 * c);
+      const uint4 qb = *reinterpret_cast<const uint4*>(blk + 32 + 32 * c);
+      const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));
+      // scale / min bytes j and j+1 (j = 2c) out of the 12 packed bytes hdr.y, hdr.z, hdr.w
+      uint32_t sc2, m2;  // two 6-bit values each, in bytes 0 and 1
+      if (c < 2) {
+        sc2 = (hdr.y >> (16 * c)) & 0x3F3Fu;
+        m2 = (hdr.z >> (16 * c)) & 0x3F3Fu;
+      } else {
+        const int sh = 16 * (c - 2);
+        sc2 = ((hdr.w >> sh) & 0x0F0Fu) | (((hdr.y >> (sh + 6)) & 0x0303u) << 4);
+        m2 = ((hdr.w >> (sh + 4)) & 0x0F0Fu) | (((hdr.z >> (sh + 6)) & 0x0303u) << 4);
+      }
+      const float ds0 = dd.x * (float)(sc2 & 0xFF), ds1 = dd.x * (float)(sc2 >> 8);
+      const float dm0 = -(dd.y * (float)(m2 & 0xFF)), dm1 = -(dd.y * (float)(m2 >> 8));
+      const uint32_t qq[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+      uint32_t o[32];  // columns 0-15: sub-block 2c (low nibbles), 16-31: sub-block 2c+1 (high)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t w = qq[i];
+        o[2 * i] = pack_f16(fmaf(ds0, (float)(w & 0xF), dm0), fmaf(ds0, (float)((w >> 8) & 0xF), dm0));
+        o[2 * i + 1] = pack_f16(fmaf(ds0, (float)((w >> 16) & 0xF), dm0),
+                                fmaf(ds0, (float)((w >> 24) & 0xF), dm0));
+        o[16 + 2 * i] = pack_f16(fmaf(ds1, (float)((w >> 4) & 0xF), dm1),
+                                 fmaf(ds1, (float)((w >> 12) & 0xF), dm1));
+        o[16 + 2 * i + 1] = pack_f16(fmaf(ds1, (float)((w >> 20) & 0xF), dm1),
+                                     fmaf(ds1, (float)(w >> 28), dm1));
+      }
+      const uint32_t taddr = lane_addr + (uint32_t)st * kQmACols;
+      if (s >= 8 && s < 11) QM_STAMP(4 * (s - 8) + 1, tid == 0);
+      HB_TMEM_ST32(taddr, o);
+      if (s & 1) {  // second half of the super-block: this warp is done with the box
+        __syncwarp();
+        if (lane == 0)
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(
+                           smem_u32(&pk_free[box % kQmPkStages]))
+                       : "memory");
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      if (s >= 8 && s < 11) QM_STAMP(4 * (s - 8) + 2, tid == 0);
+      tc_before_sync();
+      __syncwarp();
+      if (lane == 0)
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full[st]))
+                     : "memory");
+      if (s >= 8 && s < 11) QM_STAMP(4 * (s - 8) + 3, tid == 0);
+    }
+  }
+  ok = tc_wait(true, done, 0, p.status) && ok;
+  tc_after_sync();
+
+  // ---- epilogue: lane = weight row, column = token; the two issuers' accumulators add up ----
+  const int q = warp & 3, half = warp >> 2;  // expander warps: lane quarter, token half
+  const int r = q * 32 + lane, m0 = half * 32;
+  float acc[32];
+  if (warp < kExpWarps) {
+    const uint32_t base = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)m0;
+    uint32_t v[32], u[32];
+    HB_TMEM_LD32(v, base + kQmAcc0);
+    HB_TMEM_LD32(u, base + kQmAcc1);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int t = 0; t < 32; ++t) acc[t] = __fadd_rn(__uint_as_float(v[t]), __uint_as_float(u[t]));
+  }
+  // split-K: every split publishes its partial; the last one to arrive (a ticket per row
+  // tile) adds ALL partials in split order, so the f32 result does not depend on who it was
+  bool finish = true;
+  if (p.nsplit > 1) {
+    __shared__ int s_last;
+    float* mine = p.part + ((size_t)(tile * p.nsplit + split) * kQmTokens) * kQmRows;
+    if (warp < kExpWarps) {
+#pragma unroll
+      for (int t = 0; t < 32; ++t) mine[(size_t)(m0 + t) * kQmRows + r] = acc[t];
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const int t = atomicAdd(&p.tickets[tile], 1);
+      s_last = (t == p.nsplit - 1);
+      if (s_last) p.tickets[tile] = 0;
+    }
+    __syncthreads();
+    finish = s_last != 0;
+    if (finish && warp < kExpWarps) {
+      __threadfence();
+#pragma unroll
+      for (int t = 0; t < 32; ++t) acc[t] = 0.f;
+      for (int s2 = 0; s2 < p.nsplit; ++s2) {
+        const float* other =
+            p.part + ((size_t)(tile * p.nsplit + s2) * kQmTokens + m0) * kQmRows + r;
+#pragma unroll
+        for (int t = 0; t < 32; ++t) acc[t] = __fadd_rn(acc[t], __ldcg(other + (size_t)t * kQmRows));
+      }
+    }
+  }
+  if (finish && warp < kExpWarps) {
+    const int row = row0 + r;
+    if (row < p.N && ok) {
+      const int mcount = min(32, p.M - m0);
+      const size_t o0 = (size_t)m0 * p.ldy + row;
+      float res[32];
+      if (p.residual) {
+#pragma unroll
+        for (int t = 0; t < 32; ++t) res[t] = t < mcount ? p.residual[o0 + (size_t)t * p.ldy] : 0.f;
+      }
+#pragma unroll
+      for (int t = 0; t < 32; ++t)
+        if (t < mcount) p.y[o0 + (size_t)t * p.ldy] = p.residual ? __fadd_rn(acc[t], res[t]) : acc[t];
+    }
+  }
+  tc_before_sync();
+  __syncthreads();
+  if (warp == kMmaWarpA)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem));
+}
+
+}  // namespace hb
+
+using namespace hb;
+
+// y[m*ldy + n] = sum_k dequant(W)[n,k] x[m,k] (+ residual) for the M <= 64 tokens staged by
+// hb_gemm16_split (dtype f16, single term).  Q4_K only; K a multiple of 256.
+int hb_kq_mma_run(hb200_ctx* ctx, const uint8_t* d_blocks, int K, long N, int M, float* d_y,
+                  const float* d_residual, long ldy, cudaStream_t st) {
+  HB_REQUIRE(K % 256 == 0 && N >= 1 && N < (1l << 31) && M >= 1 && M <= kQmTokens,
+             "kquant (fused batched): K=%d N=%ld M=%d", K, N, M);
+  QmParams p = {};
+  TcEncodeTiledFn encode = tc_tensor_map_encoder();
+  HB_REQUIRE(encode != nullptr, "kquant (fused batched): the driver has no cuTensorMapEncodeTiled");
+  const int rowbytes = K / 256 * 144;
+  const cuuint64_t dims[2] = {(cuuint64_t)rowbytes, (cuuint64_t)N};
+  const cuuint64_t strides[1] = {(cuuint64_t)rowbytes};
+  const cuuint32_t box[2] = {144u, (cuuint32_t)kQmRows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult rc = encode(&p.tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                             const_cast<uint8_t*>(d_blocks), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  HB_REQUIRE(rc == CUDA_SUCCESS, "kquant (fused batched): cuTensorMapEncodeTiled failed (%d)",
+             (int)rc);
+  p.xb = static_cast<const uint8_t*>(ctx->d_scratch) + kScratchLmSplit;
+  p.residual = d_residual;
+  p.y = d_y;
+  p.ldy = ldy;
+  p.K = K;
+  p.N = (int)N;
+  p.M = M;
+  // kind::f16: D = f32, A and B f16, both K-major, N = 64, M = 128
+  p.idesc = (1u << 4) | ((uint32_t)(kQmN >> 3) << 17) | ((uint32_t)(kQmRows >> 4) << 24);
+  p.status = ctx->d_status;
+  static bool configured = false;
+  if (!configured) {
+    HB_CUDA(cudaFuncSetAttribute(kq_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kQmSmem));
+    configured = true;
+  }
+  const int tiles = (int)((N + kQmRows - 1) / kQmRows);
+  // split-K when the row tiles alone leave SMs idle: as many splits as fit the SMs, each at
+  // least 2 super-blocks long, partials within their scratch region, tickets within theirs
+  const int nboxes = K / 256;
+  int nsplit = ctx->sm_count / tiles;
+  if (nsplit > nboxes / 2) nsplit = nboxes / 2;
+  while (nsplit > 1 && (size_t)tiles * nsplit * kQmTokens * kQmRows * 4 >
+                           kScratchBytes - kScratchSplitK)
+    --nsplit;
+  if (nsplit < 1 || tiles > kCtxTickets) nsplit = 1;
+  p.bps = (nboxes + nsplit - 1) / nsplit;
+  p.nsplit = (nboxes + p.bps - 1) / p.bps;  // no empty split
+  p.part = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->d_scratch) + kScratchSplitK);
+  p.tickets = ctx->d_tickets;
+  HB_CUDA(launch_pdl(kq_mma_kernel, dim3((unsigned)(tiles * p.nsplit)), dim3(kQmThreads),
+                     (size_t)kQmSmem, st, ctx->pdl, p));
+  return HB200_OK;
+}

@@ -27,11 +27,10 @@
 //             per-token argmax over the tile's 128 rows (redux + ballot), then one
 //             atomicMax of the ordered (value,row) key per token.
 // Every mbarrier wait is bounded; on expiry the kernel still releases its tensor memory.
-#include <cuda.h>  // CUtensorMap and its enums only; the encoder comes from the runtime
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace hb {
 
@@ -44,7 +43,6 @@ constexpr int kLmMaxStages = 6;   // stages of a CTA alone on its SM (few row ti
 constexpr int kLmABytes = kLmRows * kLmKStep * 2;  // 16 KB
 constexpr int kLmBBytes = kLmN * kLmKStep * 2;     // 16 KB
 constexpr int kLmCtrl = 4096;     // barriers, tensor-memory slot, per-warp argmax keys
-constexpr int kLmSmem = kLmCtrl + kLmStages * (kLmABytes + kLmBBytes);
 constexpr int kLmThreads = 192;
 
 struct LmSplitParams {
@@ -52,6 +50,7 @@ struct LmSplitParams {
   const float* gamma;  // nullable
   float eps;
   int K, M, dtype;     // dtype 0 = bf16, 1 = f16
+  int single;          // 1: only the hi term, 64 rows per block (8 KB blocks)
   uint8_t* xb;         // [K/64][16 KB] operand blocks
 };
 
@@ -85,14 +84,15 @@ __global__ void __launch_bounds__(256) lm_split_kernel(const __grid_constant__ L
   const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = p.K;
   // 8 consecutive k of token row `row` -> their 16 bytes in the operand block
+  const size_t blk_bytes = p.single ? kLmBBytes / 2 : kLmBBytes;
   auto dst = [&](int row, int k) {
-    return p.xb + (size_t)(k >> 6) * kLmBBytes + (size_t)(row >> 3) * 1024 +
+    return p.xb + (size_t)(k >> 6) * blk_bytes + (size_t)(row >> 3) * 1024 +
            (size_t)((k & 63) >> 3) * 128 + (size_t)(row & 7) * 16;
   };
   if (m >= p.M) {
     for (int k = tid * 8; k < K; k += 256 * 8) {
       *reinterpret_cast<uint4*>(dst(m, k)) = make_uint4(0, 0, 0, 0);
-      *reinterpret_cast<uint4*>(dst(kLmTokens + m, k)) = make_uint4(0, 0, 0, 0);
+      if (!p.single) *reinterpret_cast<uint4*>(dst(kLmTokens + m, k)) = make_uint4(0, 0, 0, 0);
     }
     return;
   }
@@ -128,25 +128,12 @@ __global__ void __launch_bounds__(256) lm_split_kernel(const __grid_constant__ L
       lo[j] = (uint32_t)l[0] | ((uint32_t)l[1] << 16);
     }
     *reinterpret_cast<uint4*>(dst(m, k)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-    *reinterpret_cast<uint4*>(dst(kLmTokens + m, k)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    if (!p.single)
+      *reinterpret_cast<uint4*>(dst(kLmTokens + m, k)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
   }
 }
 
-// ---- tcgen05 helpers -----------------------------------------------------------------
-
-// K-major shared-memory matrix descriptor.  layout 0: no swizzle, core matrices of 8 rows x
-// 16 bytes, LBO = distance between core matrices adjacent in K, SBO = between 8-row groups.
-// layout 2: 128-byte swizzle, rows of 128 bytes in 1 KB atoms of 8 rows, SBO = 1024.
-__device__ __forceinline__ uint64_t lm_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo,
-                                            uint32_t layout) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
-  d |= (uint64_t)1 << 46;  // descriptor version of this architecture
-  d |= (uint64_t)layout << 61;
-  return d;
-}
+// kind::f16 with both operands through shared-memory descriptors.
 __device__ __forceinline__ void lm_umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
                                             uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -155,48 +142,6 @@ __device__ __forceinline__ void lm_umma_f16(uint32_t tmem_d, uint64_t adesc, uin
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ void lm_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void lm_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void lm_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void lm_tma_box(void* dst, const CUtensorMap* tm, int x, int y,
-                                           uint64_t* bar, uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
-      ".L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(dst)),
-      "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
-      : "memory");
-}
-// Bounded wait (about a tenth of a second at worst); later waits are skipped after a failure.
-__device__ __forceinline__ bool lm_wait(bool ok, uint64_t* bar, uint32_t parity,
-                                        uint32_t* status) {
-  if (!ok) return false;
-#pragma unroll 1
-  for (uint32_t it = 0; it < (1u << 18); ++it)
-    if (mbar_try_wait(bar, parity)) return true;
-  atomicOr(status, kStatusMbarTimeout);
-  return false;
-}
-
-#define LM_TMEM_LD32(v, addr)                                                                  \
-  asm volatile(                                                                                \
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                \
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"                                \
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"               \
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),    \
-        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]),             \
-        "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),          \
-        "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),          \
-        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),          \
-        "=r"(v[31])                                                                            \
-      : "r"(addr))
 
 __global__ void __launch_bounds__(kLmThreads, 2)
     lmhead_mma_kernel(const __grid_constant__ LmMmaParams p) {
@@ -226,9 +171,9 @@ __global__ void __launch_bounds__(kLmThreads, 2)
         smem_u32(tmem_slot)));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
-  lm_fence_before();
+  tc_before_sync();
   __syncthreads();
-  lm_fence_after();
+  tc_after_sync();
   const uint32_t tmem = *tmem_slot;
   bool ok = true;
 
@@ -238,7 +183,7 @@ __global__ void __launch_bounds__(kLmThreads, 2)
     auto issue_a = [&](int ks) {
       const int st = ks % S;
       mbar_arrive_expect_tx(&full[st], kLmABytes);
-      lm_tma_box(stg + (size_t)st * (kLmABytes + kLmBBytes), &p.tmap, ks * kLmKStep, (int)row0,
+      tc_tma_box_2d(stg + (size_t)st * (kLmABytes + kLmBBytes), &p.tmap, ks * kLmKStep, (int)row0,
                  &full[st], pol);
     };
     auto issue_b = [&](int ks) {
@@ -264,7 +209,7 @@ __global__ void __launch_bounds__(kLmThreads, 2)
         issue_b(ks);
       }
     for (int ks = pre; ks < nsteps; ++ks) {
-      ok = lm_wait(ok, &empty[ks % S], (uint32_t)(((ks / S) - 1) & 1), p.status);
+      ok = tc_wait(ok, &empty[ks % S], (uint32_t)(((ks / S) - 1) & 1), p.status);
       if (lane == 0 && ok) {
         issue_a(ks);
         issue_b(ks);
@@ -274,26 +219,26 @@ __global__ void __launch_bounds__(kLmThreads, 2)
     // ================= MMA issuer ===========================================================
     for (int ks = 0; ks < nsteps; ++ks) {
       const int st = ks % S;
-      ok = lm_wait(ok, &full[st], (uint32_t)((ks / S) & 1), p.status);
+      ok = tc_wait(ok, &full[st], (uint32_t)((ks / S) & 1), p.status);
       if (lane == 0) {
-        lm_fence_after();
+        tc_after_sync();
         const uint32_t abase = smem_u32(stg + (size_t)st * (kLmABytes + kLmBBytes));
         const uint32_t bbase = abase + kLmABytes;
 #pragma unroll
         for (int j = 0; j < kLmKStep / 16; ++j)  // K = 16 elements = 32 bytes per instruction
-          lm_umma_f16(tmem, lm_desc(abase + j * 32, 0, 1024, 2),
-                      lm_desc(bbase + j * 256, 128, 1024, 0), p.idesc,
+          lm_umma_f16(tmem, tc_smem_desc(abase + j * 32, 0, 1024, 2),
+                      tc_smem_desc(bbase + j * 256, 128, 1024, 0), p.idesc,
                       (ks > 0 || j > 0) ? 1u : 0u);
-        lm_commit(&empty[st]);
+        tc_commit(&empty[st]);
       }
       __syncwarp();
     }
-    if (lane == 0) lm_commit(done);
+    if (lane == 0) tc_commit(done);
   }
   // ================= epilogue (warps 2..5) ====================================================
   if (warp >= 2) {
-    ok = lm_wait(true, done, 0, p.status);
-    lm_fence_after();
+    ok = tc_wait(true, done, 0, p.status);
+    tc_after_sync();
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const long row = row0 + q * 32 + lane;
     const bool row_ok = row < p.V;
@@ -306,8 +251,8 @@ __global__ void __launch_bounds__(kLmThreads, 2)
         continue;
       }
       uint32_t hi[32], lo[32];
-      LM_TMEM_LD32(hi, lane_addr + (uint32_t)(half * 32));
-      LM_TMEM_LD32(lo, lane_addr + (uint32_t)(kLmTokens + half * 32));
+      HB_TMEM_LD32(hi, lane_addr + (uint32_t)(half * 32));
+      HB_TMEM_LD32(lo, lane_addr + (uint32_t)(kLmTokens + half * 32));
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       unsigned long long mine = 0ull;  // lane t keeps the key of token half*32 + t
 #pragma unroll
@@ -350,7 +295,7 @@ __global__ void __launch_bounds__(kLmThreads, 2)
       }
     }
   }
-  lm_fence_before();
+  tc_before_sync();
   __syncthreads();
   if (warp == 1)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 128;" ::"r"(tmem));
@@ -360,33 +305,15 @@ __global__ void __launch_bounds__(kLmThreads, 2)
 
 using namespace hb;
 
-namespace {
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn lm_tensor_map_encoder() {
-  static EncodeTiledFn fn = [] {
-    void* f = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) !=
-            cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      f = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(f);
-  }();
-  return fn;
-}
-}  // namespace
-
 // x[M][K] (M <= 64) -> hi/lo 16-bit operand blocks in the context scratch, optional RMSNorm.
+// single != 0: only the rounded value (no lo term), 64 rows and 8 KB per 64-wide K block.
 int hb_gemm16_split(hb200_ctx* ctx, int dtype, int K, const float* d_x, int M,
-                    const float* d_rms_gamma, float rms_eps, cudaStream_t st) {
+                    const float* d_rms_gamma, float rms_eps, int single, cudaStream_t st) {
   const size_t xb_bytes = (size_t)(K / kLmKStep) * kLmBBytes;
   HB_REQUIRE(kScratchLmSplit + xb_bytes <= kScratchSplitK,
              "batched 16-bit product: K=%d needs %zu bytes of activation scratch", K, xb_bytes);
   uint8_t* xb = static_cast<uint8_t*>(ctx->d_scratch) + kScratchLmSplit;
-  LmSplitParams sp = {d_x, d_rms_gamma, rms_eps, K, M, dtype, xb};
+  LmSplitParams sp = {d_x, d_rms_gamma, rms_eps, K, M, dtype, single, xb};
   HB_CUDA(launch_pdl(lm_split_kernel, dim3(kLmTokens), dim3(256), 0, st, ctx->pdl, sp));
   return HB200_OK;
 }
@@ -400,7 +327,7 @@ int hb_gemm16_mma(hb200_ctx* ctx, const void* d_table, int dtype, long V, int K,
   HB_REQUIRE(V >= 1 && V < (1l << 31), "batched 16-bit product: bad row count");
   uint8_t* xb = static_cast<uint8_t*>(ctx->d_scratch) + kScratchLmSplit;
   LmMmaParams p = {};
-  EncodeTiledFn encode = lm_tensor_map_encoder();
+  TcEncodeTiledFn encode = tc_tensor_map_encoder();
   HB_REQUIRE(encode != nullptr, "batched 16-bit product: the driver has no cuTensorMapEncodeTiled");
   const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)V};
   const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
@@ -446,7 +373,7 @@ int hb_gemm16_mma(hb200_ctx* ctx, const void* d_table, int dtype, long V, int K,
 int hb_lmhead_mma_run(hb200_ctx* ctx, const void* d_table, int dtype, long V, int K,
                       const float* d_x, int M, const float* d_rms_gamma, float rms_eps,
                       float* d_logits, unsigned long long* d_keys, cudaStream_t st) {
-  const int rc = hb_gemm16_split(ctx, dtype, K, d_x, M, d_rms_gamma, rms_eps, st);
+  const int rc = hb_gemm16_split(ctx, dtype, K, d_x, M, d_rms_gamma, rms_eps, 0, st);
   if (rc != HB200_OK) return rc;
   return hb_gemm16_mma(ctx, d_table, dtype, V, K, M, d_logits, nullptr, V, d_keys, 1, st);
 }
