@@ -27,8 +27,9 @@ struct hb200_bitnet {
   int embed_dtype;
   const float* final_norm;
   int B;
+  int Mmax;  // token rows the activation buffers hold: max(B, B * prefill chunk length)
   // device state
-  float *x, *x1, *q, *k, *v, *att, *h, *logits;
+  float *x, *x1, *q, *k, *v, *att, *h, *logits, *xlast;
   __half *kcache, *vcache;  // [layer][B][Hkv][max_seq][D]
   int32_t *pos, *len, *tok, *log_index, *token_log;
   void* lm_scratch;
@@ -99,6 +100,65 @@ int enqueue_step(hb200_bitnet* m, const int32_t* d_tokens, bool lm_head, cudaStr
   return hb200_add_i32(ctx, m->pos, 2 * B, 1, st);
 }
 
+// Prompt chunk: T consecutive positions of every sequence in one pass (tokens [B][T] on the
+// device, B*T <= 64).  The linear layers run batched on the tensor cores (bit-identical to
+// the single-token kernels), RoPE/KV write and causal attention through their prefill entry
+// points.  Positions advance by T.  With lm_head the last position's argmax is taken.
+int enqueue_prefill_chunk(hb200_bitnet* m, const int32_t* d_tokens, int T, bool lm_head,
+                          cudaStream_t st) {
+  const hb200_bitnet_config& c = m->cfg;
+  hb200_ctx* ctx = m->ctx;
+  const int B = m->B, M = B * T, Hd = c.hidden;
+  const int qdim = c.n_heads * c.head_dim, kvdim = c.n_kv_heads * c.head_dim;
+  int rc = hb200_embed_lookup(ctx, m->embed, m->embed_dtype, c.vocab, Hd, d_tokens, M, 1.0f, m->x, st);
+  if (rc) return rc;
+  // len = pos + 1 between steps; the prefill entry points want the length after all T tokens
+  rc = hb200_add_i32(ctx, m->len, B, T - 1, st);
+  if (rc) return rc;
+  const float scale = 1.0f / sqrtf((float)c.head_dim);
+  for (int l = 0; l < c.n_layers; ++l) {
+    const hb200_bitnet_layer& L = m->layers[l];
+    hb200_bitlinear_seg segs[3] = {
+        {L.wq, L.sq, nullptr, m->q, nullptr, qdim},
+        {L.wk, L.sk, nullptr, m->k, nullptr, kvdim},
+        {L.wv, L.sv, nullptr, m->v, nullptr, kvdim},
+    };
+    rc = hb200_bitlinear_forward_multi(ctx, segs, 3, Hd, m->x, M, L.attn_norm, c.rms_eps, nullptr, st);
+    if (rc) return rc;
+    __half* kc = m->kcache + (size_t)l * layer_cache_elems(m);
+    __half* vc = m->vcache + (size_t)l * layer_cache_elems(m);
+    rc = hb200_rope_kv_write_prefill(ctx, m->q, m->k, m->v, kc, vc, m->pos, B, T, c.n_heads,
+                                     c.n_kv_heads, c.head_dim, c.max_seq, c.rope_base, st);
+    if (rc) return rc;
+    rc = hb200_attn_prefill(ctx, m->q, 0, kc, vc, m->len, B, T, c.n_heads, c.n_kv_heads, c.head_dim,
+                            c.max_seq, 0, scale, m->attn_ws, m->attn_ws_bytes, m->att, st);
+    if (rc) return rc;
+    rc = hb200_bitlinear_forward(ctx, L.wo, L.so, qdim, Hd, m->att, M, L.attn_sub_norm, c.rms_eps,
+                                 m->x, nullptr, nullptr, m->x1, st);
+    if (rc) return rc;
+    rc = hb200_bitlinear_gateup_relu2(ctx, L.wgate, L.sgate, L.wup, L.sup, Hd, c.ffn, m->x1, M,
+                                      L.ffn_norm, c.rms_eps, m->h, st);
+    if (rc) return rc;
+    rc = hb200_bitlinear_forward(ctx, L.wdown, L.sdown, c.ffn, Hd, m->h, M, L.ffn_sub_norm,
+                                 c.rms_eps, m->x1, nullptr, nullptr, m->x, st);
+    if (rc) return rc;
+  }
+  if (lm_head) {
+    // hidden state of each sequence's last position -> [B][Hd]
+    HB_CUDA(cudaMemcpy2DAsync(m->xlast, (size_t)Hd * 4, m->x + (size_t)(T - 1) * Hd,
+                              (size_t)T * Hd * 4, (size_t)Hd * 4, B, cudaMemcpyDeviceToDevice, st));
+    rc = hb200_lmhead_argmax(ctx, m->embed, m->embed_dtype, c.vocab, Hd, m->xlast, B, m->final_norm,
+                             c.rms_eps, m->want_logits ? m->logits : nullptr, m->tok,
+                             m->lm_scratch, m->token_log, m->log_index, m->log_stride, st);
+    if (rc) return rc;
+    rc = hb200_add_i32(ctx, m->log_index, 1, 1, st);
+    if (rc) return rc;
+  }
+  rc = hb200_add_i32(ctx, m->pos, B, T, st);  // pos += T
+  if (rc) return rc;
+  return hb200_add_i32(ctx, m->len, B, 1, st);  // len = pos + 1 again
+}
+
 }  // namespace
 
 extern "C" int hb200_bitnet_create(hb200_ctx* ctx, const hb200_bitnet_config* cfg,
@@ -124,15 +184,20 @@ extern "C" int hb200_bitnet_create(hb200_ctx* ctx, const hb200_bitnet_config* cf
   m->log_stride = max_new_tokens > 0 ? max_new_tokens : 1;
   m->want_logits = false;
   const int B = batch, qdim = cfg->n_heads * cfg->head_dim, kvdim = cfg->n_kv_heads * cfg->head_dim;
+  // prompt chunks of T = 64 / B positions run batched: the buffers hold B * T token rows
+  const int Tmax = 64 / B;
+  const size_t R = (size_t)B * (Tmax > 1 ? Tmax : 1);
+  m->Mmax = (int)R;
   cudaError_t e = cudaSuccess;
   auto A = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
-  A(dalloc(&m->x, (size_t)B * cfg->hidden));
-  A(dalloc(&m->x1, (size_t)B * cfg->hidden));
-  A(dalloc(&m->q, (size_t)B * qdim));
-  A(dalloc(&m->k, (size_t)B * kvdim));
-  A(dalloc(&m->v, (size_t)B * kvdim));
-  A(dalloc(&m->att, (size_t)B * qdim));
-  A(dalloc(&m->h, (size_t)B * cfg->ffn));
+  A(dalloc(&m->x, R * cfg->hidden));
+  A(dalloc(&m->x1, R * cfg->hidden));
+  A(dalloc(&m->q, R * qdim));
+  A(dalloc(&m->k, R * kvdim));
+  A(dalloc(&m->v, R * kvdim));
+  A(dalloc(&m->att, R * qdim));
+  A(dalloc(&m->h, R * cfg->ffn));
+  A(dalloc(&m->xlast, (size_t)B * cfg->hidden));
   A(dalloc(&m->logits, (size_t)B * cfg->vocab));
   const size_t cache = (size_t)cfg->n_layers * layer_cache_elems(m);
   A(dalloc(&m->kcache, cache));
@@ -145,6 +210,11 @@ extern "C" int hb200_bitnet_create(hb200_ctx* ctx, const hb200_bitnet_config* cf
   A(cudaMalloc(&m->lm_scratch, hb200_lmhead_scratch_bytes(B)));
   m->attn_ws_bytes = hb200_attn_workspace_bytes(ctx, B, cfg->n_heads, cfg->n_kv_heads,
                                                 cfg->head_dim, cfg->max_seq);
+  if (Tmax > 1) {
+    const size_t pw = hb200_attn_prefill_workspace_bytes(ctx, B, Tmax, cfg->n_heads,
+                                                         cfg->n_kv_heads, cfg->head_dim, cfg->max_seq);
+    if (pw > m->attn_ws_bytes) m->attn_ws_bytes = pw;
+  }
   A(cudaMalloc(&m->attn_ws, m->attn_ws_bytes));
   if (e == cudaSuccess) e = cudaMemset(m->kcache, 0, cache * sizeof(__half));
   if (e == cudaSuccess) e = cudaMemset(m->vcache, 0, cache * sizeof(__half));
@@ -161,6 +231,7 @@ extern "C" int hb200_bitnet_destroy(hb200_bitnet* m) {
   if (!m) return HB200_OK;
   cudaFree(m->x); cudaFree(m->x1); cudaFree(m->q); cudaFree(m->k); cudaFree(m->v);
   cudaFree(m->att); cudaFree(m->h); cudaFree(m->logits); cudaFree(m->kcache); cudaFree(m->vcache);
+  cudaFree(m->xlast);
   cudaFree(m->pos); cudaFree(m->tok); cudaFree(m->log_index); cudaFree(m->token_log);
   cudaFree(m->lm_scratch); cudaFree(m->attn_ws);
   delete m;
@@ -212,12 +283,18 @@ extern "C" int hb200_bitnet_generate(hb200_bitnet* m, const int32_t* h_prompt, i
     stream = own;
   }
   m->want_logits = false;
-  // prompt tokens, position-major so each step reads a contiguous [B] slice
+  // prompt tokens in the order the prefill consumes them: chunks of T positions, each chunk
+  // sequence-major [B][t]; with T = 1 that is position-major, a contiguous [B] slice per step
+  const int T = m->Mmax / B > 1 ? m->Mmax / B : 1;
   int32_t* d_prompt = nullptr;
   HB_CUDA(cudaMalloc(&d_prompt, sizeof(int32_t) * (size_t)B * prompt_len));
   std::vector<int32_t> pm((size_t)B * prompt_len);
-  for (int b = 0; b < B; ++b)
-    for (int p = 0; p < prompt_len; ++p) pm[(size_t)p * B + b] = h_prompt[(size_t)b * prompt_len + p];
+  for (int p0 = 0; p0 < prompt_len; p0 += T) {
+    const int t = prompt_len - p0 < T ? prompt_len - p0 : T;
+    for (int b = 0; b < B; ++b)
+      for (int i = 0; i < t; ++i)
+        pm[(size_t)p0 * B + (size_t)b * t + i] = h_prompt[(size_t)b * prompt_len + p0 + i];
+  }
   cudaError_t e = cudaMemcpyAsync(d_prompt, pm.data(), pm.size() * sizeof(int32_t),
                                   cudaMemcpyHostToDevice, st);
   cudaEvent_t e0, e1, e2;
@@ -232,11 +309,16 @@ extern "C" int hb200_bitnet_generate(hb200_bitnet* m, const int32_t* h_prompt, i
     if (own) cudaStreamDestroy(own);
   };
   if (e != cudaSuccess) { cleanup(); return cuda_fail(e, "prompt upload"); }
-  // ---- prefill: one single-token forward per prompt position (as BitNet.generate :623-625);
-  //      only the last one needs the LM head, whose argmax is the first new token ----
+  // ---- prefill: the reference runs one single-token forward per prompt position
+  //      (BitNet.generate :623-625); here chunks of T = 64 / B positions go through the
+  //      batched kernels and causal prefill attention.  Only the last position needs the LM
+  //      head, whose argmax is the first new token ----
   cudaEventRecord(e0, st);
-  for (int p = 0; p < prompt_len; ++p) {
-    rc = enqueue_step(m, d_prompt + (size_t)p * B, p == prompt_len - 1, st);
+  for (int p0 = 0; p0 < prompt_len; p0 += T) {
+    const int t = prompt_len - p0 < T ? prompt_len - p0 : T;
+    const bool last = p0 + t == prompt_len;
+    rc = t > 1 ? enqueue_prefill_chunk(m, d_prompt + (size_t)p0 * B, t, last, st)
+               : enqueue_step(m, d_prompt + (size_t)p0 * B, last, st);
     if (rc) { cleanup(); return rc; }
   }
   cudaEventRecord(e1, st);

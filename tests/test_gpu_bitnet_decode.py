@@ -103,6 +103,29 @@ def test_generate_graph_equals_stepwise(ctx):
     model.close()
 
 
+@pytest.mark.parametrize("batch,plen", [(3, 50), (1, 130), (40, 5)])
+def test_chunked_prefill_equals_stepwise(ctx, batch, plen):
+    """generate() consumes the prompt in chunks of 64 // batch positions through the batched
+    tensor-core kernels and causal prefill attention (ragged last chunk; batch 40 falls back to
+    single positions); explicit single-token steps over the same prompt must give the same
+    tokens."""
+    import dataclasses
+    shape = dataclasses.replace(SMALL, max_seq=192)
+    w = random_bitnet_weights(shape, seed=9)
+    prompt = np.random.default_rng(plen).integers(0, shape.vocab, (batch, plen)).astype(np.int32)
+    model = BitNetModel(ctx, shape, w, batch=batch, max_new_tokens=12)
+    a, _, _ = model.generate(prompt, 12, use_graph=True)
+    model.reset()
+    out = []
+    for t in range(plen + 11):
+        inp = torch.from_numpy(prompt[:, t].copy()).cuda() if t < plen else None
+        tok, _ = model.step(inp)
+        if t >= plen - 1:
+            out.append(tok.copy())
+    assert np.array_equal(np.stack(out, 1), a)
+    model.close()
+
+
 def test_full_size_bitnet2b_forced_64_steps(ctx, oracle):
     """BASELINE config 3 shape (30 layers, hidden 2560, 20/5 heads, FFN 6912, vocab 128256),
     short prompt, 64 teacher-forced greedy steps against the CPU oracle."""
