@@ -519,7 +519,7 @@ static int bl_pick_rt(const hb200_ctx* ctx, long rows_total) {
 static int bl_check_common(hb200_ctx* ctx, int K, int M, const float* d_x) {
   HB_REQUIRE(ctx != nullptr, "bitlinear: null context");
   HB_REQUIRE(K > 0 && K % 128 == 0, "bitlinear: K=%d must be a positive multiple of 128", K);
-  HB_REQUIRE(M >= 1 && M <= 64, "bitlinear: M=%d outside 1..64", M);
+  HB_REQUIRE(M >= 1 && M <= 4096, "bitlinear: M=%d outside 1..4096", M);
   HB_REQUIRE(d_x != nullptr, "bitlinear: null activation pointer");
   HB_REQUIRE((reinterpret_cast<uintptr_t>(d_x) & 15) == 0, "bitlinear: x must be 16-byte aligned");
   return HB200_OK;
@@ -547,6 +547,23 @@ extern "C" int hb200_bitlinear_forward_multi(hb200_ctx* ctx, const hb200_bitline
     rows += segs[s].N;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M > 64) {  // 64 tokens per pass
+    for (int m0 = 0; m0 < M; m0 += 64) {
+      const int mc = M - m0 < 64 ? M - m0 : 64;
+      hb200_bitlinear_seg sub[kBLMaxSeg];
+      for (int s = 0; s < nseg; ++s) {
+        sub[s] = segs[s];
+        const size_t o = (size_t)m0 * segs[s].N;
+        sub[s].d_y = segs[s].d_y + o;
+        if (segs[s].d_residual) sub[s].d_residual = segs[s].d_residual + o;
+        if (segs[s].d_acc) sub[s].d_acc = segs[s].d_acc + o;
+      }
+      rc = hb200_bitlinear_forward_multi(ctx, sub, nseg, K, d_x + (size_t)m0 * K, mc, d_rms_gamma,
+                                         rms_eps, d_act_scale ? d_act_scale + m0 : nullptr, stream);
+      if (rc) return rc;
+    }
+    return HB200_OK;
+  }
   // 16 or more tokens: a real contraction -> tensor cores (weights still streamed once)
   if (M >= 16 && K <= 12288 && !ctx->no_mma)
     return hb_bitlinear_mma_run(ctx, segs, nseg, K, d_x, M, d_rms_gamma, rms_eps, d_act_scale, st);
@@ -594,6 +611,16 @@ extern "C" int hb200_bitlinear_gateup_relu2(hb200_ctx* ctx, const void* d_packed
   HB_REQUIRE(((reinterpret_cast<uintptr_t>(d_packed_gate) |
                reinterpret_cast<uintptr_t>(d_packed_up)) & 15) == 0,
              "bitlinear gate/up: weights must be 16-byte aligned");
+  if (M > 64) {  // 64 tokens per pass
+    for (int m0 = 0; m0 < M; m0 += 64) {
+      const int mc = M - m0 < 64 ? M - m0 : 64;
+      rc = hb200_bitlinear_gateup_relu2(ctx, d_packed_gate, d_scale_gate, d_packed_up, d_scale_up,
+                                        K, N, d_x + (size_t)m0 * K, mc, d_rms_gamma, rms_eps,
+                                        d_y + (size_t)m0 * N, stream);
+      if (rc) return rc;
+    }
+    return HB200_OK;
+  }
   if (M >= 16 && K <= 12288 && !ctx->no_mma &&
       kScratchGlu + (size_t)2 * M * N * sizeof(float) <= kScratchLmSplit) {
     // batched: both products on the tensor cores into scratch, then the GLU epilogue

@@ -120,7 +120,8 @@ typedef struct hb200_bitlinear_seg {
  *   d_x          [M][K] f32 activations
  *   d_rms_gamma  nullable [K]; when set x is replaced by RMSNorm(x)*gamma, eps = rms_eps
  *   d_act_scale  nullable [M]; receives d[m]
- * K must be a multiple of 128, 1 <= M <= 64.  From 16 tokens on (and K <= 12288) the
+ * K must be a multiple of 128, 1 <= M <= 4096 (64 tokens per pass).  From 16 tokens on (and
+ * K <= 12288) the
  * product runs on the tensor cores (tcgen05 kind::i8, accumulators in tensor memory,
  * the M>1 role of Hesper/Layers/BitLinear.lean:122,869,994) with identical results. */
 int hb200_bitlinear_forward(hb200_ctx *ctx, const void *d_packed, const float *d_scale,
@@ -160,8 +161,13 @@ typedef struct hb200_kquant_seg {
  * Replaces LinearLayer.forward / forwardDP4A (Hesper/Layers/Linear.lean:7115,5713)
  * and is what the hook Linear.llamaCppDp4aOverride (:65-72, consumed :5723-5740)
  * binds to: (inputF32Ptr, weightPtr, outputF32Ptr, inDim, outDim, quantTag).
- *   fmt  HB200_FMT_Q4_K (K % 256 == 0) or HB200_FMT_Q8_0 (K % 32 == 0)
- *   d_rms_gamma nullable: RMSNorm prologue as forwardFusedRMSNormLinear (:7897 region) */
+ *   fmt  HB200_FMT_Q4_K or HB200_FMT_Q8_0; K a multiple of 256; 1 <= M <= 4096
+ *   d_rms_gamma nullable: RMSNorm prologue as forwardFusedRMSNormLinear (:7897 region)
+ * Up to 15 tokens stream the weights once per token through the dp4a kernel (activations
+ * block-quantised to 16 bits, error ~2e-5).  From 16 tokens on the product runs on the
+ * tensor cores, 64 tokens per pass: Q4_K is dequantised to f16 inside the tcgen05 kernel,
+ * Q8_0 through an f16 arena of the context; weights rounded to f16, error ~4e-4 of max|y|
+ * (the bar of this path is 1e-3). */
 int hb200_kquant_forward(hb200_ctx *ctx, int fmt, const void *d_blocks, int K, int N,
                          const float *d_x, int M, const float *d_rms_gamma, float rms_eps,
                          const float *d_residual, float *d_y, hb200_stream stream);

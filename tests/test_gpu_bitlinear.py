@@ -117,7 +117,8 @@ def test_fused_qkv_multi(ctx, oracle):
 
 
 @pytest.mark.parametrize("K,N,M", [(2560, 6912, 64), (6912, 2560, 64), (2560, 2560, 33),
-                                   (128, 1, 16), (1152, 129, 20), (8192, 257, 48)])
+                                   (128, 1, 16), (1152, 129, 20), (8192, 257, 48),
+                                   (2560, 640, 150)])
 def test_batched_tensor_core_path_bit_exact(ctx, oracle, K, N, M):
     """16 or more tokens run on tcgen05 (kind::i8, accumulators in tensor memory): the int32
     results must still be bit-exact, including ragged row tiles, partial K chunks and the
