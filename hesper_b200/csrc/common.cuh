@@ -2,7 +2,6 @@
 // completed on mbarriers with bounded waits, programmatic dependent launch,
 // mixed-sign dp4a, warp reductions, and the host-side context / error plumbing.
 #pragma once
-#include <stdlib.h>
 
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -169,29 +168,9 @@ int cuda_fail(cudaError_t e, const char* what);
 
 // Launch with the programmatic-stream-serialisation attribute so consecutive
 // kernels of a decode step overlap their weight prefetch with the predecessor.
-// Every kernel asks for the largest shared-memory carve-out, whatever it uses itself: the
-// kernels of a decode step differ widely in shared memory, and an SM that has to change its
-// L1/shared split between two dependent launches drains first.
-inline void prefer_max_shared(const void* kernel) {
-  static const void* seen[64];
-  static int nseen = 0;
-  static int mode = -1;  // HB200_CARVEOUT=0 leaves the default split
-  if (mode < 0) {
-    const char* e = getenv("HB200_CARVEOUT");
-    mode = (e && e[0] == '0') ? 0 : 1;
-  }
-  if (!mode) return;
-  for (int i = 0; i < nseen; ++i)
-    if (seen[i] == kernel) return;
-  if (nseen < 64) seen[nseen++] = kernel;
-  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                       cudaSharedmemCarveoutMaxShared);
-}
-
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                               cudaStream_t stream, bool pdl, Args&&... args) {
-  prefer_max_shared(reinterpret_cast<const void*>(kernel));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
