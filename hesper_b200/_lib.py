@@ -82,6 +82,8 @@ SIGNATURES = {
     "hb200_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _f, _i, _i, _vp, _vp]),
     "hb200_rope_kv_write": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "hb200_argmax": (_i, [_vp, _vp, C.c_long, _i, _vp, _vp]),
+    "hb200_rope_kv_write_angles": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "hb200_rope_table": (_i, [_vp, _vp, _i, _i, _i, _f, _vp, _vp]),
     "hb200_lmhead_scratch_bytes": (_sz, [_i]),
     "hb200_lmhead_argmax": (_i, [_vp, _vp, _i, C.c_long, _i, _vp, _i, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "hb200_relu2_mul": (_i, [_vp, _vp, _vp, C.c_long, _vp, _vp]),

@@ -65,8 +65,8 @@ extern "C" int hb200_ctx_create(int device, hb200_ctx** out) {
     return cuda_fail(e, "cudaMalloc(status)");
   }
   e = cudaMemset(c->d_status, 0, 256);
-  if (e == cudaSuccess) e = cudaMalloc(&c->d_tickets, sizeof(int) * kCtxTickets);
-  if (e == cudaSuccess) e = cudaMemset(c->d_tickets, 0, sizeof(int) * kCtxTickets);
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_tickets, sizeof(int) * (kCtxTickets + 16));
+  if (e == cudaSuccess) e = cudaMemset(c->d_tickets, 0, sizeof(int) * (kCtxTickets + 16));
   c->scratch_bytes = kScratchBytes;
   if (e == cudaSuccess) e = cudaMalloc(&c->d_scratch, c->scratch_bytes);
   if (e == cudaSuccess) e = cudaMalloc(&c->d_arena, kArenaBytes);

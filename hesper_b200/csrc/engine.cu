@@ -30,6 +30,7 @@ struct hb200_bitnet {
   int Mmax;  // token rows the activation buffers hold: max(B, B * prefill chunk length)
   // device state
   float *x, *x1, *q, *k, *v, *att, *h, *logits, *xlast;
+  double* rope_tab;  // [B][D/2][2] the step's RoPE angles, shared by all layers
   __half *kcache, *vcache;  // [layer][B][Hkv][max_seq][D]
   int32_t *pos, *len, *tok, *log_index, *token_log;
   void* lm_scratch;
@@ -61,6 +62,8 @@ int enqueue_step(hb200_bitnet* m, const int32_t* d_tokens, bool lm_head, cudaStr
   int rc = hb200_embed_lookup(ctx, m->embed, m->embed_dtype, c.vocab, Hd, toks, B, 1.0f, m->x, st);
   if (rc) return rc;
   const float scale = 1.0f / sqrtf((float)c.head_dim);
+  rc = hb200_rope_table(ctx, m->pos, B, 1, c.head_dim, c.rope_base, m->rope_tab, st);
+  if (rc) return rc;
   for (int l = 0; l < c.n_layers; ++l) {
     const hb200_bitnet_layer& L = m->layers[l];
     hb200_bitlinear_seg segs[3] = {
@@ -68,12 +71,12 @@ int enqueue_step(hb200_bitnet* m, const int32_t* d_tokens, bool lm_head, cudaStr
         {L.wk, L.sk, nullptr, m->k, nullptr, kvdim},
         {L.wv, L.sv, nullptr, m->v, nullptr, kvdim},
     };
-    rc = hb200_bitlinear_forward_multi(ctx, segs, 3, Hd, m->x, B, L.attn_norm, c.rms_eps, nullptr, st);
-    if (rc) return rc;
     __half* kc = m->kcache + (size_t)l * layer_cache_elems(m);
     __half* vc = m->vcache + (size_t)l * layer_cache_elems(m);
-    rc = hb200_rope_kv_write(ctx, m->q, m->k, m->v, kc, vc, m->pos, B, c.n_heads, c.n_kv_heads,
-                             c.head_dim, c.max_seq, 0, c.rope_base, st);
+    rc = hb200_bitlinear_forward_multi(ctx, segs, 3, Hd, m->x, B, L.attn_norm, c.rms_eps, nullptr, st);
+    if (rc) return rc;
+    rc = hb200_rope_kv_write_angles(ctx, m->q, m->k, m->v, kc, vc, m->pos, m->rope_tab, B,
+                                    c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq, 0, st);
     if (rc) return rc;
     rc = hb200_attn_decode(ctx, m->q, 0, kc, vc, m->len, B, c.n_heads, c.n_kv_heads, c.head_dim,
                            c.max_seq, 0, scale, m->attn_ws, m->attn_ws_bytes, m->att, st);
@@ -198,6 +201,7 @@ extern "C" int hb200_bitnet_create(hb200_ctx* ctx, const hb200_bitnet_config* cf
   A(dalloc(&m->att, R * qdim));
   A(dalloc(&m->h, R * cfg->ffn));
   A(dalloc(&m->xlast, (size_t)B * cfg->hidden));
+  A(dalloc(&m->rope_tab, (size_t)B * cfg->head_dim));  // [B][D/2] x (cos, sin)
   A(dalloc(&m->logits, (size_t)B * cfg->vocab));
   const size_t cache = (size_t)cfg->n_layers * layer_cache_elems(m);
   A(dalloc(&m->kcache, cache));
@@ -231,7 +235,7 @@ extern "C" int hb200_bitnet_destroy(hb200_bitnet* m) {
   if (!m) return HB200_OK;
   cudaFree(m->x); cudaFree(m->x1); cudaFree(m->q); cudaFree(m->k); cudaFree(m->v);
   cudaFree(m->att); cudaFree(m->h); cudaFree(m->logits); cudaFree(m->kcache); cudaFree(m->vcache);
-  cudaFree(m->xlast);
+  cudaFree(m->xlast); cudaFree(m->rope_tab);
   cudaFree(m->pos); cudaFree(m->tok); cudaFree(m->log_index); cudaFree(m->token_log);
   cudaFree(m->lm_scratch); cudaFree(m->attn_ws);
   delete m;

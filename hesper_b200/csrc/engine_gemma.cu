@@ -30,6 +30,7 @@ struct hb200_gemma {
   std::vector<int> slots;       // cache slots per layer (window or max_seq)
   int32_t *pos, *len, *tok, *log_index, *token_log;
   unsigned long long* keys;
+  double* rope_tab;  // [B][D/2][2] the step's RoPE angles, shared by all layers
   void* attn_ws;
   size_t attn_ws_bytes;
   int log_stride;
@@ -100,6 +101,8 @@ int gemma_enqueue_step(hb200_gemma* m, const int32_t* d_tokens, bool lm_head, cu
   const int32_t* toks = d_tokens ? d_tokens : m->tok;
   int rc = hb200_embed_lookup(ctx, m->embed, 0, c.vocab, Hd, toks, B, c.embed_scale, m->x, st);
   if (rc) return rc;
+  rc = hb200_rope_table(ctx, m->pos, B, 1, D, c.rope_base, m->rope_tab, st);
+  if (rc) return rc;
   for (int l = 0; l < c.n_layers; ++l) {
     const hb200_gemma_layer& L = m->layers[l];
     hb200_kquant_seg segs[3] = {
@@ -108,8 +111,9 @@ int gemma_enqueue_step(hb200_gemma* m, const int32_t* d_tokens, bool lm_head, cu
                                     c.rms_eps, st);
     if (rc) return rc;
     const bool glob = layer_is_global(c, l);
-    rc = hb200_rope_kv_write(ctx, m->q, m->k, m->v, m->kc[l], m->vc[l], m->pos, B, c.local_q_heads,
-                             c.local_kv_heads, D, m->slots[l], glob ? 0 : 1, c.rope_base, st);
+    rc = hb200_rope_kv_write_angles(ctx, m->q, m->k, m->v, m->kc[l], m->vc[l], m->pos, m->rope_tab,
+                                    B, c.local_q_heads, c.local_kv_heads, D, m->slots[l],
+                                    glob ? 0 : 1, st);
     if (rc) return rc;
     // a ring cache holds exactly the window: the kernel clamps the length to the slots
     rc = hb200_attn_decode(ctx, m->q, 0, m->kc[l], m->vc[l], m->len, B, c.local_q_heads,
@@ -206,6 +210,7 @@ extern "C" int hb200_gemma_create(hb200_ctx* ctx, hb200_tp* tp, const hb200_gemm
   A(cudaMalloc(reinterpret_cast<void**>(&m->log_index), sizeof(int32_t)));
   A(cudaMalloc(reinterpret_cast<void**>(&m->token_log), sizeof(int32_t) * (size_t)B * m->log_stride));
   A(cudaMalloc(reinterpret_cast<void**>(&m->keys), sizeof(unsigned long long) * B));
+  A(cudaMalloc(reinterpret_cast<void**>(&m->rope_tab), sizeof(double) * (size_t)B * D));
   m->attn_ws_bytes = hb200_attn_workspace_bytes(ctx, B, cfg->local_q_heads, cfg->local_kv_heads, D,
                                                 max_slots);
   A(cudaMalloc(&m->attn_ws, m->attn_ws_bytes));
@@ -220,6 +225,7 @@ extern "C" int hb200_gemma_create(hb200_ctx* ctx, hb200_tp* tp, const hb200_gemm
 extern "C" int hb200_gemma_destroy(hb200_gemma* m) {
   if (!m) return HB200_OK;
   cudaFree(m->x); cudaFree(m->x1); cudaFree(m->o); cudaFree(m->q); cudaFree(m->k); cudaFree(m->v);
+  cudaFree(m->rope_tab);
   cudaFree(m->att); cudaFree(m->h); cudaFree(m->logits);
   for (auto p : m->kc) cudaFree(p);
   for (auto p : m->vc) cudaFree(p);

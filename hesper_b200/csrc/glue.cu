@@ -12,6 +12,7 @@
 #include <math_constants.h>
 
 #include "common.cuh"
+#include "rope.cuh"
 
 namespace hb {
 
@@ -70,60 +71,27 @@ __global__ void rmsnorm_kernel(const float* x, const float* gamma, const float* 
 
 // ---- RoPE (NeoX pairs d, d + D/2) + f16 KV-cache write ------------------------------------
 
-struct RopeParams {
-  float* q;          // [B][H][D] rotated in place
-  const float* k;    // [B][Hkv][D]
-  const float* v;    // [B][Hkv][D]
-  __half* k_cache;   // [B][Hkv][slots][D]
-  __half* v_cache;
-  const int32_t* pos;  // [B/T] position of each sequence's first new token
-  int B, H, Hkv, D, slots, ring;
-  int T;               // new tokens per sequence (1 = decode); B counts tokens
-  double base;
-};
-
-// One thread per (sequence, head, pair).  Heads 0..H-1 are Q heads, H..H+Hkv-1 are K heads
-// (rotated, then written to the cache as f16), and the V rows are packed alongside.
+// One thread per (token, head, pair); the element's arithmetic lives in rope.cuh.
 __global__ void rope_kv_kernel(const __grid_constant__ RopeParams p) {
   pdl_trigger();
   pdl_wait();
-  const int half = p.D >> 1;
-  const int per_seq = (p.H + 2 * p.Hkv) * half;
+  const int per_seq = (p.H + 2 * p.Hkv) * (p.D >> 1);
   const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long)p.B * per_seq) return;
-  const int b = (int)(idx / per_seq);
-  const int r = (int)(idx % per_seq);
-  const int head = r / half, i = r % half;
-  const int cb = b / p.T;  // which sequence's cache
-  const int pos = p.pos[cb] + (b - cb * p.T);
-  int slot = p.ring ? pos % p.slots : pos;
-  slot = slot < 0 ? 0 : (slot >= p.slots ? p.slots - 1 : slot);
-  if (head < p.H + p.Hkv) {
-    // theta = pos * base^(-2i/D).  The angle reaches thousands of radians, where f32
-    // loses four digits: the few thousand rotations of a step are done in double.
-    const double theta = (double)pos * pow(p.base, -2.0 * (double)i / (double)p.D);
-    double sn, cs;
-    sincos(theta, &sn, &cs);
-    if (head < p.H) {
-      float* qh = p.q + ((size_t)b * p.H + head) * p.D;
-      const double x0 = qh[i], x1 = qh[i + half];
-      qh[i] = (float)(x0 * cs - x1 * sn);
-      qh[i + half] = (float)(x0 * sn + x1 * cs);
-    } else {
-      const int kh = head - p.H;
-      const float* kk = p.k + ((size_t)b * p.Hkv + kh) * p.D;
-      const double x0 = kk[i], x1 = kk[i + half];
-      __half* dst = p.k_cache + (((size_t)cb * p.Hkv + kh) * p.slots + slot) * p.D;
-      dst[i] = __float2half_rn((float)(x0 * cs - x1 * sn));
-      dst[i + half] = __float2half_rn((float)(x0 * sn + x1 * cs));
-    }
-  } else {
-    const int vh = head - p.H - p.Hkv;
-    const float* vv = p.v + ((size_t)b * p.Hkv + vh) * p.D;
-    __half* dst = p.v_cache + (((size_t)cb * p.Hkv + vh) * p.slots + slot) * p.D;
-    dst[i] = __float2half_rn(vv[i]);
-    dst[i + half] = __float2half_rn(vv[i + half]);
-  }
+  rope_kv_element<false>(p, idx);
+}
+
+// (cos, sin) of every (token, pair) angle of a step: [B][D/2]
+__global__ void rope_table_kernel(const int32_t* pos, int B, int T, int D, double base,
+                                  double2* table) {
+  pdl_trigger();
+  pdl_wait();
+  const int half = D >> 1;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= B * half) return;
+  const int b = idx / half, i = idx % half;
+  const int cb = b / T;
+  table[idx] = rope_angle(pos[cb] + (b - cb * T), i, D, base);
 }
 
 // ---- greedy argmax: first strict maximum (Hesper/Models/BitNet.lean:474-479) ---------------
@@ -420,7 +388,7 @@ extern "C" int hb200_rmsnorm(hb200_ctx* ctx, const float* d_x, const float* d_ga
 static int rope_run(hb200_ctx* ctx, float* d_q, const float* d_k, const float* d_v,
                     void* d_k_cache, void* d_v_cache, const int32_t* d_pos, int nseq, int T, int H,
                     int Hkv, int D, int cache_slots, int ring, float rope_base,
-                    hb200_stream stream) {
+                    hb200_stream stream, const double* d_table = nullptr) {
   HB_REQUIRE(ctx && d_q && d_k && d_v && d_k_cache && d_v_cache && d_pos, "rope: null pointer");
   HB_REQUIRE(nseq >= 1 && T >= 1 && (long)nseq * T < (1l << 24) && H >= 1 && Hkv >= 1 && D >= 2 &&
                  D % 2 == 0 && cache_slots >= 1,
@@ -428,10 +396,23 @@ static int rope_run(hb200_ctx* ctx, float* d_q, const float* d_k, const float* d
   HB_REQUIRE(!(ring && T > 1), "rope: a ring cache takes one token per call");
   const int B = nseq * T;
   RopeParams p = {d_q, d_k, d_v, static_cast<__half*>(d_k_cache), static_cast<__half*>(d_v_cache),
-                  d_pos, B, H, Hkv, D, cache_slots, ring, T, (double)rope_base};
+                  d_pos, B, H, Hkv, D, cache_slots, ring, T, (double)rope_base,
+                  reinterpret_cast<const double2*>(d_table)};
   const long n = (long)B * (H + 2 * Hkv) * (D / 2);
   HB_CUDA(launch_pdl(rope_kv_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0,
                      static_cast<cudaStream_t>(stream), ctx->pdl, p));
+  return HB200_OK;
+}
+
+extern "C" int hb200_rope_table(hb200_ctx* ctx, const int32_t* d_pos, int B, int T, int D,
+                                float rope_base, double* d_table, hb200_stream stream) {
+  HB_REQUIRE(ctx && d_pos && d_table && B >= 1 && T >= 1 && D >= 2 && D % 2 == 0,
+             "rope_table: bad argument");
+  HB_REQUIRE((reinterpret_cast<uintptr_t>(d_table) & 15) == 0, "rope_table: table must be 16-byte aligned");
+  const int n = B * T * (D / 2);
+  HB_CUDA(launch_pdl(rope_table_kernel, dim3((n + 127) / 128), dim3(128), 0,
+                     static_cast<cudaStream_t>(stream), ctx->pdl, d_pos, B * T, T, D,
+                     (double)rope_base, reinterpret_cast<double2*>(d_table)));
   return HB200_OK;
 }
 
@@ -441,6 +422,16 @@ extern "C" int hb200_rope_kv_write(hb200_ctx* ctx, float* d_q, const float* d_k,
                                    float rope_base, hb200_stream stream) {
   return rope_run(ctx, d_q, d_k, d_v, d_k_cache, d_v_cache, d_pos, B, 1, H, Hkv, D, cache_slots,
                   ring, rope_base, stream);
+}
+
+extern "C" int hb200_rope_kv_write_angles(hb200_ctx* ctx, float* d_q, const float* d_k,
+                                          const float* d_v, void* d_k_cache, void* d_v_cache,
+                                          const int32_t* d_pos, const double* d_table, int B,
+                                          int H, int Hkv, int D, int cache_slots, int ring,
+                                          hb200_stream stream) {
+  HB_REQUIRE(d_table != nullptr, "rope (angles): null table");
+  return rope_run(ctx, d_q, d_k, d_v, d_k_cache, d_v_cache, d_pos, B, 1, H, Hkv, D, cache_slots,
+                  ring, 0.f, stream, d_table);
 }
 
 extern "C" int hb200_rope_kv_write_prefill(hb200_ctx* ctx, float* d_q, const float* d_k,

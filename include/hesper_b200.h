@@ -137,6 +137,17 @@ int hb200_bitlinear_forward_multi(hb200_ctx *ctx, const hb200_bitlinear_seg *seg
                                   const float *d_rms_gamma, float rms_eps,
                                   float *d_act_scale, hb200_stream stream);
 
+/* (cos, sin) in f64 of the RoPE angle of every (token, pair): d_table [B*T][D/2][2], token
+ * t of sequence b at position d_pos[b] + t.  The angles are the same in every layer, so a
+ * decode loop computes them once per step and hands them to hb200_rope_kv_write_angles,
+ * which is hb200_rope_kv_write without the pow / sincos per element (same values). */
+int hb200_rope_table(hb200_ctx *ctx, const int32_t *d_pos, int B, int T, int D, float rope_base,
+                     double *d_table, hb200_stream stream);
+int hb200_rope_kv_write_angles(hb200_ctx *ctx, float *d_q, const float *d_k, const float *d_v,
+                               void *d_k_cache, void *d_v_cache, const int32_t *d_pos,
+                               const double *d_table, int B, int H, int Hkv, int D,
+                               int cache_slots, int ring, hb200_stream stream);
+
 /* y[m,n] = relu(s_g*g[m,n])^2 * (s_u*u[m,n]) with g, u the two ternary matvecs.
  * Replaces BitLinear.forwardFusedGateUpReluSqrMul (Hesper/Layers/BitLinear.lean:1419,
  * kernel :553-621). */
