@@ -198,11 +198,11 @@ int hb_lmhead_mma_run(struct hb200_ctx* ctx, const void* d_table, int dtype, lon
 
 // Layout of the context's device scratch (one stream at a time uses it; regions of ops that
 // never overlap in time may overlap in space):
-constexpr size_t kScratchBytes = (size_t)20 << 20;
+constexpr size_t kScratchBytes = (size_t)24 << 20;
 constexpr size_t kScratchActs = 0;                     // batched ternary: d[64], sumq[64], int8 tiles
 constexpr size_t kScratchGlu = (size_t)2 << 20;       // batched gate/up products before the GLU
 constexpr size_t kScratchLmSplit = (size_t)8 << 20;   // 16-bit products: hi/lo activation tiles
-constexpr size_t kScratchSplitK = (size_t)12 << 20;   // batched ternary: split-K int32 partials
+constexpr size_t kScratchSplitK = (size_t)16 << 20;   // batched paths: split-K partials
 
 // the two halves of it, also used by the batched k-quant path (weights dequantised to f16)
 int hb_gemm16_split(struct hb200_ctx* ctx, int dtype, int K, const float* d_x, int M,
@@ -211,7 +211,7 @@ int hb_gemm16_mma(struct hb200_ctx* ctx, const void* d_table, int dtype, long V,
                   float* d_y, const float* d_residual, long ldy, unsigned long long* d_keys,
                   int table_constant, cudaStream_t st);
 // batched Q4_K with the dequantiser fused into the tensor-core kernel, kquant_mma.cu
-int hb_kq_mma_run(struct hb200_ctx* ctx, const uint8_t* d_blocks, int K, long N, int M,
+int hb_kq_mma_run(struct hb200_ctx* ctx, const uint8_t* d_blocks, int K, long N, int M, int NT,
                   float* d_y, const float* d_residual, long ldy, cudaStream_t st);
 constexpr size_t kArenaBytes = (size_t)64 << 20;  // f16 weights of one batched k-quant product
 

@@ -532,13 +532,19 @@ static int kq_batched_one(hb200_ctx* ctx, int fmt, const uint8_t* blocks, int K,
   // Q4_K: dequantiser fused into the product kernel (kquant_mma.cu; split-K when there are
   // few row tiles).  Q8_0 takes the two-kernel route below.
   if (fmt == HB200_FMT_Q4_K) {
-    for (int m0 = 0; m0 < M; m0 += 64) {
-      const int mc = M - m0 < 64 ? M - m0 : 64;
-      int rc = hb_gemm16_split(ctx, 1, K, d_x + (size_t)m0 * K, mc, gamma, eps, 1, st);
+    // tokens per pass: the tensor time of a pass does not depend on it, the activation tile
+    // and the accumulator do; K above 8192 keeps the 256-token tiles out of their scratch
+    const int cap = K <= 8192 ? 256 : 128;
+    for (int m0 = 0; m0 < M;) {
+      const int left = M - m0;
+      const int NT = left <= 64 ? 64 : (left <= 128 || cap == 128 ? 128 : 256);
+      const int mc = left < NT ? left : NT;
+      int rc = hb_gemm16_split(ctx, 1, K, d_x + (size_t)m0 * K, mc, gamma, eps, NT, st);
       if (rc != HB200_OK) return rc;
-      rc = hb_kq_mma_run(ctx, blocks, K, N, mc, y + (size_t)m0 * N,
+      rc = hb_kq_mma_run(ctx, blocks, K, N, mc, NT, y + (size_t)m0 * N,
                          residual ? residual + (size_t)m0 * N : nullptr, N, st);
       if (rc != HB200_OK) return rc;
+      m0 += mc;
     }
     return HB200_OK;
   }
@@ -748,19 +754,21 @@ extern "C" int hb200_kquant_gateup_gelu(hb200_ctx* ctx, int fmt, const void* d_b
              "kquant gate/up: blocks must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (M >= kKQBatchedFrom && !ctx->no_mma &&
-      kScratchGlu + (size_t)2 * 64 * N * sizeof(float) <= kScratchLmSplit) {
-    // both products on the tensor cores into scratch (64 tokens at a time), then the GLU
-    float* g = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->d_scratch) + kScratchGlu);
-    for (int m0 = 0; m0 < M; m0 += 64) {
-      const int mc = M - m0 < 64 ? M - m0 : 64;
-      float* u = g + (size_t)mc * N;
+      kScratchGlu + (size_t)64 * N * sizeof(float) <= kScratchLmSplit) {
+    // both products on the tensor cores: gate straight into d_y, up into scratch (as many
+    // tokens per pass as the scratch region holds, at most 128), then the GLU in place
+    float* u = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->d_scratch) + kScratchGlu);
+    const int pass =
+        kScratchGlu + (size_t)128 * N * sizeof(float) <= kScratchLmSplit ? 128 : 64;
+    for (int m0 = 0; m0 < M; m0 += pass) {
+      const int mc = M - m0 < pass ? M - m0 : pass;
+      float* g = d_y + (size_t)m0 * N;
       rc = kq_batched_one(ctx, fmt, static_cast<const uint8_t*>(d_blocks_gate), K, N,
                           d_x + (size_t)m0 * K, mc, d_rms_gamma, rms_eps, nullptr, g, st);
       if (rc == HB200_OK)
         rc = kq_batched_one(ctx, fmt, static_cast<const uint8_t*>(d_blocks_up), K, N,
                             d_x + (size_t)m0 * K, mc, d_rms_gamma, rms_eps, nullptr, u, st);
-      if (rc == HB200_OK)
-        rc = hb200_gelu_mul(ctx, g, u, (long)mc * N, d_y + (size_t)m0 * N, stream);
+      if (rc == HB200_OK) rc = hb200_gelu_mul(ctx, g, u, (long)mc * N, g, stream);
       if (rc != HB200_OK) return rc;
     }
     return HB200_OK;

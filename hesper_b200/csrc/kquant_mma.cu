@@ -28,29 +28,35 @@
 namespace hb {
 
 constexpr int kQmRows = 128;          // weight rows per CTA = MMA M
-constexpr int kQmTokens = 64;         // tokens per pass
-constexpr int kQmN = kQmTokens;       // MMA N
 constexpr int kQmStepK = 128;         // weights per pipeline step (half a super-block)
-constexpr int kQmStages = 6;          // operand stages
 constexpr int kQmACols = kQmStepK / 2;           // 64 TMEM columns of f16 pairs per stage
-constexpr int kQmBBytes = kQmN * kQmStepK * 2;   // 16 KB of activations per step
 constexpr int kQmPkStages = 3;
 constexpr int kQmPkBytes = kQmRows * 144;        // one super-block of every row: 18 KB
-constexpr int kQmAcc0 = 0, kQmAcc1 = 64, kQmA0 = 128;   // TMEM column map
-constexpr int kQmSmem = 1024 + kQmPkStages * kQmPkBytes + kQmStages * kQmBBytes;
 constexpr int kQmThreads = 352;
-static_assert(kQmA0 + kQmStages * kQmACols <= 512, "tensor memory columns");
-static_assert(kQmSmem <= 232448, "shared memory budget of one CTA");
+
+// NT tokens per pass = MMA N.  An MMA of this shape occupies the tensor pipe for the same
+// ~128 cycles whether N is 64 or 256, so a pass over more tokens costs no extra tensor time;
+// what grows is the accumulator (NT columns) and the activation tile every step brings.
+template <int NT>
+struct QmCfg {
+  static constexpr int kIssuers = NT <= 128 ? 2 : 1;        // MMA-issuing warps, one accumulator each
+  static constexpr int kA0 = kIssuers * NT;                 // first TMEM column of the A stages
+  static constexpr int kStages = NT == 64 ? 6 : (NT == 128 ? 4 : 2);
+  static constexpr int kBBytes = NT * kQmStepK * 2;         // activations per step: 16 / 32 / 64 KB
+  static constexpr int kSmem = 1024 + kQmPkStages * kQmPkBytes + kStages * kBBytes;
+  static_assert(kA0 + kStages * kQmACols <= 512, "tensor memory columns");
+  static_assert(kSmem <= 232448, "shared memory budget of one CTA");
+};
 
 struct QmParams {
   CUtensorMap tmap;      // blocks as [N rows][rowbytes], boxes of 128 rows x 144 bytes
-  const uint8_t* xb;     // f16 activations: [K/64][64 rows x 64 f16, operand layout]
+  const uint8_t* xb;     // f16 activations: [K/64][NT rows x 64 f16, operand layout]
   const float* residual; // nullable
   float* y;              // y[m * ldy + row]
   long ldy;
   int K, N, M;
   int nsplit, bps;       // split-K: CTAs per row tile, super-block boxes per split
-  float* part;           // [tile][split][64 tokens][128 rows] partial sums (nsplit > 1)
+  float* part;           // [tile][split][NT tokens][128 rows] partial sums (nsplit > 1)
   int* tickets;          // [tile] arrival counters, zero between launches
   uint32_t idesc;
   uint32_t* status;
@@ -74,7 +80,10 @@ __device__ __forceinline__ uint32_t pack_f16(float a, float b) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+template <int NT>
 __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_constant__ QmParams p) {
+  using Cfg = QmCfg<NT>;
+  constexpr int kQmStages = Cfg::kStages, kQmBBytes = Cfg::kBBytes, kQmA0 = Cfg::kA0;
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // this CTA's K range: whole super-blocks (boxes of 256 weights = 2 steps)
@@ -88,8 +97,8 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
 
   uint64_t* pk_full = reinterpret_cast<uint64_t*>(smem);  // [3] box landed (tx bytes)
   uint64_t* pk_free = pk_full + kQmPkStages;               // [3] every expander warp left it
-  uint64_t* full = pk_free + kQmPkStages;   // [6] A stored by 8 warps + activations landed
-  uint64_t* mma_done = full + kQmStages;    // [6] the MMAs that read the stage have retired
+  uint64_t* full = pk_free + kQmPkStages;   // [stages] A stored by 8 warps + activations landed
+  uint64_t* mma_done = full + kQmStages;    // [stages] the MMAs that read the stage have retired
   uint64_t* done = mma_done + kQmStages;    // [1] both issuers
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
   uint8_t* pk = smem + 1024;
@@ -159,8 +168,8 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
   } else if (warp == kMmaWarpA || warp == kMmaWarpB) {
     // ================= MMA issue: even steps -> accumulator 0, odd steps -> accumulator 1 =====
     const int which = warp == kMmaWarpA ? 0 : 1;
-    const uint32_t tmem_d = tmem + (which ? kQmAcc1 : kQmAcc0);
-    for (int s = which; s < nsteps; s += 2) {
+    const uint32_t tmem_d = tmem + (uint32_t)(which * NT);
+    for (int s = which; s < nsteps && which < Cfg::kIssuers; s += Cfg::kIssuers) {
       const int st = s % kQmStages;
       ok = tc_wait(ok, &full[st], (uint32_t)((s / kQmStages) & 1), p.status);
       if (s >= 8 && s < 12) QM_STAMP(12 + 2 * (s - 8), lane == 0);
@@ -172,7 +181,7 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
         for (int j = 0; j < kQmStepK / 16; ++j)  // K = 16 per instruction: 8 columns of A
           tc_mma_f16_ta(tmem_d, a_t + j * 8,
                         tc_smem_desc(bbase + (j >> 2) * (kQmBBytes / 2) + (j & 3) * 256, 128, 1024, 0),
-                        p.idesc, (s > 1 || j > 0) ? 1u : 0u);
+                        p.idesc, (s >= Cfg::kIssuers || j > 0) ? 1u : 0u);
         tc_commit(&mma_done[st]);
       }
       __syncwarp();
@@ -250,29 +259,59 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
   ok = tc_wait(true, done, 0, p.status) && ok;
   tc_after_sync();
 
-  // ---- epilogue: lane = weight row, column = token; the two issuers' accumulators add up ----
-  const int q = warp & 3, half = warp >> 2;  // expander warps: lane quarter, token half
-  const int r = q * 32 + lane, m0 = half * 32;
-  float acc[32];
-  if (warp < kExpWarps) {
-    const uint32_t base = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)m0;
-    uint32_t v[32], u[32];
-    HB_TMEM_LD32(v, base + kQmAcc0);
-    HB_TMEM_LD32(u, base + kQmAcc1);
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  // ---- epilogue: lane = weight row, column = token; the issuers' accumulators add up.  Warp
+  //      w owns lane quarter w & 3 and the 32-token groups w >> 2, (w >> 2) + 2, ... ----------
+  const int q = warp & 3, r = q * 32 + lane;
+  auto load_group = [&](int g, float (&acc)[32]) {  // tokens 32g .. 32g+31 of this row
+    const uint32_t base = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(32 * g);
+    uint32_t v[32];
+    HB_TMEM_LD32(v, base);
+    if (Cfg::kIssuers == 2) {
+      uint32_t u[32];
+      HB_TMEM_LD32(u, base + NT);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-    for (int t = 0; t < 32; ++t) acc[t] = __fadd_rn(__uint_as_float(v[t]), __uint_as_float(u[t]));
-  }
-  // split-K: every split publishes its partial; the last one to arrive (a ticket per row
-  // tile) adds ALL partials in split order, so the f32 result does not depend on who it was
-  bool finish = true;
-  if (p.nsplit > 1) {
-    __shared__ int s_last;
-    float* mine = p.part + ((size_t)(tile * p.nsplit + split) * kQmTokens) * kQmRows;
-    if (warp < kExpWarps) {
+      for (int t = 0; t < 32; ++t) acc[t] = __fadd_rn(__uint_as_float(v[t]), __uint_as_float(u[t]));
+    } else {
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-      for (int t = 0; t < 32; ++t) mine[(size_t)(m0 + t) * kQmRows + r] = acc[t];
+      for (int t = 0; t < 32; ++t) acc[t] = __uint_as_float(v[t]);
     }
+  };
+  auto store_group = [&](int g, const float (&acc)[32]) {
+    const int row = row0 + r, m0 = 32 * g;
+    if (row >= p.N || !ok || m0 >= p.M) return;
+    const int mcount = min(32, p.M - m0);
+    const size_t o0 = (size_t)m0 * p.ldy + row;
+    float res[32];
+    if (p.residual) {
+#pragma unroll
+      for (int t = 0; t < 32; ++t) res[t] = t < mcount ? p.residual[o0 + (size_t)t * p.ldy] : 0.f;
+    }
+#pragma unroll
+    for (int t = 0; t < 32; ++t)
+      if (t < mcount) p.y[o0 + (size_t)t * p.ldy] = p.residual ? __fadd_rn(acc[t], res[t]) : acc[t];
+  };
+  if (p.nsplit == 1) {
+    if (warp < kExpWarps)
+      for (int g = warp >> 2; g < NT / 32; g += 2) {
+        float acc[32];
+        load_group(g, acc);
+        store_group(g, acc);
+      }
+  } else {
+    // split-K: every split publishes its partial; the last one to arrive (a ticket per row
+    // tile) adds ALL partials in split order, so the f32 result does not depend on who it was
+    __shared__ int s_last;
+    float* mine = p.part + ((size_t)(tile * p.nsplit + split) * NT) * kQmRows;
+    if (warp < kExpWarps)
+      for (int g = warp >> 2; g < NT / 32; g += 2) {
+        if (32 * g >= p.M) continue;
+        float acc[32];
+        load_group(g, acc);
+#pragma unroll
+        for (int t = 0; t < 32; ++t) mine[(size_t)(32 * g + t) * kQmRows + r] = acc[t];
+      }
     __threadfence();
     __syncthreads();
     if (tid == 0) {
@@ -281,32 +320,21 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
       if (s_last) p.tickets[tile] = 0;
     }
     __syncthreads();
-    finish = s_last != 0;
-    if (finish && warp < kExpWarps) {
+    if (s_last && warp < kExpWarps) {
       __threadfence();
+      for (int g = warp >> 2; g < NT / 32; g += 2) {
+        if (32 * g >= p.M) continue;
+        float acc[32];
 #pragma unroll
-      for (int t = 0; t < 32; ++t) acc[t] = 0.f;
-      for (int s2 = 0; s2 < p.nsplit; ++s2) {
-        const float* other =
-            p.part + ((size_t)(tile * p.nsplit + s2) * kQmTokens + m0) * kQmRows + r;
+        for (int t = 0; t < 32; ++t) acc[t] = 0.f;
+        for (int s2 = 0; s2 < p.nsplit; ++s2) {
+          const float* other =
+              p.part + ((size_t)(tile * p.nsplit + s2) * NT + 32 * g) * kQmRows + r;
 #pragma unroll
-        for (int t = 0; t < 32; ++t) acc[t] = __fadd_rn(acc[t], __ldcg(other + (size_t)t * kQmRows));
+          for (int t = 0; t < 32; ++t) acc[t] = __fadd_rn(acc[t], __ldcg(other + (size_t)t * kQmRows));
+        }
+        store_group(g, acc);
       }
-    }
-  }
-  if (finish && warp < kExpWarps) {
-    const int row = row0 + r;
-    if (row < p.N && ok) {
-      const int mcount = min(32, p.M - m0);
-      const size_t o0 = (size_t)m0 * p.ldy + row;
-      float res[32];
-      if (p.residual) {
-#pragma unroll
-        for (int t = 0; t < 32; ++t) res[t] = t < mcount ? p.residual[o0 + (size_t)t * p.ldy] : 0.f;
-      }
-#pragma unroll
-      for (int t = 0; t < 32; ++t)
-        if (t < mcount) p.y[o0 + (size_t)t * p.ldy] = p.residual ? __fadd_rn(acc[t], res[t]) : acc[t];
     }
   }
   tc_before_sync();
@@ -319,12 +347,40 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
 
 using namespace hb;
 
-// y[m*ldy + n] = sum_k dequant(W)[n,k] x[m,k] (+ residual) for the M <= 64 tokens staged by
-// hb_gemm16_split (dtype f16, single term).  Q4_K only; K a multiple of 256.
-int hb_kq_mma_run(hb200_ctx* ctx, const uint8_t* d_blocks, int K, long N, int M, float* d_y,
-                  const float* d_residual, long ldy, cudaStream_t st) {
-  HB_REQUIRE(K % 256 == 0 && N >= 1 && N < (1l << 31) && M >= 1 && M <= kQmTokens,
-             "kquant (fused batched): K=%d N=%ld M=%d", K, N, M);
+template <int NT>
+static int kq_mma_launch(hb200_ctx* ctx, QmParams& p, int tiles, cudaStream_t st) {
+  using Cfg = QmCfg<NT>;
+  // kind::f16: D = f32, A and B f16, both K-major, N = NT, M = 128
+  p.idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(kQmRows >> 4) << 24);
+  // split-K when the row tiles alone leave SMs idle: as many splits as fit the SMs, each at
+  // least 2 super-blocks long, partials within their scratch region, tickets within theirs
+  const int nboxes = p.K / 256;
+  int nsplit = ctx->sm_count / tiles;
+  if (nsplit > nboxes / 2) nsplit = nboxes / 2;
+  while (nsplit > 1 && (size_t)tiles * nsplit * NT * kQmRows * 4 > kScratchBytes - kScratchSplitK)
+    --nsplit;
+  if (nsplit < 1 || tiles > kCtxTickets) nsplit = 1;
+  p.bps = (nboxes + nsplit - 1) / nsplit;
+  p.nsplit = (nboxes + p.bps - 1) / p.bps;  // no empty split
+  static bool configured = false;
+  if (!configured) {
+    HB_CUDA(cudaFuncSetAttribute(kq_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg::kSmem));
+    configured = true;
+  }
+  HB_CUDA(launch_pdl(kq_mma_kernel<NT>, dim3((unsigned)(tiles * p.nsplit)), dim3(kQmThreads),
+                     (size_t)Cfg::kSmem, st, ctx->pdl, p));
+  return HB200_OK;
+}
+
+// y[m*ldy + n] = sum_k dequant(W)[n,k] x[m,k] (+ residual) for the M <= NT tokens staged by
+// hb_gemm16_split (dtype f16, single term, NT token rows per block; NT = 64, 128 or 256).
+// Q4_K only; K a multiple of 256.
+int hb_kq_mma_run(hb200_ctx* ctx, const uint8_t* d_blocks, int K, long N, int M, int NT,
+                  float* d_y, const float* d_residual, long ldy, cudaStream_t st) {
+  HB_REQUIRE(K % 256 == 0 && N >= 1 && N < (1l << 31) && M >= 1 && M <= NT &&
+                 (NT == 64 || NT == 128 || NT == 256),
+             "kquant (fused batched): K=%d N=%ld M=%d NT=%d", K, N, M, NT);
   QmParams p = {};
   TcEncodeTiledFn encode = tc_tensor_map_encoder();
   HB_REQUIRE(encode != nullptr, "kquant (fused batched): the driver has no cuTensorMapEncodeTiled");
@@ -346,30 +402,13 @@ int hb_kq_mma_run(hb200_ctx* ctx, const uint8_t* d_blocks, int K, long N, int M,
   p.K = K;
   p.N = (int)N;
   p.M = M;
-  // kind::f16: D = f32, A and B f16, both K-major, N = 64, M = 128
-  p.idesc = (1u << 4) | ((uint32_t)(kQmN >> 3) << 17) | ((uint32_t)(kQmRows >> 4) << 24);
-  p.status = ctx->d_status;
-  static bool configured = false;
-  if (!configured) {
-    HB_CUDA(cudaFuncSetAttribute(kq_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kQmSmem));
-    configured = true;
-  }
-  const int tiles = (int)((N + kQmRows - 1) / kQmRows);
-  // split-K when the row tiles alone leave SMs idle: as many splits as fit the SMs, each at
-  // least 2 super-blocks long, partials within their scratch region, tickets within theirs
-  const int nboxes = K / 256;
-  int nsplit = ctx->sm_count / tiles;
-  if (nsplit > nboxes / 2) nsplit = nboxes / 2;
-  while (nsplit > 1 && (size_t)tiles * nsplit * kQmTokens * kQmRows * 4 >
-                           kScratchBytes - kScratchSplitK)
-    --nsplit;
-  if (nsplit < 1 || tiles > kCtxTickets) nsplit = 1;
-  p.bps = (nboxes + nsplit - 1) / nsplit;
-  p.nsplit = (nboxes + p.bps - 1) / p.bps;  // no empty split
   p.part = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->d_scratch) + kScratchSplitK);
   p.tickets = ctx->d_tickets;
-  HB_CUDA(launch_pdl(kq_mma_kernel, dim3((unsigned)(tiles * p.nsplit)), dim3(kQmThreads),
-                     (size_t)kQmSmem, st, ctx->pdl, p));
-  return HB200_OK;
+  p.status = ctx->d_status;
+  const int tiles = (int)((N + kQmRows - 1) / kQmRows);
+  switch (NT) {
+    case 64: return kq_mma_launch<64>(ctx, p, tiles, st);
+    case 128: return kq_mma_launch<128>(ctx, p, tiles, st);
+    default: return kq_mma_launch<256>(ctx, p, tiles, st);
+  }
 }

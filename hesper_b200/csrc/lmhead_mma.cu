@@ -50,7 +50,8 @@ struct LmSplitParams {
   const float* gamma;  // nullable
   float eps;
   int K, M, dtype;     // dtype 0 = bf16, 1 = f16
-  int single;          // 1: only the hi term, 64 rows per block (8 KB blocks)
+  int single;          // 0: hi rows 0..63, lo rows 64..127 of each block; else only the rounded
+                       // value, `single` token rows per block (64, 128 or 256)
   uint8_t* xb;         // [K/64][16 KB] operand blocks
 };
 
@@ -84,7 +85,7 @@ __global__ void __launch_bounds__(256) lm_split_kernel(const __grid_constant__ L
   const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = p.K;
   // 8 consecutive k of token row `row` -> their 16 bytes in the operand block
-  const size_t blk_bytes = p.single ? kLmBBytes / 2 : kLmBBytes;
+  const size_t blk_bytes = p.single ? (size_t)p.single * 128 : (size_t)kLmBBytes;
   auto dst = [&](int row, int k) {
     return p.xb + (size_t)(k >> 6) * blk_bytes + (size_t)(row >> 3) * 1024 +
            (size_t)((k & 63) >> 3) * 128 + (size_t)(row & 7) * 16;
@@ -306,15 +307,20 @@ __global__ void __launch_bounds__(kLmThreads, 2)
 using namespace hb;
 
 // x[M][K] (M <= 64) -> hi/lo 16-bit operand blocks in the context scratch, optional RMSNorm.
-// single != 0: only the rounded value (no lo term), 64 rows and 8 KB per 64-wide K block.
+// single = 64, 128 or 256: only the rounded value (no lo term), that many token rows per
+// 64-wide K block (M <= single).
 int hb_gemm16_split(hb200_ctx* ctx, int dtype, int K, const float* d_x, int M,
                     const float* d_rms_gamma, float rms_eps, int single, cudaStream_t st) {
-  const size_t xb_bytes = (size_t)(K / kLmKStep) * kLmBBytes;
+  HB_REQUIRE(single == 0 || single == 64 || single == 128 || single == 256,
+             "batched 16-bit product: %d token rows per block", single);
+  const size_t xb_bytes = (size_t)(K / kLmKStep) * (single ? (size_t)single * 128 : (size_t)kLmBBytes);
   HB_REQUIRE(kScratchLmSplit + xb_bytes <= kScratchSplitK,
              "batched 16-bit product: K=%d needs %zu bytes of activation scratch", K, xb_bytes);
+  HB_REQUIRE(M >= 1 && M <= (single ? single : kLmTokens), "batched 16-bit product: M=%d", M);
   uint8_t* xb = static_cast<uint8_t*>(ctx->d_scratch) + kScratchLmSplit;
   LmSplitParams sp = {d_x, d_rms_gamma, rms_eps, K, M, dtype, single, xb};
-  HB_CUDA(launch_pdl(lm_split_kernel, dim3(kLmTokens), dim3(256), 0, st, ctx->pdl, sp));
+  HB_CUDA(launch_pdl(lm_split_kernel, dim3(single ? single : kLmTokens), dim3(256), 0, st,
+                     ctx->pdl, sp));
   return HB200_OK;
 }
 

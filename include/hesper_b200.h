@@ -56,7 +56,7 @@ typedef void *hb200_stream;
 /* Replaces CUDAContext.init (Hesper/Backend/CUDA.lean:46; native/cuda_bridge.cpp:78-82)
  * for this path only: binds to `device` (its primary context), reads the SM
  * count, raises the kernels' dynamic shared-memory limits and allocates what the
- * operators need later: a 256-byte status block, 4096 arrival counters and 20 MB of
+ * operators need later: a 256-byte status block, 4096 arrival counters and 24 MB of
  * scratch (activation tiles, split-K partials of the batched paths) and a 64 MB arena
  * (f16 weights of one batched k-quant product).  No operator
  * allocates afterwards; a context serves one stream at a time.
