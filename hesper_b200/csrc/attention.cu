@@ -123,9 +123,13 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <int D>
+// NS stages per warp.  D <= 128: with 3 stages two CTAs share an SM (100 KB each at D = 128),
+// which hides each CTA's prologue and merge behind the other's main loop when the grid is
+// several waves deep; with 4 stages a CTA has its SM alone and more chunks in flight per
+// warp, which is what a grid that does not fill the GPU wants.
+template <int D, int NS_ = 3>
 struct AttnCfg {
-  static constexpr int kStages = D >= 256 ? 3 : 4;
+  static constexpr int kStages = NS_;
   static constexpr int kRowBytes = D * 2;
   static constexpr int kTileBytes = kChunk * kRowBytes;  // one of K or V
   static constexpr int kStageBytes = 2 * kTileBytes;
@@ -137,9 +141,9 @@ struct AttnCfg {
 // PRECISE: the scaled query and the softmax weights are each split into two f16 terms
 // (hi + lo), doubling the tensor-core work and removing their rounding from the result;
 // K and V are f16 in the cache, so what remains is f32 accumulation error (~1e-6).
-template <int D, bool PRECISE>
-__global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(const __grid_constant__ AttnParams p) {
-  using Cfg = AttnCfg<D>;
+template <int D, bool PRECISE, int NSTAGES>
+__global__ void __launch_bounds__(kAttnThreads, D >= 256 ? 1 : 2) attn_decode_kernel(const __grid_constant__ AttnParams p) {
+  using Cfg = AttnCfg<D, NSTAGES>;
   constexpr int QS = Cfg::kQStride;
   constexpr int NS = Cfg::kStages;
   constexpr int CPR = D / 8;   // 16-byte chunks per row
@@ -586,10 +590,25 @@ static int attn_pick_splits(const hb200_ctx* ctx, int B, int Hkv, int max_len) {
   return (int)want;
 }
 
+template <int D, bool PRECISE, int NSTAGES>
+static int attn_launch_ns(hb200_ctx* ctx, const AttnParams& p, cudaStream_t st);
+
 template <int D, bool PRECISE>
 static int attn_launch(hb200_ctx* ctx, const AttnParams& p, cudaStream_t st) {
-  using Cfg = AttnCfg<D>;
-  auto kern = attn_decode_kernel<D, PRECISE>;
+  // a grid of more than two waves of single CTAs: share the SMs (3 stages); else 4 stages
+  const int grid = p.B * p.Hkv * p.nsplit;
+  if constexpr (D >= 256) {
+    return attn_launch_ns<D, PRECISE, 3>(ctx, p, st);  // 4 stages would not fit at this size
+  } else {
+    if (grid > 2 * ctx->sm_count) return attn_launch_ns<D, PRECISE, 3>(ctx, p, st);
+    return attn_launch_ns<D, PRECISE, 4>(ctx, p, st);
+  }
+}
+
+template <int D, bool PRECISE, int NSTAGES>
+static int attn_launch_ns(hb200_ctx* ctx, const AttnParams& p, cudaStream_t st) {
+  using Cfg = AttnCfg<D, NSTAGES>;
+  auto kern = attn_decode_kernel<D, PRECISE, NSTAGES>;
   static bool configured = false;
   if (!configured) {
     HB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
