@@ -576,12 +576,15 @@ __global__ void __launch_bounds__(32) attn_exact_kernel(const __grid_constant__ 
     p.out[((size_t)b * p.H + h) * D + lane * DL + j] = l > 0.f ? __fdiv_rn(acc[j], l) : 0.f;
 }
 
-// Splits per (sequence, KV head): enough CTAs for a few waves over the SMs, but
+// Splits per (sequence, KV head): enough CTAs for two waves over the SMs, but
 // no split shorter than 8 chunks (128 positions) and at most kMaxSplits.
-static int attn_pick_splits(const hb200_ctx* ctx, int B, int Hkv, int max_len) {
+static int attn_pick_splits(const hb200_ctx* ctx, int B, int Hkv, int D, int max_len) {
   const long pairs = (long)B * Hkv;
   const int chunks = (max_len + kChunk - 1) / kChunk;
-  long want = (4L * ctx->sm_count + pairs - 1) / pairs;
+  // two waves of resident CTAs (measured best over the batch x length sweeps); at D <= 128
+  // two CTAs share an SM
+  const long resident = (long)ctx->sm_count * (D <= 128 ? 2 : 1);
+  long want = (2 * resident + pairs - 1) / pairs;
   long cap = chunks / 8;
   if (cap < 1) cap = 1;
   if (want > cap) want = cap;
@@ -638,7 +641,8 @@ extern "C" size_t hb200_attn_workspace_bytes(const hb200_ctx* ctx, int B, int H,
                                              int max_seq) {
   if (!ctx || B < 1 || Hkv < 1 || D < 1) return 0;
   (void)H;
-  const int ns = attn_pick_splits(ctx, B, Hkv, max_seq);
+  const int ns = attn_pick_splits(ctx, B, Hkv, D, max_seq);
+  if (ns == 1) return 256;  // a single split writes its result directly: nothing to stage
   return (size_t)B * Hkv * ns * 8 * ((size_t)D + 2) * sizeof(float) + 256;
 }
 
@@ -675,7 +679,7 @@ static int attn_run(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d
   p.T = T;
   p.scale_log2 = scale * 1.4426950408889634f;
   const int eff_len = (window > 0 && window < max_seq) ? window : max_seq;
-  p.nsplit = attn_pick_splits(ctx, B, Hkv, eff_len);
+  p.nsplit = attn_pick_splits(ctx, B, Hkv, D, eff_len);
   if (p.nsplit > 1) {
     const size_t po = (size_t)B * Hkv * p.nsplit * 8 * (size_t)D * sizeof(float);
     const size_t need = po + (size_t)B * Hkv * p.nsplit * 8 * 2 * sizeof(float);
@@ -759,7 +763,7 @@ extern "C" int hb200_attn_decode_static(hb200_ctx* ctx, const void* d_q, int q_i
   HB_REQUIRE(ctx->device >= 0 && ctx->device < 64, "attn (static scratch): device %d", ctx->device);
   // the split count the launch below will choose, hence the scratch it will touch
   const int eff_len = (window > 0 && window < max_seq) ? window : max_seq;
-  const int nsplit = attn_pick_splits(ctx, B, Hkv, eff_len);
+  const int nsplit = attn_pick_splits(ctx, B, Hkv, D, eff_len);
   const size_t need =
       nsplit > 1 ? (size_t)B * Hkv * nsplit * 8 * ((size_t)D + 2) * sizeof(float) : 0;
   if (need > (size_t)HB200_ATTN_STATIC_SCRATCH_BYTES) {

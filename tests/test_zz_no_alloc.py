@@ -57,14 +57,20 @@ def test_static_scratch_matches_workspace_entry_point_twice(ctx):
     assert torch.cuda.memory_allocated() <= before + (1 << 20)  # only the test's own tensors
 
 
-def test_shape_beyond_the_array_is_refused(ctx):
+def test_every_shape_fits_the_array(ctx):
+    """The entry point refuses shapes whose split-K partials exceed its 8 MiB array.  With two
+    waves of resident CTAs as the split target no supported shape does any more: check that
+    over a sweep of shapes through the workspace query (no launch: a call that is expected to
+    be refused must never be given buffers it could run on)."""
     from hesper_b200 import _lib
     lib = _lib.load()
-    # 64 sequences x 8 kv heads x 2 splits x 8 x (256+2) floats = 8.45 MB > 8 MiB
-    dummy = torch.zeros(16, device="cuda")
-    p = C.c_void_p(dummy.data_ptr())
-    rc = lib.hb200_attn_decode_static(ctx.handle, p, 0, p, p, p, 64, 64, 8, 256, 32768, 0,
-                                      C.c_float(1.0), p, None)
-    assert rc == -3
-    msg = lib.hb200_last_error().decode()
-    assert "built-in array holds" in msg and "hb200_attn_decode" in msg
+    cap = 8 << 20
+    worst = 0
+    for D in (64, 128, 256):
+        for G in (1, 4, 8):
+            for Hkv in (1, 2, 5, 8, 16):
+                for B in (1, 3, 16, 64, 256, 1024):
+                    for max_seq in (128, 2304, 32768, 1 << 20):
+                        n = int(lib.hb200_attn_workspace_bytes(ctx.handle, B, G * Hkv, Hkv, D, max_seq))
+                        worst = max(worst, n)
+    assert worst - 256 <= cap
