@@ -22,7 +22,9 @@
 //     accumulation is f32, the online softmax works in the exp2 domain;
 //   * the 4 warps merge through shared memory; with one split the CTA writes the
 //     normalised output itself, otherwise it writes (max, sum, unnormalised out)
-//     to the workspace and a small combine kernel merges the splits.
+//     to the workspace and a small combine kernel merges the splits (today: the last split to
+//     arrive merges them, or, for small grids, a thread-block cluster merges through the
+//     leader's shared memory).
 #include <math_constants.h>
 
 #include "common.cuh"
@@ -56,6 +58,8 @@ struct AttnParams {
   int q_is_f16;
   int B, H, Hkv, G, max_seq, window, nsplit;
   int T;             // query tokens per sequence (1 = decode); B counts query tokens, B/T caches
+  int cluster;       // != 0: the nsplit CTAs of a (sequence, KV head) form one cluster and merge
+                     // through the leader's shared memory instead of global partials + ticket
   float scale_log2;  // scale * log2(e)
   int* tickets;      // nullable: per (sequence, kv head) arrival counters, zero between calls
 };
@@ -81,6 +85,23 @@ __device__ __forceinline__ int attn_visible_len(const AttnParams& p, int b, int&
   const int t = b - cache * p.T;
   const int len = min(max(p.seqlens[cache], 0), p.max_seq) - (p.T - 1 - t);
   return max(len, 0);
+}
+
+// ---- thread-block cluster helpers (distributed shared memory) ---------------------------
+__device__ __forceinline__ void cluster_arrive_release() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_acquire() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared-memory address of `local` as seen in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t cluster_map(const void* local, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(local)), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -175,7 +196,13 @@ __global__ void __launch_bounds__(kAttnThreads, D >= 256 ? 1 : 2) attn_decode_ke
   const int nch = (len - start + kChunk - 1) / kChunk;  // chunks of this sequence (<= 0 if empty)
   int cps;                                              // chunks per split
   const int nact = attn_active_splits(nch, p.nsplit, cps);
-  if (split >= nact) return;  // an idle split of a short sequence
+  if (split >= nact) {  // an idle split of a short sequence
+    if (p.cluster) {    // the cluster's one barrier still needs every CTA
+      cluster_arrive_release();
+      cluster_wait_acquire();
+    }
+    return;
+  }
   const int c_begin = split * cps;
   const int c_end = min(nch, c_begin + cps);
 
@@ -399,6 +426,16 @@ __global__ void __launch_bounds__(kAttnThreads, D >= 256 ? 1 : 2) attn_decode_ke
     }
     if (nact == 1) {
       p.out[((size_t)b * p.H + (size_t)kvh * G + h) * D + d] = lsum > 0.f ? acc / lsum : 0.f;
+    } else if (p.cluster) {
+      // into the leader's (split 0) shared memory, behind its stages: [split][8][D] partials,
+      // then [split][8][2] (max, sum)
+      float* cp = reinterpret_cast<float*>(smem + Cfg::kSmem);
+      st_cluster_f32(cluster_map(cp + ((size_t)split * 8 + h) * D + d, 0), acc);
+      if (d == 0) {
+        float* cm = cp + (size_t)p.nsplit * 8 * D + ((size_t)split * 8 + h) * 2;
+        st_cluster_f32(cluster_map(cm, 0), mstar);
+        st_cluster_f32(cluster_map(cm + 1, 0), lsum);
+      }
     } else {
       const size_t pi = (((size_t)b * p.Hkv + kvh) * p.nsplit + split) * 8 + h;
       p.part_out[pi * D + d] = acc;
@@ -409,6 +446,47 @@ __global__ void __launch_bounds__(kAttnThreads, D >= 256 ? 1 : 2) attn_decode_ke
     }
   }
   AT_STAMP(5);
+  if (p.cluster) {
+    // one cluster barrier: every split's partial has landed in the leader's shared memory
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    if (split != 0 || nact == 1) return;
+    const float* cp = reinterpret_cast<const float*>(smem + Cfg::kSmem);
+    const float* cm = cp + (size_t)p.nsplit * 8 * D;
+    float* cw = reinterpret_cast<float*>(smem + Cfg::kQBytes);  // [nsplit][8] weights, then [8] sums
+    float* cl = cw + kMaxSplits * 8;
+    if (tid < 8) {
+      float mstar = -CUDART_INF_F;
+      for (int sidx = 0; sidx < nact; ++sidx) mstar = fmaxf(mstar, cm[(sidx * 8 + tid) * 2]);
+      float lsum = 0.f;
+      for (int sidx = 0; sidx < nact; ++sidx) {
+        const float wgt =
+            mstar == -CUDART_INF_F ? 0.f : exp2f(cm[(sidx * 8 + tid) * 2] - mstar);
+        lsum += wgt * cm[(sidx * 8 + tid) * 2 + 1];
+        cw[sidx * 8 + tid] = wgt;
+      }
+      cl[tid] = lsum;
+    }
+    __syncthreads();
+    for (int i = tid; i < G * D / 4; i += kAttnThreads) {
+      const int h = (i * 4) / D, d = (i * 4) % D;
+      const float4* src = reinterpret_cast<const float4*>(cp + (size_t)h * D + d);
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int sidx = 0; sidx < nact; ++sidx) {
+        const float4 v = src[(size_t)sidx * 2 * D];  // next split: 8*D floats further
+        const float wgt = cw[sidx * 8 + h];
+        acc.x = fmaf(wgt, v.x, acc.x);
+        acc.y = fmaf(wgt, v.y, acc.y);
+        acc.z = fmaf(wgt, v.z, acc.z);
+        acc.w = fmaf(wgt, v.w, acc.w);
+      }
+      const float lsum = cl[h];
+      const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
+      float4* dst = reinterpret_cast<float4*>(p.out + ((size_t)b * p.H + (size_t)kvh * G + h) * D + d);
+      *dst = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+    }
+    return;
+  }
   if (nact == 1 || p.tickets == nullptr) return;
 
   // ---- the last split to finish merges all splits of its (sequence, kv head) ------------
@@ -618,6 +696,45 @@ static int attn_launch_ns(hb200_ctx* ctx, const AttnParams& p, cudaStream_t st) 
     configured = true;
   }
   const int grid = p.B * p.Hkv * p.nsplit;
+  if (p.cluster) {
+    // the splits of one (sequence, KV head) as one cluster; partials in the leader's shared
+    // memory behind the stages.  Falls back to the ticket path if the launch is refused.
+    const size_t smem = (size_t)Cfg::kSmem + (size_t)p.nsplit * 8 * (D + 2) * sizeof(float);
+    static size_t cluster_smem = 0;
+    static uint32_t refused = 0;  // cluster sizes the driver would not launch
+    if (!(refused >> p.nsplit & 1u) && smem <= (size_t)ctx->smem_optin) {
+      cudaError_t e = cudaSuccess;
+      if (smem > cluster_smem) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess)
+          e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e == cudaSuccess) cluster_smem = smem;
+      }
+      if (e == cudaSuccess) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(kAttnThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = (unsigned)p.nsplit;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 2;
+        e = cudaLaunchKernelEx(&cfg, kern, p);
+      }
+      if (e == cudaSuccess) return HB200_OK;
+      cudaGetLastError();  // a refused launch leaves no sticky error; clear the last-error slot
+      refused |= 1u << p.nsplit;
+    }
+    AttnParams q = p;  // ticket path
+    q.cluster = 0;
+    return attn_launch_ns<D, PRECISE, NSTAGES>(ctx, q, st);
+  }
   HB_CUDA(launch_pdl(kern, dim3(grid), dim3(kAttnThreads), (size_t)Cfg::kSmem, st, ctx->pdl, p));
   if (p.nsplit > 1 && p.tickets == nullptr) {
     HB_CUDA(launch_pdl(attn_combine_kernel, dim3(p.B * p.H), dim3(D >= 128 ? 128 : 64), 0, st,
@@ -680,6 +797,13 @@ static int attn_run(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d
   p.scale_log2 = scale * 1.4426950408889634f;
   const int eff_len = (window > 0 && window < max_seq) ? window : max_seq;
   p.nsplit = attn_pick_splits(ctx, B, Hkv, D, eff_len);
+  // Small grids (the latency-bound case) merge their splits inside a thread-block cluster:
+  // at most 16 splits, D <= 128 so that the partials fit behind the stages.
+  if (p.nsplit > 1 && D <= 128 && (long)B * Hkv * (p.nsplit < 16 ? p.nsplit : 16) <= 2L * ctx->sm_count &&
+      ctx->attn_mode != HB200_ATTN_EXACT) {
+    if (p.nsplit > 16) p.nsplit = 16;
+    p.cluster = 1;
+  }
   if (p.nsplit > 1) {
     const size_t po = (size_t)B * Hkv * p.nsplit * 8 * (size_t)D * sizeof(float);
     const size_t need = po + (size_t)B * Hkv * p.nsplit * 8 * 2 * sizeof(float);
