@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(kAttnThreads, D >= 256 ? 1 : 2) attn_decode_ke
   int cps;                                              // chunks per split
   const int nact = attn_active_splits(nch, p.nsplit, cps);
   if (split >= nact) {  // an idle split of a short sequence
-    if (p.cluster) {    // the cluster's one barrier still needs every CTA
+    for (int i = 0; i < p.cluster; ++i) {  // the cluster's barriers still need every CTA
       cluster_arrive_release();
       cluster_wait_acquire();
     }
@@ -410,6 +410,7 @@ __global__ void __launch_bounds__(kAttnThreads, D >= 256 ? 1 : 2) attn_decode_ke
     mb[(2 * t + 1) * 2 + 1] = l1;
   }
   __syncthreads();
+  bool cluster_synced = false;
   for (int i = tid; i < G * D; i += kAttnThreads) {
     const int h = i / D, d = i % D;
     float mstar = -CUDART_INF_F;
@@ -427,9 +428,17 @@ __global__ void __launch_bounds__(kAttnThreads, D >= 256 ? 1 : 2) attn_decode_ke
     if (nact == 1) {
       p.out[((size_t)b * p.H + (size_t)kvh * G + h) * D + d] = lsum > 0.f ? acc / lsum : 0.f;
     } else if (p.cluster) {
-      // into the leader's (split 0) shared memory, behind its stages: [split][8][D] partials,
-      // then [split][8][2] (max, sum)
-      float* cp = reinterpret_cast<float*>(smem + Cfg::kSmem);
+      // into the leader's (split 0) shared memory: [split][8][D] partials, then [split][8][2]
+      // (max, sum).  cluster == 1: a region of its own behind the stages.  cluster == 2 (no
+      // room for that): the stage region itself, once every CTA of the cluster is past its
+      // main loop and its own merge reads -- one more cluster barrier.
+      if (p.cluster == 2 && !cluster_synced) {
+        cluster_arrive_release();
+        cluster_wait_acquire();
+        cluster_synced = true;
+      }
+      float* cp = p.cluster == 1 ? reinterpret_cast<float*>(smem + Cfg::kSmem)
+                                 : mm + kAttnWarps * 16;  // past this CTA's own merge arrays
       st_cluster_f32(cluster_map(cp + ((size_t)split * 8 + h) * D + d, 0), acc);
       if (d == 0) {
         float* cm = cp + (size_t)p.nsplit * 8 * D + ((size_t)split * 8 + h) * 2;
@@ -447,11 +456,17 @@ __global__ void __launch_bounds__(kAttnThreads, D >= 256 ? 1 : 2) attn_decode_ke
   }
   AT_STAMP(5);
   if (p.cluster) {
-    // one cluster barrier: every split's partial has landed in the leader's shared memory
+    if (p.cluster == 2 && !cluster_synced) {  // nact == 1: the first barrier was not reached above
+      cluster_arrive_release();
+      cluster_wait_acquire();
+    }
+    // cluster barrier: every split's partial has landed in the leader's shared memory
     cluster_arrive_release();
     cluster_wait_acquire();
     if (split != 0 || nact == 1) return;
-    const float* cp = reinterpret_cast<const float*>(smem + Cfg::kSmem);
+    const float* cp = p.cluster == 1
+                          ? reinterpret_cast<const float*>(smem + Cfg::kSmem)
+                          : mm + kAttnWarps * 16;
     const float* cm = cp + (size_t)p.nsplit * 8 * D;
     float* cw = reinterpret_cast<float*>(smem + Cfg::kQBytes);  // [nsplit][8] weights, then [8] sums
     float* cl = cw + kMaxSplits * 8;
@@ -699,7 +714,8 @@ static int attn_launch_ns(hb200_ctx* ctx, const AttnParams& p, cudaStream_t st) 
   if (p.cluster) {
     // the splits of one (sequence, KV head) as one cluster; partials in the leader's shared
     // memory behind the stages.  Falls back to the ticket path if the launch is refused.
-    const size_t smem = (size_t)Cfg::kSmem + (size_t)p.nsplit * 8 * (D + 2) * sizeof(float);
+    const size_t smem = (size_t)Cfg::kSmem +
+                        (p.cluster == 1 ? (size_t)p.nsplit * 8 * (D + 2) * sizeof(float) : 0);
     static size_t cluster_smem = 0;
     static uint32_t refused = 0;  // cluster sizes the driver would not launch
     if (!(refused >> p.nsplit & 1u) && smem <= (size_t)ctx->smem_optin) {
@@ -797,12 +813,17 @@ static int attn_run(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d
   p.scale_log2 = scale * 1.4426950408889634f;
   const int eff_len = (window > 0 && window < max_seq) ? window : max_seq;
   p.nsplit = attn_pick_splits(ctx, B, Hkv, D, eff_len);
-  // Small grids (the latency-bound case) merge their splits inside a thread-block cluster:
-  // at most 16 splits, D <= 128 so that the partials fit behind the stages.
-  if (p.nsplit > 1 && D <= 128 && (long)B * Hkv * (p.nsplit < 16 ? p.nsplit : 16) <= 2L * ctx->sm_count &&
+  // Small grids (the latency-bound case) merge their splits inside a thread-block cluster of
+  // at most 16 splits.
+  // Beyond 16 splits the cluster would have to shorten the split list; that still wins while a
+  // split stays short (<= 48 chunks of 16 positions), measured: 8000 positions in 16 splits +
+  // cluster 12.9 us against 62 splits + ticket 17.6 us, 32768 positions 30.8 against 20.0 us.
+  const bool short_splits = p.nsplit <= 16 || (eff_len + kChunk - 1) / kChunk <= 16 * 48;
+  if (p.nsplit > 1 && short_splits &&
+      (long)B * Hkv * (p.nsplit < 16 ? p.nsplit : 16) <= 2L * ctx->sm_count &&
       ctx->attn_mode != HB200_ATTN_EXACT) {
     if (p.nsplit > 16) p.nsplit = 16;
-    p.cluster = 1;
+    p.cluster = D <= 128 ? 1 : 2;  // D = 256: the partials reuse the stage region (2 barriers)
   }
   if (p.nsplit > 1) {
     const size_t po = (size_t)B * Hkv * p.nsplit * 8 * (size_t)D * sizeof(float);
