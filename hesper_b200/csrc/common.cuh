@@ -211,8 +211,18 @@ int hb_gemm16_mma(struct hb200_ctx* ctx, const void* d_table, int dtype, long V,
                   float* d_y, const float* d_residual, long ldy, unsigned long long* d_keys,
                   int table_constant, cudaStream_t st);
 // batched Q4_K with the dequantiser fused into the tensor-core kernel, kquant_mma.cu
+struct HbKqSeg {
+  const uint8_t* blocks;
+  long N;
+  float* y;
+  const float* residual;
+  long ldy;
+  int glu;
+};
+int hb_kq_mma_run_multi(struct hb200_ctx* ctx, const HbKqSeg* segs, int nseg, int K, int M,
+                        int NT, cudaStream_t st);
 int hb_kq_mma_run(struct hb200_ctx* ctx, const uint8_t* d_blocks, int K, long N, int M, int NT,
-                  float* d_y, const float* d_residual, long ldy, cudaStream_t st);
+                  float* d_y, const float* d_residual, long ldy, int glu, cudaStream_t st);
 constexpr size_t kArenaBytes = (size_t)64 << 20;  // f16 weights of one batched k-quant product
 
 struct hb200_ctx {

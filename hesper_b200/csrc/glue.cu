@@ -69,6 +69,65 @@ __global__ void rmsnorm_kernel(const float* x, const float* gamma, const float* 
   }
 }
 
+// The same for K <= 4096, K % 4 == 0 and 16-byte aligned rows: every thread holds its (up to
+// four) float4 of the row in registers, so x is read once and all loads of the launch -- x,
+// gamma, the addend -- are in flight together (one memory round trip instead of two; gamma
+// does not depend on the previous kernel and is fetched before the dependency wait).
+__global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* x, const float* gamma,
+                                                          const float* add, float eps, int K,
+                                                          float* y) {
+  __shared__ double red[8];
+  pdl_trigger();
+  const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nvec = K >> 2;
+  float4 g[4], v[4], a[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int idx = threadIdx.x + i * 256;
+    g[i] = idx < nvec ? __ldg(reinterpret_cast<const float4*>(gamma) + idx)
+                      : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_wait();
+  const float4* xm = reinterpret_cast<const float4*>(x + (size_t)m * K);
+  const float4* am = add ? reinterpret_cast<const float4*>(add + (size_t)m * K) : nullptr;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int idx = threadIdx.x + i * 256;
+    v[i] = idx < nvec ? xm[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+    a[i] = (am && idx < nvec) ? am[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  double ss = 0.0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    ss += (double)v[i].x * v[i].x + (double)v[i].y * v[i].y + (double)v[i].z * v[i].z +
+          (double)v[i].w * v[i].w;
+  ss = warp_sum(ss);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  double tot = 0.0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float rinv = (float)(1.0 / sqrt(tot / (double)K + (double)eps));
+  float4* ym = reinterpret_cast<float4*>(y + (size_t)m * K);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int idx = threadIdx.x + i * 256;
+    if (idx >= nvec) continue;
+    float4 o;
+    o.x = __fmul_rn(__fmul_rn(v[i].x, rinv), g[i].x);
+    o.y = __fmul_rn(__fmul_rn(v[i].y, rinv), g[i].y);
+    o.z = __fmul_rn(__fmul_rn(v[i].z, rinv), g[i].z);
+    o.w = __fmul_rn(__fmul_rn(v[i].w, rinv), g[i].w);
+    if (am) {
+      o.x = __fadd_rn(a[i].x, o.x);
+      o.y = __fadd_rn(a[i].y, o.y);
+      o.z = __fadd_rn(a[i].z, o.z);
+      o.w = __fadd_rn(a[i].w, o.w);
+    }
+    ym[idx] = o;
+  }
+}
+
 // ---- RoPE (NeoX pairs d, d + D/2) + f16 KV-cache write ------------------------------------
 
 // One thread per (token, head, pair); the element's arithmetic lives in rope.cuh.
@@ -380,6 +439,14 @@ extern "C" int hb200_rmsnorm(hb200_ctx* ctx, const float* d_x, const float* d_ga
                              hb200_stream stream) {
   HB_REQUIRE(ctx && d_x && d_gamma && d_y, "rmsnorm: null pointer");
   HB_REQUIRE(M >= 1 && K >= 1, "rmsnorm: M=%d K=%d", M, K);
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_gamma) |
+                         reinterpret_cast<uintptr_t>(d_add) | reinterpret_cast<uintptr_t>(d_y);
+  if (K % 4 == 0 && K <= 4096 && (bits & 15) == 0) {
+    HB_CUDA(launch_pdl(rmsnorm_vec_kernel, dim3(M), dim3(256), 0,
+                       static_cast<cudaStream_t>(stream), ctx->pdl, d_x, d_gamma, d_add, eps, K,
+                       d_y));
+    return HB200_OK;
+  }
   HB_CUDA(launch_pdl(rmsnorm_kernel, dim3(M), dim3(256), 0, static_cast<cudaStream_t>(stream),
                      ctx->pdl, d_x, d_gamma, d_add, eps, K, d_y));
   return HB200_OK;

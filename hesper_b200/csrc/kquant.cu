@@ -524,29 +524,59 @@ __global__ void __launch_bounds__(256) kq_dequant_kernel(const uint8_t* __restri
   }
 }
 
-// y[M][N] = W x (+ residual) for one tensor, any M >= 1: row chunks that fit the arena,
-// token chunks of 64.
+// One product of a batched Q4_K call: y[M][N] = W x, plus a residual or, with glu set, times
+// gelu_tanh of the gate values in `residual`.
+struct KQBatchSeg {
+  const uint8_t* blocks;
+  long N;
+  const float* residual;
+  float* y;
+  int glu;
+};
+
+// Q4_K, any M >= 1, several tensors against the same activations: the dequantiser is fused
+// into the product kernel (kquant_mma.cu; split-K when there are few row tiles).  The
+// activations of a pass are normalised, rounded and laid out once and shared by every tensor.
+static int kq_batched_q4k(hb200_ctx* ctx, const KQBatchSeg* segs, int nseg, int K,
+                          const float* d_x, int M, const float* gamma, float eps,
+                          cudaStream_t st) {
+  // tokens per pass: the tensor time of a pass does not depend on it, the activation tile
+  // and the accumulator do; K above 8192 keeps the 256-token tiles out of their scratch
+  const int cap = K <= 8192 ? 256 : 128;
+  for (int m0 = 0; m0 < M;) {
+    const int left = M - m0;
+    const int NT = left <= 64 ? 64 : (left <= 128 || cap == 128 ? 128 : 256);
+    const int mc = left < NT ? left : NT;
+    int rc = hb_gemm16_split(ctx, 1, K, d_x + (size_t)m0 * K, mc, gamma, eps, NT, st);
+    if (rc != HB200_OK) return rc;
+    // tensors without a GLU epilogue go into one launch, three at a time (their row tiles
+    // add up, so small ones like k and v no longer leave most SMs idle); an up product
+    // whose epilogue reads the gate product's output needs that launch finished first
+    for (int s = 0; s < nseg;) {
+      HbKqSeg run[3];
+      int n = 0;
+      do {
+        const KQBatchSeg& g = segs[s];
+        run[n++] = {g.blocks, g.N, g.y + (size_t)m0 * g.N,
+                    g.residual ? g.residual + (size_t)m0 * g.N : nullptr, g.N, g.glu};
+        ++s;
+      } while (n < 3 && s < nseg && !segs[s].glu && !segs[s - 1].glu);
+      rc = hb_kq_mma_run_multi(ctx, run, n, K, mc, NT, st);
+      if (rc != HB200_OK) return rc;
+    }
+    m0 += mc;
+  }
+  return HB200_OK;
+}
+
+// y[M][N] = W x (+ residual) for one tensor, any M >= 1.  Q8_0 (and the f16-arena route in
+// general): row chunks that fit the arena, token chunks of 64.
 static int kq_batched_one(hb200_ctx* ctx, int fmt, const uint8_t* blocks, int K, long N,
                           const float* d_x, int M, const float* gamma, float eps,
                           const float* residual, float* y, cudaStream_t st) {
-  // Q4_K: dequantiser fused into the product kernel (kquant_mma.cu; split-K when there are
-  // few row tiles).  Q8_0 takes the two-kernel route below.
   if (fmt == HB200_FMT_Q4_K) {
-    // tokens per pass: the tensor time of a pass does not depend on it, the activation tile
-    // and the accumulator do; K above 8192 keeps the 256-token tiles out of their scratch
-    const int cap = K <= 8192 ? 256 : 128;
-    for (int m0 = 0; m0 < M;) {
-      const int left = M - m0;
-      const int NT = left <= 64 ? 64 : (left <= 128 || cap == 128 ? 128 : 256);
-      const int mc = left < NT ? left : NT;
-      int rc = hb_gemm16_split(ctx, 1, K, d_x + (size_t)m0 * K, mc, gamma, eps, NT, st);
-      if (rc != HB200_OK) return rc;
-      rc = hb_kq_mma_run(ctx, blocks, K, N, mc, NT, y + (size_t)m0 * N,
-                         residual ? residual + (size_t)m0 * N : nullptr, N, st);
-      if (rc != HB200_OK) return rc;
-      m0 += mc;
-    }
-    return HB200_OK;
+    const KQBatchSeg g = {blocks, N, residual, y, 0};
+    return kq_batched_q4k(ctx, &g, 1, K, d_x, M, gamma, eps, st);
   }
   const int rowbytes = fmt == HB200_FMT_Q4_K ? K / 256 * 144 : K / 32 * 34;
   long chunk = (long)(kArenaBytes / ((size_t)K * 2)) / 128 * 128;
@@ -699,6 +729,13 @@ extern "C" int hb200_kquant_forward_multi(hb200_ctx* ctx, int fmt, const hb200_k
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (M >= kKQBatchedFrom && !ctx->no_mma) {  // a real contraction: tensor-core path
+    if (fmt == HB200_FMT_Q4_K) {
+      KQBatchSeg g[kKQMaxSeg];
+      for (int s = 0; s < nseg; ++s)
+        g[s] = {static_cast<const uint8_t*>(segs[s].d_blocks), segs[s].N, segs[s].d_residual,
+                segs[s].d_y, 0};
+      return kq_batched_q4k(ctx, g, nseg, K, d_x, M, d_rms_gamma, rms_eps, st);
+    }
     for (int s = 0; s < nseg; ++s) {
       rc = kq_batched_one(ctx, fmt, static_cast<const uint8_t*>(segs[s].d_blocks), K, segs[s].N,
                           d_x, M, d_rms_gamma, rms_eps, segs[s].d_residual, segs[s].d_y, st);
@@ -753,6 +790,14 @@ extern "C" int hb200_kquant_gateup_gelu(hb200_ctx* ctx, int fmt, const void* d_b
                reinterpret_cast<uintptr_t>(d_blocks_up)) & 15) == 0,
              "kquant gate/up: blocks must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M >= kKQBatchedFrom && !ctx->no_mma && fmt == HB200_FMT_Q4_K) {
+    // both products on the tensor cores against one staging of the activations: the gate
+    // product writes d_y, the up product's epilogue multiplies gelu_tanh(gate) in place
+    const KQBatchSeg g[2] = {
+        {static_cast<const uint8_t*>(d_blocks_gate), N, nullptr, d_y, 0},
+        {static_cast<const uint8_t*>(d_blocks_up), N, d_y, d_y, 1}};
+    return kq_batched_q4k(ctx, g, 2, K, d_x, M, d_rms_gamma, rms_eps, st);
+  }
   if (M >= kKQBatchedFrom && !ctx->no_mma &&
       kScratchGlu + (size_t)64 * N * sizeof(float) <= kScratchLmSplit) {
     // both products on the tensor cores: gate straight into d_y, up into scratch (as many

@@ -48,13 +48,23 @@ struct QmCfg {
   static_assert(kSmem <= 232448, "shared memory budget of one CTA");
 };
 
-struct QmParams {
-  CUtensorMap tmap;      // blocks as [N rows][rowbytes], boxes of 128 rows x 144 bytes
-  const uint8_t* xb;     // f16 activations: [K/64][NT rows x 64 f16, operand layout]
-  const float* residual; // nullable
+constexpr int kQmMaxSeg = 3;  // tensors one launch multiplies by the same activations
+
+struct QmSeg {
+  const float* residual; // nullable; with glu != 0 it holds the gate values instead
   float* y;              // y[m * ldy + row]
   long ldy;
-  int K, N, M;
+  int N;
+  int tile0;             // first row tile of this tensor in the launch
+  int glu;               // 0: y = acc (+ residual); 1: y = gelu_tanh(residual) * acc
+};
+
+struct QmParams {
+  CUtensorMap tmap[kQmMaxSeg];  // blocks as [N rows][rowbytes], boxes of 128 rows x 144 bytes
+  QmSeg seg[kQmMaxSeg];
+  int nseg;
+  const uint8_t* xb;     // f16 activations: [K/64][NT rows x 64 f16, operand layout]
+  int K, M;
   int nsplit, bps;       // split-K: CTAs per row tile, super-block boxes per split
   float* part;           // [tile][split][NT tokens][128 rows] partial sums (nsplit > 1)
   int* tickets;          // [tile] arrival counters, zero between launches
@@ -75,6 +85,13 @@ struct QmParams {
 #define QM_STAMP(i, cond) ((void)0)
 #endif
 
+// 0.5*g*(1+tanh(sqrt(2/pi)*(g+0.044715 g^3))), the gate factor of the GeGLU
+// (Hesper/Layers/FusedFFNSpec.lean:42-45), same expression as the standalone kernel
+__device__ __forceinline__ float glu_gate(float g) {
+  const float t = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+  return 0.5f * g * (1.0f + tanhf(t));
+}
+
 __device__ __forceinline__ uint32_t pack_f16(float a, float b) {
   const __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&h);
@@ -92,7 +109,13 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
   const int nboxes = min(p.bps, p.K / 256 - b0);
   const int nsteps = 2 * nboxes;
   const int s0 = 2 * b0;  // first step, in units of the whole row
-  const int row0 = tile * kQmRows;
+  int si = 0;
+#pragma unroll
+  for (int i = 1; i < kQmMaxSeg; ++i)
+    if (i < p.nseg && tile >= p.seg[i].tile0) si = i;
+  const QmSeg& sg = p.seg[si];
+  const CUtensorMap* const tmap = &p.tmap[si];
+  const int row0 = (tile - sg.tile0) * kQmRows;
   constexpr int kExpWarps = 8, kMmaWarpA = 8, kCopyWarp = 9, kMmaWarpB = 10;
 
   uint64_t* pk_full = reinterpret_cast<uint64_t*>(smem);  // [3] box landed (tx bytes)
@@ -133,13 +156,13 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
     auto issue_box = [&](int b) {
       if (lane == 0) {
         mbar_arrive_expect_tx(&pk_full[b % kQmPkStages], kQmPkBytes);
-        tc_tma_box_2d(pk + (size_t)(b % kQmPkStages) * kQmPkBytes, &p.tmap, (b0 + b) * 144, row0,
+        tc_tma_box_2d(pk + (size_t)(b % kQmPkStages) * kQmPkBytes, tmap, (b0 + b) * 144, row0,
                       &pk_full[b % kQmPkStages], pol);
       }
     };
     int bnext = 0;
     if (lane == 0)
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&p.tmap)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
     for (; bnext < kQmPkStages && bnext < nboxes; ++bnext) issue_box(bnext);  // weights: constant
     pdl_trigger();
     pdl_wait();  // the split activations come from the kernel before this one
@@ -280,17 +303,21 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
   };
   auto store_group = [&](int g, const float (&acc)[32]) {
     const int row = row0 + r, m0 = 32 * g;
-    if (row >= p.N || !ok || m0 >= p.M) return;
+    if (row >= sg.N || !ok || m0 >= p.M) return;
     const int mcount = min(32, p.M - m0);
-    const size_t o0 = (size_t)m0 * p.ldy + row;
+    const size_t o0 = (size_t)m0 * sg.ldy + row;
     float res[32];
-    if (p.residual) {
+    if (sg.residual) {
 #pragma unroll
-      for (int t = 0; t < 32; ++t) res[t] = t < mcount ? p.residual[o0 + (size_t)t * p.ldy] : 0.f;
+      for (int t = 0; t < 32; ++t) res[t] = t < mcount ? sg.residual[o0 + (size_t)t * sg.ldy] : 0.f;
     }
 #pragma unroll
     for (int t = 0; t < 32; ++t)
-      if (t < mcount) p.y[o0 + (size_t)t * p.ldy] = p.residual ? __fadd_rn(acc[t], res[t]) : acc[t];
+      if (t < mcount) {
+        float v = acc[t];
+        if (sg.residual) v = sg.glu ? glu_gate(res[t]) * v : __fadd_rn(v, res[t]);
+        sg.y[o0 + (size_t)t * sg.ldy] = v;
+      }
   };
   if (p.nsplit == 1) {
     if (warp < kExpWarps)
@@ -373,42 +400,55 @@ static int kq_mma_launch(hb200_ctx* ctx, QmParams& p, int tiles, cudaStream_t st
   return HB200_OK;
 }
 
-// y[m*ldy + n] = sum_k dequant(W)[n,k] x[m,k] (+ residual) for the M <= NT tokens staged by
-// hb_gemm16_split (dtype f16, single term, NT token rows per block; NT = 64, 128 or 256).
-// Q4_K only; K a multiple of 256.
-int hb_kq_mma_run(hb200_ctx* ctx, const uint8_t* d_blocks, int K, long N, int M, int NT,
-                  float* d_y, const float* d_residual, long ldy, cudaStream_t st) {
-  HB_REQUIRE(K % 256 == 0 && N >= 1 && N < (1l << 31) && M >= 1 && M <= NT &&
+// For each of nseg tensors: y[m*ldy + n] = sum_k dequant(W)[n,k] x[m,k] (+ residual) for the
+// M <= NT tokens staged by hb_gemm16_split (dtype f16, single term, NT token rows per block;
+// NT = 64, 128 or 256), all in ONE launch.  glu != 0: `residual` holds gate pre-activations
+// and y = gelu_tanh(gate) * product (y may be the same array as residual; the gate values
+// must come from an earlier launch).  Q4_K only; K a multiple of 256.
+int hb_kq_mma_run_multi(hb200_ctx* ctx, const HbKqSeg* segs, int nseg, int K, int M, int NT,
+                        cudaStream_t st) {
+  HB_REQUIRE(nseg >= 1 && nseg <= kQmMaxSeg && K % 256 == 0 && M >= 1 && M <= NT &&
                  (NT == 64 || NT == 128 || NT == 256),
-             "kquant (fused batched): K=%d N=%ld M=%d NT=%d", K, N, M, NT);
+             "kquant (fused batched): nseg=%d K=%d M=%d NT=%d", nseg, K, M, NT);
   QmParams p = {};
   TcEncodeTiledFn encode = tc_tensor_map_encoder();
   HB_REQUIRE(encode != nullptr, "kquant (fused batched): the driver has no cuTensorMapEncodeTiled");
   const int rowbytes = K / 256 * 144;
-  const cuuint64_t dims[2] = {(cuuint64_t)rowbytes, (cuuint64_t)N};
-  const cuuint64_t strides[1] = {(cuuint64_t)rowbytes};
-  const cuuint32_t box[2] = {144u, (cuuint32_t)kQmRows};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult rc = encode(&p.tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
-                             const_cast<uint8_t*>(d_blocks), dims, strides, box, estr,
-                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  HB_REQUIRE(rc == CUDA_SUCCESS, "kquant (fused batched): cuTensorMapEncodeTiled failed (%d)",
-             (int)rc);
+  int tiles = 0;
+  for (int s = 0; s < nseg; ++s) {
+    const HbKqSeg& g = segs[s];
+    HB_REQUIRE(g.N >= 1 && g.N < (1l << 31) && g.blocks && g.y,
+               "kquant (fused batched): tensor %d has no rows or a null pointer", s);
+    HB_REQUIRE(!g.glu || g.residual, "kquant (fused batched): GLU epilogue without gate values");
+    const cuuint64_t dims[2] = {(cuuint64_t)rowbytes, (cuuint64_t)g.N};
+    const cuuint64_t strides[1] = {(cuuint64_t)rowbytes};
+    const cuuint32_t box[2] = {144u, (cuuint32_t)kQmRows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult rc = encode(&p.tmap[s], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                               const_cast<uint8_t*>(g.blocks), dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    HB_REQUIRE(rc == CUDA_SUCCESS, "kquant (fused batched): cuTensorMapEncodeTiled failed (%d)",
+               (int)rc);
+    p.seg[s] = {g.residual, g.y, g.ldy, (int)g.N, tiles, g.glu};
+    tiles += (int)((g.N + kQmRows - 1) / kQmRows);
+  }
+  p.nseg = nseg;
   p.xb = static_cast<const uint8_t*>(ctx->d_scratch) + kScratchLmSplit;
-  p.residual = d_residual;
-  p.y = d_y;
-  p.ldy = ldy;
   p.K = K;
-  p.N = (int)N;
   p.M = M;
   p.part = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->d_scratch) + kScratchSplitK);
   p.tickets = ctx->d_tickets;
   p.status = ctx->d_status;
-  const int tiles = (int)((N + kQmRows - 1) / kQmRows);
   switch (NT) {
     case 64: return kq_mma_launch<64>(ctx, p, tiles, st);
     case 128: return kq_mma_launch<128>(ctx, p, tiles, st);
     default: return kq_mma_launch<256>(ctx, p, tiles, st);
   }
+}
+
+int hb_kq_mma_run(hb200_ctx* ctx, const uint8_t* d_blocks, int K, long N, int M, int NT,
+                  float* d_y, const float* d_residual, long ldy, int glu, cudaStream_t st) {
+  const HbKqSeg g = {d_blocks, N, d_y, d_residual, ldy, glu};
+  return hb_kq_mma_run_multi(ctx, &g, 1, K, M, NT, st);
 }

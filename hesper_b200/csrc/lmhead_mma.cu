@@ -98,6 +98,69 @@ __global__ void __launch_bounds__(256) lm_split_kernel(const __grid_constant__ L
     return;
   }
   const float* xg = p.x + (size_t)m * K;
+  auto emit = [&](int k, const float (&v)[8]) {
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint16_t h[2], l[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        h[e] = round16(v[2 * j + e], p.dtype);
+        l[e] = round16(__fsub_rn(v[2 * j + e], widen16(h[e], p.dtype)), p.dtype);
+      }
+      hi[j] = (uint32_t)h[0] | ((uint32_t)h[1] << 16);
+      lo[j] = (uint32_t)l[0] | ((uint32_t)l[1] << 16);
+    }
+    *reinterpret_cast<uint4*>(dst(m, k)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    if (!p.single)
+      *reinterpret_cast<uint4*>(dst(kLmTokens + m, k)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+  };
+  constexpr int kHeld = 5;  // 8-element groups a thread keeps in registers: K <= 10240
+  const bool aligned =
+      ((reinterpret_cast<uintptr_t>(xg) | reinterpret_cast<uintptr_t>(p.gamma)) & 15) == 0;
+  if (K <= kHeld * 2048 && aligned) {
+    // the row is read once and stays in registers between the sum of squares and the rounding
+    float v[kHeld][8];
+#pragma unroll
+    for (int i = 0; i < kHeld; ++i) {
+      const int k = tid * 8 + i * 2048;
+      const bool in = k < K;
+      const float4 a = in ? *reinterpret_cast<const float4*>(xg + k) : make_float4(0, 0, 0, 0);
+      const float4 b = in ? *reinterpret_cast<const float4*>(xg + k + 4) : make_float4(0, 0, 0, 0);
+      v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w;
+      v[i][4] = b.x; v[i][5] = b.y; v[i][6] = b.z; v[i][7] = b.w;
+    }
+    if (p.gamma) {
+      double ss = 0.0;
+#pragma unroll
+      for (int i = 0; i < kHeld; ++i)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += (double)v[i][e] * v[i][e];
+      ss = warp_sum(ss);
+      if (lane == 0) red[warp] = ss;
+      __syncthreads();
+      ss = 0.0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += red[i];
+      const float rinv = (float)(1.0 / sqrt(ss / (double)K + (double)p.eps));
+#pragma unroll
+      for (int i = 0; i < kHeld; ++i) {
+        const int k = tid * 8 + i * 2048;
+        if (k >= K) continue;
+        const float4 ga = __ldg(reinterpret_cast<const float4*>(p.gamma + k));
+        const float4 gb = __ldg(reinterpret_cast<const float4*>(p.gamma + k + 4));
+        const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] = __fmul_rn(__fmul_rn(v[i][e], rinv), g[e]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kHeld; ++i) {
+      const int k = tid * 8 + i * 2048;
+      if (k < K) emit(k, v[i]);
+    }
+    return;
+  }
   float rinv = 1.f;
   if (p.gamma) {
     double ss = 0.0;
@@ -114,23 +177,11 @@ __global__ void __launch_bounds__(256) lm_split_kernel(const __grid_constant__ L
     rinv = (float)(1.0 / sqrt(ss / (double)K + (double)p.eps));
   }
   for (int k = tid * 8; k < K; k += 256 * 8) {
-    uint32_t hi[4], lo[4];
+    float v[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      uint16_t h[2], l[2];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int kk = k + 2 * j + e;
-        const float v = p.gamma ? __fmul_rn(__fmul_rn(xg[kk], rinv), p.gamma[kk]) : xg[kk];
-        h[e] = round16(v, p.dtype);
-        l[e] = round16(__fsub_rn(v, widen16(h[e], p.dtype)), p.dtype);
-      }
-      hi[j] = (uint32_t)h[0] | ((uint32_t)h[1] << 16);
-      lo[j] = (uint32_t)l[0] | ((uint32_t)l[1] << 16);
-    }
-    *reinterpret_cast<uint4*>(dst(m, k)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-    if (!p.single)
-      *reinterpret_cast<uint4*>(dst(kLmTokens + m, k)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    for (int e = 0; e < 8; ++e)
+      v[e] = p.gamma ? __fmul_rn(__fmul_rn(xg[k + e], rinv), p.gamma[k + e]) : xg[k + e];
+    emit(k, v);
   }
 }
 

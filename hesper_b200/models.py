@@ -107,7 +107,8 @@ class BitNetModel:
             if isinstance(a, torch.Tensor):
                 t = a.to(dev).contiguous()
             else:
-                t = torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+                a = np.ascontiguousarray(a)
+                t = torch.from_numpy(a if a.flags.writeable else a.copy()).to(dev)
             self._keep.append(t)
             return t
 

@@ -132,9 +132,11 @@ def test_batched_row_chunks_of_the_arena(ctx, oracle):
     _check(y[[0, 19]], oracle.q4k_matvec(blocks, K, N, x[[0, 19]]))
 
 
-@pytest.mark.parametrize("M", [16, 70])
-def test_batched_gate_up_and_multi(ctx, oracle, M):
-    K, N = 2560, 1000
+@pytest.mark.parametrize("K,N,M", [(2560, 1000, 16), (2560, 1000, 70), (2560, 1000, 256),
+                                   (512, 9000, 200), (10240, 640, 150)])
+def test_batched_gate_up_and_multi(ctx, oracle, K, N, M):
+    """Gate and up share one staging of the activations; the GLU is the up product's epilogue
+    (with and without split-K, 64 / 128 / 256 tokens per pass, several passes)."""
     rng = np.random.default_rng(M)
     bg = formats.random_q4k(rng, N, K)
     bu = formats.random_q4k(rng, N, K)
