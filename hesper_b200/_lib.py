@@ -76,6 +76,10 @@ SIGNATURES = {
     "hb200_kquant_forward": (_i, [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _f, _vp, _vp, _vp]),
     "hb200_kquant_forward_multi": (_i, [_vp, _i, C.POINTER(KQuantSeg), _i, _i, _vp, _i, _vp, _f, _vp]),
     "hb200_kquant_gateup_gelu": (_i, [_vp, _i, _vp, _vp, _i, _i, _vp, _i, _vp, _f, _vp, _vp]),
+    "hb200_kquant_forward_multi_pre": (_i, [_vp, _i, C.POINTER(KQuantSeg), _i, _i, _vp, _i, _vp, _vp,
+                                            _vp, _vp, _f, _vp]),
+    "hb200_kquant_gateup_gelu_pre": (_i, [_vp, _i, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _f,
+                                          _vp, _vp]),
     "hb200_attn_workspace_bytes": (_sz, [_vp, _i, _i, _i, _i, _i]),
     "hb200_attn_decode_static": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _vp]),
     "hb200_embed_lookup": (_i, [_vp, _vp, _i, C.c_long, _i, _vp, _i, _f, _vp, _vp]),

@@ -207,6 +207,9 @@ constexpr size_t kScratchSplitK = (size_t)16 << 20;   // batched paths: split-K 
 // the two halves of it, also used by the batched k-quant path (weights dequantised to f16)
 int hb_gemm16_split(struct hb200_ctx* ctx, int dtype, int K, const float* d_x, int M,
                     const float* d_rms_gamma, float rms_eps, int single, cudaStream_t st);
+int hb_gemm16_split_pre(struct hb200_ctx* ctx, int dtype, int K, const float* d_x, int M,
+                        const float* d_pre_base, const float* d_pre_gamma, float* d_pre_out,
+                        const float* d_rms_gamma, float rms_eps, int single, cudaStream_t st);
 int hb_gemm16_mma(struct hb200_ctx* ctx, const void* d_table, int dtype, long V, int K, int M,
                   float* d_y, const float* d_residual, long ldy, unsigned long long* d_keys,
                   int table_constant, cudaStream_t st);

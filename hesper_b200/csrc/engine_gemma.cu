@@ -12,6 +12,7 @@
 // of the LM head, and the matching input columns of o_proj and down_proj.  The only
 // exchange is one f32 sum all-reduce of hidden*batch elements after o_proj and after
 // down_proj, and one u64 max all-reduce of batch argmax keys per token.
+#include <cstdlib>
 #include <vector>
 
 #include "common.cuh"
@@ -38,22 +39,48 @@ struct hb200_gemma {
 
 namespace hb {
 
-// keys[m] = best (value, global index) of this rank's logits slice
-__global__ void argmax_keys_kernel(const float* logits, int V, int voffset,
-                                   unsigned long long* keys) {
-  __shared__ unsigned long long red[32];
+// keys[m] = max(keys[m], best (value, global index) of this rank's logits slice): ordered
+// keys, so the maximum is the largest value and, among equals, the smallest index.  The grid
+// is (chunks of `chunk` logits, tokens); every CTA folds its chunk and issues one atomicMax,
+// whose result does not depend on the order of arrival.  keys[] must be zero on entry
+// (keys_to_tokens_kernel leaves it so).
+__device__ __forceinline__ unsigned long long argmax_key(float v, uint32_t index) {
+  if (!(v == v)) return 0ull;
+  uint32_t u = __float_as_uint(v);
+  u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - index);
+}
+__global__ void __launch_bounds__(256) argmax_keys_kernel(const float* logits, int V, int voffset,
+                                                          int chunk, unsigned long long* keys) {
+  __shared__ unsigned long long red[8];
   pdl_trigger();
   pdl_wait();
-  const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int m = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float* row = logits + (size_t)m * V;
+  const int i0 = blockIdx.x * chunk, i1 = min(V, i0 + chunk);
   unsigned long long best = 0;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = row[i];
-    if (v == v) {
-      uint32_t u = __float_as_uint(v);
-      u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-      const unsigned long long k =
-          ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)(i + voffset));
+  if ((reinterpret_cast<uintptr_t>(row + i0) & 15) == 0) {
+    const int nvec = (i1 - i0) >> 2;
+    const float4* r4 = reinterpret_cast<const float4*>(row + i0);
+    for (int j = threadIdx.x; j < nvec; j += 256) {
+      const float4 v = r4[j];
+      const uint32_t g = (uint32_t)(i0 + 4 * j + voffset);
+      unsigned long long k = argmax_key(v.x, g);
+      best = k > best ? k : best;
+      k = argmax_key(v.y, g + 1);
+      best = k > best ? k : best;
+      k = argmax_key(v.z, g + 2);
+      best = k > best ? k : best;
+      k = argmax_key(v.w, g + 3);
+      best = k > best ? k : best;
+    }
+    for (int i = i0 + 4 * nvec + threadIdx.x; i < i1; i += 256) {
+      const unsigned long long k = argmax_key(row[i], (uint32_t)(i + voffset));
+      best = k > best ? k : best;
+    }
+  } else {
+    for (int i = i0 + threadIdx.x; i < i1; i += 256) {
+      const unsigned long long k = argmax_key(row[i], (uint32_t)(i + voffset));
       best = k > best ? k : best;
     }
   }
@@ -65,18 +92,21 @@ __global__ void argmax_keys_kernel(const float* logits, int V, int voffset,
   if (lane == 0) red[warp] = best;
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) best = red[i] > best ? red[i] : best;
-    keys[m] = best;
+#pragma unroll
+    for (int i = 1; i < 8; ++i) best = red[i] > best ? red[i] : best;
+    if (best) atomicMax(keys + m, best);
   }
 }
 
-__global__ void keys_to_tokens_kernel(const unsigned long long* keys, int M, int32_t* tok,
+// Turns the reduced keys into tokens, logs them, and zeroes the keys for the next step.
+__global__ void keys_to_tokens_kernel(unsigned long long* keys, int M, int32_t* tok,
                                       int32_t* log, const int32_t* log_index, int log_stride) {
   pdl_trigger();
   pdl_wait();
   const int m = blockIdx.x * blockDim.x + threadIdx.x;
   if (m >= M) return;
   const unsigned long long k = keys[m];
+  keys[m] = 0ull;
   const int32_t t = k ? (int32_t)(0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull)) : 0;
   tok[m] = t;
   const int li = log_index[0];
@@ -103,12 +133,22 @@ int gemma_enqueue_step(hb200_gemma* m, const int32_t* d_tokens, bool lm_head, cu
   if (rc) return rc;
   rc = hb200_rope_table(ctx, m->pos, B, 1, D, c.rope_base, m->rope_tab, st);
   if (rc) return rc;
+  // With one rank nothing has to be exchanged between a block's output projection and its
+  // post-norm, so the post-norm + residual add runs inside the prologue of the NEXT matvec
+  // launch (the o_proj / down_proj output stays in m->o until then): two launches fewer per
+  // layer.  The last layer's post-FFN norm has no next matvec and runs on its own.
+  const bool fold = m->tp == nullptr && getenv("HB200_NO_FOLD") == nullptr;
   for (int l = 0; l < c.n_layers; ++l) {
     const hb200_gemma_layer& L = m->layers[l];
     hb200_kquant_seg segs[3] = {
         {L.wq, nullptr, m->q, qdim}, {L.wk, nullptr, m->k, kvdim}, {L.wv, nullptr, m->v, kvdim}};
-    rc = hb200_kquant_forward_multi(ctx, HB200_FMT_Q4_K, segs, 3, Hd, m->x, B, L.attn_norm,
-                                    c.rms_eps, st);
+    if (fold && l > 0)  // x = x1 + rmsnorm(o) * post_ffn_norm of the previous layer
+      rc = hb200_kquant_forward_multi_pre(ctx, HB200_FMT_Q4_K, segs, 3, Hd, m->o, B, m->x1,
+                                          m->layers[l - 1].post_ffn_norm, m->x, L.attn_norm,
+                                          c.rms_eps, st);
+    else
+      rc = hb200_kquant_forward_multi(ctx, HB200_FMT_Q4_K, segs, 3, Hd, m->x, B, L.attn_norm,
+                                      c.rms_eps, st);
     if (rc) return rc;
     const bool glob = layer_is_global(c, l);
     rc = hb200_rope_kv_write_angles(ctx, m->q, m->k, m->v, m->kc[l], m->vc[l], m->pos, m->rope_tab,
@@ -123,29 +163,40 @@ int gemma_enqueue_step(hb200_gemma* m, const int32_t* d_tokens, bool lm_head, cu
     rc = hb200_kquant_forward(ctx, HB200_FMT_Q4_K, L.wo, qdim, Hd, m->att, B, nullptr, 0.f, nullptr,
                               m->o, st);
     if (rc) return rc;
-    rc = hb200_tp_allreduce_rmsnorm(m->tp, ctx, m->o, L.post_attn_norm, m->x, c.rms_eps, B, Hd,
-                                    m->x1, st);
-    if (rc) return rc;
-    rc = hb200_kquant_gateup_gelu(ctx, HB200_FMT_Q4_K, L.wgate, L.wup, Hd, c.local_ffn, m->x1, B,
-                                  L.ffn_norm, c.rms_eps, m->h, st);
+    if (fold) {  // x1 = x + rmsnorm(o) * post_attn_norm, then the gated FFN on x1
+      rc = hb200_kquant_gateup_gelu_pre(ctx, HB200_FMT_Q4_K, L.wgate, L.wup, Hd, c.local_ffn, m->o,
+                                        B, m->x, L.post_attn_norm, m->x1, L.ffn_norm, c.rms_eps,
+                                        m->h, st);
+    } else {
+      rc = hb200_tp_allreduce_rmsnorm(m->tp, ctx, m->o, L.post_attn_norm, m->x, c.rms_eps, B, Hd,
+                                      m->x1, st);
+      if (rc) return rc;
+      rc = hb200_kquant_gateup_gelu(ctx, HB200_FMT_Q4_K, L.wgate, L.wup, Hd, c.local_ffn, m->x1, B,
+                                    L.ffn_norm, c.rms_eps, m->h, st);
+    }
     if (rc) return rc;
     rc = hb200_kquant_forward(ctx, HB200_FMT_Q4_K, L.wdown, c.local_ffn, Hd, m->h, B, nullptr, 0.f,
                               nullptr, m->o, st);
     if (rc) return rc;
-    rc = hb200_tp_allreduce_rmsnorm(m->tp, ctx, m->o, L.post_ffn_norm, m->x1, c.rms_eps, B, Hd,
-                                    m->x, st);
-    if (rc) return rc;
+    if (!fold || l == c.n_layers - 1) {
+      rc = hb200_tp_allreduce_rmsnorm(m->tp, ctx, m->o, L.post_ffn_norm, m->x1, c.rms_eps, B, Hd,
+                                      m->x, st);
+      if (rc) return rc;
+    }
   }
   if (lm_head) {
     rc = hb200_kquant_forward(ctx, HB200_FMT_Q4_K, m->lm_head, Hd, c.local_vocab, m->x, B,
                               m->final_norm, c.rms_eps, nullptr, m->logits, st);
     if (rc) return rc;
-    HB_CUDA(launch_pdl(argmax_keys_kernel, dim3(B), dim3(1024), 0, st, ctx->pdl,
-                       (const float*)m->logits, c.local_vocab, c.vocab_offset, m->keys));
+    // enough CTAs to spread a single token's logits over the SMs, few atomics at large batch
+    const int chunk = B <= 8 ? 2048 : 8192;
+    HB_CUDA(launch_pdl(argmax_keys_kernel, dim3((c.local_vocab + chunk - 1) / chunk, B),
+                       dim3(256), 0, st, ctx->pdl, (const float*)m->logits, c.local_vocab,
+                       c.vocab_offset, chunk, m->keys));
     rc = hb200_tp_allreduce_max_u64(m->tp, m->keys, (size_t)B, st);
     if (rc) return rc;
     HB_CUDA(launch_pdl(keys_to_tokens_kernel, dim3((B + 63) / 64), dim3(64), 0, st, ctx->pdl,
-                       (const unsigned long long*)m->keys, B, m->tok, m->token_log,
+                       m->keys, B, m->tok, m->token_log,
                        (const int32_t*)m->log_index, m->log_stride));
     rc = hb200_add_i32(ctx, m->log_index, 1, 1, st);
     if (rc) return rc;
@@ -210,6 +261,7 @@ extern "C" int hb200_gemma_create(hb200_ctx* ctx, hb200_tp* tp, const hb200_gemm
   A(cudaMalloc(reinterpret_cast<void**>(&m->log_index), sizeof(int32_t)));
   A(cudaMalloc(reinterpret_cast<void**>(&m->token_log), sizeof(int32_t) * (size_t)B * m->log_stride));
   A(cudaMalloc(reinterpret_cast<void**>(&m->keys), sizeof(unsigned long long) * B));
+  A(cudaMemset(m->keys, 0, sizeof(unsigned long long) * B));
   A(cudaMalloc(reinterpret_cast<void**>(&m->rope_tab), sizeof(double) * (size_t)B * D));
   m->attn_ws_bytes = hb200_attn_workspace_bytes(ctx, B, cfg->local_q_heads, cfg->local_kv_heads, D,
                                                 max_slots);

@@ -68,6 +68,11 @@ struct KQParams {
   const float* gamma;
   float eps;
   uint32_t* status;
+  // optional step in front of the prologue: x' = pre_base + rmsnorm(x) * pre_gamma, which the
+  // matvec (and its own optional RMSNorm) then consumes; CTA 0 also writes x' to pre_out
+  const float* pre_base;
+  const float* pre_gamma;
+  float* pre_out;
 };
 
 template <int NS>
@@ -209,14 +214,16 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
   // slot simply the tile's index in the CTA, so no slot is wasted on a warp with fewer tiles.
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // [nslots]
   size_t off = ((size_t)p.nslots * sizeof(uint64_t) + 127) & ~size_t(127);
-  double* red_f64 = reinterpret_cast<double*>(smem + off);  // [16]
-  off += 16 * sizeof(double);
+  double* red_f64 = reinterpret_cast<double*>(smem + off);  // [32]: two sets of warp sums
+  off += 32 * sizeof(double);
   uint32_t* xhi = reinterpret_cast<uint32_t*>(smem + off);  // [K] int8 hi plane
   off += (size_t)K;
   uint32_t* xlo = reinterpret_cast<uint32_t*>(smem + off);  // [K] uint8 lo plane
   off += (size_t)K;
   float4* xtab = reinterpret_cast<float4*>(smem + off);  // [K/64] chunk scales and sums
   off += (size_t)nchunk * sizeof(float4);
+  float4* xs4 = reinterpret_cast<float4*>(smem + off);  // [K] floats, only with the pre-step
+  if (p.pre_gamma) off += (size_t)K * sizeof(float);
   off = (off + 127) & ~size_t(127);
   uint8_t* wstage = smem + off;
   auto slot_of = [&](int k) { return warp + (k % S) * kKQWarps; };
@@ -231,7 +238,7 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
       if (slot_of(s) < p.nslots) mbar_init(&bars[slot_of(s)], 1);
     fence_mbar_init();
   }
-  if (tid < 16) red_f64[tid] = 0.0;
+  if (tid < 32) red_f64[tid] = 0.0;
   __syncwarp();
   const uint64_t pol = policy_evict_first();
 
@@ -273,12 +280,24 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
   const int M = p.M;
   const float* const xbase = p.x;
   const float* const gamma = p.gamma;
+  // Rows of up to 2 float4 per thread are kept in registers from their first read to the
+  // quantisation; the norm weights are constants of the model and are fetched here, before
+  // the wait on the previous kernel.
+  constexpr int kHeld = 2;
+  const int nvec = K >> 2;
+  const bool held = nvec <= kHeld * kKQThreads;
+  float4 hgm[kHeld];
+#pragma unroll
+  for (int j = 0; j < kHeld; ++j) {
+    const int i = tid + j * kKQThreads;
+    hgm[j] = (held && gamma && i < nvec) ? __ldg(reinterpret_cast<const float4*>(gamma) + i)
+                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   HB_STAMP(1);
   pdl_trigger();
   pdl_wait();
   HB_STAMP(2);
 
-  const int nvec = K >> 2;
   const Q4KSel sel_main = q4k_sel(lane & 3);  // in whole passes a lane's chunk index is lane & 3
   const int npass = nchunk >> 5;   // whole passes: lane l owns chunk pass*32 + l
   const int rem = nchunk & 31;     // chunks left per row; rem*kRows tasks per tile
@@ -289,12 +308,40 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
     // ---- activation prologue: (RMSNorm), per-32 block 16-bit quantisation ------
     __syncthreads();
     const float4* xg = reinterpret_cast<const float4*>(xbase + (size_t)m * K);
+    const bool pre = p.pre_gamma != nullptr;
     float rinv = 1.f;
-    if (gamma) {
+    double ss2 = 0.0;  // sum of squares of the row the matvec consumes, when already known
+    float4 hx[kHeld];  // that row, when held in registers
+#pragma unroll
+    for (int j = 0; j < kHeld; ++j) {
+      const int i = tid + j * kKQThreads;
+      hx[j] = (held && !pre && i < nvec) ? __ldg(xg + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (pre) {
+      // x' = base + rmsnorm(x) * pre_gamma, same operation order as the standalone kernel.
+      // Rows of up to 2 float4 per thread stay in registers with their gamma and base, so
+      // that all loads of the step are in flight together (one memory round trip).
+      const float4* pg = reinterpret_cast<const float4*>(p.pre_gamma);
+      const float4* bg = reinterpret_cast<const float4*>(p.pre_base + (size_t)m * K);
+      float4* og = reinterpret_cast<float4*>(p.pre_out + (size_t)m * K);
+      float4 hv[kHeld], hg[kHeld], hb[kHeld];
       double ss = 0.0;
-      for (int i = tid; i < nvec; i += kKQThreads) {
-        const float4 v = __ldg(xg + i);
-        ss += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
+      auto sq = [](const float4& v) {
+        return (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
+      };
+      if (held) {
+#pragma unroll
+        for (int j = 0; j < kHeld; ++j) {
+          const int i = tid + j * kKQThreads;
+          const bool in = i < nvec;
+          hv[j] = in ? __ldg(xg + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+          hg[j] = in ? __ldg(pg + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+          hb[j] = in ? __ldg(bg + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < kHeld; ++j) ss += sq(hv[j]);
+      } else {
+        for (int i = tid; i < nvec; i += kKQThreads) ss += sq(__ldg(xg + i));
       }
       ss = warp_sum(ss);
       if (lane == 0) red_f64[warp] = ss;
@@ -302,22 +349,63 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
       ss = 0.0;
 #pragma unroll
       for (int i = 0; i < kKQWarps; ++i) ss += red_f64[i];
+      const float r1 = (float)(1.0 / sqrt(ss / (double)K + (double)p.eps));
+      auto step = [&](int i, const float4& v, const float4& g, const float4& b) {
+        float4 r;
+        r.x = __fadd_rn(b.x, __fmul_rn(__fmul_rn(v.x, r1), g.x));
+        r.y = __fadd_rn(b.y, __fmul_rn(__fmul_rn(v.y, r1), g.y));
+        r.z = __fadd_rn(b.z, __fmul_rn(__fmul_rn(v.z, r1), g.z));
+        r.w = __fadd_rn(b.w, __fmul_rn(__fmul_rn(v.w, r1), g.w));
+        xs4[i] = r;
+        if (blockIdx.x == 0) og[i] = r;
+        ss2 += sq(r);
+        return r;
+      };
+      if (held) {
+#pragma unroll
+        for (int j = 0; j < kHeld; ++j) {
+          const int i = tid + j * kKQThreads;
+          if (i < nvec) hx[j] = step(i, hv[j], hg[j], hb[j]);
+        }
+      } else {
+        for (int i = tid; i < nvec; i += kKQThreads) step(i, __ldg(xg + i), __ldg(pg + i), __ldg(bg + i));
+      }
+      if (gamma) {  // the second set of slots: the first may still be being read
+        ss2 = warp_sum(ss2);
+        if (lane == 0) red_f64[16 + warp] = ss2;
+      }
+      __syncthreads();
+    }
+    auto load_x = [&](int i) { return pre ? xs4[i] : __ldg(xg + i); };
+    if (gamma) {
+      double ss = 0.0;
+      if (pre) {
+#pragma unroll
+        for (int i = 0; i < kKQWarps; ++i) ss += red_f64[16 + i];
+      } else {
+        if (held) {
+#pragma unroll
+          for (int j = 0; j < kHeld; ++j)
+            ss += (double)hx[j].x * hx[j].x + (double)hx[j].y * hx[j].y +
+                  (double)hx[j].z * hx[j].z + (double)hx[j].w * hx[j].w;
+        } else {
+          for (int i = tid; i < nvec; i += kKQThreads) {
+            const float4 v = load_x(i);
+            ss += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
+          }
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) red_f64[warp] = ss;
+        __syncthreads();
+        ss = 0.0;
+#pragma unroll
+        for (int i = 0; i < kKQWarps; ++i) ss += red_f64[i];
+      }
       rinv = (float)(1.0 / sqrt(ss / (double)K + (double)p.eps));
     }
-    // every group of 8 lanes owns one 32-element block; nvec is a multiple of 8
-    for (int i0 = warp * 32; i0 < nvec; i0 += kKQThreads) {
-      const int i = i0 + lane;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (i < nvec) {
-        v = __ldg(xg + i);  // second read of x hits L1/L2
-        if (gamma) {
-          const float4 g = __ldg(reinterpret_cast<const float4*>(gamma) + i);
-          v.x = v.x * rinv * g.x;
-          v.y = v.y * rinv * g.y;
-          v.z = v.z * rinv * g.z;
-          v.w = v.w * rinv * g.w;
-        }
-      }
+    // every group of 8 lanes owns one 32-element block; nvec is a multiple of 8.  v = the
+    // normalised float4 number i of the row (zero beyond the row).
+    auto quant4 = [&](int i, float4 v) {
       float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
       float sum = (v.x + v.y) + (v.z + v.w);
 #pragma unroll
@@ -349,6 +437,30 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
             t[2] = sum;
           }
         }
+      }
+    };
+    auto scaled = [&](float4 v, const float4& g) {
+      if (gamma) {
+        v.x = v.x * rinv * g.x;
+        v.y = v.y * rinv * g.y;
+        v.z = v.z * rinv * g.z;
+        v.w = v.w * rinv * g.w;
+      }
+      return v;
+    };
+    if (held) {
+#pragma unroll
+      for (int j = 0; j < kHeld; ++j) {
+        const int i0 = warp * 32 + j * kKQThreads;  // warp-uniform: the shuffles stay whole
+        if (i0 < nvec) quant4(i0 + lane, scaled(hx[j], hgm[j]));
+      }
+    } else {
+      for (int i0 = warp * 32; i0 < nvec; i0 += kKQThreads) {
+        const int i = i0 + lane;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < nvec)
+          v = scaled(load_x(i), gamma ? __ldg(reinterpret_cast<const float4*>(gamma) + i) : v);
+        quant4(i, v);
       }
     }
     __syncthreads();
@@ -524,6 +636,15 @@ __global__ void __launch_bounds__(256) kq_dequant_kernel(const uint8_t* __restri
   }
 }
 
+// The optional pre-step (x' = base + rmsnorm(x) * pre_gamma, x' also written to pre_out) in
+// front of a matvec call: inside the streaming kernel's prologue at small batch sizes, inside
+// the activation staging kernel of the batched Q4_K path, its own launch otherwise.
+struct KQPre {
+  const float* base;
+  const float* gamma;
+  float* out;
+};
+
 // One product of a batched Q4_K call: y[M][N] = W x, plus a residual or, with glu set, times
 // gelu_tanh of the gate values in `residual`.
 struct KQBatchSeg {
@@ -538,8 +659,8 @@ struct KQBatchSeg {
 // into the product kernel (kquant_mma.cu; split-K when there are few row tiles).  The
 // activations of a pass are normalised, rounded and laid out once and shared by every tensor.
 static int kq_batched_q4k(hb200_ctx* ctx, const KQBatchSeg* segs, int nseg, int K,
-                          const float* d_x, int M, const float* gamma, float eps,
-                          cudaStream_t st) {
+                          const float* d_x, int M, const KQPre& pre, const float* gamma,
+                          float eps, cudaStream_t st) {
   // tokens per pass: the tensor time of a pass does not depend on it, the activation tile
   // and the accumulator do; K above 8192 keeps the 256-token tiles out of their scratch
   const int cap = K <= 8192 ? 256 : 128;
@@ -547,7 +668,10 @@ static int kq_batched_q4k(hb200_ctx* ctx, const KQBatchSeg* segs, int nseg, int 
     const int left = M - m0;
     const int NT = left <= 64 ? 64 : (left <= 128 || cap == 128 ? 128 : 256);
     const int mc = left < NT ? left : NT;
-    int rc = hb_gemm16_split(ctx, 1, K, d_x + (size_t)m0 * K, mc, gamma, eps, NT, st);
+    int rc = hb_gemm16_split_pre(ctx, 1, K, d_x + (size_t)m0 * K, mc,
+                                 pre.gamma ? pre.base + (size_t)m0 * K : nullptr, pre.gamma,
+                                 pre.gamma ? pre.out + (size_t)m0 * K : nullptr, gamma, eps, NT,
+                                 st);
     if (rc != HB200_OK) return rc;
     // tensors without a GLU epilogue go into one launch, three at a time (their row tiles
     // add up, so small ones like k and v no longer leave most SMs idle); an up product
@@ -576,7 +700,7 @@ static int kq_batched_one(hb200_ctx* ctx, int fmt, const uint8_t* blocks, int K,
                           const float* residual, float* y, cudaStream_t st) {
   if (fmt == HB200_FMT_Q4_K) {
     const KQBatchSeg g = {blocks, N, residual, y, 0};
-    return kq_batched_q4k(ctx, &g, 1, K, d_x, M, gamma, eps, st);
+    return kq_batched_q4k(ctx, &g, 1, K, d_x, M, KQPre{nullptr, nullptr, nullptr}, gamma, eps, st);
   }
   const int rowbytes = fmt == HB200_FMT_Q4_K ? K / 256 * 144 : K / 32 * 34;
   long chunk = (long)(kArenaBytes / ((size_t)K * 2)) / 128 * 128;
@@ -616,10 +740,10 @@ static int kq_batched_one(hb200_ctx* ctx, int fmt, const uint8_t* blocks, int K,
 
 // ---- host side --------------------------------------------------------------------
 
-static size_t kq_smem_bytes(int nslots, int rows, int K, int rowbytes) {
+static size_t kq_smem_bytes(int nslots, int rows, int K, int rowbytes, bool pre) {
   auto up128 = [](size_t v) { return (v + 127) & ~size_t(127); };
   size_t off = up128((size_t)nslots * 8);
-  off += 16 * 8 + 2 * (size_t)K + (size_t)(K / 64) * 16;
+  off += 32 * 8 + 2 * (size_t)K + (size_t)(K / 64) * 16 + (pre ? (size_t)K * 4 : 0);
   off = up128(off);
   return off + (size_t)nslots * rows * (size_t)rowbytes;
 }
@@ -635,7 +759,8 @@ struct KQPlan {
 //      prefetch (tallest tile wins);
 //  (b) a ring of >= 2 stages inside half of the shared memory, most bytes in flight;
 //  (c) the same inside the whole shared memory;  (d) whatever fits.
-static bool kq_plan(const hb200_ctx* ctx, long rows, int K, int rowbytes, bool gu, KQPlan* out) {
+static bool kq_plan(const hb200_ctx* ctx, long rows, int K, int rowbytes, bool gu, bool pre,
+                    KQPlan* out) {
   // One CTA per SM (the kernel wants ~166 registers per thread; capping it at the 80 that
   // would let two launches share an SM made it re-derive addresses and constants inside
   // the chunk loop for no net gain), so "half" below only keeps headroom for the L1.
@@ -651,7 +776,7 @@ static bool kq_plan(const hb200_ctx* ctx, long rows, int K, int rowbytes, bool g
       const int srows = gu ? 2 * rt : rt;
       for (int st = (tpw < 4 ? tpw : 4); st >= 1; --st) {
         const int nslots = kKQWarps * st < tpc ? kKQWarps * st : tpc;
-        const size_t sm = kq_smem_bytes(nslots, srows, K, rowbytes);
+        const size_t sm = kq_smem_bytes(nslots, srows, K, rowbytes, pre);
         bool ok = false;
         if (pass == 0) ok = st == tpw && sm <= half;
         if (pass == 1) ok = st >= 2 && sm <= half;
@@ -711,11 +836,23 @@ static int kq_rowbytes(int fmt, int K) { return fmt == HB200_FMT_Q4_K ? K / 256 
 
 using namespace hb;
 
-extern "C" int hb200_kquant_forward_multi(hb200_ctx* ctx, int fmt, const hb200_kquant_seg* segs,
-                                          int nseg, int K, const float* d_x, int M,
-                                          const float* d_rms_gamma, float rms_eps,
-                                          hb200_stream stream) {
+static int kq_pre_check(const KQPre& pre, const float* d_x) {
+  if (!pre.gamma) return HB200_OK;
+  HB_REQUIRE(pre.base && pre.out, "kquant (pre-step): null pointer");
+  HB_REQUIRE(((reinterpret_cast<uintptr_t>(pre.base) | reinterpret_cast<uintptr_t>(pre.gamma) |
+               reinterpret_cast<uintptr_t>(pre.out)) & 15) == 0,
+             "kquant (pre-step): arrays must be 16-byte aligned");
+  HB_REQUIRE(pre.out != pre.base && pre.out != d_x,
+             "kquant (pre-step): the output may not alias an input");
+  return HB200_OK;
+}
+
+static int kq_forward_multi_impl(hb200_ctx* ctx, int fmt, const hb200_kquant_seg* segs, int nseg,
+                                 int K, const float* d_x, int M, const KQPre& pre,
+                                 const float* d_rms_gamma, float rms_eps, hb200_stream stream) {
   int rc = kq_check(ctx, fmt, K, M, d_x);
+  if (rc) return rc;
+  rc = kq_pre_check(pre, d_x);
   if (rc) return rc;
   HB_REQUIRE(segs && nseg >= 1 && nseg <= kKQMaxSeg, "kquant: nseg=%d outside 1..%d", nseg,
              kKQMaxSeg);
@@ -734,7 +871,12 @@ extern "C" int hb200_kquant_forward_multi(hb200_ctx* ctx, int fmt, const hb200_k
       for (int s = 0; s < nseg; ++s)
         g[s] = {static_cast<const uint8_t*>(segs[s].d_blocks), segs[s].N, segs[s].d_residual,
                 segs[s].d_y, 0};
-      return kq_batched_q4k(ctx, g, nseg, K, d_x, M, d_rms_gamma, rms_eps, st);
+      return kq_batched_q4k(ctx, g, nseg, K, d_x, M, pre, d_rms_gamma, rms_eps, st);
+    }
+    if (pre.gamma) {
+      rc = hb200_rmsnorm(ctx, d_x, pre.gamma, pre.base, rms_eps, M, K, pre.out, stream);
+      if (rc != HB200_OK) return rc;
+      d_x = pre.out;
     }
     for (int s = 0; s < nseg; ++s) {
       rc = kq_batched_one(ctx, fmt, static_cast<const uint8_t*>(segs[s].d_blocks), K, segs[s].N,
@@ -746,7 +888,7 @@ extern "C" int hb200_kquant_forward_multi(hb200_ctx* ctx, int fmt, const hb200_k
   HB_REQUIRE(M <= 64, "kquant: M=%d needs the batched path (HB200_NO_MMA is set)", M);
   const int rowbytes = kq_rowbytes(fmt, K);
   KQPlan plan;
-  if (!kq_plan(ctx, rows, K, rowbytes, false, &plan)) {
+  if (!kq_plan(ctx, rows, K, rowbytes, false, pre.gamma != nullptr, &plan)) {
     set_error("kquant: K=%d does not fit the shared-memory budget", K);
     return HB200_ERR_UNSUPPORTED;
   }
@@ -767,8 +909,31 @@ extern "C" int hb200_kquant_forward_multi(hb200_ctx* ctx, int fmt, const hb200_k
   p.gamma = d_rms_gamma;
   p.eps = rms_eps;
   p.status = ctx->d_status;
+  p.pre_base = pre.base;
+  p.pre_gamma = pre.gamma;
+  p.pre_out = pre.out;
   return fmt == HB200_FMT_Q4_K ? kq_dispatch<12, false>(ctx, p, plan, st)
                                : kq_dispatch<8, false>(ctx, p, plan, st);
+}
+
+extern "C" int hb200_kquant_forward_multi(hb200_ctx* ctx, int fmt, const hb200_kquant_seg* segs,
+                                          int nseg, int K, const float* d_x, int M,
+                                          const float* d_rms_gamma, float rms_eps,
+                                          hb200_stream stream) {
+  return kq_forward_multi_impl(ctx, fmt, segs, nseg, K, d_x, M, KQPre{nullptr, nullptr, nullptr},
+                               d_rms_gamma, rms_eps, stream);
+}
+
+extern "C" int hb200_kquant_forward_multi_pre(hb200_ctx* ctx, int fmt,
+                                              const hb200_kquant_seg* segs, int nseg, int K,
+                                              const float* d_o, int M, const float* d_pre_base,
+                                              const float* d_pre_gamma, float* d_x_out,
+                                              const float* d_rms_gamma, float rms_eps,
+                                              hb200_stream stream) {
+  HB_REQUIRE(d_pre_gamma != nullptr, "kquant (pre-step): null gamma");
+  return kq_forward_multi_impl(ctx, fmt, segs, nseg, K, d_o, M,
+                               KQPre{d_pre_base, d_pre_gamma, d_x_out}, d_rms_gamma, rms_eps,
+                               stream);
 }
 
 extern "C" int hb200_kquant_forward(hb200_ctx* ctx, int fmt, const void* d_blocks, int K, int N,
@@ -779,24 +944,32 @@ extern "C" int hb200_kquant_forward(hb200_ctx* ctx, int fmt, const void* d_block
   return hb200_kquant_forward_multi(ctx, fmt, &s, 1, K, d_x, M, d_rms_gamma, rms_eps, stream);
 }
 
-extern "C" int hb200_kquant_gateup_gelu(hb200_ctx* ctx, int fmt, const void* d_blocks_gate,
-                                        const void* d_blocks_up, int K, int N, const float* d_x,
-                                        int M, const float* d_rms_gamma, float rms_eps,
-                                        float* d_y, hb200_stream stream) {
+static int kq_gateup_impl(hb200_ctx* ctx, int fmt, const void* d_blocks_gate,
+                          const void* d_blocks_up, int K, int N, const float* d_x, int M,
+                          const KQPre& pre, const float* d_rms_gamma, float rms_eps, float* d_y,
+                          hb200_stream stream) {
   int rc = kq_check(ctx, fmt, K, M, d_x);
+  if (rc) return rc;
+  rc = kq_pre_check(pre, d_x);
   if (rc) return rc;
   HB_REQUIRE(N >= 1 && d_blocks_gate && d_blocks_up && d_y, "kquant gate/up: bad argument");
   HB_REQUIRE(((reinterpret_cast<uintptr_t>(d_blocks_gate) |
                reinterpret_cast<uintptr_t>(d_blocks_up)) & 15) == 0,
              "kquant gate/up: blocks must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M >= kKQBatchedFrom && !ctx->no_mma && pre.gamma && fmt != HB200_FMT_Q4_K) {
+    rc = hb200_rmsnorm(ctx, d_x, pre.gamma, pre.base, rms_eps, M, K, pre.out, stream);
+    if (rc != HB200_OK) return rc;
+    return kq_gateup_impl(ctx, fmt, d_blocks_gate, d_blocks_up, K, N, pre.out, M,
+                          KQPre{nullptr, nullptr, nullptr}, d_rms_gamma, rms_eps, d_y, stream);
+  }
   if (M >= kKQBatchedFrom && !ctx->no_mma && fmt == HB200_FMT_Q4_K) {
     // both products on the tensor cores against one staging of the activations: the gate
     // product writes d_y, the up product's epilogue multiplies gelu_tanh(gate) in place
     const KQBatchSeg g[2] = {
         {static_cast<const uint8_t*>(d_blocks_gate), N, nullptr, d_y, 0},
         {static_cast<const uint8_t*>(d_blocks_up), N, d_y, d_y, 1}};
-    return kq_batched_q4k(ctx, g, 2, K, d_x, M, d_rms_gamma, rms_eps, st);
+    return kq_batched_q4k(ctx, g, 2, K, d_x, M, pre, d_rms_gamma, rms_eps, st);
   }
   if (M >= kKQBatchedFrom && !ctx->no_mma &&
       kScratchGlu + (size_t)64 * N * sizeof(float) <= kScratchLmSplit) {
@@ -821,7 +994,7 @@ extern "C" int hb200_kquant_gateup_gelu(hb200_ctx* ctx, int fmt, const void* d_b
   HB_REQUIRE(M <= 64, "kquant gate/up: M=%d needs the batched path", M);
   const int rowbytes = kq_rowbytes(fmt, K);
   KQPlan plan;
-  if (!kq_plan(ctx, N, K, rowbytes, true, &plan)) {
+  if (!kq_plan(ctx, N, K, rowbytes, true, pre.gamma != nullptr, &plan)) {
     set_error("kquant gate/up: K=%d does not fit the shared-memory budget", K);
     return HB200_ERR_UNSUPPORTED;
   }
@@ -838,6 +1011,28 @@ extern "C" int hb200_kquant_gateup_gelu(hb200_ctx* ctx, int fmt, const void* d_b
   p.gamma = d_rms_gamma;
   p.eps = rms_eps;
   p.status = ctx->d_status;
+  p.pre_base = pre.base;
+  p.pre_gamma = pre.gamma;
+  p.pre_out = pre.out;
   return fmt == HB200_FMT_Q4_K ? kq_dispatch<12, true>(ctx, p, plan, st)
                                : kq_dispatch<8, true>(ctx, p, plan, st);
+}
+
+extern "C" int hb200_kquant_gateup_gelu(hb200_ctx* ctx, int fmt, const void* d_blocks_gate,
+                                        const void* d_blocks_up, int K, int N, const float* d_x,
+                                        int M, const float* d_rms_gamma, float rms_eps,
+                                        float* d_y, hb200_stream stream) {
+  return kq_gateup_impl(ctx, fmt, d_blocks_gate, d_blocks_up, K, N, d_x, M,
+                        KQPre{nullptr, nullptr, nullptr}, d_rms_gamma, rms_eps, d_y, stream);
+}
+
+extern "C" int hb200_kquant_gateup_gelu_pre(hb200_ctx* ctx, int fmt, const void* d_blocks_gate,
+                                            const void* d_blocks_up, int K, int N,
+                                            const float* d_o, int M, const float* d_pre_base,
+                                            const float* d_pre_gamma, float* d_x_out,
+                                            const float* d_rms_gamma, float rms_eps, float* d_y,
+                                            hb200_stream stream) {
+  HB_REQUIRE(d_pre_gamma != nullptr, "kquant (pre-step): null gamma");
+  return kq_gateup_impl(ctx, fmt, d_blocks_gate, d_blocks_up, K, N, d_o, M,
+                        KQPre{d_pre_base, d_pre_gamma, d_x_out}, d_rms_gamma, rms_eps, d_y, stream);
 }

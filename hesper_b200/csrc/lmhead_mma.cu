@@ -53,6 +53,11 @@ struct LmSplitParams {
   int single;          // 0: hi rows 0..63, lo rows 64..127 of each block; else only the rounded
                        // value, `single` token rows per block (64, 128 or 256)
   uint8_t* xb;         // [K/64][16 KB] operand blocks
+  // optional step in front: x' = pre_base + rmsnorm(x) * pre_gamma, written to pre_out and
+  // used as the row from there on (K <= 10240, 16-byte aligned arrays)
+  const float* pre_base;
+  const float* pre_gamma;
+  float* pre_out;
 };
 
 struct LmMmaParams {
@@ -130,7 +135,7 @@ __global__ void __launch_bounds__(256) lm_split_kernel(const __grid_constant__ L
       v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w;
       v[i][4] = b.x; v[i][5] = b.y; v[i][6] = b.z; v[i][7] = b.w;
     }
-    if (p.gamma) {
+    auto row_rinv = [&]() {  // 1 / rms of the row held in v (block-wide)
       double ss = 0.0;
 #pragma unroll
       for (int i = 0; i < kHeld; ++i)
@@ -142,7 +147,32 @@ __global__ void __launch_bounds__(256) lm_split_kernel(const __grid_constant__ L
       ss = 0.0;
 #pragma unroll
       for (int i = 0; i < 8; ++i) ss += red[i];
-      const float rinv = (float)(1.0 / sqrt(ss / (double)K + (double)p.eps));
+      __syncthreads();  // red may be written again
+      return (float)(1.0 / sqrt(ss / (double)K + (double)p.eps));
+    };
+    if (p.pre_gamma) {
+      const float r1 = row_rinv();
+      const float* bg = p.pre_base + (size_t)m * K;
+      float* og = p.pre_out + (size_t)m * K;
+#pragma unroll
+      for (int i = 0; i < kHeld; ++i) {
+        const int k = tid * 8 + i * 2048;
+        if (k >= K) continue;
+        const float4 ga = __ldg(reinterpret_cast<const float4*>(p.pre_gamma + k));
+        const float4 gb = __ldg(reinterpret_cast<const float4*>(p.pre_gamma + k + 4));
+        const float4 ba = *reinterpret_cast<const float4*>(bg + k);
+        const float4 bb = *reinterpret_cast<const float4*>(bg + k + 4);
+        const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+        const float b[8] = {ba.x, ba.y, ba.z, ba.w, bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          v[i][e] = __fadd_rn(b[e], __fmul_rn(__fmul_rn(v[i][e], r1), g[e]));
+        *reinterpret_cast<float4*>(og + k) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+        *reinterpret_cast<float4*>(og + k + 4) = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+      }
+    }
+    if (p.gamma) {
+      const float rinv = row_rinv();
 #pragma unroll
       for (int i = 0; i < kHeld; ++i) {
         const int k = tid * 8 + i * 2048;
@@ -362,6 +392,23 @@ using namespace hb;
 // 64-wide K block (M <= single).
 int hb_gemm16_split(hb200_ctx* ctx, int dtype, int K, const float* d_x, int M,
                     const float* d_rms_gamma, float rms_eps, int single, cudaStream_t st) {
+  return hb_gemm16_split_pre(ctx, dtype, K, d_x, M, nullptr, nullptr, nullptr, d_rms_gamma,
+                             rms_eps, single, st);
+}
+
+// The same with x' = d_pre_base + rmsnorm(d_x) * d_pre_gamma computed first (written to
+// d_pre_out and staged); d_pre_gamma null: no such step.
+int hb_gemm16_split_pre(hb200_ctx* ctx, int dtype, int K, const float* d_x, int M,
+                        const float* d_pre_base, const float* d_pre_gamma, float* d_pre_out,
+                        const float* d_rms_gamma, float rms_eps, int single, cudaStream_t st) {
+  if (d_pre_gamma) {
+    HB_REQUIRE(d_pre_base && d_pre_out && K <= 10240 &&
+                   ((reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_rms_gamma) |
+                     reinterpret_cast<uintptr_t>(d_pre_base) |
+                     reinterpret_cast<uintptr_t>(d_pre_gamma) |
+                     reinterpret_cast<uintptr_t>(d_pre_out)) & 15) == 0,
+               "batched 16-bit product: pre-step needs K <= 10240 and 16-byte aligned arrays");
+  }
   HB_REQUIRE(single == 0 || single == 64 || single == 128 || single == 256,
              "batched 16-bit product: %d token rows per block", single);
   const size_t xb_bytes = (size_t)(K / kLmKStep) * (single ? (size_t)single * 128 : (size_t)kLmBBytes);
@@ -369,7 +416,8 @@ int hb_gemm16_split(hb200_ctx* ctx, int dtype, int K, const float* d_x, int M,
              "batched 16-bit product: K=%d needs %zu bytes of activation scratch", K, xb_bytes);
   HB_REQUIRE(M >= 1 && M <= (single ? single : kLmTokens), "batched 16-bit product: M=%d", M);
   uint8_t* xb = static_cast<uint8_t*>(ctx->d_scratch) + kScratchLmSplit;
-  LmSplitParams sp = {d_x, d_rms_gamma, rms_eps, K, M, dtype, single, xb};
+  LmSplitParams sp = {d_x, d_rms_gamma, rms_eps, K, M, dtype, single, xb,
+                      d_pre_base, d_pre_gamma, d_pre_out};
   HB_CUDA(launch_pdl(lm_split_kernel, dim3(single ? single : kLmTokens), dim3(256), 0, st,
                      ctx->pdl, sp));
   return HB200_OK;

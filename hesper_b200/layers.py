@@ -238,11 +238,22 @@ class LinearLayer:
 
     @staticmethod
     def forward_fused_gate_up(gate: "LinearLayer", up: "LinearLayer", x, *, rms_gamma=None,
-                              eps: float = 1e-6, out=None, stream=None) -> torch.Tensor:
-        """forwardFusedGateUp / forwardFusedNormGateUp (Hesper/Layers/Linear.lean:7295,7506)."""
+                              eps: float = 1e-6, out=None, stream=None, pre=None):
+        """forwardFusedGateUp / forwardFusedNormGateUp (Hesper/Layers/Linear.lean:7295,7506).
+
+        pre=(base, gamma): the layer input becomes x' = base + rmsnorm(x) * gamma first
+        (a post-norm with its residual add); returns (y, x') in that case."""
         x, M = gate._x(x)
         y = out if out is not None else torch.empty((M, gate.out_dim), dtype=torch.float32,
                                                     device=x.device)
+        if pre is not None:
+            base, pg = pre
+            xo = torch.empty_like(x)
+            check(gate.ctx._lib.hb200_kquant_gateup_gelu_pre(
+                gate.ctx.handle, int(gate.fmt), _ptr(gate.blocks), _ptr(up.blocks), gate.in_dim,
+                gate.out_dim, _ptr(x), M, _ptr(base), _ptr(pg), _ptr(xo), _ptr(rms_gamma),
+                C.c_float(eps), _ptr(y), _stream_handle(stream)))
+            return y, xo
         check(gate.ctx._lib.hb200_kquant_gateup_gelu(
             gate.ctx.handle, int(gate.fmt), _ptr(gate.blocks), _ptr(up.blocks), gate.in_dim,
             gate.out_dim, _ptr(x), M, _ptr(rms_gamma), C.c_float(eps), _ptr(y),
@@ -251,8 +262,11 @@ class LinearLayer:
 
     @staticmethod
     def forward_multi(layers: Sequence["LinearLayer"], x, *, rms_gamma=None, eps: float = 1e-6,
-                      residuals=None, stream=None):
-        """forwardFusedQKV / forwardFusedNormQKV / forwardFusedKV (:7413-7660)."""
+                      residuals=None, stream=None, pre=None):
+        """forwardFusedQKV / forwardFusedNormQKV / forwardFusedKV (:7413-7660).
+
+        pre=(base, gamma): the layers' input becomes x' = base + rmsnorm(x) * gamma first;
+        returns (ys, x') in that case."""
         l0 = layers[0]
         x, M = l0._x(x)
         segs = (KQuantSeg * len(layers))()
@@ -263,6 +277,13 @@ class LinearLayer:
             ys.append(y)
             segs[i] = KQuantSeg(l.blocks.data_ptr(), r.data_ptr() if r is not None else None,
                                 y.data_ptr(), l.out_dim)
+        if pre is not None:
+            base, pg = pre
+            xo = torch.empty_like(x)
+            check(l0.ctx._lib.hb200_kquant_forward_multi_pre(
+                l0.ctx.handle, int(l0.fmt), segs, len(layers), l0.in_dim, _ptr(x), M, _ptr(base),
+                _ptr(pg), _ptr(xo), _ptr(rms_gamma), C.c_float(eps), _stream_handle(stream)))
+            return ys, xo
         check(l0.ctx._lib.hb200_kquant_forward_multi(
             l0.ctx.handle, int(l0.fmt), segs, len(layers), l0.in_dim, _ptr(x), M, _ptr(rms_gamma),
             C.c_float(eps), _stream_handle(stream)))

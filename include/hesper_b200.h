@@ -197,6 +197,26 @@ int hb200_kquant_gateup_gelu(hb200_ctx *ctx, int fmt, const void *d_blocks_gate,
                              int M, const float *d_rms_gamma, float rms_eps, float *d_y,
                              hb200_stream stream);
 
+/* The two calls above with a residual step in front, for layers that normalise a block's
+ * output before adding it to the stream (post-attention / post-FFN norms, e.g.
+ * Hesper/Models/Gemma4.lean:904-925 followed by the next block's fused norm + matvec):
+ *   x' = d_pre_base + rmsnorm(d_o) * d_pre_gamma      (also written to d_x_out, [M][K])
+ *   then hb200_kquant_forward_multi / hb200_kquant_gateup_gelu on x'.
+ * The step has no launch of its own: up to 15 tokens it runs inside the matvec kernel's
+ * prologue, from 16 tokens inside the kernel that stages the activations for the tensor-core
+ * product (Q8_0 from 16 tokens: one hb200_rmsnorm launch).  d_x_out may alias neither input; all
+ * arrays 16-byte aligned; rms_eps serves both norms. */
+int hb200_kquant_forward_multi_pre(hb200_ctx *ctx, int fmt, const hb200_kquant_seg *segs,
+                                   int nseg, int K, const float *d_o, int M,
+                                   const float *d_pre_base, const float *d_pre_gamma,
+                                   float *d_x_out, const float *d_rms_gamma, float rms_eps,
+                                   hb200_stream stream);
+int hb200_kquant_gateup_gelu_pre(hb200_ctx *ctx, int fmt, const void *d_blocks_gate,
+                                 const void *d_blocks_up, int K, int N, const float *d_o,
+                                 int M, const float *d_pre_base, const float *d_pre_gamma,
+                                 float *d_x_out, const float *d_rms_gamma, float rms_eps,
+                                 float *d_y, hb200_stream stream);
+
 /* ---- decode attention ------------------------------------------------------ */
 
 /* Bytes of scratch hb200_attn_decode needs for this shape (split-K partials). */

@@ -154,6 +154,43 @@ def test_batched_gate_up_and_multi(ctx, oracle, K, N, M):
 
 
 @pytest.mark.parametrize("fmt", [12, 8])
+@pytest.mark.parametrize("M", [1, 3, 20])
+def test_post_norm_folded_into_the_next_matvec(ctx, oracle, fmt, M):
+    """x' = base + rmsnorm(o) * g1 in front of a fused-norm q/k/v call and of a gate/up call:
+    x' and the products equal the oracle's evaluation of the same chain (streaming kernel's
+    prologue for M < 16, separate launch in front of the tensor-core path from 16 on)."""
+    K, N = 2560, 384
+    rng = np.random.default_rng(100 + M + fmt)
+    ba = formats.random_kquant(rng, fmt, N, K)
+    bb = formats.random_kquant(rng, fmt, N, K)
+    o = rng.standard_normal((M, K)).astype(np.float32)
+    base = rng.standard_normal((M, K)).astype(np.float32)
+    g1 = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    g2 = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    la = LinearLayer.create_from_bytes(ctx, ba, fmt, K, N)
+    lb = LinearLayer.create_from_bytes(ctx, bb, fmt, K, N)
+    xp = np.stack([base[m].astype(np.float64) + oracle.rmsnorm_f64(o[m], g1, 1e-6)
+                   for m in range(M)])
+    xn = np.stack([oracle.rmsnorm_f64(xp[m].astype(np.float32), g2, 1e-6)
+                   for m in range(M)]).astype(np.float32)
+    do, dbase, dg1, dg2 = _dev(o), _dev(base), _dev(g1), _dev(g2)
+    ys, xo = LinearLayer.forward_multi([la, lb], do, rms_gamma=dg2, eps=1e-6, pre=(dbase, dg1))
+    ctx.check()
+    assert np.max(np.abs(xo.cpu().numpy() - xp)) <= 1e-5 * np.max(np.abs(xp))
+    _check(ys[0], oracle.kquant_matvec(fmt, ba, K, N, xn))
+    _check(ys[1], oracle.kquant_matvec(fmt, bb, K, N, xn))
+    y, xo2 = LinearLayer.forward_fused_gate_up(la, lb, do, rms_gamma=dg2, eps=1e-6,
+                                               pre=(dbase, dg1))
+    ctx.check()
+    assert torch.equal(xo, xo2)
+    _check(y, oracle.kquant_gateup_gelu(ba, bb, fmt, K, N, xn), tol=2e-3)
+    # and the unfused sequence of calls gives the same x' bit for bit
+    ref = LinearLayer.forward_multi([la, lb], xo, rms_gamma=dg2, eps=1e-6)
+    ctx.check()
+    _check(ys[0], ref[0].cpu().numpy(), tol=1e-6)
+
+
+@pytest.mark.parametrize("fmt", [12, 8])
 def test_linearity_full_size(ctx, fmt):
     """Size-independent property at the benchmark shape: y(a*x) = a*y(x) for a power of two
     (the block quantiser scales exactly), and zero input gives zero output."""
