@@ -217,6 +217,11 @@ __global__ void __launch_bounds__(BLCfg<WPL, MT, RT, GU>::kThreads,
   const int M = p.M;
   const float* const xbase = p.x;
   const float* const gamma = p.gamma;
+  // the norm weights are constants of the model: pull their lines into L1 now, so that the
+  // loads after the sum-of-squares reduction do not pay a second trip to L2
+  if (gamma)
+    for (int i = tid * 32; i < K; i += kThreads * 32)
+      asm volatile("prefetch.global.L1 [%0];" ::"l"(gamma + i));
   HB_STAMP(1);
   pdl_trigger();
   pdl_wait();  // activations (and residuals) come from the previous kernel

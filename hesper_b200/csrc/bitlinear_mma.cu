@@ -92,6 +92,9 @@ __global__ void __launch_bounds__(256) quant_act_kernel(const __grid_constant__ 
   __shared__ int red_i[8];
   extern __shared__ __align__(16) float xs[];  // [K]
   pdl_trigger();
+  if (p.gamma)  // constants of the model: into L1 before the wait on the previous kernel
+    for (int i = threadIdx.x * 32; i < p.K; i += 256 * 32)
+      asm volatile("prefetch.global.L1 [%0];" ::"l"(p.gamma + i));
   pdl_wait();
   const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = p.K, nvec = K >> 2;

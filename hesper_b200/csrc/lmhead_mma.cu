@@ -86,6 +86,11 @@ __device__ __forceinline__ float widen16(uint16_t h, int dtype) {
 __global__ void __launch_bounds__(256) lm_split_kernel(const __grid_constant__ LmSplitParams p) {
   __shared__ double red[8];
   pdl_trigger();
+  // norm weights are constants of the model: into L1 before the wait on the previous kernel
+  for (int i = threadIdx.x * 32; i < p.K; i += 256 * 32) {
+    if (p.gamma) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.gamma + i));
+    if (p.pre_gamma) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.pre_gamma + i));
+  }
   pdl_wait();
   const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = p.K;
