@@ -10,6 +10,8 @@
 #include <dlfcn.h>
 #include <string.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace hb {
@@ -95,8 +97,15 @@ constexpr int kNcclSum = 0, kNcclMax = 2, kNcclUint64 = 5, kNcclFloat32 = 7;
 constexpr int kPeerMaxRanks = 8;
 constexpr int kPeerMaxCtas = 64;
 constexpr size_t kPeerSlotBytes = (size_t)2560 * 64 * 4;  // hidden 2560 x 64 tokens of f32
-constexpr size_t kPeerFlagBytes = (size_t)2 * kPeerMaxRanks * kPeerMaxCtas * sizeof(uint32_t);
-constexpr size_t kPeerBufBytes = 2 * kPeerMaxRanks * kPeerSlotBytes + kPeerFlagBytes;
+// one flag per 128-byte line: the CTAs of a launch poll and are written to concurrently, and
+// flags sharing a line made every poll contend with the incoming remote stores
+constexpr int kPeerFlagStride = 32;
+constexpr size_t kPeerFlagBytes =
+    (size_t)2 * kPeerMaxRanks * kPeerMaxCtas * kPeerFlagStride * sizeof(uint32_t);
+// A second region of the same shape for the flag-in-data exchange below: every 8-byte word
+// is {f32 value, u32 sequence number}, so it holds half as many values per slot.
+constexpr size_t kPeerLLBase = 2 * kPeerMaxRanks * kPeerSlotBytes + kPeerFlagBytes;
+constexpr size_t kPeerBufBytes = kPeerLLBase + 2 * kPeerMaxRanks * kPeerSlotBytes;
 
 struct PeerParams {
   unsigned char* buf[kPeerMaxRanks];  // every rank's exchange buffer (own one included)
@@ -135,12 +144,14 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const __grid_consta
     const uint4 x = io[v];
     for (int r = 0; r < W; ++r) reinterpret_cast<uint4*>(p.buf[r] + slot_off)[v] = x;
   }
-  __threadfence_system();
+  // the barrier orders every thread's pushes before the flag writers' fence + release store
+  // (cumulative at system scope), so one fence per flag writer is enough
   __syncthreads();
   const size_t flag_base = 2 * kPeerMaxRanks * kPeerSlotBytes;
   if (tid < W) {
     uint32_t* f = reinterpret_cast<uint32_t*>(p.buf[tid] + flag_base) +
-                  ((size_t)epoch * kPeerMaxRanks + p.rank) * kPeerMaxCtas + cta;
+                  (((size_t)epoch * kPeerMaxRanks + p.rank) * kPeerMaxCtas + cta) * kPeerFlagStride;
+    __threadfence_system();
     st_release_sys(f, seq);
   }
   // ---- wait for every rank's chunk (flags in this rank's own buffer) ------------------------
@@ -149,7 +160,7 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const __grid_consta
   __syncthreads();
   if (tid < W) {
     const uint32_t* f = reinterpret_cast<const uint32_t*>(p.buf[p.rank] + flag_base) +
-                        ((size_t)epoch * kPeerMaxRanks + tid) * kPeerMaxCtas + cta;
+                        (((size_t)epoch * kPeerMaxRanks + tid) * kPeerMaxCtas + cta) * kPeerFlagStride;
     bool got = false;
 #pragma unroll 1
     for (uint32_t it = 0; it < (1u << 21); ++it) {  // about a second at worst
@@ -219,28 +230,51 @@ __global__ void __launch_bounds__(256) peer_allreduce_rmsnorm_kernel(
   __shared__ double red[8];
   __shared__ int s_ok;
   pdl_trigger();
-  pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, m = blockIdx.x, W = p.nranks;
-  const int K = p.K;
+  const int K = p.K, nvec = K >> 2;
+  // Rows of up to 3 float4 per thread (K <= 3072) never leave the registers, and every load
+  // that does not depend on the exchange is issued before the wait it can hide behind: the
+  // norm weights (constants of the model) before the wait on the previous kernel, the
+  // addend before the poll for the peers' flags.
+  constexpr int kH = 3;
+  const bool held = nvec <= kH * 256;
+  float4 g4[kH];
+#pragma unroll
+  for (int j = 0; j < kH; ++j) {
+    const int v = tid + j * 256;
+    g4[j] = (held && v < nvec) ? __ldg(reinterpret_cast<const float4*>(p.gamma) + v)
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_wait();
   const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(p.seq) + 1u;
   const int epoch = (int)(seq & 1u);
   const size_t slot_off = ((size_t)epoch * kPeerMaxRanks + p.rank) * kPeerSlotBytes;
   const uint4* xin = reinterpret_cast<const uint4*>(p.x + (size_t)m * K);
-  for (int v = tid; v < (K >> 2); v += 256) {
+  for (int v = tid; v < nvec; v += 256) {
     const uint4 x = xin[v];
     for (int r = 0; r < W; ++r)
       reinterpret_cast<uint4*>(p.buf[r] + slot_off + (size_t)m * K * 4)[v] = x;
   }
-  __threadfence_system();
+  float4 a4[kH];
+#pragma unroll
+  for (int j = 0; j < kH; ++j) {
+    const int v = tid + j * 256;
+    a4[j] = (held && p.add && v < nvec)
+                ? reinterpret_cast<const float4*>(p.add + (size_t)m * K)[v]
+                : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   if (tid == 0) s_ok = 1;
+  // the barrier orders every thread's pushes before the flag writers' release stores below
+  // (release at system scope is cumulative over what happened before it in this CTA)
   __syncthreads();
   const size_t flag_base = 2 * kPeerMaxRanks * kPeerSlotBytes;
   if (tid < W) {
     uint32_t* f = reinterpret_cast<uint32_t*>(p.buf[tid] + flag_base) +
-                  ((size_t)epoch * kPeerMaxRanks + p.rank) * kPeerMaxCtas + m;
+                  (((size_t)epoch * kPeerMaxRanks + p.rank) * kPeerMaxCtas + m) * kPeerFlagStride;
+    __threadfence_system();
     st_release_sys(f, seq);
     const uint32_t* g = reinterpret_cast<const uint32_t*>(p.buf[p.rank] + flag_base) +
-                        ((size_t)epoch * kPeerMaxRanks + tid) * kPeerMaxCtas + m;
+                        (((size_t)epoch * kPeerMaxRanks + tid) * kPeerMaxCtas + m) * kPeerFlagStride;
     bool got = false;
 #pragma unroll 1
     for (uint32_t it = 0; it < (1u << 21); ++it) {
@@ -255,9 +289,56 @@ __global__ void __launch_bounds__(256) peer_allreduce_rmsnorm_kernel(
     }
   }
   __syncthreads();
-  if (s_ok) {
-    const unsigned char* mine = p.buf[p.rank] + (size_t)epoch * kPeerMaxRanks * kPeerSlotBytes +
-                                (size_t)m * K * 4;
+  const unsigned char* mine = p.buf[p.rank] + (size_t)epoch * kPeerMaxRanks * kPeerSlotBytes +
+                              (size_t)m * K * 4;
+  if (s_ok && held) {
+    float4 s4[kH];
+#pragma unroll
+    for (int j = 0; j < kH; ++j) {
+      const int v = tid + j * 256;
+      s4[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (v < nvec) {
+        s4[j] = __ldcg(reinterpret_cast<const float4*>(mine) + v);
+        for (int r = 1; r < W; ++r) {  // rank order: the same sum on every rank
+          const float4 t =
+              __ldcg(reinterpret_cast<const float4*>(mine + (size_t)r * kPeerSlotBytes) + v);
+          s4[j].x = __fadd_rn(s4[j].x, t.x);
+          s4[j].y = __fadd_rn(s4[j].y, t.y);
+          s4[j].z = __fadd_rn(s4[j].z, t.z);
+          s4[j].w = __fadd_rn(s4[j].w, t.w);
+        }
+      }
+    }
+    double ss = 0.0;
+#pragma unroll
+    for (int j = 0; j < kH; ++j)
+      ss += (double)s4[j].x * s4[j].x + (double)s4[j].y * s4[j].y + (double)s4[j].z * s4[j].z +
+            (double)s4[j].w * s4[j].w;
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    double tot = 0.0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float rinv = (float)(1.0 / sqrt(tot / (double)K + (double)p.eps));
+#pragma unroll
+    for (int j = 0; j < kH; ++j) {
+      const int v = tid + j * 256;
+      if (v >= nvec) continue;
+      float4 o;
+      o.x = __fmul_rn(__fmul_rn(s4[j].x, rinv), g4[j].x);
+      o.y = __fmul_rn(__fmul_rn(s4[j].y, rinv), g4[j].y);
+      o.z = __fmul_rn(__fmul_rn(s4[j].z, rinv), g4[j].z);
+      o.w = __fmul_rn(__fmul_rn(s4[j].w, rinv), g4[j].w);
+      if (p.add) {
+        o.x = __fadd_rn(a4[j].x, o.x);
+        o.y = __fadd_rn(a4[j].y, o.y);
+        o.z = __fadd_rn(a4[j].z, o.z);
+        o.w = __fadd_rn(a4[j].w, o.w);
+      }
+      reinterpret_cast<float4*>(p.y + (size_t)m * K)[v] = o;
+    }
+  } else if (s_ok) {
     double ss = 0.0;
     for (int k = tid; k < K; k += 256) {
       float a = __ldcg(reinterpret_cast<const float*>(mine) + k);
@@ -279,6 +360,162 @@ __global__ void __launch_bounds__(256) peer_allreduce_rmsnorm_kernel(
     }
   }
   __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const uint32_t t = atomicAdd(&p.seq[1], 1u);
+    if (t == gridDim.x - 1) {
+      p.seq[1] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(p.seq) = seq;
+    }
+  }
+}
+
+// The fused exchange + RMSNorm again, with the flag carried IN the data (the scheme NCCL calls
+// LL): every value travels as one 8-byte store {value, sequence number of this call}, which
+// the memory system performs atomically (two of them per 16-byte access), so the receiver needs no separate flag, the sender
+// no fence and no wait for its stores to be acknowledged -- one NVLink crossing instead of
+// three on the critical path.  Each thread polls exactly the words it will add (bounded), the
+// own contribution never leaves the registers, sums are formed in rank order (bit-identical
+// on all ranks and to the other exchange paths).  K <= 3072, K % 4 == 0, M * K * 8 bytes
+// within a slot.  A slot is reused every second call and sequence numbers only grow, so a
+// stale word can never pass for a fresh one.
+// Two {value, flag} words per 16-byte access: each aligned 8-byte half arrives whole.
+__device__ __forceinline__ void st_pairs_sys(void* p, float v0, float v1, uint32_t flag) {
+  asm volatile("st.volatile.global.v4.b32 [%0], {%1, %2, %3, %2};" ::"l"(p),
+               "r"(__float_as_uint(v0)), "r"(flag), "r"(__float_as_uint(v1))
+               : "memory");
+}
+__device__ __forceinline__ bool ld_pairs_sys(const void* p, uint32_t want, float* v0, float* v1) {
+  uint32_t a, fa, b, fb;
+  asm volatile("ld.volatile.global.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(a), "=r"(fa), "=r"(b), "=r"(fb)
+               : "l"(p)
+               : "memory");
+  *v0 = __uint_as_float(a);
+  *v1 = __uint_as_float(b);
+  return fa == want && fb == want;
+}
+
+__global__ void __launch_bounds__(256) peer_allreduce_rmsnorm_ll_kernel(
+    const __grid_constant__ PeerNormParams p) {
+  __shared__ double red[8];
+  __shared__ int s_bad;
+  pdl_trigger();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, m = blockIdx.x, W = p.nranks;
+  const int K = p.K, nvec = K >> 2;
+  constexpr int kH = 3;
+  float4 g4[kH];
+#pragma unroll
+  for (int j = 0; j < kH; ++j) {
+    const int v = tid + j * 256;
+    g4[j] = v < nvec ? __ldg(reinterpret_cast<const float4*>(p.gamma) + v)
+                     : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (tid == 0) s_bad = 0;
+  pdl_wait();
+  const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(p.seq) + 1u;
+  const int epoch = (int)(seq & 1u);
+  const size_t row_off = (size_t)m * K * 8;
+  // ---- push this rank's row to every other rank ---------------------------------------
+  float4 x4[kH];
+#pragma unroll
+  for (int j = 0; j < kH; ++j) {
+    const int v = tid + j * 256;
+    x4[j] = v < nvec ? reinterpret_cast<const float4*>(p.x + (size_t)m * K)[v]
+                     : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int r = 0; r < W; ++r) {
+    if (r == p.rank) continue;
+    unsigned char* dst = p.buf[r] + kPeerLLBase +
+                         ((size_t)epoch * kPeerMaxRanks + p.rank) * kPeerSlotBytes + row_off;
+#pragma unroll
+    for (int j = 0; j < kH; ++j) {
+      const int v = tid + j * 256;
+      if (v >= nvec) continue;
+      unsigned char* d = dst + (size_t)v * 32;
+      st_pairs_sys(d, x4[j].x, x4[j].y, seq);
+      st_pairs_sys(d + 16, x4[j].z, x4[j].w, seq);
+    }
+  }
+  float4 a4[kH];
+#pragma unroll
+  for (int j = 0; j < kH; ++j) {
+    const int v = tid + j * 256;
+    a4[j] = (p.add && v < nvec) ? reinterpret_cast<const float4*>(p.add + (size_t)m * K)[v]
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  // ---- collect in rank order ------------------------------------------------------------
+  float4 s4[kH];
+  bool ok = true;
+  for (int r = 0; r < W; ++r) {
+    const unsigned char* src = p.buf[p.rank] + kPeerLLBase +
+                               ((size_t)epoch * kPeerMaxRanks + r) * kPeerSlotBytes + row_off;
+#pragma unroll
+    for (int j = 0; j < kH; ++j) {
+      const int v = tid + j * 256;
+      float4 t = x4[j];
+      if (r != p.rank && v < nvec) {
+        const unsigned char* q = src + (size_t)v * 32;
+        float* tv = reinterpret_cast<float*>(&t);
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          bool got = false;
+#pragma unroll 1
+          for (uint32_t it = 0; ok && it < (1u << 21); ++it)
+            if (ld_pairs_sys(q + 16 * e, seq, &tv[2 * e], &tv[2 * e + 1])) {
+              got = true;
+              break;
+            }
+          ok = ok && got;
+        }
+      }
+      if (r == 0) {
+        s4[j] = t;
+      } else {
+        s4[j].x = __fadd_rn(s4[j].x, t.x);
+        s4[j].y = __fadd_rn(s4[j].y, t.y);
+        s4[j].z = __fadd_rn(s4[j].z, t.z);
+        s4[j].w = __fadd_rn(s4[j].w, t.w);
+      }
+    }
+  }
+  if (!ok) {
+    s_bad = 1;
+    atomicOr(p.status, kStatusMbarTimeout);
+  }
+  double ss = 0.0;
+#pragma unroll
+  for (int j = 0; j < kH; ++j)
+    ss += (double)s4[j].x * s4[j].x + (double)s4[j].y * s4[j].y + (double)s4[j].z * s4[j].z +
+          (double)s4[j].w * s4[j].w;
+  ss = warp_sum(ss);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  if (!s_bad) {
+    double tot = 0.0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float rinv = (float)(1.0 / sqrt(tot / (double)K + (double)p.eps));
+#pragma unroll
+    for (int j = 0; j < kH; ++j) {
+      const int v = tid + j * 256;
+      if (v >= nvec) continue;
+      float4 o;
+      o.x = __fmul_rn(__fmul_rn(s4[j].x, rinv), g4[j].x);
+      o.y = __fmul_rn(__fmul_rn(s4[j].y, rinv), g4[j].y);
+      o.z = __fmul_rn(__fmul_rn(s4[j].z, rinv), g4[j].z);
+      o.w = __fmul_rn(__fmul_rn(s4[j].w, rinv), g4[j].w);
+      if (p.add) {
+        o.x = __fadd_rn(a4[j].x, o.x);
+        o.y = __fadd_rn(a4[j].y, o.y);
+        o.z = __fadd_rn(a4[j].z, o.z);
+        o.w = __fadd_rn(a4[j].w, o.w);
+      }
+      reinterpret_cast<float4*>(p.y + (size_t)m * K)[v] = o;
+    }
+  }
+  // ---- the last CTA to finish advances the sequence number -----------------------------
   if (tid == 0) {
     __threadfence();
     const uint32_t t = atomicAdd(&p.seq[1], 1u);
@@ -446,9 +683,15 @@ extern "C" int hb200_tp_allreduce_rmsnorm(hb200_tp* tp, hb200_ctx* ctx, float* d
                                           int M, int K, float* d_y, hb200_stream stream) {
   HB_REQUIRE(ctx && d_x && d_gamma && d_y && M >= 1 && K >= 1, "tp_allreduce_rmsnorm: bad argument");
   if (tp && tp->nranks > 1) {
-    if (tp->peer_ready && M <= kPeerMaxCtas && K % 4 == 0 &&
+    static const int fuse_max = [] {
+      const char* e = getenv("HB200_TP_FUSE_MAX");  // tokens up to which the fused kernel runs
+      const int v = e ? atoi(e) : kPeerMaxCtas;
+      return v < 0 ? 0 : (v > kPeerMaxCtas ? kPeerMaxCtas : v);
+    }();
+    if (tp->peer_ready && M <= fuse_max && K % 4 == 0 &&
         (size_t)M * K * 4 <= kPeerSlotBytes && (size_t)K * 4 <= 48 * 1024 &&
-        (reinterpret_cast<uintptr_t>(d_x) & 15) == 0) {
+        ((reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_gamma) |
+          reinterpret_cast<uintptr_t>(d_add) | reinterpret_cast<uintptr_t>(d_y)) & 15) == 0) {
       PeerNormParams p = {};
       for (int r = 0; r < tp->nranks; ++r) p.buf[r] = tp->peer_buf[r];
       p.x = d_x;
@@ -461,8 +704,13 @@ extern "C" int hb200_tp_allreduce_rmsnorm(hb200_tp* tp, hb200_ctx* ctx, float* d
       p.nranks = tp->nranks;
       p.seq = tp->d_seq;
       p.status = ctx->d_status;
-      HB_CUDA(launch_pdl(peer_allreduce_rmsnorm_kernel, dim3(M), dim3(256), (size_t)K * 4,
-                         static_cast<cudaStream_t>(stream), ctx->pdl, p));
+      static const bool no_ll = getenv("HB200_TP_NO_LL") != nullptr;
+      if (!no_ll && K <= 3072 && (size_t)M * K * 8 <= kPeerSlotBytes)
+        HB_CUDA(launch_pdl(peer_allreduce_rmsnorm_ll_kernel, dim3(M), dim3(256), 0,
+                           static_cast<cudaStream_t>(stream), ctx->pdl, p));
+      else
+        HB_CUDA(launch_pdl(peer_allreduce_rmsnorm_kernel, dim3(M), dim3(256), (size_t)K * 4,
+                           static_cast<cudaStream_t>(stream), ctx->pdl, p));
       return HB200_OK;
     }
     const int rc = hb200_tp_allreduce_f32(tp, d_x, (size_t)M * K, stream);

@@ -13,6 +13,8 @@ under a few GB, so that a full-metric capture of one to three launches ends in a
            ring of 12 matrices K=2560 N=10240, 2 passes
   bitnet1 / bitnet64   BitNet-2B-shaped decode loop at batch 1 / 64: 2 prompt positions and
            3 new tokens, launched one by one (no graph) so that a launch list sees each kernel
+  gemma1 / gemma32 / gemma256   Gemma-4-E4B-shaped Q4_K decode loop (one rank) at batch 1 / 32 /
+           256: 3 tokens at position 8000, launched one by one
 """
 from __future__ import annotations
 
@@ -95,6 +97,16 @@ def main(name: str) -> None:
         m = BitNetModel(ctx, shape, w, batch=B, max_new_tokens=8)
         prompt = rng.integers(0, shape.vocab, (B, 2)).astype(np.int32)
         m.generate(prompt, 3, use_graph=False)
+        m.close()
+    elif name in ("gemma1", "gemma32", "gemma256"):
+        from hesper_b200 import tp
+        B = int(name[5:])
+        S = tp.GemmaShape()
+        plan = tp.plan(S, 0, 1)
+        shard = tp.random_gemma_shard_device(S, plan, seed=7)
+        m = tp.GemmaModel(ctx, S, shard, plan, None, batch=B, max_new_tokens=8)
+        m.set_position(8000)
+        m.generate(None, 3, use_graph=False)
         m.close()
     elif name == "attn":
         B, H, Hkv, D, L = 16, 8, 2, 256, 4096
