@@ -105,7 +105,9 @@ constexpr size_t kPeerFlagBytes =
 // A second region of the same shape for the flag-in-data exchange below: every 8-byte word
 // is {f32 value, u32 sequence number}, so it holds half as many values per slot.
 constexpr size_t kPeerLLBase = 2 * kPeerMaxRanks * kPeerSlotBytes + kPeerFlagBytes;
-constexpr size_t kPeerBufBytes = kPeerLLBase + 2 * kPeerMaxRanks * kPeerSlotBytes;
+constexpr int kPeerLLMaxTokens = 256;
+constexpr size_t kPeerLLSlotBytes = (size_t)2560 * kPeerLLMaxTokens * 8;  // 5 MB per (epoch, rank)
+constexpr size_t kPeerBufBytes = kPeerLLBase + 2 * kPeerMaxRanks * kPeerLLSlotBytes;
 
 struct PeerParams {
   unsigned char* buf[kPeerMaxRanks];  // every rank's exchange buffer (own one included)
@@ -378,7 +380,7 @@ __global__ void __launch_bounds__(256) peer_allreduce_rmsnorm_kernel(
 // three on the critical path.  Each thread polls exactly the words it will add (bounded), the
 // own contribution never leaves the registers, sums are formed in rank order (bit-identical
 // on all ranks and to the other exchange paths).  K <= 3072, K % 4 == 0, M * K * 8 bytes
-// within a slot.  A slot is reused every second call and sequence numbers only grow, so a
+// within a slot (256 tokens of 2560).  A slot is reused every second call and sequence numbers only grow, so a
 // stale word can never pass for a fresh one.
 // Two {value, flag} words per 16-byte access: each aligned 8-byte half arrives whole.
 __device__ __forceinline__ void st_pairs_sys(void* p, float v0, float v1, uint32_t flag) {
@@ -428,7 +430,7 @@ __global__ void __launch_bounds__(256) peer_allreduce_rmsnorm_ll_kernel(
   for (int r = 0; r < W; ++r) {
     if (r == p.rank) continue;
     unsigned char* dst = p.buf[r] + kPeerLLBase +
-                         ((size_t)epoch * kPeerMaxRanks + p.rank) * kPeerSlotBytes + row_off;
+                         ((size_t)epoch * kPeerMaxRanks + p.rank) * kPeerLLSlotBytes + row_off;
 #pragma unroll
     for (int j = 0; j < kH; ++j) {
       const int v = tid + j * 256;
@@ -450,7 +452,7 @@ __global__ void __launch_bounds__(256) peer_allreduce_rmsnorm_ll_kernel(
   bool ok = true;
   for (int r = 0; r < W; ++r) {
     const unsigned char* src = p.buf[p.rank] + kPeerLLBase +
-                               ((size_t)epoch * kPeerMaxRanks + r) * kPeerSlotBytes + row_off;
+                               ((size_t)epoch * kPeerMaxRanks + r) * kPeerLLSlotBytes + row_off;
 #pragma unroll
     for (int j = 0; j < kH; ++j) {
       const int v = tid + j * 256;
@@ -684,14 +686,19 @@ extern "C" int hb200_tp_allreduce_rmsnorm(hb200_tp* tp, hb200_ctx* ctx, float* d
   HB_REQUIRE(ctx && d_x && d_gamma && d_y && M >= 1 && K >= 1, "tp_allreduce_rmsnorm: bad argument");
   if (tp && tp->nranks > 1) {
     static const int fuse_max = [] {
-      const char* e = getenv("HB200_TP_FUSE_MAX");  // tokens up to which the fused kernel runs
-      const int v = e ? atoi(e) : kPeerMaxCtas;
-      return v < 0 ? 0 : (v > kPeerMaxCtas ? kPeerMaxCtas : v);
+      const char* e = getenv("HB200_TP_FUSE_MAX");  // tokens up to which the fused kernels run
+      const int v = e ? atoi(e) : kPeerLLMaxTokens;
+      return v < 0 ? 0 : v;
     }();
-    if (tp->peer_ready && M <= fuse_max && K % 4 == 0 &&
-        (size_t)M * K * 4 <= kPeerSlotBytes && (size_t)K * 4 <= 48 * 1024 &&
+    static const bool no_ll = getenv("HB200_TP_NO_LL") != nullptr;
+    const bool aligned =
         ((reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_gamma) |
-          reinterpret_cast<uintptr_t>(d_add) | reinterpret_cast<uintptr_t>(d_y)) & 15) == 0) {
+          reinterpret_cast<uintptr_t>(d_add) | reinterpret_cast<uintptr_t>(d_y)) & 15) == 0;
+    const bool ll = !no_ll && K <= 3072 && M <= kPeerLLMaxTokens &&
+                    (size_t)M * K * 8 <= kPeerLLSlotBytes;
+    const bool flagged = M <= kPeerMaxCtas && (size_t)M * K * 4 <= kPeerSlotBytes &&
+                         (size_t)K * 4 <= 48 * 1024;
+    if (tp->peer_ready && M <= fuse_max && K % 4 == 0 && aligned && (ll || flagged)) {
       PeerNormParams p = {};
       for (int r = 0; r < tp->nranks; ++r) p.buf[r] = tp->peer_buf[r];
       p.x = d_x;
@@ -704,8 +711,7 @@ extern "C" int hb200_tp_allreduce_rmsnorm(hb200_tp* tp, hb200_ctx* ctx, float* d
       p.nranks = tp->nranks;
       p.seq = tp->d_seq;
       p.status = ctx->d_status;
-      static const bool no_ll = getenv("HB200_TP_NO_LL") != nullptr;
-      if (!no_ll && K <= 3072 && (size_t)M * K * 8 <= kPeerSlotBytes)
+      if (ll)
         HB_CUDA(launch_pdl(peer_allreduce_rmsnorm_ll_kernel, dim3(M), dim3(256), 0,
                            static_cast<cudaStream_t>(stream), ctx->pdl, p));
       else

@@ -43,6 +43,39 @@ def check_allreduce(hb, ctx, comm, rank, world):
                                          C.c_void_p(st.cuda_stream))
     st.synchronize()
     ok = ok and np.array_equal(keys.cpu().numpy(), np.max(np.stack(allk), axis=0))
+    # the exchange fused with the RMSNorm (+ residual) that follows it: rank-order sum, then
+    # the stand-alone kernel's arithmetic.  K = 2560 takes the flag-in-data kernel (up to 256
+    # tokens), K = 4096 the flagged one (up to 64), 300 tokens the unfused route.
+    lib = hb.load()
+    for it, (M, K) in enumerate([(1, 2560), (32, 2560), (200, 2560), (256, 2560), (5, 4096),
+                                 (64, 2560), (300, 2560), (1, 2560)]):
+        parts = [np.random.default_rng(5000 + 10 * it + r).standard_normal((M, K)).astype(np.float32)
+                 for r in range(world)]
+        total = parts[0].copy()
+        for r in range(1, world):
+            total = (total + parts[r]).astype(np.float32)
+        rng = np.random.default_rng(77 + it)
+        gamma = torch.from_numpy((1 + 0.1 * rng.standard_normal(K)).astype(np.float32)).cuda()
+        add = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32)).cuda()
+        x = torch.from_numpy(parts[rank].copy()).cuda()
+        y = torch.empty_like(x)
+        want = torch.empty_like(x)
+        t = torch.from_numpy(total).cuda()
+        torch.cuda.synchronize()
+        rc = lib.hb200_tp_allreduce_rmsnorm(comm.handle, ctx.handle, C.c_void_p(x.data_ptr()),
+                                            C.c_void_p(gamma.data_ptr()), C.c_void_p(add.data_ptr()),
+                                            C.c_float(1e-6), M, K, C.c_void_p(y.data_ptr()),
+                                            C.c_void_p(st.cuda_stream))
+        ok = ok and rc == 0
+        rc = lib.hb200_rmsnorm(ctx.handle, C.c_void_p(t.data_ptr()), C.c_void_p(gamma.data_ptr()),
+                               C.c_void_p(add.data_ptr()), C.c_float(1e-6), M, K,
+                               C.c_void_p(want.data_ptr()), C.c_void_p(st.cuda_stream))
+        ok = ok and rc == 0
+        st.synchronize()
+        if comm.peer_attached and K == 2560:
+            ok = ok and bool(torch.equal(y, want))
+        else:
+            ok = ok and bool(torch.allclose(y, want, rtol=1e-5, atol=1e-5))
     # graph replay: the sequence number advances on the device
     x = torch.full((2560,), float(rank + 1), device="cuda")
     torch.cuda.synchronize()
