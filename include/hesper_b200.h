@@ -61,7 +61,11 @@ typedef void *hb200_stream;
  * (f16 weights of one batched k-quant product).  No operator
  * allocates afterwards; a context serves one stream at a time.
  * Environment: HB200_NO_PDL=1 launches without programmatic dependent launch,
- * HB200_NO_MMA=1 keeps the batched (>= 16 token) operators off the tensor-core kernels. */
+ * HB200_NO_MMA=1 keeps the batched (>= 16 token) operators off the tensor-core kernels.
+ * Measurement knobs of the decode loops and the exchange (same value on every rank):
+ * HB200_NO_FOLD=1 keeps the post-norms of the Gemma-shape loop as launches of their own,
+ * HB200_TP_NO_LL=1 / HB200_TP_FUSE_MAX=<tokens> / HB200_TP_NO_PEER=1 select the
+ * flag-after-data kernel, the unfused exchange above a batch size, or NCCL. */
 int hb200_ctx_create(int device, hb200_ctx **out);
 int hb200_ctx_destroy(hb200_ctx *ctx);
 
