@@ -164,8 +164,10 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const __grid_consta
     const uint32_t* f = reinterpret_cast<const uint32_t*>(p.buf[p.rank] + flag_base) +
                         (((size_t)epoch * kPeerMaxRanks + tid) * kPeerMaxCtas + cta) * kPeerFlagStride;
     bool got = false;
+    const uint32_t lim =
+        (*reinterpret_cast<volatile uint32_t*>(p.status) & kStatusMbarTimeout) ? 1u : (1u << 21);
 #pragma unroll 1
-    for (uint32_t it = 0; it < (1u << 21); ++it) {  // about a second at worst
+    for (uint32_t it = 0; it < lim; ++it) {  // about a second at worst, once per context
       if (ld_acquire_sys(f) == seq) {
         got = true;
         break;
@@ -278,8 +280,10 @@ __global__ void __launch_bounds__(256) peer_allreduce_rmsnorm_kernel(
     const uint32_t* g = reinterpret_cast<const uint32_t*>(p.buf[p.rank] + flag_base) +
                         (((size_t)epoch * kPeerMaxRanks + tid) * kPeerMaxCtas + m) * kPeerFlagStride;
     bool got = false;
+    const uint32_t lim =
+        (*reinterpret_cast<volatile uint32_t*>(p.status) & kStatusMbarTimeout) ? 1u : (1u << 21);
 #pragma unroll 1
-    for (uint32_t it = 0; it < (1u << 21); ++it) {
+    for (uint32_t it = 0; it < lim; ++it) {
       if (ld_acquire_sys(g) == seq) {
         got = true;
         break;
@@ -449,7 +453,9 @@ __global__ void __launch_bounds__(256) peer_allreduce_rmsnorm_ll_kernel(
   }
   // ---- collect in rank order ------------------------------------------------------------
   float4 s4[kH];
-  bool ok = true;
+  // once a wait has run out the context is in error: later exchanges do not wait again, so a
+  // broken run ends in seconds instead of a second per exchange
+  bool ok = (*reinterpret_cast<volatile uint32_t*>(p.status) & kStatusMbarTimeout) == 0;
   for (int r = 0; r < W; ++r) {
     const unsigned char* src = p.buf[p.rank] + kPeerLLBase +
                                ((size_t)epoch * kPeerMaxRanks + r) * kPeerLLSlotBytes + row_off;
