@@ -156,22 +156,30 @@ __global__ void __launch_bounds__(256) lm_split_kernel(const __grid_constant__ L
       return (float)(1.0 / sqrt(ss / (double)K + (double)p.eps));
     };
     if (p.pre_gamma) {
-      const float r1 = row_rinv();
+      // the addend is fetched before the reduction, so that it shares the row's trip to L2
       const float* bg = p.pre_base + (size_t)m * K;
       float* og = p.pre_out + (size_t)m * K;
+      float b[kHeld][8];
+#pragma unroll
+      for (int i = 0; i < kHeld; ++i) {
+        const int k = tid * 8 + i * 2048;
+        const bool in = k < K;
+        const float4 ba = in ? *reinterpret_cast<const float4*>(bg + k) : make_float4(0, 0, 0, 0);
+        const float4 bb = in ? *reinterpret_cast<const float4*>(bg + k + 4) : make_float4(0, 0, 0, 0);
+        b[i][0] = ba.x; b[i][1] = ba.y; b[i][2] = ba.z; b[i][3] = ba.w;
+        b[i][4] = bb.x; b[i][5] = bb.y; b[i][6] = bb.z; b[i][7] = bb.w;
+      }
+      const float r1 = row_rinv();
 #pragma unroll
       for (int i = 0; i < kHeld; ++i) {
         const int k = tid * 8 + i * 2048;
         if (k >= K) continue;
         const float4 ga = __ldg(reinterpret_cast<const float4*>(p.pre_gamma + k));
         const float4 gb = __ldg(reinterpret_cast<const float4*>(p.pre_gamma + k + 4));
-        const float4 ba = *reinterpret_cast<const float4*>(bg + k);
-        const float4 bb = *reinterpret_cast<const float4*>(bg + k + 4);
         const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
-        const float b[8] = {ba.x, ba.y, ba.z, ba.w, bb.x, bb.y, bb.z, bb.w};
 #pragma unroll
         for (int e = 0; e < 8; ++e)
-          v[i][e] = __fadd_rn(b[e], __fmul_rn(__fmul_rn(v[i][e], r1), g[e]));
+          v[i][e] = __fadd_rn(b[i][e], __fmul_rn(__fmul_rn(v[i][e], r1), g[e]));
         *reinterpret_cast<float4*>(og + k) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
         *reinterpret_cast<float4*>(og + k + 4) = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
       }
