@@ -799,10 +799,9 @@ static bool kq_plan(const hb200_ctx* ctx, long rows, int K, int rowbytes, bool g
 template <int FMT, int RT, bool GU>
 static int kq_launch(hb200_ctx* ctx, KQParams& p, size_t smem, cudaStream_t st) {
   auto kern = kquant_kernel<FMT, RT, GU>;
-  static size_t configured = 0;
-  if (smem > configured) {
-    HB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = smem;
+  {
+    const int rc = hb_func_smem(ctx, reinterpret_cast<const void*>(kern), smem);
+    if (rc != HB200_OK) return rc;
   }
   const int grid = p.ntiles < ctx->sm_count ? p.ntiles : ctx->sm_count;
   HB_CUDA(launch_pdl(kern, dim3(grid), dim3(kKQThreads), smem, st, ctx->pdl, p));
@@ -886,6 +885,11 @@ static int kq_forward_multi_impl(hb200_ctx* ctx, int fmt, const hb200_kquant_seg
     return HB200_OK;
   }
   HB_REQUIRE(M <= 64, "kquant: M=%d needs the batched path (HB200_NO_MMA is set)", M);
+  if (M == 1) {  // one token: integer tensor-core matvec when the rows fit shared memory
+    rc = hb_kq_mv_run(ctx, fmt, segs, nseg, K, 0, d_x, pre.base, pre.gamma, pre.out, d_rms_gamma,
+                      rms_eps, st);
+    if (rc <= 0) return rc;
+  }
   const int rowbytes = kq_rowbytes(fmt, K);
   KQPlan plan;
   if (!kq_plan(ctx, rows, K, rowbytes, false, pre.gamma != nullptr, &plan)) {
@@ -992,6 +996,12 @@ static int kq_gateup_impl(hb200_ctx* ctx, int fmt, const void* d_blocks_gate,
     return HB200_OK;
   }
   HB_REQUIRE(M <= 64, "kquant gate/up: M=%d needs the batched path", M);
+  if (M == 1) {
+    const hb200_kquant_seg gs[2] = {{d_blocks_gate, nullptr, d_y, N}, {d_blocks_up, nullptr, d_y, N}};
+    rc = hb_kq_mv_run(ctx, fmt, gs, 2, K, 1, d_x, pre.base, pre.gamma, pre.out, d_rms_gamma,
+                      rms_eps, st);
+    if (rc <= 0) return rc;
+  }
   const int rowbytes = kq_rowbytes(fmt, K);
   KQPlan plan;
   if (!kq_plan(ctx, N, K, rowbytes, true, pre.gamma != nullptr, &plan)) {

@@ -205,6 +205,105 @@ def test_linearity_full_size(ctx, fmt):
     assert torch.equal(layer.forward(x), y1)  # deterministic
 
 
+# ---- the mma.sync one-token kernel, forced on at every shape that fits (ctx_mv) -------------
+
+@pytest.mark.parametrize("fmt", [12, 8])
+@pytest.mark.parametrize("K,N", [(2560, 10240), (2560, 2048), (2048, 2560), (10240, 2560),
+                                 (256, 1), (512, 7), (768, 33), (4096, 1000), (1280, 2560)])
+def test_mv_kernel_shapes(ctx_mv, oracle, fmt, K, N):
+    """Ragged last tiles, fewer super-blocks than warps (K < 2560), several per warp (K = 10240),
+    one row, with residual and with the RMSNorm prologue."""
+    rng = np.random.default_rng(5 * K + N + fmt)
+    blocks = formats.random_kquant(rng, fmt, N, K)
+    x = rng.standard_normal((1, K)).astype(np.float32)
+    res = rng.standard_normal((1, N)).astype(np.float32)
+    gamma = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    layer = LinearLayer.create_from_bytes(ctx_mv, blocks, fmt, K, N)
+    def check(y, ref, design=None):
+        if N >= 4:
+            err = _check(y, ref)
+            assert design is None or err < design
+        else:  # a single output can cancel to almost nothing: measure against the terms' size
+            assert np.max(np.abs(y.cpu().numpy() - ref)) <= 1e-3 * np.sqrt(K) * 0.3
+
+    check(layer.forward(_dev(x), residual=_dev(res)),
+          oracle.kquant_matvec(fmt, blocks, K, N, x, residual=res), design=2e-4)
+    xn = oracle.rmsnorm_f64(x[0], gamma, 1e-6).astype(np.float32)[None, :]
+    check(layer.forward(_dev(x), rms_gamma=_dev(gamma), eps=1e-6),
+          oracle.kquant_matvec(fmt, blocks, K, N, xn))
+    ctx_mv.check()
+
+
+@pytest.mark.parametrize("fmt", [12, 8])
+def test_mv_kernel_matches_streaming_kernel_on_heavy_tails(ctx, ctx_mv, oracle, fmt):
+    """Activations with outliers 100x the typical size: the per-32 block scales keep both
+    kernels inside the bar."""
+    K, N = 2560, 640
+    rng = np.random.default_rng(31 + fmt)
+    blocks = formats.random_kquant(rng, fmt, N, K)
+    x = rng.standard_normal((1, K)).astype(np.float32)
+    x[0, rng.integers(0, K, 12)] *= 100.0
+    ref = oracle.kquant_matvec(fmt, blocks, K, N, x)
+    _check(LinearLayer.create_from_bytes(ctx_mv, blocks, fmt, K, N).forward(_dev(x)), ref)
+    _check(LinearLayer.create_from_bytes(ctx, blocks, fmt, K, N).forward(_dev(x)), ref)
+
+
+@pytest.mark.parametrize("fmt", [12, 8])
+def test_mv_kernel_fused_paths(ctx_mv, oracle, fmt):
+    """q/k/v in one launch (rows of a CTA straddle tensors), gate/up GELU (tiles of 8 + 8 rows),
+    and the folded post-norm in front of both."""
+    K = 2560
+    rng = np.random.default_rng(9 + fmt)
+    shapes = [2048, 520, 504]
+    blocks = [formats.random_kquant(rng, fmt, n, K) for n in shapes]
+    x = rng.standard_normal((1, K)).astype(np.float32)
+    gamma = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    layers = [LinearLayer.create_from_bytes(ctx_mv, b, fmt, K, n) for b, n in zip(blocks, shapes)]
+    ys = LinearLayer.forward_multi(layers, _dev(x), rms_gamma=_dev(gamma), eps=1e-6)
+    xn = oracle.rmsnorm_f64(x[0], gamma, 1e-6).astype(np.float32)[None, :]
+    for b, n, y in zip(blocks, shapes, ys):
+        _check(y, oracle.kquant_matvec(fmt, b, K, n, xn))
+    for N in (10240, 1000, 8):
+        bg = formats.random_kquant(rng, fmt, N, K)
+        bu = formats.random_kquant(rng, fmt, N, K)
+        g = LinearLayer.create_from_bytes(ctx_mv, bg, fmt, K, N)
+        u = LinearLayer.create_from_bytes(ctx_mv, bu, fmt, K, N)
+        _check(LinearLayer.forward_fused_gate_up(g, u, _dev(x)),
+               oracle.kquant_gateup_gelu(bg, bu, fmt, K, N, x))
+    # folded post-norm: x' = base + rmsnorm(o) * g1, then RMSNorm(g2) and the products
+    N = 384
+    ba = formats.random_kquant(rng, fmt, N, K)
+    bb = formats.random_kquant(rng, fmt, N, K)
+    o = rng.standard_normal((1, K)).astype(np.float32)
+    base = rng.standard_normal((1, K)).astype(np.float32)
+    g1 = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    la = LinearLayer.create_from_bytes(ctx_mv, ba, fmt, K, N)
+    lb = LinearLayer.create_from_bytes(ctx_mv, bb, fmt, K, N)
+    xp = base[0].astype(np.float64) + oracle.rmsnorm_f64(o[0], g1, 1e-6)
+    xn = oracle.rmsnorm_f64(xp.astype(np.float32), gamma, 1e-6).astype(np.float32)[None, :]
+    ys, xo = LinearLayer.forward_multi([la, lb], _dev(o), rms_gamma=_dev(gamma), eps=1e-6,
+                                       pre=(_dev(base), _dev(g1)))
+    assert np.max(np.abs(xo.cpu().numpy()[0] - xp)) <= 1e-5 * np.max(np.abs(xp))
+    _check(ys[0], oracle.kquant_matvec(fmt, ba, K, N, xn))
+    _check(ys[1], oracle.kquant_matvec(fmt, bb, K, N, xn))
+    y, xo2 = LinearLayer.forward_fused_gate_up(la, lb, _dev(o), rms_gamma=_dev(gamma), eps=1e-6,
+                                               pre=(_dev(base), _dev(g1)))
+    assert torch.equal(xo, xo2)
+    _check(y, oracle.kquant_gateup_gelu(ba, bb, fmt, K, N, xn))
+    ctx_mv.check()
+
+
+def test_mv_kernel_deterministic_and_linear(ctx_mv):
+    K, N = 2560, 10240
+    rng = np.random.default_rng(22)
+    layer = LinearLayer.create_from_bytes(ctx_mv, formats.random_q4k(rng, N, K), 12, K, N)
+    x = _dev(rng.standard_normal((1, K)).astype(np.float32))
+    y1 = layer.forward(x)
+    assert torch.equal(layer.forward(x), y1)
+    assert torch.equal(layer.forward(x * 4.0), y1 * 4.0)
+    assert not layer.forward(torch.zeros_like(x)).any()
+
+
 def test_bad_arguments(ctx):
     from hesper_b200 import HesperB200Error
     layer = LinearLayer.create_from_bytes(ctx, np.zeros(144, np.uint8), 12, 256, 1)
