@@ -63,6 +63,7 @@ _vp, _i, _f, _sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
 # name -> (restype, argtypes); the single source of truth for the Python side.
 SIGNATURES = {
     "hb200_ctx_create": (_i, [_i, C.POINTER(_vp)]),
+    "hb200_ctx_create_current": (_i, [C.POINTER(_vp)]),
     "hb200_ctx_destroy": (_i, [_vp]),
     "hb200_last_error": (C.c_char_p, []),
     "hb200_version": (_i, []),

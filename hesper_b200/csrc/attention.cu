@@ -705,10 +705,9 @@ template <int D, bool PRECISE, int NSTAGES>
 static int attn_launch_ns(hb200_ctx* ctx, const AttnParams& p, cudaStream_t st) {
   using Cfg = AttnCfg<D, NSTAGES>;
   auto kern = attn_decode_kernel<D, PRECISE, NSTAGES>;
-  static bool configured = false;
-  if (!configured) {
-    HB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
-    configured = true;
+  {
+    const int rc = hb_func_smem(ctx, reinterpret_cast<const void*>(kern), (size_t)Cfg::kSmem);
+    if (rc != HB200_OK) return rc;
   }
   const int grid = p.B * p.Hkv * p.nsplit;
   if (p.cluster) {
@@ -716,15 +715,16 @@ static int attn_launch_ns(hb200_ctx* ctx, const AttnParams& p, cudaStream_t st) 
     // memory behind the stages.  Falls back to the ticket path if the launch is refused.
     const size_t smem = (size_t)Cfg::kSmem +
                         (p.cluster == 1 ? (size_t)p.nsplit * 8 * (D + 2) * sizeof(float) : 0);
-    static size_t cluster_smem = 0;
-    static uint32_t refused = 0;  // cluster sizes the driver would not launch
+    // per context: which cluster sizes the driver would not launch, and whether this kernel
+    // was already allowed non-portable cluster sizes there
+    uint32_t& refused = ctx->attn_cluster_refused;
     if (!(refused >> p.nsplit & 1u) && smem <= (size_t)ctx->smem_optin) {
       cudaError_t e = cudaSuccess;
-      if (smem > cluster_smem) {
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e == cudaSuccess)
-          e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-        if (e == cudaSuccess) cluster_smem = smem;
+      if (hb_func_smem(ctx, reinterpret_cast<const void*>(kern), smem) != HB200_OK)
+        e = cudaErrorInvalidValue;
+      if (e == cudaSuccess && !hb_func_flag(ctx, reinterpret_cast<const void*>(kern))) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e == cudaSuccess) hb_func_set_flag(ctx, reinterpret_cast<const void*>(kern));
       }
       if (e == cudaSuccess) {
         cudaLaunchConfig_t cfg = {};
@@ -892,9 +892,9 @@ extern "C" int hb200_attn_prefill(hb200_ctx* ctx, const void* d_q, int q_is_f16,
 // memory.  Every GPU that loads the library carries those 8 MiB until the process exits.
 static __device__ __align__(256) unsigned char g_attn_static_scratch[HB200_ATTN_STATIC_SCRATCH_BYTES];
 
-// Device address of the array, looked up once per device.  In host code the array's name
-// is only a handle for the runtime, never a pointer a kernel could use.
-static void* g_attn_static_scratch_addr[64] = {};
+// In host code the array's name is only a handle for the runtime, never a pointer a kernel
+// could use: its device address is looked up once per context (hence at least once per device,
+// with that device current) and kept in the context.
 
 extern "C" int hb200_attn_decode_static(hb200_ctx* ctx, const void* d_q, int q_is_f16,
                                         const void* d_k, const void* d_v,
@@ -905,7 +905,6 @@ extern "C" int hb200_attn_decode_static(hb200_ctx* ctx, const void* d_q, int q_i
   HB_REQUIRE(B >= 1 && H >= 1 && Hkv >= 1 && H % Hkv == 0 && max_seq >= 1 && window >= 0 && D >= 1,
              "attn (static scratch): B=%d H=%d Hkv=%d D=%d max_seq=%d window=%d", B, H, Hkv, D,
              max_seq, window);
-  HB_REQUIRE(ctx->device >= 0 && ctx->device < 64, "attn (static scratch): device %d", ctx->device);
   // the split count the launch below will choose, hence the scratch it will touch
   const int eff_len = (window > 0 && window < max_seq) ? window : max_seq;
   const int nsplit = attn_pick_splits(ctx, B, Hkv, D, eff_len);
@@ -922,14 +921,14 @@ extern "C" int hb200_attn_decode_static(hb200_ctx* ctx, const void* d_q, int q_i
   HB_REQUIRE(cur == ctx->device,
              "attn (static scratch): device %d is current but the context belongs to device %d",
              cur, ctx->device);
-  void*& addr = g_attn_static_scratch_addr[ctx->device];
-  if (addr == nullptr) {  // first call on this device
+  void*& addr = ctx->attn_static_addr;
+  if (addr == nullptr) {  // first call of this context
     void* p = nullptr;
     HB_CUDA(cudaGetSymbolAddress(&p, g_attn_static_scratch));
     addr = p;
   }
-  // Nothing in the array has to be cleared: the decode kernel writes every partial
-  // (max, sum, output row) that the combine kernel of the same call reads.
+  // Nothing in the array has to be cleared: every split writes its partial (max, sum, output
+  // row) before the last split to arrive -- or the combine launch -- of the same call reads it.
   return hb200_attn_decode(ctx, d_q, q_is_f16, d_k, d_v, d_seqlens, B, H, Hkv, D, max_seq, window,
                            scale, addr, (size_t)HB200_ATTN_STATIC_SCRATCH_BYTES, d_out, stream);
 }

@@ -490,10 +490,9 @@ static int bl_launch(hb200_ctx* ctx, BLParams& p, cudaStream_t st) {
     }
   }
   p.stages = stages;
-  static size_t configured = 0;
-  if (smem > configured) {
-    HB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = smem;
+  {
+    const int rc = hb_func_smem(ctx, reinterpret_cast<const void*>(kern), smem);
+    if (rc != HB200_OK) return rc;
   }
   HB_CUDA(launch_pdl(kern, dim3(grid), dim3(Cfg::kThreads), smem, st, ctx->pdl, p));
   return HB200_OK;

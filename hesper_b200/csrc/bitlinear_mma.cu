@@ -611,11 +611,9 @@ int hb_bitlinear_mma_run(hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int ns
   p.d = d;
   p.sumq = sumq;
   p.status = ctx->d_status;
-  static bool configured = false;
-  if (!configured) {
-    HB_CUDA(cudaFuncSetAttribute(bitlinear_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kMmaSmem));
-    configured = true;
+  {
+    const int rc = hb_func_smem(ctx, reinterpret_cast<const void*>(bitlinear_mma_kernel), (size_t)kMmaSmem);
+    if (rc != HB200_OK) return rc;
   }
   HB_CUDA(launch_pdl(bitlinear_mma_kernel, dim3(t * p.nsplit), dim3(kMmaThreads + 96), (size_t)kMmaSmem, st,
                      ctx->pdl, p));

@@ -56,6 +56,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Same, but the warp may stay suspended for up to `ns` nanoseconds per try: for waits that sit
+// beside another kernel's compute on the same SM and must not take its issue slots.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_quiet(uint64_t* bar, uint32_t parity, uint32_t* status) {
+#pragma unroll 1
+  for (uint32_t it = 0; it < (1u << 16); ++it) {  // 2^16 tries of up to 20 us each
+    if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
+  }
+  if (status) atomicOr(status, kStatusMbarTimeout);
+  return false;
+}
+
 // Bounded wait: each try_wait already blocks for a hardware time slice, so the
 // cap below is seconds of wall time, far beyond any legitimate copy.  On expiry
 // the status word is set and the caller carries on (results are then invalid
@@ -240,4 +262,27 @@ struct hb200_ctx {
   bool pdl;            // use programmatic dependent launch
   int attn_mode;       // HB200_ATTN_FAST / PRECISE / EXACT
   bool no_mma;         // HB200_NO_MMA=1: keep batched ternary products on the dp4a kernel
+  int mv_mode;         // HB200_MV: 0 never the tensor-core matvec, 1 where it measured faster, 2 wherever it fits
+  size_t smem_per_sm;  // shared memory of one SM (two co-resident launches must fit in it)
+  // dynamic shared memory already granted to each kernel in this context's CUDA context
+  // (the attribute is per device and per context, so it cannot live in a process-wide static)
+  struct FuncSmem {
+    const void* func;
+    size_t bytes;
+    bool flag;  // kernel-specific: non-portable cluster sizes already allowed
+  } func_smem[96];
+  int n_func_smem;
+  uint32_t attn_cluster_refused;  // bit n: the driver refused a cluster of n attention CTAs
+  void* attn_static_addr;         // device address of the built-in attention scratch array here
+  bool adopted;                   // lives in the caller's own CUDA context: never switch devices
 };
+
+// Raises cudaFuncAttributeMaxDynamicSharedMemorySize of `func` to `bytes` once per context.
+int hb_func_smem(struct hb200_ctx* ctx, const void* func, size_t bytes);
+bool hb_func_flag(struct hb200_ctx* ctx, const void* func);
+void hb_func_set_flag(struct hb200_ctx* ctx, const void* func);
+
+// one-token Q4_K / Q8_0 matvec on mma.sync (kquant_mv.cu); 1 = shape not covered
+int hb_kq_mv_run(struct hb200_ctx* ctx, int fmt, const hb200_kquant_seg* segs, int nseg, int K,
+                 int gu, const float* d_x, const float* pre_base, const float* pre_gamma,
+                 float* pre_out, const float* gamma, float eps, cudaStream_t st);

@@ -26,19 +26,39 @@ int cuda_fail(cudaError_t e, const char* what) {
 
 }  // namespace hb
 
+int hb_func_smem(hb200_ctx* ctx, const void* func, size_t bytes) {
+  for (int i = 0; i < ctx->n_func_smem; ++i) {
+    if (ctx->func_smem[i].func == func) {
+      if (ctx->func_smem[i].bytes >= bytes) return HB200_OK;
+      HB_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+      ctx->func_smem[i].bytes = bytes;
+      return HB200_OK;
+    }
+  }
+  HB_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+  if (ctx->n_func_smem < 96) ctx->func_smem[ctx->n_func_smem++] = {func, bytes, false};
+  return HB200_OK;
+}
+
+bool hb_func_flag(hb200_ctx* ctx, const void* func) {
+  for (int i = 0; i < ctx->n_func_smem; ++i)
+    if (ctx->func_smem[i].func == func) return ctx->func_smem[i].flag;
+  return false;
+}
+
+void hb_func_set_flag(hb200_ctx* ctx, const void* func) {
+  for (int i = 0; i < ctx->n_func_smem; ++i)
+    if (ctx->func_smem[i].func == func) ctx->func_smem[i].flag = true;
+}
+
 using namespace hb;
 
 extern "C" const char* hb200_last_error(void) { return g_err; }
 
 extern "C" int hb200_version(void) { return 100; }
 
-extern "C" int hb200_ctx_create(int device, hb200_ctx** out) {
-  HB_REQUIRE(out != nullptr, "ctx_create: null output pointer");
-  *out = nullptr;
-  int count = 0;
-  HB_CUDA(cudaGetDeviceCount(&count));
-  HB_REQUIRE(device >= 0 && device < count, "ctx_create: device %d of %d", device, count);
-  HB_CUDA(cudaSetDevice(device));
+// Builds the context object on whatever CUDA context is current on this thread.
+static int ctx_build(int device, bool adopted, hb200_ctx** out) {
   cudaDeviceProp prop;
   HB_CUDA(cudaGetDeviceProperties(&prop, device));
   if (prop.major != 10) {
@@ -47,24 +67,28 @@ extern "C" int hb200_ctx_create(int device, hb200_ctx** out) {
     return HB200_ERR_UNSUPPORTED;
   }
   hb200_ctx* c = new hb200_ctx();
+  c->d_status = nullptr;
   c->d_tickets = nullptr;
   c->d_scratch = nullptr;
   c->d_arena = nullptr;
   c->device = device;
   c->sm_count = prop.multiProcessorCount;
   c->smem_optin = (int)prop.sharedMemPerBlockOptin;
+  c->smem_per_sm = (size_t)prop.sharedMemPerMultiprocessor;
   c->pdl = true;
   c->attn_mode = HB200_ATTN_FAST;
   c->no_mma = false;
   if (const char* e2 = getenv("HB200_NO_MMA")) c->no_mma = e2[0] == '1';
+  c->mv_mode = 1;
+  if (const char* e3 = getenv("HB200_MV")) c->mv_mode = e3[0] == '0' ? 0 : (e3[0] == '2' ? 2 : 1);
+  c->n_func_smem = 0;
+  c->attn_cluster_refused = 0;
+  c->attn_static_addr = nullptr;
+  c->adopted = adopted;
   const char* env = getenv("HB200_NO_PDL");
   if (env && env[0] == '1') c->pdl = false;
   cudaError_t e = cudaMalloc(&c->d_status, 256);
-  if (e != cudaSuccess) {
-    delete c;
-    return cuda_fail(e, "cudaMalloc(status)");
-  }
-  e = cudaMemset(c->d_status, 0, 256);
+  if (e == cudaSuccess) e = cudaMemset(c->d_status, 0, 256);
   if (e == cudaSuccess) e = cudaMalloc(&c->d_tickets, sizeof(int) * (kCtxTickets + 16));
   if (e == cudaSuccess) e = cudaMemset(c->d_tickets, 0, sizeof(int) * (kCtxTickets + 16));
   c->scratch_bytes = kScratchBytes;
@@ -80,6 +104,37 @@ extern "C" int hb200_ctx_create(int device, hb200_ctx** out) {
   }
   *out = c;
   return HB200_OK;
+}
+
+extern "C" int hb200_ctx_create(int device, hb200_ctx** out) {
+  HB_REQUIRE(out != nullptr, "ctx_create: null output pointer");
+  *out = nullptr;
+  int count = 0;
+  HB_CUDA(cudaGetDeviceCount(&count));
+  HB_REQUIRE(device >= 0 && device < count, "ctx_create: device %d of %d", device, count);
+  HB_CUDA(cudaSetDevice(device));
+  return ctx_build(device, false, out);
+}
+
+extern "C" int hb200_ctx_create_current(hb200_ctx** out) {
+  HB_REQUIRE(out != nullptr, "ctx_create_current: null output pointer");
+  *out = nullptr;
+  // The caller's context, as the driver API sees it: a host that made its context with
+  // cuCtxCreate (native/cuda_bridge.cpp:78-82) has it current on this thread, and the CUDA
+  // runtime then works inside it.  No device switch, no primary-context retain.
+  typedef int (*cuCtxGetCurrent_t)(void**);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  HB_CUDA(cudaGetDriverEntryPoint("cuCtxGetCurrent", &fn, cudaEnableDefault, &q));
+  HB_REQUIRE(fn != nullptr && q == cudaDriverEntryPointSuccess,
+             "ctx_create_current: the driver does not export cuCtxGetCurrent");
+  void* cur = nullptr;
+  const int drc = reinterpret_cast<cuCtxGetCurrent_t>(fn)(&cur);
+  HB_REQUIRE(drc == 0 && cur != nullptr,
+             "ctx_create_current: no CUDA context is current on this thread (driver code %d)", drc);
+  int device = -1;
+  HB_CUDA(cudaGetDevice(&device));
+  return ctx_build(device, true, out);
 }
 
 extern "C" int hb200_ctx_destroy(hb200_ctx* ctx) {

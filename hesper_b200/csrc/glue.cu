@@ -410,13 +410,8 @@ template <int MT>
 static cudaError_t lm_launch(hb200_ctx* ctx, const LMParams& p, int grid, size_t smem,
                              cudaStream_t st) {
   auto kern = lmhead_kernel<MT>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         ctx->smem_optin);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  if (hb_func_smem(ctx, reinterpret_cast<const void*>(kern), (size_t)ctx->smem_optin) != HB200_OK)
+    return cudaErrorInvalidValue;
   return launch_pdl(kern, dim3(grid), dim3(kLMThreads), smem, st, ctx->pdl, p);
 }
 

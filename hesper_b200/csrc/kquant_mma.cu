@@ -389,11 +389,9 @@ static int kq_mma_launch(hb200_ctx* ctx, QmParams& p, int tiles, cudaStream_t st
   if (nsplit < 1 || tiles > kCtxTickets) nsplit = 1;
   p.bps = (nboxes + nsplit - 1) / nsplit;
   p.nsplit = (nboxes + p.bps - 1) / p.bps;  // no empty split
-  static bool configured = false;
-  if (!configured) {
-    HB_CUDA(cudaFuncSetAttribute(kq_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 Cfg::kSmem));
-    configured = true;
+  {
+    const int rc = hb_func_smem(ctx, reinterpret_cast<const void*>(kq_mma_kernel<NT>), (size_t)Cfg::kSmem);
+    if (rc != HB200_OK) return rc;
   }
   HB_CUDA(launch_pdl(kq_mma_kernel<NT>, dim3((unsigned)(tiles * p.nsplit)), dim3(kQmThreads),
                      (size_t)Cfg::kSmem, st, ctx->pdl, p));

@@ -471,11 +471,10 @@ int hb_gemm16_mma(hb200_ctx* ctx, const void* d_table, int dtype, long V, int K,
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kLmN >> 3) << 17) |
             ((uint32_t)(kLmRows >> 4) << 24);
   p.status = ctx->d_status;
-  static bool configured = false;
-  if (!configured) {
-    HB_CUDA(cudaFuncSetAttribute(lmhead_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kLmCtrl + kLmMaxStages * (kLmABytes + kLmBBytes)));
-    configured = true;
+  {
+    const int rc = hb_func_smem(ctx, reinterpret_cast<const void*>(lmhead_mma_kernel),
+                                (size_t)(kLmCtrl + kLmMaxStages * (kLmABytes + kLmBBytes)));
+    if (rc != HB200_OK) return rc;
   }
   const long ntiles = (V + kLmRows - 1) / kLmRows;
   // few row tiles: every CTA has an SM to itself, so it takes the deeper ring (192 KB in

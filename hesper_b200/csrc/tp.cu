@@ -590,7 +590,7 @@ extern "C" int hb200_tp_init(hb200_ctx* ctx, int rank, int nranks, const unsigne
   *out = nullptr;
   int rc = nccl_load();
   if (rc) return rc;
-  HB_CUDA(cudaSetDevice(ctx->device));
+  if (!ctx->adopted) HB_CUDA(cudaSetDevice(ctx->device));
   NcclId nid;
   memcpy(nid.internal, id, 128);
   ncclComm_t comm = nullptr;
@@ -610,7 +610,7 @@ extern "C" size_t hb200_tp_peer_handle_bytes(void) { return sizeof(cudaIpcMemHan
 extern "C" int hb200_tp_peer_export(hb200_tp* tp, unsigned char* out_handle) {
   HB_REQUIRE(tp && out_handle, "tp_peer_export: null argument");
   HB_REQUIRE(tp->nranks <= kPeerMaxRanks, "tp_peer_export: at most %d ranks", kPeerMaxRanks);
-  HB_CUDA(cudaSetDevice(tp->ctx->device));
+  if (!tp->ctx->adopted) HB_CUDA(cudaSetDevice(tp->ctx->device));
   if (!tp->peer_buf[tp->rank]) {
     void* b = nullptr;
     HB_CUDA(cudaMalloc(&b, kPeerBufBytes));
@@ -629,7 +629,7 @@ extern "C" int hb200_tp_peer_export(hb200_tp* tp, unsigned char* out_handle) {
 extern "C" int hb200_tp_peer_attach(hb200_tp* tp, const unsigned char* all_handles) {
   HB_REQUIRE(tp && all_handles, "tp_peer_attach: null argument");
   HB_REQUIRE(tp->peer_buf[tp->rank] != nullptr, "tp_peer_attach: call hb200_tp_peer_export first");
-  HB_CUDA(cudaSetDevice(tp->ctx->device));
+  if (!tp->ctx->adopted) HB_CUDA(cudaSetDevice(tp->ctx->device));
   for (int r = 0; r < tp->nranks; ++r) {
     if (r == tp->rank || tp->peer_buf[r]) continue;
     cudaIpcMemHandle_t h;

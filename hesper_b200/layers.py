@@ -45,11 +45,17 @@ def _need(t: torch.Tensor, dtype, name: str) -> torch.Tensor:
 class Context:
     """One per GPU: mirrors CUDAContext.init (Hesper/Backend/CUDA.lean:46)."""
 
-    def __init__(self, device: int = 0):
+    def __init__(self, device: int = 0, adopt_current: bool = False):
+        """`adopt_current`: build the context inside the CUDA context that is current on this
+        thread (a host that called cuCtxCreate itself, as native/cuda_bridge.cpp:78-82 does)
+        instead of binding to `device`'s primary context."""
         self._lib = _lib.load()
         self.device = int(device)
         h = C.c_void_p()
-        check(self._lib.hb200_ctx_create(self.device, C.byref(h)))
+        if adopt_current:
+            check(self._lib.hb200_ctx_create_current(C.byref(h)))
+        else:
+            check(self._lib.hb200_ctx_create(self.device, C.byref(h)))
         self._h = h
 
     @property

@@ -61,12 +61,24 @@ typedef void *hb200_stream;
  * (f16 weights of one batched k-quant product).  No operator
  * allocates afterwards; a context serves one stream at a time.
  * Environment: HB200_NO_PDL=1 launches without programmatic dependent launch,
- * HB200_NO_MMA=1 keeps the batched (>= 16 token) operators off the tensor-core kernels.
+ * HB200_NO_MMA=1 keeps the batched (>= 16 token) operators off the tensor-core kernels,
+ * HB200_MV=0 / 2 keeps one-token k-quant matvecs off the mma.sync kernel / uses it wherever the
+ * shape fits (default 1: where it measured faster than the streaming kernel).
  * Measurement knobs of the decode loops and the exchange (same value on every rank):
  * HB200_NO_FOLD=1 keeps the post-norms of the Gemma-shape loop as launches of their own,
  * HB200_TP_NO_LL=1 / HB200_TP_FUSE_MAX=<tokens> / HB200_TP_NO_PEER=1 select the
  * flag-after-data kernel, the unfused exchange above a batch size, or NCCL. */
 int hb200_ctx_create(int device, hb200_ctx **out);
+
+/* The same object inside the CUDA context that is current on the calling thread, for a host
+ * that made its own context with the driver API -- Hesper does: cuCtxCreate on device 0,
+ * native/cuda_bridge.cpp:78-82 -- and hands over CUdeviceptr / CUstream values that live in
+ * it.  No cudaSetDevice, no primary-context retain: the device is the current context's,
+ * every buffer of the library is allocated there, kernels are loaded there on first use.
+ * The caller keeps that context current on the thread for every later call with this
+ * handle and destroys the handle before the context.  Fails with HB200_ERR_INVALID when no
+ * context is current. */
+int hb200_ctx_create_current(hb200_ctx **out);
 int hb200_ctx_destroy(hb200_ctx *ctx);
 
 /* Message of the last failing call on this thread (never NULL).
@@ -272,15 +284,18 @@ int hb200_attn_prefill(hb200_ctx *ctx, const void *d_q, int q_is_f16, const void
  * the library image, so the call never allocates or frees device memory, neither directly
  * nor through a library.  It is meant for hosts where a device allocation at this point is
  * not an option: a runtime that has already handed the whole GPU to its own buffer pool
- * (Hesper's pooled CUDABuffer allocator works that way), a thread that may not stall on the
- * device-wide synchronisation cudaMalloc can imply, or code running in a host callback,
- * where CUDA API calls are not allowed at all.
+ * (Hesper's pooled CUDABuffer allocator works that way), or a thread that may not stall on
+ * the device-wide synchronisation cudaMalloc can imply.  It still makes ordinary CUDA
+ * runtime calls (device query, kernel launch), so it is not for host callbacks.
  *
  *   - Shapes whose partials exceed the array are refused with HB200_ERR_UNSUPPORTED and
- *     a message naming both sizes (the BASELINE sweeps up to batch 64 x 32768 positions
- *     at 8/2 heads, D = 256, fit); use hb200_attn_decode for larger ones.
- *   - The first call on a device looks up the array's device address.  Make that first
- *     call before any stream capture is started on the thread.
+ *     a message naming both sizes; use hb200_attn_decode for those.  With the current split
+ *     rule (about two waves of resident CTAs, at most 64 splits) no supported shape reaches
+ *     the limit -- the decode sweeps up to batch 64 x 32768 positions at 8/2 heads, D = 256
+ *     stay below 5 MiB -- so the check guards future split rules.
+ *   - The first call of a context looks up the array's device address (with the context's
+ *     device current).  Make that first call before any stream capture is started on the
+ *     thread.
  *   - All calls on a device share the one array and find the previous call's partials in
  *     it; that is harmless (every value read is written first within the same call), but
  *     two calls that overlap on the GPU, e.g. on different streams, race on it.  Keep calls
