@@ -1,11 +1,12 @@
 #!/usr/bin/env python
 """bench.py -- headline benchmark of the B200 quantized-inference hot path.
 
-Metric (BASELINE.json): quant matvec HBM GB/s.  Workload at every N: BASELINE config 1,
+Metric: quant matvec HBM GB/s.  Workload at every N: benchmark configuration 1,
 the GGUF Q4_K dequant-fused matvec K=2560 -> N=10240 at batch 1, run as a ring of R
 distinct weight matrices (R * 14.7 MB >> the 126 MB L2), so that every launch streams its
-weights from HBM as it does inside a real decode step.  One "step" = one pass over the
-ring = R matvec launches, captured in one CUDA graph and replayed.
+weights from HBM as it does inside a real decode step.  One pass over the ring = R matvec
+launches, captured in one CUDA graph; one "step" = `--passes` replays of it (default 100, so
+that the timed region of 20 steps lasts about half a second).
 
   value    = algorithmic bytes of all ranks' launches / device time (inputs resident)
   e2e      = the same pass driven from HOST buffers through the C ABI: pinned-host
@@ -13,7 +14,7 @@ ring = R matvec launches, captured in one CUDA graph and replayed.
   roofline = the matvec kernel against the measured HBM copy peak (MEASURED_PEAKS.json)
   cpu_baseline = the CPU oracle (a C restatement of the reference's Lean spec; the
              reference itself cannot be built here) on the box's host cores
-  extra    = the other BASELINE configs (ternary i2_s ring, Q8_0 ring, decode attention)
+  extra    = the other benchmark configurations (ternary i2_s ring, Q8_0 ring, decode attention)
 
 `--impl reference` times that CPU restatement alone, on the same workload and metric.
 With N > 1 each rank streams its own ring (the path shards by weight tensor; no
@@ -39,6 +40,20 @@ Q4K_BYTES = 14_796_800      # weights 14 745 600 + x 10 240 + y 40 960
 Q80_BYTES = 27_904_000
 I2S_BYTES = 4_489_220       # K=2560, N=6912 ternary: W + scale + x + acc + y
 FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_traffic():
+    """DRAM bytes per launch of the headline kernel (read + written), from the committed
+    profiler summary of that kernel; None when the summary is absent."""
+    import re
+    p = os.path.join(ROOT, "profiles", "kq_mv_q4k_K2560_N10240.md")
+    try:
+        txt = open(p).read()
+        rd = re.search(r"dram__bytes_read\.sum\s*\|\s*([0-9.]+)\s*MB", txt)
+        wr = re.search(r"dram__bytes_write\.sum\s*\|\s*([0-9.]+)\s*MB", txt)
+        return (float(rd.group(1)) + float(wr.group(1))) * 1e6
+    except Exception:
+        return None
 
 
 def measured_peak():
@@ -105,6 +120,8 @@ def run_reference(args):
     from hesper_b200 import formats
     from oracle import oracle as orc
     orc.lib()
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its workers: ask for the cores again
+    orc.set_num_threads(os.cpu_count() or 1)
     cores = orc.num_threads()
     ring, x = cpu_ring(0x1337C0DE)
     orc.q4k_matvec(ring[0], K1, N1, x)  # touch
@@ -151,8 +168,9 @@ def build_ring(torch, ctx, fmt, K, N, R, seed):
             for r in range(R)]
 
 
-def time_graph(torch, st, fn, steps, warmup):
-    """Capture fn() on stream st, replay warmup + steps times, return seconds per step."""
+def time_graph(torch, st, fn, steps, warmup, passes=1):
+    """Capture fn() on stream st; a step is `passes` replays.  Runs warmup + steps steps and
+    returns (seconds per step, graph), timed with CUDA events on st."""
     # inputs were produced on the default stream: order the side stream after them
     torch.cuda.synchronize()
     with torch.cuda.stream(st):
@@ -161,13 +179,13 @@ def time_graph(torch, st, fn, steps, warmup):
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=st):
             fn()
-        for _ in range(warmup):
+        for _ in range(warmup * passes):
             g.replay()
         st.synchronize()
         e0 = torch.cuda.Event(enable_timing=True)
         e1 = torch.cuda.Event(enable_timing=True)
         e0.record(st)
-        for _ in range(steps):
+        for _ in range(steps * passes):
             g.replay()
         e1.record(st)
         st.synchronize()
@@ -188,6 +206,7 @@ def cpu_ring(seed, R=8):
 def cpu_baseline(sample_seconds=12.0):
     from oracle import oracle as orc
     orc.lib()
+    orc.set_num_threads(os.cpu_count() or 1)
     ring, x = cpu_ring(1)
     orc.q4k_matvec(ring[0], K1, N1, x)
     t0 = time.perf_counter()
@@ -239,19 +258,15 @@ def run_ours(args):
     # ---- device-resident throughput (the headline `value`) ----
     barrier()
     with ClockSampler(local) as clk:
-        sec, graph = time_graph(torch, st, ring_pass, args.steps, max(3, args.warmup))
-        # keep the sampler fed for short runs: a few more replays outside the timed region
-        t_end = time.time() + 0.6
-        while time.time() < t_end:
-            graph.replay()
-        torch.cuda.synchronize()
+        P = max(1, args.passes)
+        sec, graph = time_graph(torch, st, ring_pass, args.steps, max(3, args.warmup), P)
     barrier()
     tsec = torch.tensor([sec], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(tsec, op=dist.ReduceOp.MAX)
     sec_max = float(tsec.item())
-    value = world * R * Q4K_BYTES / sec_max / 1e9
-    per_launch = sec / R
+    value = world * P * R * Q4K_BYTES / sec_max / 1e9
+    per_launch = sec / (P * R)
     peak, peak_src = measured_peak()
     achieved = Q4K_BYTES / per_launch / 1e9
 
@@ -260,10 +275,12 @@ def run_ours(args):
     hy = torch.empty(R, N1).pin_memory()
 
     def e2e_step():
+        # every pass of the step brings its activations from the host and takes its results back
         with torch.cuda.stream(st):
-            xs.copy_(hx, non_blocking=True)
-            graph.replay()
-            hy.copy_(ys, non_blocking=True)
+            for _ in range(P):
+                xs.copy_(hx, non_blocking=True)
+                graph.replay()
+                hy.copy_(ys, non_blocking=True)
         st.synchronize()
 
     for _ in range(3):
@@ -276,7 +293,7 @@ def run_ours(args):
     te = torch.tensor([e2e_sec], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_val = world * R * Q4K_BYTES / float(te.item()) / 1e9
+    e2e_val = world * P * R * Q4K_BYTES / float(te.item()) / 1e9
 
     extra = {}
     if rank == 0 and not args.no_extra:
@@ -296,21 +313,23 @@ def run_ours(args):
             "metric": "quant matvec HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": sec_max * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "int8 x int16 dp4a, f32 accumulate", "data": "synthetic",
+            "dtype": "u8 (4-bit quants) x s16 (two s8 planes) integer mma, f32 accumulate",
+            "data": "synthetic",
             "config": {"workload": f"cfg1 GGUF Q4_K matvec K={K1} N={N1} batch 1, ring of {R} "
                                    f"distinct matrices per GPU ({R * 14.7456:.0f} MB > L2: inputs "
-                                   "larger than L2, no flush needed), one CUDA graph per pass, "
-                                   "programmatic dependent launch between matvecs",
+                                   f"larger than L2, no flush needed), one CUDA graph per pass, "
+                                   f"{P} passes per step, programmatic dependent launch between "
+                                   "matvecs",
                        "pct_of_8TBs": value / world / 8000.0 * 100.0},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": (None if args.traffic != args.traffic else args.traffic), "peak_source": peak_src,
-                         "kernel": "kquant_kernel<12,RT,false>",
+                         "frac": achieved / peak, "traffic": measured_traffic(),
+                         "peak_source": peak_src, "kernel": "kq_mv_kernel<12,false>",
                          "algorithmic_bytes_per_launch": Q4K_BYTES,
                          "us_per_launch": per_launch * 1e6},
             "cpu_baseline": cpu,
-            "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": R * K1 * 4,
-                    "d2h_bytes_per_step": R * N1 * 4},
-            "gpu_launches": R * args.steps,
+            "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": P * R * K1 * 4,
+                    "d2h_bytes_per_step": P * R * N1 * 4},
+            "gpu_launches": P * R * args.steps,
             "clocks": clk.summary(),
             "extra": extra,
         }
@@ -322,7 +341,7 @@ def run_ours(args):
 
 
 def run_extra(torch, ctx, st, hb, args):
-    """Other BASELINE configs, device-resident, each as GB/s of algorithmic bytes."""
+    """The other benchmark configurations, device-resident, each as GB/s of algorithmic bytes."""
     from hesper_b200 import BitLinear, formats
     out = {}
     steps, warm = max(5, args.steps // 2), 3
@@ -426,8 +445,13 @@ def run_batched(torch, ctx, st, steps, warm):
 
 
 def run_tp_decode(torch, dist, ctx, hb, rank, world):
-    """BASELINE config 4: Gemma-4-E4B-shaped Q4_K model, tensor-parallel over `world` GPUs,
-    random-init shards generated on each GPU, decode at context ~8000 of 8192."""
+    """Configuration 4: Gemma-4-E4B-shaped Q4_K model, tensor-parallel over `world` GPUs,
+    random-init (every rank draws the same tensors and keeps its slice), decode at context
+    ~8000 of 8192.  Beside the timing, the greedy tokens are checked: all ranks must hold the
+    same tokens, and at world > 1 rank 0 also decodes the unsharded model from the same seed and
+    reports how many of the first 8 tokens of sequence 0 agree (random-init logits have
+    near-ties, so a different summation order may legitimately flip a token: reported, not
+    asserted)."""
     from hesper_b200 import tp
     S = tp.GemmaShape()
     out = {"tp": world}
@@ -440,6 +464,7 @@ def run_tp_decode(torch, dist, ctx, hb, rank, world):
         # algorithmic bytes per token per the whole job: Q4_K layers + LM head + bf16 embedding
         # row + f16 KV (35 sliding-window layers x 512 positions, 7 global layers x ctx)
         wbytes = 42 * 51_609_600 + 377_487_360
+        first8 = {}
         for B, steps in ((1, 64), (32, 16), (256, 8)):
             model = tp.GemmaModel(ctx, S, shard, plan, comm, batch=B, max_new_tokens=steps)
             model.set_position(8000)
@@ -447,18 +472,42 @@ def run_tp_decode(torch, dist, ctx, hb, rank, world):
             model.set_position(8000)
             if world > 1:
                 dist.barrier()
-            _, _, ms = model.generate(None, steps, use_graph=True)
+            toks, _, ms = model.generate(None, steps, use_graph=True)
             t = torch.tensor([ms], device="cuda", dtype=torch.float64)
             if world > 1:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
             kv = B * (35 * 512 + 7 * 8000) * 2048
             us = ms / steps * 1e3
-            out[f"B{B}"] = {"tok_s": B * steps / ms * 1e3, "us_per_step": us,
-                            "roofline_us_at_measured_peak": (wbytes + kv) / world / measured_peak()[0] / 1e3,
-                            "allreduces_per_step": 84 if world > 1 else 0}
+            roof = (wbytes + kv) / world / measured_peak()[0] / 1e3
+            rec = {"tok_s": B * steps / ms * 1e3, "us_per_step": us,
+                   "roofline_us_at_measured_peak": roof, "frac_of_roofline": roof / us,
+                   "allreduces_per_step": 84 if world > 1 else 0}
+            n8 = min(8, steps)
+            mine = torch.from_numpy(np.ascontiguousarray(toks[:, :n8])).cuda()
+            first8[B] = toks[0, :n8].tolist()
+            if world > 1:
+                allt = [torch.empty_like(mine) for _ in range(world)]
+                dist.all_gather(allt, mine)
+                rec["ranks_agree"] = bool(all(torch.equal(allt[0], a) for a in allt))
+                assert rec["ranks_agree"], "tensor-parallel ranks hold different greedy tokens"
+            out[f"B{B}"] = rec
             model.close()
             del model
+        if world > 1 and rank == 0:
+            # the unsharded model from the same seed on this GPU, batch 1
+            del shard
+            torch.cuda.empty_cache()
+            p1 = tp.plan(S, 0, 1)
+            one = tp.GemmaModel(ctx, S, tp.random_gemma_shard_device(S, p1, seed=7), p1, None,
+                                batch=1, max_new_tokens=8)
+            one.set_position(8000)
+            t1, _, _ = one.generate(None, 8, use_graph=True)
+            one.close()
+            same = sum(int(a == b) for a, b in zip(t1[0].tolist(), first8[1]))
+            out["B1"]["first8_equal_to_unsharded"] = same
+    except AssertionError:
+        raise
     except Exception as e:  # keep the headline line alive if a side measurement fails
         out["error"] = repr(e)[:300]
     finally:
@@ -468,7 +517,7 @@ def run_tp_decode(torch, dist, ctx, hb, rank, world):
 
 
 def run_bitnet_decode(torch, ctx, hb):
-    """BASELINE config 3: BitNet-b1.58-2B-shaped model, random-init, 2048-token random prompt
+    """Configuration 3: BitNet-b1.58-2B-shaped model, random-init, 2048-token random prompt
     then 128 greedy tokens at batch 1 and at batch 64 (graph replay; the prompt is consumed
     one position per step through the same decode path)."""
     from hesper_b200.models import BitNetShape, BitNetModel, random_bitnet_weights_device
@@ -497,6 +546,131 @@ def run_bitnet_decode(torch, ctx, hb):
     return out
 
 
+# ----------------------------------------------------------------------------- profiler cases
+
+CASES = """Small fixed workloads for profiler captures: `python bench.py --case <name>`.
+Each runs a handful of launches of one kernel on inputs larger than the L2 but well under a
+few GB, so that a full-metric capture of one to three launches ends in a minute.
+  q4k      ring of 12 Q4_K matrices K=2560 N=10240 (177 MB), 3 passes
+  q80      ring of 8 Q8_0 matrices (223 MB), 3 passes
+  i2s      ring of 40 ternary matrices K=2560 N=6912 (177 MB), 3 passes
+  attn     decode attention B=16 L=4096, 8q/2kv heads, D=256 (268 MB of KV), 6 calls
+  i2s_mma  64-token ternary product on the tensor cores, ring of 40 matrices (177 MB), 2 passes
+  lmhead64 64-token LM head on the tensor cores, one bf16 table V=128256 K=2560 (657 MB), 3 calls
+  q4k_b32  32-token Q4_K product on the tensor cores, ring of 12 matrices, 2 passes
+  bitnet1 / bitnet64   BitNet-2B-shaped decode loop at batch 1 / 64: 2 prompt positions and
+           3 new tokens, launched one by one (no graph) so that a launch list sees each kernel
+  gemma1 / gemma32 / gemma256   Gemma-4-E4B-shaped Q4_K decode loop (one rank): 3 tokens at
+           position 8000, launched one by one
+"""
+
+
+def run_case(name: str) -> int:
+    import torch
+    import hesper_b200 as hb
+    from hesper_b200 import formats
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --case needs a CUDA device")
+    ctx = hb.Context(0)
+    rng = np.random.default_rng(0)
+    if name in ("q4k", "q80"):
+        fmt, R = (12, 12) if name == "q4k" else (8, 8)
+        K, N = 2560, 10240
+        base = torch.from_numpy(formats.random_kquant(rng, fmt, N, K)).cuda()
+        rb = formats.kquant_row_bytes(fmt, K)
+        layers = [hb.LinearLayer(ctx, torch.roll(base, r * rb), fmt, K, N) for r in range(R)]
+        x = torch.randn(1, K, device="cuda")
+        y = torch.empty(1, N, device="cuda")
+        torch.cuda.synchronize()
+        for _ in range(3):
+            for l in layers:
+                l.forward(x, out=y)
+    elif name == "i2s":
+        K, N, R = 2560, 6912, 40
+        base = torch.from_numpy(formats.i2s_pack(formats.random_ternary(rng, N, K))).cuda()
+        sc = torch.tensor([0.05], device="cuda")
+        layers = [hb.BitLinear(ctx, torch.roll(base, r * 640), sc, K, N) for r in range(R)]
+        x = torch.randn(1, K, device="cuda")
+        y = torch.empty(1, N, device="cuda")
+        torch.cuda.synchronize()
+        for _ in range(3):
+            for l in layers:
+                l.forward(x, out=y)
+    elif name == "q4k_b32":
+        K, N, R, M = 2560, 10240, 12, 32
+        base = torch.from_numpy(formats.random_kquant(rng, 12, N, K)).cuda()
+        rb = formats.kquant_row_bytes(12, K)
+        layers = [hb.LinearLayer(ctx, torch.roll(base, r * rb), 12, K, N) for r in range(R)]
+        x = torch.randn(M, K, device="cuda")
+        y = torch.empty(M, N, device="cuda")
+        torch.cuda.synchronize()
+        for _ in range(2):
+            for l in layers:
+                l.forward(x, out=y)
+    elif name == "i2s_mma":
+        K, N, R, M = 2560, 6912, 40, 64
+        base = torch.from_numpy(formats.i2s_pack(formats.random_ternary(rng, N, K))).cuda()
+        sc = torch.tensor([0.05], device="cuda")
+        layers = [hb.BitLinear(ctx, torch.roll(base, r * 640), sc, K, N) for r in range(R)]
+        x = torch.randn(M, K, device="cuda")
+        y = torch.empty(M, N, device="cuda")
+        torch.cuda.synchronize()
+        for _ in range(2):
+            for l in layers:
+                l.forward(x, out=y)
+    elif name == "lmhead64":
+        from hesper_b200 import _lib
+        lib = _lib.load()
+        V, K, M = 128256, 2560, 64
+        table = (torch.randn(V, K, device="cuda") * 0.02).to(torch.bfloat16)
+        x = torch.randn(M, K, device="cuda")
+        arg = torch.zeros(M, dtype=torch.int32, device="cuda")
+        scr = torch.zeros(M, dtype=torch.int64, device="cuda")
+        torch.cuda.synchronize()
+        for _ in range(3):
+            rc = lib.hb200_lmhead_argmax(ctx.handle, table.data_ptr(), 0, V, K, x.data_ptr(), M,
+                                         None, 0.0, None, arg.data_ptr(), scr.data_ptr(), None,
+                                         None, 0, None)
+            assert rc == 0
+    elif name in ("bitnet1", "bitnet64"):
+        from hesper_b200.models import BitNetModel, BitNetShape, random_bitnet_weights_device
+        B = 1 if name == "bitnet1" else 64
+        shape = BitNetShape.bitnet_2b(max_seq=2304)
+        w = random_bitnet_weights_device(shape)
+        m = BitNetModel(ctx, shape, w, batch=B, max_new_tokens=8)
+        prompt = rng.integers(0, shape.vocab, (B, 2)).astype(np.int32)
+        m.generate(prompt, 3, use_graph=False)
+        m.close()
+    elif name in ("gemma1", "gemma32", "gemma256"):
+        from hesper_b200 import tp
+        B = int(name[5:])
+        S = tp.GemmaShape()
+        plan = tp.plan(S, 0, 1)
+        shard = tp.random_gemma_shard_device(S, plan, seed=7)
+        m = tp.GemmaModel(ctx, S, shard, plan, None, batch=B, max_new_tokens=8)
+        m.set_position(8000)
+        m.generate(None, 3, use_graph=False)
+        m.close()
+    elif name == "attn":
+        B, H, Hkv, D, L = 16, 8, 2, 256, 4096
+        q = torch.randn(B, H, D, device="cuda").half()
+        k = torch.randn(B, Hkv, L, D, device="cuda").half()
+        v = torch.randn(B, Hkv, L, D, device="cuda").half()
+        lens = torch.full((B,), L, dtype=torch.int32, device="cuda")
+        ws = hb.flash_attention_workspace(ctx, B, H, Hkv, D, L)
+        torch.cuda.synchronize()
+        for _ in range(6):
+            hb.execute_flash_attention_v11(ctx, q, k, v, lens, num_heads=H, num_kv_heads=Hkv,
+                                           head_dim=D, max_seq_len=L, scale=1 / 16, workspace=ws)
+    else:
+        raise SystemExit(f"unknown case {name}")
+    torch.cuda.synchronize()
+    ctx.check()
+    print("ok")
+    return 0
+
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -506,10 +680,11 @@ def main():
     ap.add_argument("--ring", type=int, default=40, help="distinct weight matrices per pass")
     ap.add_argument("--no-extra", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--traffic", type=float, default=14_790_000.0,
-                    help="dram bytes per launch of the Q4_K kernel from the committed ncu capture "
-                         "(profiles/kquant_q4k_K2560_N10240.md); null it with --traffic nan")
+    ap.add_argument("--passes", type=int, default=100, help="ring passes (graph replays) per step")
+    ap.add_argument("--case", default=None, help="run one small profiler workload and exit:\n" + CASES)
     args = ap.parse_args()
+    if args.case:
+        return run_case(args.case)
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)

@@ -64,19 +64,6 @@ struct AttnParams {
   int* tickets;      // nullable: per (sequence, kv head) arrival counters, zero between calls
 };
 
-#ifdef HB_PROFILE
-__device__ unsigned long long g_attn_stamps[16];
-#define AT_STAMP(i)                                                                        \
-  do {                                                                                     \
-    if (blockIdx.x == 0 && threadIdx.x == 0) {                                             \
-      unsigned long long t_;                                                               \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                               \
-      g_attn_stamps[i] = t_;                                                               \
-    }                                                                                      \
-  } while (0)
-#else
-#define AT_STAMP(i) ((void)0)
-#endif
 
 // Query token b of a launch with T tokens per sequence: its cache index and how many
 // positions it sees (causal: token t of the T appended ones sees all but the T-1-t last).
@@ -182,17 +169,14 @@ __global__ void __launch_bounds__(kAttnThreads, D >= 256 ? 1 : 2) attn_decode_ke
   __half* qsl = qs + 8 * QS;                       // lo plane (PRECISE only)
   uint8_t* stage0 = smem + Cfg::kQBytes + (size_t)warp * NS * Cfg::kStageBytes;
 
-  AT_STAMP(0);
   pdl_trigger();
   pdl_wait();  // q, the cache and seqlens come from earlier kernels of the step
-  AT_STAMP(1);
 
   // a length outside [0, max_seq] can only come from a corrupt input: clamp, never overrun
   int cb;  // which sequence's cache
   const int len = attn_visible_len(p, b, cb);
   int start = 0;
   if (p.window > 0 && len > p.window) start = len - p.window;
-  AT_STAMP(2);
   const int nch = (len - start + kChunk - 1) / kChunk;  // chunks of this sequence (<= 0 if empty)
   int cps;                                              // chunks per split
   const int nact = attn_active_splits(nch, p.nsplit, cps);
@@ -262,7 +246,6 @@ __global__ void __launch_bounds__(kAttnThreads, D >= 256 ? 1 : 2) attn_decode_ke
     }
   }
   __syncthreads();
-  AT_STAMP(3);
   // B fragments of Q^T: head g, dims 16s+2t(+1) and 16s+2t+8(+9).  The fast path keeps
   // them in registers; the precise path re-reads hi and lo from shared memory per k-step.
   constexpr int QR = PRECISE ? 1 : KS;
@@ -389,7 +372,6 @@ __global__ void __launch_bounds__(kAttnThreads, D >= 256 ? 1 : 2) attn_decode_ke
   }
   cp_async_wait<0>();
   __syncthreads();  // every warp is done with its stages: reuse them for the merge
-  AT_STAMP(4);
 
   // ---- merge the 4 warps ---------------------------------------------------------
   float* mo = reinterpret_cast<float*>(smem + Cfg::kQBytes);  // [warps][8 heads][D]
@@ -454,7 +436,6 @@ __global__ void __launch_bounds__(kAttnThreads, D >= 256 ? 1 : 2) attn_decode_ke
       }
     }
   }
-  AT_STAMP(5);
   if (p.cluster) {
     if (p.cluster == 2 && !cluster_synced) {  // nact == 1: the first barrier was not reached above
       cluster_arrive_release();
@@ -516,7 +497,6 @@ __global__ void __launch_bounds__(kAttnThreads, D >= 256 ? 1 : 2) attn_decode_ke
     s_last = (t == nact - 1);
   }
   __syncthreads();
-  AT_STAMP(6);
   if (!s_last) return;
   __threadfence();
   float* cw = reinterpret_cast<float*>(smem + Cfg::kQBytes);  // [nsplit][8] weights, then [8] sums
@@ -763,12 +743,6 @@ static int attn_launch_ns(hb200_ctx* ctx, const AttnParams& p, cudaStream_t st) 
 
 using namespace hb;
 
-#ifdef HB_PROFILE
-extern "C" __attribute__((visibility("default"))) void hb200_prof_read_attn(unsigned long long* out) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, g_attn_stamps, sizeof(unsigned long long) * 16);
-}
-#endif
 
 extern "C" size_t hb200_attn_workspace_bytes(const hb200_ctx* ctx, int B, int H, int Hkv, int D,
                                              int max_seq) {

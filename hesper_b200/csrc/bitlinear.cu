@@ -36,20 +36,6 @@
 
 namespace hb {
 
-#ifdef HB_PROFILE
-__device__ __forceinline__ unsigned long long gtimer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define HB_STAMP(i)                                                         \
-  do {                                                                      \
-    if (blockIdx.x == 0 && threadIdx.x == 0)                                \
-      reinterpret_cast<unsigned long long*>(p.status)[1 + (i)] = gtimer();  \
-  } while (0)
-#else
-#define HB_STAMP(i) ((void)0)
-#endif
 
 constexpr int kBLMaxSeg = 4;
 
@@ -157,7 +143,6 @@ __global__ void __launch_bounds__(BLCfg<WPL, MT, RT, GU>::kThreads,
   const int t0 = (int)(((long long)blockIdx.x * p.ntiles) / G);
   const int t1 = (int)(((long long)(blockIdx.x + 1) * p.ntiles) / G);
 
-  HB_STAMP(0);
   if (lane == 0) {
     for (int s = 0; s < S; ++s) mbar_init(&mybar[s], 1);
     fence_mbar_init();
@@ -222,10 +207,8 @@ __global__ void __launch_bounds__(BLCfg<WPL, MT, RT, GU>::kThreads,
   if (gamma)
     for (int i = tid * 32; i < K; i += kThreads * 32)
       asm volatile("prefetch.global.L1 [%0];" ::"l"(gamma + i));
-  HB_STAMP(1);
   pdl_trigger();
   pdl_wait();  // activations (and residuals) come from the previous kernel
-  HB_STAMP(2);
 
   const int nchunks = (words + 32 * WPL - 1) / (32 * WPL);
   const int nvec = K >> 2;
@@ -280,7 +263,6 @@ __global__ void __launch_bounds__(BLCfg<WPL, MT, RT, GU>::kThreads,
           amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
         }
       }
-      HB_STAMP(3);
       // non-negative floats order like their bit patterns: one redux per warp
       const uint32_t wmax = __reduce_max_sync(0xffffffffu, __float_as_uint(amax));
       if (lane == 0) red_u32[mt * 16 + warp] = wmax;
@@ -294,7 +276,6 @@ __global__ void __launch_bounds__(BLCfg<WPL, MT, RT, GU>::kThreads,
         }
         amax = __uint_as_float(mx);
       }
-      HB_STAMP(4);
       const float d = __fdiv_rn(amax, 127.0f);
       const float inv = amax == 0.f ? 0.f : __fdiv_rn(127.0f, amax);
       int sumq = 0;
@@ -321,7 +302,6 @@ __global__ void __launch_bounds__(BLCfg<WPL, MT, RT, GU>::kThreads,
       }
     }
     __syncthreads();
-    HB_STAMP(5);
 
     // ---- streaming main loop (per warp) --------------------------------------
     // Token groups after the first stream the weights again (from L2 by then).
@@ -349,7 +329,6 @@ __global__ void __launch_bounds__(BLCfg<WPL, MT, RT, GU>::kThreads,
       int seg, row, nr;
       tile_at(t, seg, row, nr);
       mbar_wait(&mybar[stage], parity, p.status);
-      HB_STAMP(6);
       const uint32_t* ws = reinterpret_cast<const uint32_t*>(wstage + (size_t)stage * stage_bytes);
 
       // Rows beyond `nr` of a partial tile are computed on whatever the stage
@@ -402,7 +381,6 @@ __global__ void __launch_bounds__(BLCfg<WPL, MT, RT, GU>::kThreads,
         }
       }
       __syncwarp();  // every lane has finished reading this stage
-      HB_STAMP(7);
       if (tprod < t1) produce();  // refill it with the warp's tile S ahead
 
       // ---- reduce and store ---------------------------------------------------
@@ -440,7 +418,6 @@ __global__ void __launch_bounds__(BLCfg<WPL, MT, RT, GU>::kThreads,
       ++consumed;
     }
   }
-  HB_STAMP(8);
 }
 
 // ---- host side ------------------------------------------------------------------

@@ -178,38 +178,7 @@ __global__ void __launch_bounds__(256) quant_act_kernel(const __grid_constant__ 
   }
 }
 
-#ifdef HB_PROFILE
-__device__ int g_mma_dbg = 0;  // bit0: skip MMAs, bit1: skip expansion stores, bit2: skip B copies
-extern "C" __attribute__((visibility("default"))) void hb200_prof_set_mma_dbg(int v) {
-  cudaMemcpyToSymbol(g_mma_dbg, &v, sizeof(int));
-}
-__device__ __forceinline__ unsigned long long gtimer2() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define MMA_STAMP(i, cond)                                                    \
-  do {                                                                        \
-    if (blockIdx.x == 0 && (cond))                                            \
-      reinterpret_cast<unsigned long long*>(p.status)[1 + (i)] = gtimer2();   \
-  } while (0)
-#define MMA_DBG(bit) ((g_mma_dbg >> (bit)) & 1)
-// fine-grained stamps go to the 512 bytes after d[] and sumq[] in the context scratch
-#define MMA_FINE(i, cond)                                                              \
-  do {                                                                                 \
-    if (blockIdx.x == 0 && (cond))                                                     \
-      reinterpret_cast<unsigned long long*>(const_cast<float*>(p.d))[64 + (i)] = gtimer2(); \
-  } while (0)
-extern "C" __attribute__((visibility("default"))) void hb200_prof_read_fine(hb200_ctx* ctx,
-                                                                            unsigned long long* out) {
-  cudaDeviceSynchronize();
-  cudaMemcpy(out, (char*)ctx->d_scratch + 512, 512, cudaMemcpyDeviceToHost);
-}
-#else
-#define MMA_FINE(i, cond) ((void)0)
-#define MMA_STAMP(i, cond) ((void)0)
 #define MMA_DBG(bit) 0
-#endif
 
 // ---- tcgen05 helpers --------------------------------------------------------------------
 
@@ -260,7 +229,6 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
   const int seg_N = p.seg[seg].N;
   const int row0 = (tile - p.seg[seg].tile0) * kMmaRows;
   const int nrows = min(kMmaRows, seg_N - row0);
-  MMA_STAMP(0, tid == 0);
 
   if (tid == 0) {
     for (int i = 0; i < kPkStages; ++i) {
@@ -301,7 +269,6 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
     cnext = min(kPkStages, nchunks);
     pdl_trigger();
     pdl_wait();  // the quantised activations come from the kernel before this one
-    MMA_STAMP(1, lane == 0);
     for (int s = 0; s < nsteps; ++s) {
       const int st = s % kStages;
       if (s >= kStages)  // the MMAs that read this stage kStages steps ago must have retired
@@ -342,7 +309,6 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
     for (int s = which; s < nsteps; s += 2) {
       const int st = s % kStages;
       ok = tc_wait(ok, &full[st], (uint32_t)((s / kStages) & 1), p.status);
-      if (s < 10) MMA_FINE(2 * s, lane == 0);
       if (lane == 0) {
         tc_after_sync();
         const uint32_t a_t = tmem + kAccCols + (uint32_t)st * (kStepGroups * kAGroupCols);
@@ -360,9 +326,7 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
         tc_commit(&mma_done[st]);  // arrives once these (and all earlier) MMAs have retired
       }
       __syncwarp();
-      if (s < 10) MMA_FINE(2 * s + 1, lane == 0);
     }
-    MMA_STAMP(3, lane == 0);
     if (lane == 0) tc_commit(done);
   } else {
     // ================= expander warps ========================================================
@@ -371,7 +335,6 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
     const int q = warp & 3, h = warp >> 2;
     const int erow = q * 32 + lane;
     const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16) + kAccCols + 16u * h;
-    MMA_STAMP(5, tid == 0);
     for (int s = 0; s < nsteps; ++s) {
       const int st = s % kStages;
       if (s >= kStages) {
@@ -379,7 +342,6 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
         tc_after_sync();
       }
       const int ng = min(kStepGroups, ngroups - s * kStepGroups);
-      if (s < 10) MMA_FINE(20 + 2 * s, tid == 0);
 #pragma unroll
       for (int gg = 0; gg < kStepGroups; ++gg) {
         if (gg >= ng) break;
@@ -423,9 +385,7 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
       if (lane == 0)
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full[st]))
                      : "memory");
-      if (s < 10) MMA_FINE(21 + 2 * s, tid == 0);
     }
-    MMA_STAMP(7, tid == 0);
     pdl_wait();  // d and sum(q) come from the quantiser
     if (tid < kMmaTokens) {
       sd[tid] = p.d[tid];
@@ -435,7 +395,6 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
   ok = tc_wait(true, done, 0, p.status) && ok;
   tc_after_sync();
   __syncthreads();  // sd / ssum visible; every warp past its loop
-  MMA_STAMP(4, tid == 0);
 
   // ---- epilogue: TMEM lane = weight row, column = token; warps w and w+4 share lanes ------
   const int q = warp & 3, half = warp >> 2;  // lane quarter, token half (expander warps only)
@@ -474,7 +433,6 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
     }
   }
-  MMA_STAMP(13, tid == 0);
 
   // ---- split-K: publish the int32 partial, the last split of the tile to arrive adds them ---
   // Integer addition commutes, so the result is bit-identical to the unsplit product.
@@ -541,9 +499,7 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
           yp[(size_t)t * seg_N] = y;
         }
     }
-    MMA_STAMP(14, tid == 0);
   }
-  MMA_STAMP(8, tid == 0);
   tc_before_sync();
   __syncthreads();
   if (warp == kMmaWarp)

@@ -28,20 +28,6 @@
 
 namespace hb {
 
-#ifdef HB_PROFILE
-__device__ __forceinline__ unsigned long long kq_gtimer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define HB_STAMP(i)                                                           \
-  do {                                                                        \
-    if (blockIdx.x == 0 && threadIdx.x == 0)                                  \
-      reinterpret_cast<unsigned long long*>(p.status)[1 + (i)] = kq_gtimer(); \
-  } while (0)
-#else
-#define HB_STAMP(i) ((void)0)
-#endif
 
 constexpr int kKQMaxSeg = 4;
 constexpr int kKQBatchedFrom = 16;  // tokens from which the tensor-core path takes over
@@ -232,7 +218,6 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
   const int t0 = (int)(((long long)blockIdx.x * p.ntiles) / G);
   const int t1 = (int)(((long long)(blockIdx.x + 1) * p.ntiles) / G);
 
-  HB_STAMP(0);
   if (lane == 0) {
     for (int s = 0; s < S; ++s)
       if (slot_of(s) < p.nslots) mbar_init(&bars[slot_of(s)], 1);
@@ -293,10 +278,8 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
     hgm[j] = (held && gamma && i < nvec) ? __ldg(reinterpret_cast<const float4*>(gamma) + i)
                                          : make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  HB_STAMP(1);
   pdl_trigger();
   pdl_wait();
-  HB_STAMP(2);
 
   const Q4KSel sel_main = q4k_sel(lane & 3);  // in whole passes a lane's chunk index is lane & 3
   const int npass = nchunk >> 5;   // whole passes: lane l owns chunk pass*32 + l
@@ -464,7 +447,6 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
       }
     }
     __syncthreads();
-    HB_STAMP(3);
 
     if (m > 0) {  // later tokens stream the weights again (from L2)
       tprod = t0 + warp;
@@ -478,7 +460,6 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
       int seg, row, nr;
       tile_at(t, seg, row, nr);
       mbar_wait(&bars[sslot], parity, p.status);
-      HB_STAMP(4 + 2 * (consumed & 1));
       const uint8_t* ws = wstage + (size_t)sslot * stage_bytes;
 
       float acc[kNS];
@@ -531,7 +512,6 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
         for (int rr = 0; rr < kRows; ++rr) acc[rr] += (r == rr) ? v : 0.f;
       }
       __syncwarp();
-      HB_STAMP(5 + 2 * (consumed & 1));
       if (tprod < t1) produce();
 
       // ---- reduce and store -----------------------------------------------------
@@ -559,7 +539,6 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
       ++consumed;
     }
   }
-  HB_STAMP(8);
 }
 
 // ---- batched path: dequantise to f16, then the 16-bit tensor-core product ---------------

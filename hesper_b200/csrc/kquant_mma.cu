@@ -72,18 +72,6 @@ struct QmParams {
   uint32_t* status;
 };
 
-#ifdef HB_PROFILE
-#define QM_STAMP(i, cond)                                                                 \
-  do {                                                                                    \
-    if (blockIdx.x == 0 && (cond)) {                                                      \
-      unsigned long long t_;                                                              \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
-      reinterpret_cast<unsigned long long*>(p.status)[1 + (i)] = t_;                      \
-    }                                                                                     \
-  } while (0)
-#else
-#define QM_STAMP(i, cond) ((void)0)
-#endif
 
 // 0.5*g*(1+tanh(sqrt(2/pi)*(g+0.044715 g^3))), the gate factor of the GeGLU
 // (Hesper/Layers/FusedFFNSpec.lean:42-45), same expression as the standalone kernel
@@ -195,7 +183,6 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
     for (int s = which; s < nsteps && which < Cfg::kIssuers; s += Cfg::kIssuers) {
       const int st = s % kQmStages;
       ok = tc_wait(ok, &full[st], (uint32_t)((s / kQmStages) & 1), p.status);
-      if (s >= 8 && s < 12) QM_STAMP(12 + 2 * (s - 8), lane == 0);
       if (lane == 0) {
         tc_after_sync();
         const uint32_t a_t = tmem + kQmA0 + (uint32_t)st * kQmACols;
@@ -208,7 +195,6 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
         tc_commit(&mma_done[st]);
       }
       __syncwarp();
-      if (s >= 8 && s < 12) QM_STAMP(13 + 2 * (s - 8), lane == 0);
     }
     if (lane == 0) tc_commit(done);
   } else {
@@ -228,7 +214,6 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
       }
       // super-block of this row: f16 d, f16 dmin, 12 bytes of 6-bit scales and mins, 128 bytes
       // of nibbles (Hesper/Quantization/Q4_K_M.lean:13-52,120-144)
-      if (s >= 8 && s < 11) QM_STAMP(4 * (s - 8), tid == 0);
       const uint8_t* blk = pk + (size_t)(box % kQmPkStages) * kQmPkBytes + (size_t)erow * 144;
       const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
       const uint4 qa = *reinterpret_cast<const uint4*>(blk + 16 + 32 * c);
@@ -260,7 +245,6 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
                                      fmaf(ds1, (float)(w >> 28), dm1));
       }
       const uint32_t taddr = lane_addr + (uint32_t)st * kQmACols;
-      if (s >= 8 && s < 11) QM_STAMP(4 * (s - 8) + 1, tid == 0);
       HB_TMEM_ST32(taddr, o);
       if (s & 1) {  // second half of the super-block: this warp is done with the box
         __syncwarp();
@@ -270,13 +254,11 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
                        : "memory");
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      if (s >= 8 && s < 11) QM_STAMP(4 * (s - 8) + 2, tid == 0);
       tc_before_sync();
       __syncwarp();
       if (lane == 0)
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full[st]))
                      : "memory");
-      if (s >= 8 && s < 11) QM_STAMP(4 * (s - 8) + 3, tid == 0);
     }
   }
   ok = tc_wait(true, done, 0, p.status) && ok;

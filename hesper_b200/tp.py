@@ -29,7 +29,8 @@ Q4K = formats.Q4K_BLOCK_BYTES
 
 @dataclasses.dataclass
 class GemmaShape:
-    """BASELINE config 4: Gemma-4-E4B-shaped (Hesper/Models/Gemma4/Config.lean:19-45, simplified)."""
+    """Gemma-4-E4B-shaped benchmark model (Hesper/Models/Gemma4/Config.lean:19-45, simplified:
+    one head size, 5 sliding-window layers per global layer, plain Q4_K layers)."""
     n_layers: int = 42
     hidden: int = 2560
     n_heads: int = 8
@@ -93,8 +94,8 @@ def shard_cols(blocks: np.ndarray, N: int, K: int, cols: range) -> np.ndarray:
 
 
 def random_gemma_weights(shape: GemmaShape, seed: int = 0x1337C0DE):
-    """Full (unsharded) random-init weights in GGUF Q4_K block form, numpy, per BASELINE config 1's
-    distributions; bf16 embedding ~ N(0, 0.02)."""
+    """Full (unsharded) random-init weights in GGUF Q4_K block form, numpy, with d in U(1e-3, 1e-2), dmin in U(0, 1e-2),
+    uniform 6-bit scales / mins and 4-bit quants; bf16 embedding ~ N(0, 0.02)."""
     rng = np.random.default_rng(seed)
     qd, kvd = shape.n_heads * shape.head_dim, shape.n_kv_heads * shape.head_dim
     layers = []
@@ -137,7 +138,7 @@ def shard_weights(shape: GemmaShape, w: dict, p: ShardPlan) -> dict:
 
 
 def random_q4k_device(n_blocks: int, gen: torch.Generator, device="cuda") -> torch.Tensor:
-    """Random Q4_K blocks generated on the GPU (benchmarks): d, dmin in the BASELINE ranges as
+    """Random Q4_K blocks generated on the GPU (benchmarks): d in U(1e-3, 1e-2), dmin in U(0, 1e-2) as
     f16, every other byte uniform (all bit patterns of scales and quants are valid)."""
     b = torch.randint(0, 256, (n_blocks, Q4K), dtype=torch.uint8, device=device, generator=gen)
     d = torch.empty(n_blocks, device=device).uniform_(1e-3, 1e-2, generator=gen).half()
@@ -148,28 +149,47 @@ def random_q4k_device(n_blocks: int, gen: torch.Generator, device="cuda") -> tor
 
 
 def random_gemma_shard_device(shape: GemmaShape, p: ShardPlan, seed: int = 7, device="cuda") -> dict:
-    """This rank's shard of a random-init model, generated directly on its GPU (the full model
-    is never materialised): for benchmarks, not for parity."""
-    g = torch.Generator(device=device).manual_seed(seed + 1000 * p.rank)
-    gshared = torch.Generator(device=device).manual_seed(seed)  # replicated tensors
+    """This rank's shard of a random-init model, generated on its GPU.  Every tensor is drawn
+    whole from its own seed (the same on every rank) and the rank keeps its slice, so the
+    shards of any TP size are slices of ONE model and the tokens of different TP sizes can be
+    compared.  One full tensor is alive at a time (the largest, the LM head, is 377 MB)."""
     D, Hd = shape.head_dim, shape.hidden
-    bpr = Hd // 256
+    qd, kvd = shape.n_heads * D, shape.n_kv_heads * D
+    qrows = slice(p.q_heads.start * D, p.q_heads.stop * D)
+    kvrows = slice(p.kv_heads.start * D, p.kv_heads.stop * D)
+    frows = slice(p.ffn_rows.start, p.ffn_rows.stop)
+    counter = [0]
+
+    def gen():
+        counter[0] += 1
+        return torch.Generator(device=device).manual_seed(seed * 100003 + counter[0])
+
+    def full(N, K):
+        return random_q4k_device(N * (K // 256), gen(), device).view(N, K // 256, Q4K)
+
+    def rows(N, K, sl):
+        return full(N, K)[sl].contiguous().reshape(-1)
+
+    def cols(N, K, sl):  # input columns, in super-blocks of 256
+        return full(N, K)[:, sl.start // 256:sl.stop // 256].contiguous().reshape(-1)
+
     layers = []
     for _ in range(shape.n_layers):
-        S = {n: 1.0 + 0.05 * torch.randn(Hd, device=device, generator=gshared)
+        S = {n: 1.0 + 0.05 * torch.randn(Hd, device=device, generator=gen())
              for n in ("attn_norm", "post_attn_norm", "ffn_norm", "post_ffn_norm")}
-        S["wq"] = random_q4k_device(p.local_q * D * bpr, g, device)
-        S["wk"] = random_q4k_device(p.local_kv * D * bpr, g, device)
-        S["wv"] = random_q4k_device(p.local_kv * D * bpr, g, device)
-        S["wo"] = random_q4k_device(Hd * (p.local_q * D // 256), g, device)
-        S["wgate"] = random_q4k_device(len(p.ffn_rows) * bpr, g, device)
-        S["wup"] = random_q4k_device(len(p.ffn_rows) * bpr, g, device)
-        S["wdown"] = random_q4k_device(Hd * (len(p.ffn_rows) // 256), g, device)
+        S["wq"] = rows(qd, Hd, qrows)
+        S["wk"] = rows(kvd, Hd, kvrows)
+        S["wv"] = rows(kvd, Hd, kvrows)
+        S["wo"] = cols(Hd, qd, qrows)
+        S["wgate"] = rows(shape.ffn, Hd, frows)
+        S["wup"] = rows(shape.ffn, Hd, frows)
+        S["wdown"] = cols(Hd, shape.ffn, frows)
         layers.append(S)
-    emb = (0.02 * torch.randn(shape.vocab, Hd, device=device, generator=gshared)).to(torch.bfloat16)
-    return {"layers": layers, "embed": emb.view(torch.int16),
-            "final_norm": 1.0 + 0.05 * torch.randn(Hd, device=device, generator=gshared),
-            "lm_head": random_q4k_device(len(p.vocab_rows) * bpr, g, device)}
+    emb = (0.02 * torch.randn(shape.vocab, Hd, device=device, generator=gen())).to(torch.bfloat16)
+    final_norm = 1.0 + 0.05 * torch.randn(Hd, device=device, generator=gen())
+    lm_head = rows(shape.vocab, Hd, slice(p.vocab_rows.start, p.vocab_rows.stop))
+    return {"layers": layers, "embed": emb.view(torch.int16), "final_norm": final_norm,
+            "lm_head": lm_head}
 
 
 class TensorParallel:

@@ -477,12 +477,13 @@ int hb200_tp_allreduce_rmsnorm(hb200_tp *tp, hb200_ctx *ctx, float *d_x, const f
  * never joined shows up here or as an error of the next collective, not as a GPU fault. */
 int hb200_tp_check(hb200_tp *tp);
 
-/* ---- Gemma-4-E4B-shaped tensor-parallel decode loop (BASELINE config 4) ----------------- */
+/* ---- Gemma-4-E4B-shaped tensor-parallel decode loop ----------------------------------
+ * (benchmark shape: 42 layers, hidden 2560, 8/2 heads of 256, GeGLU FFN 10240, vocab 262144) */
 
 /* Global shape plus this rank's share.  Layer l is a global-attention layer when
  * (l+1) % global_every == 0, else a sliding-window layer whose cache is a ring of `window`
- * slots.  Shape source: Hesper/Models/Gemma4/Config.lean:19-45, simplified as BASELINE.json
- * config 4 states it (no per-layer embeddings, MoE, towers or per-head q/k norms). */
+ * slots.  Shape source: Hesper/Models/Gemma4/Config.lean:19-45, simplified to one head size
+ * and plain layers (no per-layer embeddings, MoE, towers or per-head q/k norms). */
 typedef struct hb200_gemma_config {
   int n_layers, hidden, head_dim, vocab, max_seq, window, global_every;
   int local_q_heads, local_kv_heads, local_ffn, local_vocab, vocab_offset;

@@ -105,7 +105,7 @@ def test_sliding_window_and_ragged(ctx, oracle, window):
 
 
 def test_long_context_properties(ctx):
-    """BASELINE-size call (L = 32768, batch 4) checked through size-independent properties:
+    """Benchmark-size call (L = 32768, batch 4) checked through size-independent properties:
     constant V rows give that constant back; doubling every score's scale-invariant part
     (all keys equal) gives the mean of V; and the call is deterministic."""
     B, H, Hkv, D, L = 4, 8, 2, 256, 32768

@@ -127,7 +127,7 @@ def test_chunked_prefill_equals_stepwise(ctx, batch, plen):
 
 
 def test_full_size_bitnet2b_forced_64_steps(ctx, oracle):
-    """BASELINE config 3 shape (30 layers, hidden 2560, 20/5 heads, FFN 6912, vocab 128256),
+    """BitNet-b1.58-2B shape (30 layers, hidden 2560, 20/5 heads, FFN 6912, vocab 128256),
     short prompt, 64 teacher-forced greedy steps against the CPU oracle."""
     shape = BitNetShape.bitnet_2b(max_seq=128)
     w = random_bitnet_weights(shape, seed=4)

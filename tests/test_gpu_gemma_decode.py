@@ -64,7 +64,7 @@ def test_generate_graph_equals_eager(ctx):
 
 def test_tp2_matches_oracle_when_two_gpus():
     if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs (run with gpurun --gpus 2)")
+        pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
                         "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port",
