@@ -109,6 +109,8 @@ SIGNATURES = {
     "hb200_tp_allreduce_f32": (_i, [_vp, _vp, _sz, _vp]),
     "hb200_tp_allreduce_max_u64": (_i, [_vp, _vp, _sz, _vp]),
     "hb200_tp_check": (_i, [_vp]),
+    "hb200_tp_set_timeout_ms": (_i, [_vp, _i]),
+    "hb200_tp_align": (_i, [_vp, _vp]),
     "hb200_tp_allreduce_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _i, _i, _vp, _vp]),
     "hb200_tp_peer_handle_bytes": (_sz, []),
     "hb200_tp_peer_export": (_i, [_vp, _vp]),

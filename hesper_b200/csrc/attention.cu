@@ -766,7 +766,7 @@ static int attn_run(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d
   HB_REQUIRE(B >= 1 && H >= 1 && Hkv >= 1 && H % Hkv == 0, "attn: B=%d H=%d Hkv=%d", B, H, Hkv);
   const int G = H / Hkv;
   HB_REQUIRE(G <= 8, "attn: %d query heads per KV head (at most 8)", G);
-  HB_REQUIRE(D == 64 || D == 128 || D == 256, "attn: head_dim %d not in {64,128,256}", D);
+  HB_REQUIRE(D == 32 || D == 64 || D == 128 || D == 256, "attn: head_dim %d not in {32,64,128,256}", D);
   HB_REQUIRE(max_seq >= 1 && window >= 0, "attn: max_seq=%d window=%d", max_seq, window);
   HB_REQUIRE(((reinterpret_cast<uintptr_t>(d_k) | reinterpret_cast<uintptr_t>(d_v)) & 15) == 0,
              "attn: K/V cache must be 16-byte aligned");
@@ -786,7 +786,7 @@ static int attn_run(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d
   p.T = T;
   p.scale_log2 = scale * 1.4426950408889634f;
   const int eff_len = (window > 0 && window < max_seq) ? window : max_seq;
-  p.nsplit = attn_pick_splits(ctx, B, Hkv, D, eff_len);
+  p.nsplit = D == 32 ? 1 : attn_pick_splits(ctx, B, Hkv, D, eff_len);
   // Small grids (the latency-bound case) merge their splits inside a thread-block cluster of
   // at most 16 splits.
   // Beyond 16 splits the cluster would have to shorten the split list; that still wins while a
@@ -813,9 +813,12 @@ static int attn_run(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d
     p.tickets = (B * Hkv <= hb::kCtxTickets) ? ctx->d_tickets : nullptr;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (ctx->attn_mode == HB200_ATTN_EXACT) {
+  // head_dim 32 (the reference's smallest golden case, a debugging size) is below the MMA
+  // kernel's tile: it always takes the one-warp-per-head kernel
+  if (ctx->attn_mode == HB200_ATTN_EXACT || D == 32) {
     const dim3 grid(B * H);
     switch (D) {
+      case 32: HB_CUDA(launch_pdl(attn_exact_kernel<32>, grid, dim3(32), 0, st, ctx->pdl, p)); break;
       case 64: HB_CUDA(launch_pdl(attn_exact_kernel<64>, grid, dim3(32), 0, st, ctx->pdl, p)); break;
       case 128: HB_CUDA(launch_pdl(attn_exact_kernel<128>, grid, dim3(32), 0, st, ctx->pdl, p)); break;
       default: HB_CUDA(launch_pdl(attn_exact_kernel<256>, grid, dim3(32), 0, st, ctx->pdl, p)); break;

@@ -363,6 +363,10 @@ extern "C" int hb200_gemma_generate(hb200_gemma* m, const int32_t* h_prompt, int
   } else {
     HB_CUDA(cudaMemsetAsync(m->log_index, 0, sizeof(int32_t), st));
   }
+  // the ranks reach this point after host work of different length; the exchanges that
+  // follow wait with a deadline, so meet here first
+  rc = hb200_tp_align(m->tp, st);
+  if (rc) { cleanup(); return rc; }
   cudaEventRecord(e0, st);
   for (int p = 0; p < prompt_len; ++p) {
     rc = gemma_enqueue_step(m, d_prompt + (size_t)p * B, p == prompt_len - 1, st);
@@ -381,6 +385,8 @@ extern "C" int hb200_gemma_generate(hb200_gemma* m, const int32_t* h_prompt, int
       }
       if (e == cudaSuccess) e = cudaGraphInstantiate(&exec, graph, 0);
       if (e != cudaSuccess) { cleanup(); return cuda_fail(e, "decode graph capture"); }
+      rc = hb200_tp_align(m->tp, st);  // capture and instantiation take different time per rank
+      if (rc) { cleanup(); return rc; }
       cudaEventRecord(e1, st);
       for (int s = 0; s < steps; ++s) {
         e = cudaGraphLaunch(exec, st);

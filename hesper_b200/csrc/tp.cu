@@ -109,7 +109,25 @@ constexpr int kPeerLLMaxTokens = 256;
 constexpr size_t kPeerLLSlotBytes = (size_t)2560 * kPeerLLMaxTokens * 8;  // 5 MB per (epoch, rank)
 constexpr size_t kPeerBufBytes = kPeerLLBase + 2 * kPeerMaxRanks * kPeerLLSlotBytes;
 
+// Bounded waits: a poll loop looks at the nanosecond timer every 256 polls and gives up
+// `timeout_ns` after it started (default one second, hb200_tp_set_timeout_ms changes it).
+__device__ __forceinline__ unsigned long long tp_now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+struct Deadline {
+  unsigned long long end;
+  uint32_t polls;
+  __device__ __forceinline__ explicit Deadline(unsigned long long timeout_ns)
+      : end(tp_now_ns() + timeout_ns), polls(0) {}
+  __device__ __forceinline__ bool expired() {
+    return ((++polls & 255u) == 0u) && tp_now_ns() > end;
+  }
+};
+
 struct PeerParams {
+  unsigned long long timeout_ns;
   unsigned char* buf[kPeerMaxRanks];  // every rank's exchange buffer (own one included)
   void* io;                           // local vector, reduced in place
   size_t n;                           // elements
@@ -164,14 +182,16 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const __grid_consta
     const uint32_t* f = reinterpret_cast<const uint32_t*>(p.buf[p.rank] + flag_base) +
                         (((size_t)epoch * kPeerMaxRanks + tid) * kPeerMaxCtas + cta) * kPeerFlagStride;
     bool got = false;
-    const uint32_t lim =
-        (*reinterpret_cast<volatile uint32_t*>(p.status) & kStatusMbarTimeout) ? 1u : (1u << 21);
+    // once a wait has run out the context is in error: later exchanges look once and go on
+    const bool dead = (*reinterpret_cast<volatile uint32_t*>(p.status) & kStatusMbarTimeout) != 0;
+    Deadline dl(p.timeout_ns);
 #pragma unroll 1
-    for (uint32_t it = 0; it < lim; ++it) {  // about a second at worst, once per context
+    for (;;) {
       if (ld_acquire_sys(f) == seq) {
         got = true;
         break;
       }
+      if (dead || dl.expired()) break;
     }
     if (!got) {
       s_ok = 0;
@@ -217,6 +237,8 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const __grid_consta
 // (bit-identical to the plain all-reduce) and writes y = add + RMSNorm(sum) * gamma with the
 // arithmetic of the stand-alone RMSNorm kernel (f64 sum of squares in the same order).
 struct PeerNormParams {
+  unsigned long long timeout_ns;
+  int tok_per_rank;  // two-shot exchange: tokens [r*tok_per_rank, (r+1)*tok_per_rank) belong to rank r
   unsigned char* buf[kPeerMaxRanks];
   const float* x;      // [M][K] this rank's partial sums
   const float* gamma;  // [K]
@@ -280,14 +302,15 @@ __global__ void __launch_bounds__(256) peer_allreduce_rmsnorm_kernel(
     const uint32_t* g = reinterpret_cast<const uint32_t*>(p.buf[p.rank] + flag_base) +
                         (((size_t)epoch * kPeerMaxRanks + tid) * kPeerMaxCtas + m) * kPeerFlagStride;
     bool got = false;
-    const uint32_t lim =
-        (*reinterpret_cast<volatile uint32_t*>(p.status) & kStatusMbarTimeout) ? 1u : (1u << 21);
+    const bool dead = (*reinterpret_cast<volatile uint32_t*>(p.status) & kStatusMbarTimeout) != 0;
+    Deadline dl(p.timeout_ns);
 #pragma unroll 1
-    for (uint32_t it = 0; it < lim; ++it) {
+    for (;;) {
       if (ld_acquire_sys(g) == seq) {
         got = true;
         break;
       }
+      if (dead || dl.expired()) break;
     }
     if (!got) {
       s_ok = 0;
@@ -456,6 +479,7 @@ __global__ void __launch_bounds__(256) peer_allreduce_rmsnorm_ll_kernel(
   // once a wait has run out the context is in error: later exchanges do not wait again, so a
   // broken run ends in seconds instead of a second per exchange
   bool ok = (*reinterpret_cast<volatile uint32_t*>(p.status) & kStatusMbarTimeout) == 0;
+  Deadline dl(p.timeout_ns);
   for (int r = 0; r < W; ++r) {
     const unsigned char* src = p.buf[p.rank] + kPeerLLBase +
                                ((size_t)epoch * kPeerMaxRanks + r) * kPeerLLSlotBytes + row_off;
@@ -470,11 +494,13 @@ __global__ void __launch_bounds__(256) peer_allreduce_rmsnorm_ll_kernel(
         for (int e = 0; e < 2; ++e) {
           bool got = false;
 #pragma unroll 1
-          for (uint32_t it = 0; ok && it < (1u << 21); ++it)
+          while (ok) {
             if (ld_pairs_sys(q + 16 * e, seq, &tv[2 * e], &tv[2 * e + 1])) {
               got = true;
               break;
             }
+            if (dl.expired()) break;
+          }
           ok = ok && got;
         }
       }
@@ -535,6 +561,175 @@ __global__ void __launch_bounds__(256) peer_allreduce_rmsnorm_ll_kernel(
   }
 }
 
+// The two-shot form of the same exchange for larger batches (reduce-scatter, then all-gather,
+// by TOKEN): rank r owns tokens [r*T, (r+1)*T).  The CTA of a token pushes this rank's partial
+// row to the owner only; the owner adds the W rows in rank order, applies the RMSNorm
+// (+ residual) -- it holds the whole row -- and pushes the finished row to every peer, whose CTA
+// of that token copies it out.  Per rank and exchange 2*n*(W-1)/W values cross NVLink instead
+// of the one-shot's n*(W-1), and every rank holds the owner's bits.  Same slots, sequence
+// numbers and flag-in-data words as the one-shot kernel: in a rank's buffer the rows it owns
+// receive partials (slot of the sender), the other rows receive results (slot of the owner).
+__global__ void __launch_bounds__(256) peer_allreduce_rmsnorm_ll2_kernel(
+    const __grid_constant__ PeerNormParams p) {
+  __shared__ double red[8];
+  __shared__ int s_bad;
+  pdl_trigger();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, m = blockIdx.x, W = p.nranks;
+  const int K = p.K, nvec = K >> 2;
+  const int owner = m / p.tok_per_rank;
+  constexpr int kH = 3;
+  float4 g4[kH];
+#pragma unroll
+  for (int j = 0; j < kH; ++j) {
+    const int v = tid + j * 256;
+    g4[j] = (owner == p.rank && v < nvec) ? __ldg(reinterpret_cast<const float4*>(p.gamma) + v)
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (tid == 0) s_bad = 0;
+  pdl_wait();
+  const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(p.seq) + 1u;
+  const int epoch = (int)(seq & 1u);
+  const size_t row_off = (size_t)m * K * 8;
+  auto slot = [&](int in_rank, int from_rank) {
+    return p.buf[in_rank] + kPeerLLBase +
+           ((size_t)epoch * kPeerMaxRanks + from_rank) * kPeerLLSlotBytes + row_off;
+  };
+  bool ok = (*reinterpret_cast<volatile uint32_t*>(p.status) & kStatusMbarTimeout) == 0;
+  Deadline dl(p.timeout_ns);
+  auto poll = [&](const unsigned char* q, float4& t) {
+    float* tv = reinterpret_cast<float*>(&t);
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      bool got = false;
+#pragma unroll 1
+      while (ok) {
+        if (ld_pairs_sys(q + 16 * e, seq, &tv[2 * e], &tv[2 * e + 1])) {
+          got = true;
+          break;
+        }
+        if (dl.expired()) break;
+      }
+      ok = ok && got;
+    }
+  };
+  float4 x4[kH];
+#pragma unroll
+  for (int j = 0; j < kH; ++j) {
+    const int v = tid + j * 256;
+    x4[j] = v < nvec ? reinterpret_cast<const float4*>(p.x + (size_t)m * K)[v]
+                     : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (owner != p.rank) {
+    // ---- not mine: partial row to the owner, finished row back from it ---------------------
+    unsigned char* dst = slot(owner, p.rank);
+#pragma unroll
+    for (int j = 0; j < kH; ++j) {
+      const int v = tid + j * 256;
+      if (v >= nvec) continue;
+      st_pairs_sys(dst + (size_t)v * 32, x4[j].x, x4[j].y, seq);
+      st_pairs_sys(dst + (size_t)v * 32 + 16, x4[j].z, x4[j].w, seq);
+    }
+    const unsigned char* src = slot(p.rank, owner);
+    float4 y4[kH];
+#pragma unroll
+    for (int j = 0; j < kH; ++j) {
+      const int v = tid + j * 256;
+      y4[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (v < nvec) poll(src + (size_t)v * 32, y4[j]);
+    }
+    if (!ok) {
+      s_bad = 1;
+      atomicOr(p.status, kStatusMbarTimeout);
+    }
+    __syncthreads();
+    if (!s_bad) {
+#pragma unroll
+      for (int j = 0; j < kH; ++j) {
+        const int v = tid + j * 256;
+        if (v < nvec) reinterpret_cast<float4*>(p.y + (size_t)m * K)[v] = y4[j];
+      }
+    }
+  } else {
+    // ---- mine: collect in rank order, normalise, send the row to everybody -----------------
+    float4 a4[kH];
+#pragma unroll
+    for (int j = 0; j < kH; ++j) {
+      const int v = tid + j * 256;
+      a4[j] = (p.add && v < nvec) ? reinterpret_cast<const float4*>(p.add + (size_t)m * K)[v]
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float4 s4[kH];
+    for (int r = 0; r < W; ++r) {
+      const unsigned char* src = slot(p.rank, r);
+#pragma unroll
+      for (int j = 0; j < kH; ++j) {
+        const int v = tid + j * 256;
+        float4 t = x4[j];
+        if (r != p.rank && v < nvec) poll(src + (size_t)v * 32, t);
+        if (r == 0) {
+          s4[j] = t;
+        } else {
+          s4[j].x = __fadd_rn(s4[j].x, t.x);
+          s4[j].y = __fadd_rn(s4[j].y, t.y);
+          s4[j].z = __fadd_rn(s4[j].z, t.z);
+          s4[j].w = __fadd_rn(s4[j].w, t.w);
+        }
+      }
+    }
+    if (!ok) {
+      s_bad = 1;
+      atomicOr(p.status, kStatusMbarTimeout);
+    }
+    double ss = 0.0;
+#pragma unroll
+    for (int j = 0; j < kH; ++j)
+      ss += (double)s4[j].x * s4[j].x + (double)s4[j].y * s4[j].y + (double)s4[j].z * s4[j].z +
+            (double)s4[j].w * s4[j].w;
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    if (!s_bad) {
+      double tot = 0.0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) tot += red[i];
+      const float rinv = (float)(1.0 / sqrt(tot / (double)K + (double)p.eps));
+#pragma unroll
+      for (int j = 0; j < kH; ++j) {
+        const int v = tid + j * 256;
+        if (v >= nvec) continue;
+        float4 o;
+        o.x = __fmul_rn(__fmul_rn(s4[j].x, rinv), g4[j].x);
+        o.y = __fmul_rn(__fmul_rn(s4[j].y, rinv), g4[j].y);
+        o.z = __fmul_rn(__fmul_rn(s4[j].z, rinv), g4[j].z);
+        o.w = __fmul_rn(__fmul_rn(s4[j].w, rinv), g4[j].w);
+        if (p.add) {
+          o.x = __fadd_rn(a4[j].x, o.x);
+          o.y = __fadd_rn(a4[j].y, o.y);
+          o.z = __fadd_rn(a4[j].z, o.z);
+          o.w = __fadd_rn(a4[j].w, o.w);
+        }
+        reinterpret_cast<float4*>(p.y + (size_t)m * K)[v] = o;
+        for (int r = 0; r < W; ++r) {
+          if (r == p.rank) continue;
+          unsigned char* d = slot(r, p.rank) + (size_t)v * 32;
+          st_pairs_sys(d, o.x, o.y, seq);
+          st_pairs_sys(d + 16, o.z, o.w, seq);
+        }
+      }
+    }
+  }
+  // ---- the last CTA to finish advances the sequence number -----------------------------
+  if (tid == 0) {
+    __threadfence();
+    const uint32_t t = atomicAdd(&p.seq[1], 1u);
+    if (t == gridDim.x - 1) {
+      p.seq[1] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(p.seq) = seq;
+    }
+  }
+}
+
 }  // namespace hb
 
 using namespace hb;
@@ -546,15 +741,23 @@ struct hb200_tp {
   unsigned char* peer_buf[kPeerMaxRanks];  // mapped exchange buffers, [rank] is the local one
   bool peer_ready;
   uint32_t* d_seq;   // sequence number and finishing ticket of the peer all-reduce
+  float* d_align;    // one float for hb200_tp_align
+  unsigned long long timeout_ns;  // bound of every device-side wait of the exchange kernels
+  // path selection, read from the environment ONCE at init (same values on every rank: a
+  // rank that chose another path than its peers would wait for stores that never come)
+  int fuse_max;      // HB200_TP_FUSE_MAX: tokens up to which the fused kernels run
+  int two_shot_from; // HB200_TP_TWO_SHOT_FROM: tokens from which the exchange is two-shot
+  bool no_ll;        // HB200_TP_NO_LL: flag-after-data kernel instead of flag-in-data
 };
 
 // In-place reduction of n elements through the peer buffers, or HB200_ERR_UNSUPPORTED when
 // this call does not qualify (not attached, too large, unaligned).
 template <typename T, bool kMax>
 static int peer_allreduce(hb200_tp* tp, T* d_buf, size_t n, cudaStream_t st) {
-  if (!tp->peer_ready || n * sizeof(T) > kPeerSlotBytes ||
-      (reinterpret_cast<uintptr_t>(d_buf) & 15) != 0 || (n * sizeof(T)) % 16 != 0)
-    return HB200_ERR_UNSUPPORTED;
+  if (!tp->peer_ready || n * sizeof(T) > kPeerSlotBytes || (n * sizeof(T)) % 16 != 0)
+    return HB200_ERR_UNSUPPORTED;  // the same answer on every rank: NCCL takes the call
+  HB_REQUIRE((reinterpret_cast<uintptr_t>(d_buf) & 15) == 0,
+             "tp_allreduce: the buffer must be 16-byte aligned");
   PeerParams p = {};
   for (int r = 0; r < tp->nranks; ++r) p.buf[r] = tp->peer_buf[r];
   p.io = d_buf;
@@ -563,6 +766,7 @@ static int peer_allreduce(hb200_tp* tp, T* d_buf, size_t n, cudaStream_t st) {
   p.nranks = tp->nranks;
   p.seq = tp->d_seq;
   p.status = tp->ctx->d_status;
+  p.timeout_ns = tp->timeout_ns;
   // one CTA per 16 KB, the same count on every rank (it depends on n only)
   size_t ctas = (n * sizeof(T) + 16383) / 16384;
   if (ctas > kPeerMaxCtas) ctas = kPeerMaxCtas;
@@ -601,7 +805,40 @@ extern "C" int hb200_tp_init(hb200_ctx* ctx, int rank, int nranks, const unsigne
   tp->rank = rank;
   tp->nranks = nranks;
   tp->ctx = ctx;
+  tp->timeout_ns = 1000000000ull;
+  const char* e = getenv("HB200_TP_FUSE_MAX");
+  tp->fuse_max = e ? atoi(e) : kPeerLLMaxTokens;
+  if (tp->fuse_max < 0) tp->fuse_max = 0;
+  e = getenv("HB200_TP_TWO_SHOT_FROM");
+  tp->two_shot_from = e ? atoi(e) : 33;
+  tp->no_ll = getenv("HB200_TP_NO_LL") != nullptr;
+  cudaError_t ce = cudaMalloc(reinterpret_cast<void**>(&tp->d_align), sizeof(float));
+  if (ce == cudaSuccess) ce = cudaMemset(tp->d_align, 0, sizeof(float));
+  if (ce != cudaSuccess) {
+    if (g_nccl.comm_destroy) g_nccl.comm_destroy(comm);
+    delete tp;
+    return cuda_fail(ce, "tp_init: scratch");
+  }
   *out = tp;
+  return HB200_OK;
+}
+
+extern "C" int hb200_tp_set_timeout_ms(hb200_tp* tp, int ms) {
+  HB_REQUIRE(tp != nullptr && ms >= 1 && ms <= 60000, "tp_set_timeout_ms: %d ms outside 1..60000", ms);
+  tp->timeout_ns = (unsigned long long)ms * 1000000ull;
+  return HB200_OK;
+}
+
+// Brings the ranks together on the host before a run of bounded waits: one NCCL all-reduce
+// of a single float (NCCL's own wait has no deadline, so late ranks are simply waited for),
+// then a stream synchronisation.  Host-side work that differs between ranks -- allocation,
+// prompt upload, graph capture -- would otherwise eat into the first exchange's deadline.
+extern "C" int hb200_tp_align(hb200_tp* tp, hb200_stream stream) {
+  if (!tp || tp->nranks == 1) return HB200_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int r = g_nccl.all_reduce(tp->d_align, tp->d_align, 1, kNcclFloat32, kNcclSum, tp->comm, st);
+  if (r != 0) return nccl_fail(r, "ncclAllReduce(align)");
+  HB_CUDA(cudaStreamSynchronize(st));
   return HB200_OK;
 }
 
@@ -654,6 +891,7 @@ extern "C" int hb200_tp_destroy(hb200_tp* tp) {
       cudaIpcCloseMemHandle(tp->peer_buf[r]);
   }
   if (tp->d_seq) cudaFree(tp->d_seq);
+  if (tp->d_align) cudaFree(tp->d_align);
   if (tp->comm && g_nccl.comm_destroy) g_nccl.comm_destroy(tp->comm);
   delete tp;
   return HB200_OK;
@@ -691,20 +929,17 @@ extern "C" int hb200_tp_allreduce_rmsnorm(hb200_tp* tp, hb200_ctx* ctx, float* d
                                           int M, int K, float* d_y, hb200_stream stream) {
   HB_REQUIRE(ctx && d_x && d_gamma && d_y && M >= 1 && K >= 1, "tp_allreduce_rmsnorm: bad argument");
   if (tp && tp->nranks > 1) {
-    static const int fuse_max = [] {
-      const char* e = getenv("HB200_TP_FUSE_MAX");  // tokens up to which the fused kernels run
-      const int v = e ? atoi(e) : kPeerLLMaxTokens;
-      return v < 0 ? 0 : v;
-    }();
-    static const bool no_ll = getenv("HB200_TP_NO_LL") != nullptr;
-    const bool aligned =
-        ((reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_gamma) |
-          reinterpret_cast<uintptr_t>(d_add) | reinterpret_cast<uintptr_t>(d_y)) & 15) == 0;
-    const bool ll = !no_ll && K <= 3072 && M <= kPeerLLMaxTokens &&
+    // The path is chosen from values that are the same on every rank (M, K, the rank count,
+    // whether the peers are attached, the switches read at init): a rank-local fact such as a
+    // pointer's alignment is an error, never a reason to take another path than the peers.
+    const bool ll = !tp->no_ll && K <= 3072 && M <= kPeerLLMaxTokens &&
                     (size_t)M * K * 8 <= kPeerLLSlotBytes;
     const bool flagged = M <= kPeerMaxCtas && (size_t)M * K * 4 <= kPeerSlotBytes &&
                          (size_t)K * 4 <= 48 * 1024;
-    if (tp->peer_ready && M <= fuse_max && K % 4 == 0 && aligned && (ll || flagged)) {
+    if (tp->peer_ready && M <= tp->fuse_max && K % 4 == 0 && (ll || flagged)) {
+      HB_REQUIRE(((reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_gamma) |
+                   reinterpret_cast<uintptr_t>(d_add) | reinterpret_cast<uintptr_t>(d_y)) & 15) == 0,
+                 "tp_allreduce_rmsnorm: arrays must be 16-byte aligned");
       PeerNormParams p = {};
       for (int r = 0; r < tp->nranks; ++r) p.buf[r] = tp->peer_buf[r];
       p.x = d_x;
@@ -717,7 +952,13 @@ extern "C" int hb200_tp_allreduce_rmsnorm(hb200_tp* tp, hb200_ctx* ctx, float* d
       p.nranks = tp->nranks;
       p.seq = tp->d_seq;
       p.status = ctx->d_status;
-      if (ll)
+      p.timeout_ns = tp->timeout_ns;
+      p.tok_per_rank = (M + tp->nranks - 1) / tp->nranks;
+      const bool two_shot = ll && M >= tp->two_shot_from && M >= tp->nranks;
+      if (two_shot)
+        HB_CUDA(launch_pdl(peer_allreduce_rmsnorm_ll2_kernel, dim3(M), dim3(256), 0,
+                           static_cast<cudaStream_t>(stream), ctx->pdl, p));
+      else if (ll)
         HB_CUDA(launch_pdl(peer_allreduce_rmsnorm_ll_kernel, dim3(M), dim3(256), 0,
                            static_cast<cudaStream_t>(stream), ctx->pdl, p));
       else

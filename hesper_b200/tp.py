@@ -255,6 +255,14 @@ class TensorParallel:
     def check(self):
         check(self.ctx._lib.hb200_tp_check(self._h))
 
+    def set_timeout_ms(self, ms: int):
+        """Bound of the exchange kernels' device-side waits (default one second)."""
+        check(self.ctx._lib.hb200_tp_set_timeout_ms(self._h, int(ms)))
+
+    def align(self, stream=None):
+        """Host-side meeting point of the ranks before a run of bounded waits."""
+        check(self.ctx._lib.hb200_tp_align(self._h, _stream_handle(stream)))
+
     def close(self):
         if getattr(self, "_h", None) is not None and self._h.value:
             self.ctx._lib.hb200_tp_destroy(self._h)

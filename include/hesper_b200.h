@@ -252,7 +252,8 @@ size_t hb200_attn_workspace_bytes(const hb200_ctx *ctx, int B, int H, int Hkv, i
  *   window     0 = full attention; else only the last `window` positions
  *              (rule of flashAttentionSWAKernel, Hesper/WGSL/FlashAttention.lean:1621-1624)
  *   d_out      [B][H][D] f32
- * D in {64, 128, 256}; H/Hkv in {1, 2, 4, 8}. */
+ * D in {64, 128, 256}, plus 32 on a slow one-warp-per-head kernel (the reference's smallest
+ * golden case); H/Hkv in {1, 2, 4, 8}. */
 int hb200_attn_decode(hb200_ctx *ctx, const void *d_q, int q_is_f16, const void *d_k,
                       const void *d_v, const int32_t *d_seqlens, int B, int H, int Hkv,
                       int D, int max_seq, int window, float scale, void *d_workspace,
@@ -465,10 +466,16 @@ int hb200_tp_peer_attach(hb200_tp *tp, const unsigned char *all_handles);
 int hb200_tp_peer_attached(const hb200_tp *tp);
 
 /* The exchange and the RMSNorm that follows it in the decode loop as one operator:
- * y = d_add + RMSNorm(sum over ranks of d_x) * gamma.  With the peer buffers attached
- * (M <= 64) it is ONE kernel: a CTA per token pushes its row, waits for the peers, adds in
- * rank order and normalises; otherwise it is hb200_tp_allreduce_f32 + hb200_rmsnorm (d_x
- * then holds the sum).  tp NULL or one rank: hb200_rmsnorm alone. */
+ * y = d_add + RMSNorm(sum over ranks of d_x) * gamma.  With the peer buffers attached it is
+ * ONE kernel, a CTA per token.  Up to 32 tokens every rank pushes its row to all peers, waits,
+ * adds in rank order and normalises (one shot).  From 33 tokens (and K <= 3072, M <= 256) the
+ * exchange is two-shot by token: a row goes only to the rank that owns the token, which
+ * reduces, normalises and sends the finished row to everybody -- 2(W-1)/W of the payload per
+ * rank instead of W-1 times it.  Otherwise it is hb200_tp_allreduce_f32 + hb200_rmsnorm (d_x
+ * then holds the sum).  tp NULL or one rank: hb200_rmsnorm alone.  The path depends only on
+ * M, K, the rank count and the switches read at hb200_tp_init (HB200_TP_FUSE_MAX,
+ * HB200_TP_TWO_SHOT_FROM, HB200_TP_NO_LL: same values on every rank); arrays that are not
+ * 16-byte aligned are an error, not a reason to take another path than the peers. */
 int hb200_tp_allreduce_rmsnorm(hb200_tp *tp, hb200_ctx *ctx, float *d_x, const float *d_gamma,
                                const float *d_add, float eps, int M, int K, float *d_y,
                                hb200_stream stream);
@@ -476,6 +483,18 @@ int hb200_tp_allreduce_rmsnorm(hb200_tp *tp, hb200_ctx *ctx, float *d_x, const f
 /* Host-side health check of the communicator (ncclCommGetAsyncError): a peer that died or
  * never joined shows up here or as an error of the next collective, not as a GPU fault. */
 int hb200_tp_check(hb200_tp *tp);
+
+/* Bound of every device-side wait of the exchange kernels (default 1000 ms).  A wait that
+ * runs out raises the context's status flag (hb200_ctx_check then returns
+ * HB200_ERR_TIMEOUT), the kernel returns, and later exchanges of that context look once and
+ * go on, so a run with a missing peer ends quickly and the GPU stays usable. */
+int hb200_tp_set_timeout_ms(hb200_tp *tp, int ms);
+
+/* Host-side meeting point of the ranks (one 4-byte NCCL all-reduce, then a stream
+ * synchronisation).  Call it after rank-local host work of unknown length -- allocation,
+ * upload, graph capture -- and before a run of exchanges, whose waits are bounded: the
+ * decode loops do. */
+int hb200_tp_align(hb200_tp *tp, hb200_stream stream);
 
 /* ---- Gemma-4-E4B-shaped tensor-parallel decode loop ----------------------------------
  * (benchmark shape: 42 layers, hidden 2560, 8/2 heads of 256, GeGLU FFN 10240, vocab 262144) */

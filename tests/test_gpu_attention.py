@@ -34,9 +34,6 @@ def _check(out, ref, tol=TOL):
 
 @pytest.mark.parametrize("H,Hkv,D,max_seq,L,seed,window", FLASH_ATTN_CASES)
 def test_reference_lcg_cases(ctx, oracle, H, Hkv, D, max_seq, L, seed, window):
-    if D == 32:
-        pytest.skip("head_dim 32 is below the kernel's minimum of 64 (the reference case "
-                    "is a debugging size)")
     q, s1 = oracle.lcg_fill(seed, H * D)
     k, s2 = oracle.lcg_fill(s1, Hkv * max_seq * D)
     v, _ = oracle.lcg_fill(s2, Hkv * max_seq * D)

@@ -135,3 +135,41 @@ def test_full_size_bitnet2b_forced_64_steps(ctx, oracle):
     mism, devs = _forced_compare(ctx, oracle, shape, w, prompt, 64)
     assert mism == 0
     _check_devs(devs)
+
+
+@pytest.mark.parametrize("mode", ["FAST", "PRECISE"])
+def test_full_size_bitnet2b_other_attention_modes_are_reported(ctx, oracle, mode):
+    """The non-reproducible attention modes on the full-size random-init model, against the f64
+    oracle: a record, not a parity claim.  Random ternary weights with an int8 re-quantiser
+    after every block amplify an attention difference of 1e-6 into logit noise of the order of
+    the logit spread, so these modes flip most greedy tokens of THIS model (measured: FAST
+    43/64, PRECISE 31/64; logit deviation 1.5 to 2.5 standard deviations) while the EXACT mode
+    above flips none.  What is asserted is only that the run is sane (finite logits of the
+    oracle's scale); the counts are printed for the results table."""
+    from oracle.oracle import BitNetOracle
+    shape = BitNetShape.bitnet_2b(max_seq=128)
+    w = random_bitnet_weights(shape, seed=4)
+    prompt = np.random.default_rng(3).integers(0, shape.vocab, (1, 4)).astype(np.int32)
+    ctx.set_attn_mode(ctx.ATTN_FAST if mode == "FAST" else ctx.ATTN_PRECISE)
+    model = BitNetModel(ctx, shape, w, batch=1, max_new_tokens=70)
+    o = BitNetOracle(shape, w)
+    toks, devs, flips, beyond = list(prompt[0]), [], 0, 0
+    for t in range(prompt.shape[1] + 64):
+        cur = np.array([toks[t]], np.int32)
+        g_tok, g_logits = model.step(torch.from_numpy(cur).cuda(), want_logits=True)
+        o_tok, o_logits = o.step(int(cur[0]))
+        sd = float(np.std(o_logits))
+        assert np.isfinite(g_logits).all()
+        assert 0.5 * sd < float(np.std(g_logits[0])) < 2.0 * sd
+        devs.append(float(np.max(np.abs(g_logits[0] - o_logits))) / sd)
+        if t >= prompt.shape[1] - 1:
+            if t + 1 >= len(toks):
+                toks.append(o_tok)
+            if int(g_tok[0]) != o_tok:
+                flips += 1
+                top2 = np.partition(o_logits, -2)[-2:]
+                beyond += int((top2[1] - top2[0]) > MARGIN * sd)
+    o.close()
+    model.close()
+    print(f"BITNET_FULL_SIZE_{mode} flips={flips}/64 beyond_margin={beyond} "
+          f"max_logit_dev_over_sd={max(devs):.3f}")

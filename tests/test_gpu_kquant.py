@@ -146,6 +146,9 @@ def test_batched_gate_up_and_multi(ctx, oracle, K, N, M):
     y = LinearLayer.forward_fused_gate_up(g, u, _dev(x))
     ctx.check()
     rows = [0, M - 1]
+    # gelu(gate) * up is a PRODUCT of two k-quant outputs: on the tensor-core path each factor
+    # carries the f16 rounding of its weights and activations (~4e-4 of its own scale, inside
+    # the 1e-3 bar, checked on ys below), so the product is held to twice the bar
     _check(y[rows], oracle.kquant_gateup_gelu(bg, bu, 12, K, N, x[rows]), tol=2e-3)
     ys = LinearLayer.forward_multi([g, u], _dev(x))
     ctx.check()
@@ -183,7 +186,9 @@ def test_post_norm_folded_into_the_next_matvec(ctx, oracle, fmt, M):
                                                pre=(dbase, dg1))
     ctx.check()
     assert torch.equal(xo, xo2)
-    _check(y, oracle.kquant_gateup_gelu(ba, bb, fmt, K, N, xn), tol=2e-3)
+    # one token and three take the streaming kernels (1e-3 holds for the product too); 20
+    # tokens take the f16 tensor-core path, where the product of two outputs gets twice the bar
+    _check(y, oracle.kquant_gateup_gelu(ba, bb, fmt, K, N, xn), tol=TOL if M < 16 else 2e-3)
     # and the unfused sequence of calls gives the same x' bit for bit
     ref = LinearLayer.forward_multi([la, lb], xo, rms_gamma=dg2, eps=1e-6)
     ctx.check()

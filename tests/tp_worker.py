@@ -94,6 +94,61 @@ def check_allreduce(hb, ctx, comm, rank, world):
     return ok
 
 
+def withheld_exchange(hb, ctx, comm, rank, world):
+    """Failure detection without a GPU fault: rank 1 does not take part in three exchanges (a
+    host-side decision), rank 0's kernels must give up by themselves when their deadline
+    passes, flag the context, let the later exchanges through at once, and leave the GPU and
+    the process usable.  Plain peer stores only (NVLS is off for this run)."""
+    import ctypes as C
+    import time
+    from hesper_b200 import HesperB200Error
+    lib = hb.load()
+    if not comm.peer_attached:
+        return True  # nothing to time out on the NCCL route: not the subject of this check
+    comm.set_timeout_ms(50)
+    M, K = 4, 2560
+    st = torch.cuda.Stream()
+    x = torch.ones(M, K, device="cuda") * (rank + 1)
+    gamma = torch.ones(K, device="cuda")
+    y = torch.empty_like(x)
+
+    def exchange():
+        rc = lib.hb200_tp_allreduce_rmsnorm(comm.handle, ctx.handle, C.c_void_p(x.data_ptr()),
+                                            C.c_void_p(gamma.data_ptr()), None, C.c_float(1e-6),
+                                            M, K, C.c_void_p(y.data_ptr()),
+                                            C.c_void_p(st.cuda_stream))
+        assert rc == 0, lib.hb200_last_error()
+
+    torch.cuda.synchronize()
+    exchange()                      # everybody takes part: completes, no flag
+    st.synchronize()
+    ok = ctx.check() == 0
+    dist.barrier()
+    if rank == 0:
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        for i in range(3):          # rank 1 withholds these three
+            ev[i].record(st)
+            exchange()
+        ev[3].record(st)
+        t0 = time.perf_counter()
+        st.synchronize()            # returns: the waits are bounded
+        ok = ok and (time.perf_counter() - t0) < 5.0
+        first, second, third = (ev[i].elapsed_time(ev[i + 1]) for i in range(3))
+        ok = ok and 30.0 <= first <= 500.0          # waited for its 50 ms deadline, once
+        ok = ok and second < 10.0 and third < 10.0  # context already in error: look once, go on
+        try:
+            ctx.check()
+            ok = False                              # the expired wait must be reported
+        except HesperB200Error as e:
+            ok = ok and e.code == -4                # HB200_ERR_TIMEOUT
+        ok = ok and ctx.check() == 0                # reported once, then cleared
+        # the GPU and the library are still usable
+        t = torch.ones(8, device="cuda")
+        ok = ok and float((t * 2).sum().item()) == 16.0
+    dist.barrier()                  # rank 1 stays (its buffer mapped) until rank 0 is done
+    return ok
+
+
 def main():
     rank = int(os.environ["RANK"])
     world = int(os.environ["WORLD_SIZE"])
@@ -105,6 +160,16 @@ def main():
     from tp_common import SMALL_GEMMA as S
     ctx = hb.Context(local)
     comm = tp.TensorParallel.from_torch_distributed(ctx)
+    if "--withhold" in sys.argv:
+        ok = withheld_exchange(hb, ctx, comm, rank, world)
+        oks = [None] * world
+        dist.all_gather_object(oks, bool(ok))
+        comm.close()
+        dist.barrier()
+        if rank == 0:
+            print("TP_TIMEOUT_OK" if all(oks) else "TP_TIMEOUT_FAIL", flush=True)
+        dist.destroy_process_group()
+        sys.exit(0 if all(oks) else 1)
     ok_ar = check_allreduce(hb, ctx, comm, rank, world)
     w = tp.random_gemma_weights(S, seed=31)
     p = tp.plan(S, rank, world)
