@@ -171,6 +171,13 @@ def main():
         dist.destroy_process_group()
         sys.exit(0 if all(oks) else 1)
     ok_ar = check_allreduce(hb, ctx, comm, rank, world)
+    if "--full-shape" in sys.argv:
+        # the benchmark model's widths (hidden 2560, 8/2 heads of 256, FFN 10240, vocab 262144)
+        # with two layers, one sliding-window and one global: every sharding rule of TP 2, 4 and
+        # 8 is exercised (KV heads replicated beyond 2 ranks, 5-block row splits at 8)
+        import dataclasses
+        S = dataclasses.replace(tp.GemmaShape(), n_layers=2, max_seq=128, window=16,
+                                global_every=2)
     w = tp.random_gemma_weights(S, seed=31)
     p = tp.plan(S, rank, world)
     model = hb.GemmaModel(ctx, S, tp.shard_weights(S, w, p), p, comm, batch=2, max_new_tokens=8)
@@ -202,6 +209,7 @@ def main():
         toks = box[0]
     comm.check()
     ctx.check()
+    comm_attached = comm.peer_attached
     oks = [None] * world
     dist.all_gather_object(oks, bool(ok_ar))
     flag = [ok and all(oks)]
@@ -210,7 +218,10 @@ def main():
     comm.close()
     dist.barrier()
     if rank == 0:
-        print("TP_PARITY_OK" if flag[0] else "TP_PARITY_FAIL", flush=True)
+        print(("TP_PARITY_OK" if flag[0] else "TP_PARITY_FAIL") +
+              f" world={world} layers={S.n_layers} hidden={S.hidden} heads={S.n_heads}/"
+              f"{S.n_kv_heads} ffn={S.ffn} vocab={S.vocab} steps=24 batch=2 "
+              f"peer_exchange={int(comm_attached)}", flush=True)
     dist.destroy_process_group()
     sys.exit(0 if flag[0] else 1)
 
