@@ -234,7 +234,7 @@ __global__ void __launch_bounds__(BLCfg<WPL, MT, RT, GU>::kThreads,
       if (gamma) {
         double ss = 0.0;
         for (int i = tid; i < nvec; i += kThreads) {
-          const float4 v = __ldg(xg + i);
+          const float4 v = __ldcg(xg + i);
           xs[i] = v;
           ss += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
         }
@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(BLCfg<WPL, MT, RT, GU>::kThreads,
         }
       } else {
         for (int i = tid; i < nvec; i += kThreads) {
-          const float4 v = __ldg(xg + i);
+          const float4 v = __ldcg(xg + i);
           xs[i] = v;
           amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
         }
@@ -548,6 +548,10 @@ extern "C" int hb200_bitlinear_forward_multi(hb200_ctx* ctx, const hb200_bitline
   // 16 or more tokens: a real contraction -> tensor cores (weights still streamed once)
   if (M >= 16 && K <= 12288 && !ctx->no_mma)
     return hb_bitlinear_mma_run(ctx, segs, nseg, K, d_x, M, d_rms_gamma, rms_eps, d_act_scale, st);
+  if (M == 1) {  // one token: integer tensor-core matvec when the rows fit shared memory
+    rc = hb_bl_mv_run(ctx, segs, nseg, K, 0, d_x, d_rms_gamma, rms_eps, d_act_scale, st);
+    if (rc <= 0) return rc;
+  }
   const int rt = bl_pick_rt(ctx, rows);
   BLParams p = {};
   int t = 0;
@@ -613,6 +617,13 @@ extern "C" int hb200_bitlinear_gateup_relu2(hb200_ctx* ctx, const void* d_packed
                               static_cast<cudaStream_t>(stream));
     if (rc) return rc;
     return hb200_relu2_mul(ctx, g, u, (long)M * N, d_y, stream);
+  }
+  if (M == 1) {
+    const hb200_bitlinear_seg gs[2] = {{d_packed_gate, d_scale_gate, nullptr, d_y, nullptr, N},
+                                       {d_packed_up, d_scale_up, nullptr, d_y, nullptr, N}};
+    rc = hb_bl_mv_run(ctx, gs, 2, K, 1, d_x, d_rms_gamma, rms_eps, nullptr,
+                      static_cast<cudaStream_t>(stream));
+    if (rc <= 0) return rc;
   }
   // a gate/up tile streams 2*RT rows, so the row count that matters doubles
   const int rt = bl_pick_rt(ctx, 2L * N) == 4 ? 4 : 2;

@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(256) quant_act_kernel(const __grid_constant__ 
   if (p.gamma) {
     double ss = 0.0;
     for (int i = tid; i < nvec; i += 256) {
-      const float4 v = __ldg(xg + i);
+      const float4 v = __ldcg(xg + i);
       x4[i] = v;
       ss += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
     }
@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(256) quant_act_kernel(const __grid_constant__ 
     }
   } else {
     for (int i = tid; i < nvec; i += 256) {
-      const float4 v = __ldg(xg + i);
+      const float4 v = __ldcg(xg + i);
       x4[i] = v;
       amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
     }

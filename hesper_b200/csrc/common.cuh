@@ -121,6 +121,14 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
 // depends on have completed and their writes are visible; `pdl_trigger` lets
 // the next kernel in the stream start its independent prologue (weight
 // prefetch).  Both are no-ops when the launch carries no such dependency.
+// Rule for every kernel launched this way: a buffer that an earlier kernel of the chain writes
+// (activations, residual streams) is never read through the read-only path (__ldg /
+// ld.global.nc) -- this kernel is resident while its predecessor still runs on the same SM, the
+// predecessor's own loads can leave lines of that buffer in L1, and the read-only path may
+// return them after the wait.  Such buffers are read with __ldcg (ld.global.cg, L2) or plain
+// loads; __ldg is for weights, scales and norm weights only.  Seen once: a two-launches-per-SM
+// matvec that read the hidden state with __ldg lost token parity on a 2-layer model while every
+// single-operator test stayed bit-exact.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -282,6 +290,10 @@ int hb_func_smem(struct hb200_ctx* ctx, const void* func, size_t bytes);
 bool hb_func_flag(struct hb200_ctx* ctx, const void* func);
 void hb_func_set_flag(struct hb200_ctx* ctx, const void* func);
 
+// one-token ternary matvec on mma.sync (bitlinear_mv.cu); 1 = shape not covered
+int hb_bl_mv_run(struct hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int nseg, int K, int gu,
+                 const float* d_x, const float* gamma, float eps, float* d_act_scale,
+                 cudaStream_t st);
 // one-token Q4_K / Q8_0 matvec on mma.sync (kquant_mv.cu); 1 = shape not covered
 int hb_kq_mv_run(struct hb200_ctx* ctx, int fmt, const hb200_kquant_seg* segs, int nseg, int K,
                  int gu, const float* d_x, const float* pre_base, const float* pre_gamma,

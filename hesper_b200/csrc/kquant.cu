@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
 #pragma unroll
     for (int j = 0; j < kHeld; ++j) {
       const int i = tid + j * kKQThreads;
-      hx[j] = (held && !pre && i < nvec) ? __ldg(xg + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      hx[j] = (held && !pre && i < nvec) ? __ldcg(xg + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (pre) {
       // x' = base + rmsnorm(x) * pre_gamma, same operation order as the standalone kernel.
@@ -317,14 +317,14 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
         for (int j = 0; j < kHeld; ++j) {
           const int i = tid + j * kKQThreads;
           const bool in = i < nvec;
-          hv[j] = in ? __ldg(xg + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+          hv[j] = in ? __ldcg(xg + i) : make_float4(0.f, 0.f, 0.f, 0.f);
           hg[j] = in ? __ldg(pg + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-          hb[j] = in ? __ldg(bg + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+          hb[j] = in ? __ldcg(bg + i) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int j = 0; j < kHeld; ++j) ss += sq(hv[j]);
       } else {
-        for (int i = tid; i < nvec; i += kKQThreads) ss += sq(__ldg(xg + i));
+        for (int i = tid; i < nvec; i += kKQThreads) ss += sq(__ldcg(xg + i));
       }
       ss = warp_sum(ss);
       if (lane == 0) red_f64[warp] = ss;
@@ -351,7 +351,7 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
           if (i < nvec) hx[j] = step(i, hv[j], hg[j], hb[j]);
         }
       } else {
-        for (int i = tid; i < nvec; i += kKQThreads) step(i, __ldg(xg + i), __ldg(pg + i), __ldg(bg + i));
+        for (int i = tid; i < nvec; i += kKQThreads) step(i, __ldcg(xg + i), __ldg(pg + i), __ldcg(bg + i));
       }
       if (gamma) {  // the second set of slots: the first may still be being read
         ss2 = warp_sum(ss2);
@@ -359,7 +359,7 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
       }
       __syncthreads();
     }
-    auto load_x = [&](int i) { return pre ? xs4[i] : __ldg(xg + i); };
+    auto load_x = [&](int i) { return pre ? xs4[i] : __ldcg(xg + i); };
     if (gamma) {
       double ss = 0.0;
       if (pre) {

@@ -66,6 +66,18 @@ struct MvParams {
 struct MvSmem {
   size_t part, side, xfrag, xtab, xs, w, total;
 };
+// Bytes between two rows in shared memory.  A warp's fragment load touches eight rows at the same
+// column (eight words per row for Q4_K): with a stride of 8 words (mod 32) the rows spread over
+// all banks, with 0 (K = 2048, 10240, ...) they would all start on the same bank.  The padding
+// is a multiple of 16 bytes, so a row still is a legal bulk-copy destination.
+__host__ __device__ inline int mv_row_stride(int rowbytes) {
+  const int w = rowbytes >> 2;
+  return rowbytes + 4 * ((((8 - w) % 32) + 32) % 32);
+}
+// Words between two rows of the {d, dmin} side array: eight rows at one column collide only when
+// the stride is a multiple of 8 words.
+__host__ __device__ inline int mv_side_stride(int nsb) { return (nsb & 7) ? nsb : nsb + 1; }
+
 __host__ __device__ inline MvSmem mv_smem(int fmt, int nslot, int rows_cap, int rows_max, int K,
                                           int rowbytes, bool pre) {
   const int nsb = K >> 8;
@@ -74,7 +86,7 @@ __host__ __device__ inline MvSmem mv_smem(int fmt, int nslot, int rows_cap, int 
   s.part = off;
   off += (size_t)nslot * rows_cap * sizeof(float);
   s.side = off;
-  if (fmt == 12) off += (size_t)rows_max * nsb * sizeof(uint32_t);
+  if (fmt == 12) off += (size_t)rows_max * mv_side_stride(nsb) * sizeof(uint32_t);
   off = (off + 15) & ~size_t(15);
   s.xfrag = off;
   off += (size_t)nsb * 512;
@@ -84,7 +96,7 @@ __host__ __device__ inline MvSmem mv_smem(int fmt, int nslot, int rows_cap, int 
   if (pre) off += (size_t)K * sizeof(float);
   off = (off + 127) & ~size_t(127);
   s.w = off;
-  s.total = off + (size_t)rows_max * rowbytes;
+  s.total = off + (size_t)rows_max * mv_row_stride(rowbytes);
   return s;
 }
 
@@ -198,6 +210,8 @@ __global__ void __launch_bounds__(kMvThreads, 2) kq_mv_kernel(const __grid_const
   const int K = p.K;
   const int nsb = K >> 8;
   const int rowbytes = nsb * kUnit;
+  const int stride = mv_row_stride(rowbytes);
+  const int sstride = mv_side_stride(nsb);
 
   pdl_trigger();
 
@@ -221,8 +235,37 @@ __global__ void __launch_bounds__(kMvThreads, 2) kq_mv_kernel(const __grid_const
   float* xs = reinterpret_cast<float*>(smem + L.xs);             // [K] with the pre-step
   uint8_t* wbase = smem + L.w;
 
-  // lane 0 of warp w starts the copies of tiles w, w + 10, ...
-  if (lane == 0) {
+  // Warp w starts the copies of tiles w, w + 10, ...: one copy per tile (or per segment piece)
+  // from lane 0 where rows sit back to back, else one copy per row from lanes 0..15.
+  if (stride != rowbytes) {
+    const uint64_t pol = policy_evict_first();
+    for (int j = warp; j < ntiles; j += kMvWarps) {
+      const int a = v0 + 16 * j;
+      const int e = min(a + 16, v1);
+      if (lane == 0) {
+        mbar_init(&bars[j], 1);
+        fence_mbar_init();
+        mbar_arrive_expect_tx(&bars[j], (uint32_t)(e - a) * rowbytes);
+      }
+      __syncwarp();
+      if (lane < e - a) {
+        const int vr = a + lane;  // virtual row
+        const uint8_t* src;
+        if (GU) {
+          // rows 0..7 of the tile are gate rows, 8..15 the up rows of the same outputs
+          src = p.seg[lane >> 3].w + ((size_t)(a >> 1) + (lane & 7)) * rowbytes;
+        } else {
+          int sg = 0;
+#pragma unroll
+          for (int s = 1; s < kMvMaxSeg; ++s)
+            if (s < p.nseg && vr >= p.seg[s].row0) sg = s;
+          src = p.seg[sg].w + (size_t)(vr - p.seg[sg].row0) * rowbytes;
+        }
+        bulk_g2s_stream(wbase + (size_t)(16 * j + lane) * stride, src, (uint32_t)rowbytes,
+                        &bars[j], pol);
+      }
+    }
+  } else if (lane == 0) {
     const uint64_t pol = policy_evict_first();
     for (int j = warp; j < ntiles; j += kMvWarps) {
       mbar_init(&bars[j], 1);
@@ -276,8 +319,8 @@ __global__ void __launch_bounds__(kMvThreads, 2) kq_mv_kernel(const __grid_const
         const uint32_t mask_hi = upper ? 0x3030u : 0u;
         const uint32_t m_extra = upper ? 4u : 0u;
         for (int sb = slot; sb < nsb; sb += nslot) {
-          uint8_t* rA = wbase + (size_t)lrA * rowbytes + (size_t)sb * kUnit;
-          uint8_t* rB = wbase + (size_t)lrB * rowbytes + (size_t)sb * kUnit;
+          uint8_t* rA = wbase + (size_t)lrA * stride + (size_t)sb * kUnit;
+          uint8_t* rB = wbase + (size_t)lrB * stride + (size_t)sb * kUnit;
           const uint4 hA = *reinterpret_cast<const uint4*>(rA);
           const uint4 hB = *reinterpret_cast<const uint4*>(rB);
           auto chunk_word = [&](const uint4& h) {
@@ -292,8 +335,8 @@ __global__ void __launch_bounds__(kMvThreads, 2) kq_mv_kernel(const __grid_const
           *reinterpret_cast<uint32_t*>(rA + 4 * t) = wA;
           *reinterpret_cast<uint32_t*>(rB + 4 * t) = wB;
           if (t == 0) {
-            side[lrA * nsb + sb] = hA.x;
-            side[lrB * nsb + sb] = hB.x;
+            side[lrA * sstride + sb] = hA.x;
+            side[lrB * sstride + sb] = hB.x;
           }
           __syncwarp();
         }
@@ -323,6 +366,9 @@ __global__ void __launch_bounds__(kMvThreads, 2) kq_mv_kernel(const __grid_const
 
   // ---- activation prologue: (pre-step), (RMSNorm), per-32 block 16-bit quantisation --------
   {
+    // x, the pre-step's base and the residual were written by the kernel this one depends on,
+    // while this kernel was already resident: they are read past L1 (ld.global.cg), never through
+    // the read-only path, whose lines an earlier kernel on this SM may have filled before.
     const float4* xg = reinterpret_cast<const float4*>(p.x);
     float rinv = 1.f;
     double ss2 = 0.0;
@@ -331,8 +377,8 @@ __global__ void __launch_bounds__(kMvThreads, 2) kq_mv_kernel(const __grid_const
     for (int j = 0; j < kHeld; ++j) {
       const int i = tid + j * kMvThreads;
       const bool in = held && !pre && i < n8;
-      hx[j][0] = in ? __ldg(xg + 2 * i) : zero4;
-      hx[j][1] = in ? __ldg(xg + 2 * i + 1) : zero4;
+      hx[j][0] = in ? __ldcg(xg + 2 * i) : zero4;
+      hx[j][1] = in ? __ldcg(xg + 2 * i + 1) : zero4;
     }
     auto sq = [](const float4& v) {
       return (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
@@ -351,15 +397,15 @@ __global__ void __launch_bounds__(kMvThreads, 2) kq_mv_kernel(const __grid_const
           const bool in = i < n8;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            hv[j][h] = in ? __ldg(xg + 2 * i + h) : zero4;
+            hv[j][h] = in ? __ldcg(xg + 2 * i + h) : zero4;
             hg[j][h] = in ? __ldg(pg + 2 * i + h) : zero4;
-            hb[j][h] = in ? __ldg(bg + 2 * i + h) : zero4;
+            hb[j][h] = in ? __ldcg(bg + 2 * i + h) : zero4;
           }
         }
 #pragma unroll
         for (int j = 0; j < kHeld; ++j) ss += sq(hv[j][0]) + sq(hv[j][1]);
       } else {
-        for (int i = tid; i < 2 * n8; i += kMvThreads) ss += sq(__ldg(xg + i));
+        for (int i = tid; i < 2 * n8; i += kMvThreads) ss += sq(__ldcg(xg + i));
       }
       ss = warp_sum(ss);
       if (lane == 0) red[warp] = ss;
@@ -390,7 +436,7 @@ __global__ void __launch_bounds__(kMvThreads, 2) kq_mv_kernel(const __grid_const
         }
       } else {
         for (int i = tid; i < 2 * n8; i += kMvThreads)
-          step(i, __ldg(xg + i), __ldg(pg + i), __ldg(bg + i));
+          step(i, __ldcg(xg + i), __ldg(pg + i), __ldcg(bg + i));
       }
       if (gamma) {
         ss2 = warp_sum(ss2);
@@ -399,7 +445,7 @@ __global__ void __launch_bounds__(kMvThreads, 2) kq_mv_kernel(const __grid_const
       __syncthreads();
     }
     auto load_x = [&](int i) {
-      return pre ? reinterpret_cast<const float4*>(xs)[i] : __ldg(xg + i);
+      return pre ? reinterpret_cast<const float4*>(xs)[i] : __ldcg(xg + i);
     };
     if (gamma) {
       double ss = 0.0;
@@ -521,10 +567,10 @@ __global__ void __launch_bounds__(kMvThreads, 2) kq_mv_kernel(const __grid_const
       // two tiles per iteration: their dependency chains are independent and interleave
       auto unit = [&](int j, float& vA, float& vB) {
         const int lrA = min(16 * j + g, nrows - 1), lrB = min(16 * j + g + 8, nrows - 1);
-        const uint8_t* rA = wbase + (size_t)lrA * rowbytes + (size_t)sb * kUnit;
-        const uint8_t* rB = wbase + (size_t)lrB * rowbytes + (size_t)sb * kUnit;
+        const uint8_t* rA = wbase + (size_t)lrA * stride + (size_t)sb * kUnit;
+        const uint8_t* rB = wbase + (size_t)lrB * stride + (size_t)sb * kUnit;
         if (FMT == 12)
-          mv_unit_q4k(rA, rB, side[lrA * nsb + sb], side[lrB * nsb + sb], t, col, vA, vB);
+          mv_unit_q4k(rA, rB, side[lrA * sstride + sb], side[lrB * sstride + sb], t, col, vA, vB);
         else
           mv_unit_q80(rA, rB, t, col, vA, vB);
       };
@@ -569,7 +615,7 @@ __global__ void __launch_bounds__(kMvThreads, 2) kq_mv_kernel(const __grid_const
         if (s < p.nseg && vr >= p.seg[s].row0) sg = s;
       const MvSeg& S = p.seg[sg];
       const int o = vr - S.row0;
-      if (S.residual) v += S.residual[o];
+      if (S.residual) v += __ldcg(S.residual + o);
       S.y[o] = v;
     }
   } else {
