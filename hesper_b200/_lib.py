@@ -121,12 +121,16 @@ SIGNATURES = {
     "hb200_gemma_reset": (_i, [_vp, _vp]),
     "hb200_gemma_set_position": (_i, [_vp, _i, _vp]),
     "hb200_gemma_step": (_i, [_vp, _vp, _vp]),
+    "hb200_gemma_prefill": (_i, [_vp, _vp, _i, _i, _vp]),
+    "hb200_gemma_chunk": (_i, [_vp]),
     "hb200_gemma_local_logits": (_vp, [_vp]),
     "hb200_gemma_tokens": (_vp, [_vp]),
     "hb200_gemma_generate": (_i, [_vp, _vp, _i, _i, _i, _vp, C.POINTER(_f), C.POINTER(_f), _vp]),
     "hb200_attn_decode": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp, _vp]),
     "hb200_attn_prefill_workspace_bytes": (_sz, [_vp, _i, _i, _i, _i, _i, _i]),
     "hb200_attn_prefill": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp, _vp]),
+    "hb200_attn_ring": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp, _vp]),
+    "hb200_rope_kv_write_prefill_angles": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "hb200_rope_kv_write_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
 }
 

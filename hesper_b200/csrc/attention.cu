@@ -27,6 +27,8 @@
 //     leader's shared memory).
 #include <math_constants.h>
 
+#include <optional>
+
 #include "common.cuh"
 
 namespace hb {
@@ -62,6 +64,9 @@ struct AttnParams {
                      // through the leader's shared memory instead of global partials + ticket
   float scale_log2;  // scale * log2(e)
   int* tickets;      // nullable: per (sequence, kv head) arrival counters, zero between calls
+  int ring;          // != 0: the cache is a ring of max_seq slots, position p lives in slot
+                     // p % max_seq, seqlens are true lengths (they may exceed max_seq) and the
+                     // window (>= 1, window + T - 1 <= max_seq) says which positions are alive
 };
 
 
@@ -70,8 +75,9 @@ struct AttnParams {
 __device__ __forceinline__ int attn_visible_len(const AttnParams& p, int b, int& cache) {
   cache = b / p.T;
   const int t = b - cache * p.T;
-  const int len = min(max(p.seqlens[cache], 0), p.max_seq) - (p.T - 1 - t);
-  return max(len, 0);
+  int raw = max(p.seqlens[cache], 0);
+  if (!p.ring) raw = min(raw, p.max_seq);
+  return max(raw - (p.T - 1 - t), 0);
 }
 
 // ---- thread-block cluster helpers (distributed shared memory) ---------------------------
@@ -198,13 +204,16 @@ __global__ void __launch_bounds__(kAttnThreads, D >= 256 ? 1 : 2) attn_decode_ke
     uint8_t* ks = stage0 + (size_t)st * Cfg::kStageBytes;
     uint8_t* vs = ks + Cfg::kTileBytes;
     const int pos0 = start + c * kChunk;
+    const int slot0 = p.ring ? pos0 % p.max_seq : pos0;
 #pragma unroll
     for (int i = 0; i < kChunk * CPR / 32; ++i) {
       const int qd = lane + 32 * i;
       const int row = qd / CPR, cc = qd % CPR;
       const int pos = pos0 + row;
       const bool ok = pos < len;
-      const size_t goff = (size_t)(ok ? pos : 0) * D + cc * 8;
+      int slot = slot0 + row;
+      if (p.ring && slot >= p.max_seq) slot -= p.max_seq;
+      const size_t goff = (size_t)(ok ? slot : 0) * D + cc * 8;
       const int soff = row * Cfg::kRowBytes + ((cc ^ (row & 7)) << 4);
       cp_async16(ks + soff, kbase + goff, ok);
       cp_async16(vs + soff, vbase + goff, ok);
@@ -628,7 +637,8 @@ __global__ void __launch_bounds__(32) attn_exact_kernel(const __grid_constant__ 
   const __half* kb = p.k + ((size_t)cb * p.Hkv + kvh) * (size_t)p.max_seq * D + lane * DL;
   const __half* vb = p.v + ((size_t)cb * p.Hkv + kvh) * (size_t)p.max_seq * D + lane * DL;
   float m = -CUDART_INF_F, l = 0.f;
-  for (int s = start; s < len; ++s) {
+  for (int ps = start; ps < len; ++ps) {
+    const int s = p.ring ? ps % p.max_seq : ps;  // slot of position ps
     float part = 0.f;
 #pragma unroll
     for (int j = 0; j < DL; ++j) part = fmaf(q[j], __half2float(kb[(size_t)s * D + j]), part);
@@ -758,7 +768,7 @@ extern "C" size_t hb200_attn_workspace_bytes(const hb200_ctx* ctx, int B, int H,
 static int attn_run(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d_k,
                     const void* d_v, const int32_t* d_seqlens, int nseq, int T, int H, int Hkv,
                     int D, int max_seq, int window, float scale, void* d_workspace,
-                    size_t workspace_bytes, float* d_out, hb200_stream stream) {
+                    size_t workspace_bytes, float* d_out, hb200_stream stream, int ring = 0) {
   HB_REQUIRE(ctx != nullptr, "attn: null context");
   HB_REQUIRE(d_q && d_k && d_v && d_seqlens && d_out, "attn: null pointer");
   HB_REQUIRE(nseq >= 1 && T >= 1 && (long)nseq * T < (1l << 24), "attn: B=%d T=%d", nseq, T);
@@ -768,6 +778,8 @@ static int attn_run(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d
   HB_REQUIRE(G <= 8, "attn: %d query heads per KV head (at most 8)", G);
   HB_REQUIRE(D == 32 || D == 64 || D == 128 || D == 256, "attn: head_dim %d not in {32,64,128,256}", D);
   HB_REQUIRE(max_seq >= 1 && window >= 0, "attn: max_seq=%d window=%d", max_seq, window);
+  HB_REQUIRE(!ring || (window >= 1 && (long)window + T - 1 <= max_seq),
+             "attn (ring): window %d + %d query tokens - 1 must fit the %d slots", window, T, max_seq);
   HB_REQUIRE(((reinterpret_cast<uintptr_t>(d_k) | reinterpret_cast<uintptr_t>(d_v)) & 15) == 0,
              "attn: K/V cache must be 16-byte aligned");
   AttnParams p = {};
@@ -784,6 +796,7 @@ static int attn_run(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d
   p.max_seq = max_seq;
   p.window = window;
   p.T = T;
+  p.ring = ring;
   p.scale_log2 = scale * 1.4426950408889634f;
   const int eff_len = (window > 0 && window < max_seq) ? window : max_seq;
   p.nsplit = D == 32 ? 1 : attn_pick_splits(ctx, B, Hkv, D, eff_len);
@@ -813,6 +826,9 @@ static int attn_run(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d
     p.tickets = (B * Hkv <= hb::kCtxTickets) ? ctx->d_tickets : nullptr;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the arrival counters are the context's: calls on two streams must not interleave on them
+  std::optional<ScratchUse> use;
+  if (p.tickets && !p.cluster) use.emplace(ctx, st);
   // head_dim 32 (the reference's smallest golden case, a debugging size) is below the MMA
   // kernel's tile: it always takes the one-warp-per-head kernel
   if (ctx->attn_mode == HB200_ATTN_EXACT || D == 32) {
@@ -860,6 +876,15 @@ extern "C" int hb200_attn_prefill(hb200_ctx* ctx, const void* d_q, int q_is_f16,
                                   hb200_stream stream) {
   return attn_run(ctx, d_q, q_is_f16, d_k, d_v, d_seqlens, B, T, H, Hkv, D, max_seq, window, scale,
                   d_workspace, workspace_bytes, d_out, stream);
+}
+
+extern "C" int hb200_attn_ring(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d_k,
+                               const void* d_v, const int32_t* d_seqlens, int B, int T, int H,
+                               int Hkv, int D, int slots, int window, float scale,
+                               void* d_workspace, size_t workspace_bytes, float* d_out,
+                               hb200_stream stream) {
+  return attn_run(ctx, d_q, q_is_f16, d_k, d_v, d_seqlens, B, T, H, Hkv, D, slots, window, scale,
+                  d_workspace, workspace_bytes, d_out, stream, 1);
 }
 
 // ---- the same operator for callers that must not allocate -----------------------------

@@ -609,6 +609,7 @@ extern "C" int hb200_bitlinear_gateup_relu2(hb200_ctx* ctx, const void* d_packed
   if (M >= 16 && K <= 12288 && !ctx->no_mma &&
       kScratchGlu + (size_t)2 * M * N * sizeof(float) <= kScratchLmSplit) {
     // batched: both products on the tensor cores into scratch, then the GLU epilogue
+    ScratchUse use(ctx, static_cast<cudaStream_t>(stream));
     float* g = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->d_scratch) + kScratchGlu);
     float* u = g + (size_t)M * N;
     hb200_bitlinear_seg segs[2] = {{d_packed_gate, d_scale_gate, nullptr, g, nullptr, N},

@@ -515,6 +515,7 @@ using namespace hb;
 int hb_bitlinear_mma_run(hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int nseg, int K,
                          const float* d_x, int M, const float* d_rms_gamma, float rms_eps,
                          float* d_act_scale, cudaStream_t st) {
+  ScratchUse use(ctx, st);  // quantised activation tiles, split-K partials, tickets
   const size_t xq_bytes = (size_t)(K / 128) * kBBytes;
   HB_REQUIRE(xq_bytes + 1024 <= kScratchGlu,
              "bitlinear (batched): K=%d needs %zu bytes of activation scratch", K, xq_bytes);

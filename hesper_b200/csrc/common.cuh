@@ -232,6 +232,8 @@ constexpr size_t kScratchBytes = (size_t)24 << 20;
 constexpr size_t kScratchActs = 0;                     // batched ternary: d[64], sumq[64], int8 tiles
 constexpr size_t kScratchGlu = (size_t)2 << 20;       // batched gate/up products before the GLU
 constexpr size_t kScratchLmSplit = (size_t)8 << 20;   // 16-bit products: hi/lo activation tiles
+constexpr size_t kScratchRowScale = ((size_t)16 << 20) - 4096;  // f16 products: one power-of-two
+                                                       // scale per staged activation row
 constexpr size_t kScratchSplitK = (size_t)16 << 20;   // batched paths: split-K partials
 
 // the two halves of it, also used by the batched k-quant path (weights dequantised to f16)
@@ -280,6 +282,12 @@ struct hb200_ctx {
     bool flag;  // kernel-specific: non-portable cluster sizes already allowed
   } func_smem[96];
   int n_func_smem;
+  // The scratch, the arrival counters and the arena serve one stream at a time: ScratchUse
+  // orders a call behind the previous user when it arrives on another stream.
+  cudaEvent_t scratch_done;     // end of the last use outside a stream capture
+  cudaStream_t scratch_stream;  // the stream that use was on (never dereferenced: compared only)
+  bool scratch_used;
+  int scratch_depth;            // nesting of ScratchUse on the calling thread
   uint32_t attn_cluster_refused;  // bit n: the driver refused a cluster of n attention CTAs
   void* attn_static_addr;         // device address of the built-in attention scratch array here
   bool adopted;                   // lives in the caller's own CUDA context: never switch devices
@@ -289,6 +297,20 @@ struct hb200_ctx {
 int hb_func_smem(struct hb200_ctx* ctx, const void* func, size_t bytes);
 bool hb_func_flag(struct hb200_ctx* ctx, const void* func);
 void hb_func_set_flag(struct hb200_ctx* ctx, const void* func);
+
+// Scope of one operator call that touches the context's scratch, arrival counters or arena.
+// Entering on another stream than the previous user's makes this stream wait for the event
+// recorded at the end of that use; leaving records the event.  Inside a stream capture nothing
+// is recorded or waited for (an event from outside cannot enter a capture): graphs that share a
+// context are ordered by whoever replays them.
+struct ScratchUse {
+  struct hb200_ctx* c;
+  cudaStream_t st;
+  ScratchUse(struct hb200_ctx* ctx, cudaStream_t stream);
+  ~ScratchUse();
+  ScratchUse(const ScratchUse&) = delete;
+  ScratchUse& operator=(const ScratchUse&) = delete;
+};
 
 // one-token ternary matvec on mma.sync (bitlinear_mv.cu); 1 = shape not covered
 int hb_bl_mv_run(struct hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int nseg, int K, int gu,

@@ -51,6 +51,34 @@ void hb_func_set_flag(hb200_ctx* ctx, const void* func) {
     if (ctx->func_smem[i].func == func) ctx->func_smem[i].flag = true;
 }
 
+ScratchUse::ScratchUse(hb200_ctx* ctx, cudaStream_t stream) : c(ctx), st(stream) {
+  if (c->scratch_depth++ > 0) return;  // an operator inside an operator: the outer scope rules
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) {
+    cudaGetLastError();
+    return;
+  }
+  if (cs != cudaStreamCaptureStatusNone) return;
+  if (c->scratch_used && c->scratch_stream != st && c->scratch_done != nullptr)
+    cudaStreamWaitEvent(st, c->scratch_done, 0);
+}
+
+ScratchUse::~ScratchUse() {
+  if (--c->scratch_depth > 0) return;
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) {
+    cudaGetLastError();
+    return;
+  }
+  if (cs != cudaStreamCaptureStatusNone || c->scratch_done == nullptr) return;
+  if (cudaEventRecord(c->scratch_done, st) == cudaSuccess) {
+    c->scratch_stream = st;
+    c->scratch_used = true;
+  } else {
+    cudaGetLastError();
+  }
+}
+
 using namespace hb;
 
 extern "C" const char* hb200_last_error(void) { return g_err; }
@@ -85,6 +113,10 @@ static int ctx_build(int device, bool adopted, hb200_ctx** out) {
   c->attn_cluster_refused = 0;
   c->attn_static_addr = nullptr;
   c->adopted = adopted;
+  c->scratch_done = nullptr;
+  c->scratch_stream = nullptr;
+  c->scratch_used = false;
+  c->scratch_depth = 0;
   const char* env = getenv("HB200_NO_PDL");
   if (env && env[0] == '1') c->pdl = false;
   cudaError_t e = cudaMalloc(&c->d_status, 256);
@@ -94,11 +126,13 @@ static int ctx_build(int device, bool adopted, hb200_ctx** out) {
   c->scratch_bytes = kScratchBytes;
   if (e == cudaSuccess) e = cudaMalloc(&c->d_scratch, c->scratch_bytes);
   if (e == cudaSuccess) e = cudaMalloc(&c->d_arena, kArenaBytes);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->scratch_done, cudaEventDisableTiming);
   if (e != cudaSuccess) {
     cudaFree(c->d_status);
     cudaFree(c->d_tickets);
     cudaFree(c->d_scratch);
     cudaFree(c->d_arena);
+    if (c->scratch_done) cudaEventDestroy(c->scratch_done);
     delete c;
     return cuda_fail(e, "context buffers");
   }
@@ -143,6 +177,7 @@ extern "C" int hb200_ctx_destroy(hb200_ctx* ctx) {
   cudaFree(ctx->d_tickets);
   cudaFree(ctx->d_scratch);
   cudaFree(ctx->d_arena);
+  if (ctx->scratch_done) cudaEventDestroy(ctx->scratch_done);
   delete ctx;
   return HB200_OK;
 }

@@ -214,8 +214,10 @@ extern "C" int hb200_bitnet_create(hb200_ctx* ctx, const hb200_bitnet_config* cf
   A(cudaMalloc(&m->lm_scratch, hb200_lmhead_scratch_bytes(B)));
   m->attn_ws_bytes = hb200_attn_workspace_bytes(ctx, B, cfg->n_heads, cfg->n_kv_heads,
                                                 cfg->head_dim, cfg->max_seq);
-  if (Tmax > 1) {
-    const size_t pw = hb200_attn_prefill_workspace_bytes(ctx, B, Tmax, cfg->n_heads,
+  // the split count, hence the partials, depend on the query tokens of a pass, and not
+  // monotonically: size for every chunk length a prompt can end with
+  for (int T = 2; T <= Tmax; ++T) {
+    const size_t pw = hb200_attn_prefill_workspace_bytes(ctx, B, T, cfg->n_heads,
                                                          cfg->n_kv_heads, cfg->head_dim, cfg->max_seq);
     if (pw > m->attn_ws_bytes) m->attn_ws_bytes = pw;
   }

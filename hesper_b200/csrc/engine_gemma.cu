@@ -12,6 +12,7 @@
 // of the LM head, and the matching input columns of o_proj and down_proj.  The only
 // exchange is one f32 sum all-reduce of hidden*batch elements after o_proj and after
 // down_proj, and one u64 max all-reduce of batch argmax keys per token.
+#include <algorithm>
 #include <cstdlib>
 #include <vector>
 
@@ -26,12 +27,14 @@ struct hb200_gemma {
   const void* lm_head;
   const float* final_norm;
   int B;
+  int chunk_T;  // prompt positions per sequence one prefill pass takes (1: position by position)
   float *x, *x1, *q, *k, *v, *att, *o, *h, *logits;
   std::vector<__half*> kc, vc;  // per layer
-  std::vector<int> slots;       // cache slots per layer (window or max_seq)
+  std::vector<int> slots;       // cache slots per layer (ring of window + chunk - 1, or max_seq)
+  std::vector<int> win;         // attention window per layer (0: all positions)
   int32_t *pos, *len, *tok, *log_index, *token_log;
   unsigned long long* keys;
-  double* rope_tab;  // [B][D/2][2] the step's RoPE angles, shared by all layers
+  double* rope_tab;  // [B * chunk_T][D/2][2] the pass's RoPE angles, shared by all layers
   void* attn_ws;
   size_t attn_ws_bytes;
   int log_stride;
@@ -123,16 +126,27 @@ bool layer_is_global(const hb200_gemma_config& c, int l) {
   return c.global_every > 0 && (l + 1) % c.global_every == 0;
 }
 
-int gemma_enqueue_step(hb200_gemma* m, const int32_t* d_tokens, bool lm_head, cudaStream_t st) {
+// One pass over all layers for T consecutive positions of every sequence (T = 1: a decode
+// step; T > 1: a prompt chunk, d_tokens [nseq][T]).  Rows of every activation buffer are
+// (sequence, token) pairs in that order.  Sliding-window layers keep a ring of window + chunk_T - 1
+// slots, so the T positions written at the start of the pass overwrite nothing the pass's
+// earliest query still attends to.  The LM head runs on each sequence's last row only.
+int gemma_enqueue_step(hb200_gemma* m, const int32_t* d_tokens, bool lm_head, cudaStream_t st,
+                       int T = 1) {
   const hb200_gemma_config& c = m->cfg;
   hb200_ctx* ctx = m->ctx;
-  const int B = m->B, Hd = c.hidden, D = c.head_dim;
+  const int nseq = m->B, Hd = c.hidden, D = c.head_dim;
+  const int B = nseq * T;  // rows
   const int qdim = c.local_q_heads * D, kvdim = c.local_kv_heads * D;
   const int32_t* toks = d_tokens ? d_tokens : m->tok;
   int rc = hb200_embed_lookup(ctx, m->embed, 0, c.vocab, Hd, toks, B, c.embed_scale, m->x, st);
   if (rc) return rc;
-  rc = hb200_rope_table(ctx, m->pos, B, 1, D, c.rope_base, m->rope_tab, st);
+  rc = hb200_rope_table(ctx, m->pos, nseq, T, D, c.rope_base, m->rope_tab, st);
   if (rc) return rc;
+  if (T > 1) {  // lengths after the chunk: pos + T (they stand at pos + 1 between passes)
+    rc = hb200_add_i32(ctx, m->len, nseq, T - 1, st);
+    if (rc) return rc;
+  }
   // With one rank nothing has to be exchanged between a block's output projection and its
   // post-norm, so the post-norm + residual add runs inside the prologue of the NEXT matvec
   // launch (the o_proj / down_proj output stays in m->o until then): two launches fewer per
@@ -150,15 +164,19 @@ int gemma_enqueue_step(hb200_gemma* m, const int32_t* d_tokens, bool lm_head, cu
       rc = hb200_kquant_forward_multi(ctx, HB200_FMT_Q4_K, segs, 3, Hd, m->x, B, L.attn_norm,
                                       c.rms_eps, st);
     if (rc) return rc;
-    const bool glob = layer_is_global(c, l);
-    rc = hb200_rope_kv_write_angles(ctx, m->q, m->k, m->v, m->kc[l], m->vc[l], m->pos, m->rope_tab,
-                                    B, c.local_q_heads, c.local_kv_heads, D, m->slots[l],
-                                    glob ? 0 : 1, st);
+    const bool ring = m->slots[l] < c.max_seq;
+    rc = hb200_rope_kv_write_prefill_angles(ctx, m->q, m->k, m->v, m->kc[l], m->vc[l], m->pos,
+                                            m->rope_tab, nseq, T, c.local_q_heads,
+                                            c.local_kv_heads, D, m->slots[l], ring ? 1 : 0, st);
     if (rc) return rc;
-    // a ring cache holds exactly the window: the kernel clamps the length to the slots
-    rc = hb200_attn_decode(ctx, m->q, 0, m->kc[l], m->vc[l], m->len, B, c.local_q_heads,
-                           c.local_kv_heads, D, m->slots[l], 0, c.attn_scale, m->attn_ws,
+    if (ring)  // position p sits in slot p % slots; the last `window` positions are alive
+      rc = hb200_attn_ring(ctx, m->q, 0, m->kc[l], m->vc[l], m->len, nseq, T, c.local_q_heads,
+                           c.local_kv_heads, D, m->slots[l], c.window, c.attn_scale, m->attn_ws,
                            m->attn_ws_bytes, m->att, st);
+    else  // linear cache: a global layer, or a window too close to max_seq for a ring to pay
+      rc = hb200_attn_prefill(ctx, m->q, 0, m->kc[l], m->vc[l], m->len, nseq, T, c.local_q_heads,
+                              c.local_kv_heads, D, m->slots[l], m->win[l], c.attn_scale,
+                              m->attn_ws, m->attn_ws_bytes, m->att, st);
     if (rc) return rc;
     rc = hb200_kquant_forward(ctx, HB200_FMT_Q4_K, L.wo, qdim, Hd, m->att, B, nullptr, 0.f, nullptr,
                               m->o, st);
@@ -185,23 +203,34 @@ int gemma_enqueue_step(hb200_gemma* m, const int32_t* d_tokens, bool lm_head, cu
     }
   }
   if (lm_head) {
-    rc = hb200_kquant_forward(ctx, HB200_FMT_Q4_K, m->lm_head, Hd, c.local_vocab, m->x, B,
+    const float* xl = m->x;
+    if (T > 1) {  // each sequence's last row, packed into x1 (free after the last layer)
+      HB_CUDA(cudaMemcpy2DAsync(m->x1, sizeof(float) * Hd, m->x + (size_t)(T - 1) * Hd,
+                                sizeof(float) * Hd * T, sizeof(float) * Hd, nseq,
+                                cudaMemcpyDeviceToDevice, st));
+      xl = m->x1;
+    }
+    rc = hb200_kquant_forward(ctx, HB200_FMT_Q4_K, m->lm_head, Hd, c.local_vocab, xl, nseq,
                               m->final_norm, c.rms_eps, nullptr, m->logits, st);
     if (rc) return rc;
     // enough CTAs to spread a single token's logits over the SMs, few atomics at large batch
-    const int chunk = B <= 8 ? 2048 : 8192;
-    HB_CUDA(launch_pdl(argmax_keys_kernel, dim3((c.local_vocab + chunk - 1) / chunk, B),
+    const int chunk = nseq <= 8 ? 2048 : 8192;
+    HB_CUDA(launch_pdl(argmax_keys_kernel, dim3((c.local_vocab + chunk - 1) / chunk, nseq),
                        dim3(256), 0, st, ctx->pdl, (const float*)m->logits, c.local_vocab,
                        c.vocab_offset, chunk, m->keys));
-    rc = hb200_tp_allreduce_max_u64(m->tp, m->keys, (size_t)B, st);
+    rc = hb200_tp_allreduce_max_u64(m->tp, m->keys, (size_t)nseq, st);
     if (rc) return rc;
-    HB_CUDA(launch_pdl(keys_to_tokens_kernel, dim3((B + 63) / 64), dim3(64), 0, st, ctx->pdl,
-                       m->keys, B, m->tok, m->token_log,
+    HB_CUDA(launch_pdl(keys_to_tokens_kernel, dim3((nseq + 63) / 64), dim3(64), 0, st, ctx->pdl,
+                       m->keys, nseq, m->tok, m->token_log,
                        (const int32_t*)m->log_index, m->log_stride));
     rc = hb200_add_i32(ctx, m->log_index, 1, 1, st);
     if (rc) return rc;
   }
-  return hb200_add_i32(ctx, m->pos, 2 * B, 1, st);
+  // pos += T; len = pos + 1 again (the two arrays are adjacent: one launch for a decode step)
+  if (T == 1) return hb200_add_i32(ctx, m->pos, 2 * nseq, 1, st);
+  rc = hb200_add_i32(ctx, m->pos, nseq, T, st);
+  if (rc) return rc;
+  return hb200_add_i32(ctx, m->len, nseq, 1, st);
 }
 
 }  // namespace
@@ -228,7 +257,17 @@ extern "C" int hb200_gemma_create(hb200_ctx* ctx, hb200_tp* tp, const hb200_gemm
   m->final_norm = d_final_norm;
   m->B = batch;
   m->log_stride = max_new_tokens > 0 ? max_new_tokens : 1;
-  const int B = batch, D = cfg->head_dim, qdim = cfg->local_q_heads * D, kvdim = cfg->local_kv_heads * D;
+  // prompt chunks: up to 256 rows per pass (the widest batched product), HB200_GEMMA_CHUNK caps
+  // the positions per sequence (1 = position by position)
+  int chunk_T = 256 / batch;
+  if (const char* ev = getenv("HB200_GEMMA_CHUNK")) {
+    const int cap = atoi(ev);
+    if (cap >= 1 && cap < chunk_T) chunk_T = cap;
+  }
+  if (chunk_T < 1) chunk_T = 1;
+  m->chunk_T = chunk_T;
+  const int B = batch * chunk_T;  // rows of the activation buffers
+  const int D = cfg->head_dim, qdim = cfg->local_q_heads * D, kvdim = cfg->local_kv_heads * D;
   cudaError_t e = cudaSuccess;
   auto A = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
   auto F = [&](float** p, size_t n) { A(cudaMalloc(reinterpret_cast<void**>(p), n * sizeof(float))); };
@@ -240,31 +279,43 @@ extern "C" int hb200_gemma_create(hb200_ctx* ctx, hb200_tp* tp, const hb200_gemm
   F(&m->v, (size_t)B * kvdim);
   F(&m->att, (size_t)B * qdim);
   F(&m->h, (size_t)B * cfg->local_ffn);
-  F(&m->logits, (size_t)B * cfg->local_vocab);
+  F(&m->logits, (size_t)batch * cfg->local_vocab);
   m->kc.assign(cfg->n_layers, nullptr);
   m->vc.assign(cfg->n_layers, nullptr);
   m->slots.assign(cfg->n_layers, 0);
+  m->win.assign(cfg->n_layers, 0);
   int max_slots = 1;
   for (int l = 0; l < cfg->n_layers; ++l) {
     const bool glob = layer_is_global(*cfg, l) || cfg->window <= 0 || cfg->window >= cfg->max_seq;
-    m->slots[l] = glob ? cfg->max_seq : cfg->window;
+    // a ring keeps the window plus the positions a prompt chunk adds before its first query
+    // has looked back; if that is no shorter than the whole sequence the cache is linear
+    m->slots[l] = glob ? cfg->max_seq : cfg->window + chunk_T - 1;
+    if (m->slots[l] > cfg->max_seq) m->slots[l] = cfg->max_seq;
+    m->win[l] = glob ? 0 : cfg->window;
     if (m->slots[l] > max_slots) max_slots = m->slots[l];
-    const size_t n = (size_t)B * cfg->local_kv_heads * m->slots[l] * D;
+    const size_t n = (size_t)batch * cfg->local_kv_heads * m->slots[l] * D;
     A(cudaMalloc(reinterpret_cast<void**>(&m->kc[l]), n * sizeof(__half)));
     A(cudaMalloc(reinterpret_cast<void**>(&m->vc[l]), n * sizeof(__half)));
     if (e == cudaSuccess) e = cudaMemset(m->kc[l], 0, n * sizeof(__half));
     if (e == cudaSuccess) e = cudaMemset(m->vc[l], 0, n * sizeof(__half));
   }
-  A(cudaMalloc(reinterpret_cast<void**>(&m->pos), sizeof(int32_t) * 2 * B));
-  m->len = m->pos ? m->pos + B : nullptr;
-  A(cudaMalloc(reinterpret_cast<void**>(&m->tok), sizeof(int32_t) * B));
+  A(cudaMalloc(reinterpret_cast<void**>(&m->pos), sizeof(int32_t) * 2 * batch));
+  m->len = m->pos ? m->pos + batch : nullptr;
+  A(cudaMalloc(reinterpret_cast<void**>(&m->tok), sizeof(int32_t) * batch));
   A(cudaMalloc(reinterpret_cast<void**>(&m->log_index), sizeof(int32_t)));
-  A(cudaMalloc(reinterpret_cast<void**>(&m->token_log), sizeof(int32_t) * (size_t)B * m->log_stride));
-  A(cudaMalloc(reinterpret_cast<void**>(&m->keys), sizeof(unsigned long long) * B));
-  A(cudaMemset(m->keys, 0, sizeof(unsigned long long) * B));
+  A(cudaMalloc(reinterpret_cast<void**>(&m->token_log), sizeof(int32_t) * (size_t)batch * m->log_stride));
+  A(cudaMalloc(reinterpret_cast<void**>(&m->keys), sizeof(unsigned long long) * batch));
+  A(cudaMemset(m->keys, 0, sizeof(unsigned long long) * batch));
   A(cudaMalloc(reinterpret_cast<void**>(&m->rope_tab), sizeof(double) * (size_t)B * D));
-  m->attn_ws_bytes = hb200_attn_workspace_bytes(ctx, B, cfg->local_q_heads, cfg->local_kv_heads, D,
-                                                max_slots);
+  m->attn_ws_bytes = hb200_attn_workspace_bytes(ctx, batch, cfg->local_q_heads,
+                                                cfg->local_kv_heads, D, max_slots);
+  // the split count, hence the partials, depend on the number of query tokens in a pass, and
+  // not monotonically: size for every pass length a prompt can end with
+  for (int T = 2; T <= chunk_T; ++T) {
+    const size_t pw = hb200_attn_prefill_workspace_bytes(ctx, batch, T, cfg->local_q_heads,
+                                                         cfg->local_kv_heads, D, max_slots);
+    if (pw > m->attn_ws_bytes) m->attn_ws_bytes = pw;
+  }
   A(cudaMalloc(&m->attn_ws, m->attn_ws_bytes));
   if (e != cudaSuccess) {
     hb200_gemma_destroy(m);
@@ -304,6 +355,15 @@ extern "C" int hb200_gemma_step(hb200_gemma* m, const int32_t* d_tokens, hb200_s
   HB_REQUIRE(m != nullptr, "gemma_step: null model");
   return gemma_enqueue_step(m, d_tokens, true, static_cast<cudaStream_t>(stream));
 }
+
+extern "C" int hb200_gemma_prefill(hb200_gemma* m, const int32_t* d_tokens, int T, int want_token,
+                                   hb200_stream stream) {
+  HB_REQUIRE(m != nullptr && d_tokens != nullptr, "gemma_prefill: null argument");
+  HB_REQUIRE(T >= 1 && T <= m->chunk_T, "gemma_prefill: %d positions per pass, at most %d", T,
+             m->chunk_T);
+  return gemma_enqueue_step(m, d_tokens, want_token != 0, static_cast<cudaStream_t>(stream), T);
+}
+extern "C" int hb200_gemma_chunk(const hb200_gemma* m) { return m ? m->chunk_T : 0; }
 
 extern "C" const float* hb200_gemma_local_logits(const hb200_gemma* m) { return m ? m->logits : nullptr; }
 extern "C" const int32_t* hb200_gemma_tokens(const hb200_gemma* m) { return m ? m->tok : nullptr; }
@@ -354,9 +414,14 @@ extern "C" int hb200_gemma_generate(hb200_gemma* m, const int32_t* h_prompt, int
     if (rc) { cleanup(); return rc; }
     e = cudaMalloc(reinterpret_cast<void**>(&d_prompt), sizeof(int32_t) * (size_t)B * prompt_len);
     if (e != cudaSuccess) { cleanup(); return cuda_fail(e, "prompt buffer"); }
+    // chunk after chunk, each as [sequence][token of the chunk]
     std::vector<int32_t> pm((size_t)B * prompt_len);
-    for (int b = 0; b < B; ++b)
-      for (int p = 0; p < prompt_len; ++p) pm[(size_t)p * B + b] = h_prompt[(size_t)b * prompt_len + p];
+    for (int p0 = 0; p0 < prompt_len; p0 += m->chunk_T) {
+      const int T = std::min(m->chunk_T, prompt_len - p0);
+      for (int b = 0; b < B; ++b)
+        for (int t = 0; t < T; ++t)
+          pm[(size_t)B * p0 + (size_t)b * T + t] = h_prompt[(size_t)b * prompt_len + p0 + t];
+    }
     e = cudaMemcpyAsync(d_prompt, pm.data(), pm.size() * sizeof(int32_t), cudaMemcpyHostToDevice, st);
     if (e != cudaSuccess) { cleanup(); return cuda_fail(e, "prompt upload"); }
     cudaStreamSynchronize(st);
@@ -368,8 +433,9 @@ extern "C" int hb200_gemma_generate(hb200_gemma* m, const int32_t* h_prompt, int
   rc = hb200_tp_align(m->tp, st);
   if (rc) { cleanup(); return rc; }
   cudaEventRecord(e0, st);
-  for (int p = 0; p < prompt_len; ++p) {
-    rc = gemma_enqueue_step(m, d_prompt + (size_t)p * B, p == prompt_len - 1, st);
+  for (int p0 = 0; p0 < prompt_len; p0 += m->chunk_T) {
+    const int T = std::min(m->chunk_T, prompt_len - p0);
+    rc = gemma_enqueue_step(m, d_prompt + (size_t)B * p0, p0 + T == prompt_len, st, T);
     if (rc) { cleanup(); return rc; }
   }
   cudaEventRecord(e1, st);

@@ -455,7 +455,8 @@ static int rope_run(hb200_ctx* ctx, float* d_q, const float* d_k, const float* d
   HB_REQUIRE(nseq >= 1 && T >= 1 && (long)nseq * T < (1l << 24) && H >= 1 && Hkv >= 1 && D >= 2 &&
                  D % 2 == 0 && cache_slots >= 1,
              "rope: bad shape");
-  HB_REQUIRE(!(ring && T > 1), "rope: a ring cache takes one token per call");
+  HB_REQUIRE(!ring || T <= cache_slots, "rope: %d tokens per call into a ring of %d slots", T,
+             cache_slots);
   const int B = nseq * T;
   RopeParams p = {d_q, d_k, d_v, static_cast<__half*>(d_k_cache), static_cast<__half*>(d_v_cache),
                   d_pos, B, H, Hkv, D, cache_slots, ring, T, (double)rope_base,
@@ -503,6 +504,17 @@ extern "C" int hb200_rope_kv_write_prefill(hb200_ctx* ctx, float* d_q, const flo
                                            hb200_stream stream) {
   return rope_run(ctx, d_q, d_k, d_v, d_k_cache, d_v_cache, d_pos0, B, T, H, Hkv, D, cache_slots, 0,
                   rope_base, stream);
+}
+
+extern "C" int hb200_rope_kv_write_prefill_angles(hb200_ctx* ctx, float* d_q, const float* d_k,
+                                                  const float* d_v, void* d_k_cache,
+                                                  void* d_v_cache, const int32_t* d_pos0,
+                                                  const double* d_table, int B, int T, int H,
+                                                  int Hkv, int D, int cache_slots, int ring,
+                                                  hb200_stream stream) {
+  HB_REQUIRE(d_table != nullptr, "rope (prefill, angles): null table");
+  return rope_run(ctx, d_q, d_k, d_v, d_k_cache, d_v_cache, d_pos0, B, T, H, Hkv, D, cache_slots,
+                  ring, 0.f, stream, d_table);
 }
 
 extern "C" int hb200_argmax(hb200_ctx* ctx, const float* d_logits, long V, int M, int32_t* d_out,

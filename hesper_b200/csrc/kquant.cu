@@ -640,6 +640,7 @@ struct KQBatchSeg {
 static int kq_batched_q4k(hb200_ctx* ctx, const KQBatchSeg* segs, int nseg, int K,
                           const float* d_x, int M, const KQPre& pre, const float* gamma,
                           float eps, cudaStream_t st) {
+  ScratchUse use(ctx, st);  // staged activations, row scales, split-K partials, tickets
   // tokens per pass: the tensor time of a pass does not depend on it, the activation tile
   // and the accumulator do; K above 8192 keeps the 256-token tiles out of their scratch
   const int cap = K <= 8192 ? 256 : 128;
@@ -681,6 +682,7 @@ static int kq_batched_one(hb200_ctx* ctx, int fmt, const uint8_t* blocks, int K,
     const KQBatchSeg g = {blocks, N, residual, y, 0};
     return kq_batched_q4k(ctx, &g, 1, K, d_x, M, KQPre{nullptr, nullptr, nullptr}, gamma, eps, st);
   }
+  ScratchUse use(ctx, st);  // the f16 arena and the staged activations
   const int rowbytes = fmt == HB200_FMT_Q4_K ? K / 256 * 144 : K / 32 * 34;
   long chunk = (long)(kArenaBytes / ((size_t)K * 2)) / 128 * 128;
   HB_REQUIRE(chunk >= 128 && rowbytes <= 48 * 1024,
@@ -958,6 +960,7 @@ static int kq_gateup_impl(hb200_ctx* ctx, int fmt, const void* d_blocks_gate,
       kScratchGlu + (size_t)64 * N * sizeof(float) <= kScratchLmSplit) {
     // both products on the tensor cores: gate straight into d_y, up into scratch (as many
     // tokens per pass as the scratch region holds, at most 128), then the GLU in place
+    ScratchUse use(ctx, st);  // `u` must survive until the GLU kernel has read it
     float* u = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->d_scratch) + kScratchGlu);
     const int pass =
         kScratchGlu + (size_t)128 * N * sizeof(float) <= kScratchLmSplit ? 128 : 64;

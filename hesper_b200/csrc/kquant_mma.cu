@@ -64,6 +64,7 @@ struct QmParams {
   QmSeg seg[kQmMaxSeg];
   int nseg;
   const uint8_t* xb;     // f16 activations: [K/64][NT rows x 64 f16, operand layout]
+  const float* rowscale; // [NT] power of two each token's row was divided by before rounding
   int K, M;
   int nsplit, bps;       // split-K: CTAs per row tile, super-block boxes per split
   float* part;           // [tile][split][NT tokens][128 rows] partial sums (nsplit > 1)
@@ -285,10 +286,15 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
   };
   auto store_group = [&](int g, const float (&acc)[32]) {
     const int row = row0 + r, m0 = 32 * g;
-    if (row >= sg.N || !ok || m0 >= p.M) return;
+    if (m0 >= p.M) return;  // the same for the whole warp
     const int mcount = min(32, p.M - m0);
+    // lane t fetches token m0 + t's row scale, a shuffle hands it to every row
+    const float my_rs = lane < mcount ? __ldcg(p.rowscale + m0 + lane) : 0.f;
+    float res[32], rs[32];
+#pragma unroll
+    for (int t = 0; t < 32; ++t) rs[t] = __shfl_sync(0xffffffffu, my_rs, t);
+    if (row >= sg.N || !ok) return;
     const size_t o0 = (size_t)m0 * sg.ldy + row;
-    float res[32];
     if (sg.residual) {
 #pragma unroll
       for (int t = 0; t < 32; ++t) res[t] = t < mcount ? sg.residual[o0 + (size_t)t * sg.ldy] : 0.f;
@@ -296,7 +302,7 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
 #pragma unroll
     for (int t = 0; t < 32; ++t)
       if (t < mcount) {
-        float v = acc[t];
+        float v = acc[t] * rs[t];
         if (sg.residual) v = sg.glu ? glu_gate(res[t]) * v : __fadd_rn(v, res[t]);
         sg.y[o0 + (size_t)t * sg.ldy] = v;
       }
@@ -415,6 +421,8 @@ int hb_kq_mma_run_multi(hb200_ctx* ctx, const HbKqSeg* segs, int nseg, int K, in
   }
   p.nseg = nseg;
   p.xb = static_cast<const uint8_t*>(ctx->d_scratch) + kScratchLmSplit;
+  p.rowscale = reinterpret_cast<const float*>(static_cast<const uint8_t*>(ctx->d_scratch) +
+                                              kScratchRowScale);
   p.K = K;
   p.M = M;
   p.part = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->d_scratch) + kScratchSplitK);

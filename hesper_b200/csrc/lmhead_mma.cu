@@ -58,6 +58,10 @@ struct LmSplitParams {
   const float* pre_base;
   const float* pre_gamma;
   float* pre_out;
+  // f16 staging only: the row is divided by a power of two s that brings its largest magnitude
+  // into [2^13, 2^14) -- f16 has 5 exponent bits, an activation above 65504 would round to
+  // infinity and one below 6e-5 lose bits -- and s is stored here for the product's epilogue
+  float* rowscale;     // nullable [M]
 };
 
 struct LmMmaParams {
@@ -71,6 +75,7 @@ struct LmMmaParams {
   int K, M;
   int stages;          // kLmStages or kLmMaxStages
   int table_constant;  // the table is not written by kernels of this stream (weights proper)
+  const float* rowscale;  // nullable [M]: factor the staging divided each token's row by
   uint32_t idesc;
   uint32_t* status;
 };
@@ -85,6 +90,7 @@ __device__ __forceinline__ float widen16(uint16_t h, int dtype) {
 
 __global__ void __launch_bounds__(256) lm_split_kernel(const __grid_constant__ LmSplitParams p) {
   __shared__ double red[8];
+  __shared__ float redf[8];
   pdl_trigger();
   // norm weights are constants of the model: into L1 before the wait on the previous kernel
   for (int i = threadIdx.x * 32; i < p.K; i += 256 * 32) {
@@ -108,8 +114,28 @@ __global__ void __launch_bounds__(256) lm_split_kernel(const __grid_constant__ L
     return;
   }
   const float* xg = p.x + (size_t)m * K;
-  auto emit = [&](int k, const float (&v)[8]) {
+  float inv_s = 1.f;  // 1 / row scale, set before the first emit
+  // block-wide: the power of two that brings `amax` into [2^13, 2^14); stores it, returns 1/s
+  auto row_scale = [&](float amax) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 16));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    if (lane == 0) redf[warp] = amax;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, redf[i]);
+    int e = 13;  // an all-zero (or non-finite) row keeps s = 1
+    if (amax > 0.f && amax <= 3.0e38f) e = min(max(ilogbf(amax), -100), 120);
+    if (tid == 0) p.rowscale[m] = ldexpf(1.f, e - 13);
+    return ldexpf(1.f, 13 - e);
+  };
+  auto emit = [&](int k, const float (&vin)[8]) {
     uint32_t hi[4], lo[4];
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = vin[e] * inv_s;  // exact: a power of two
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       uint16_t h[2], l[2];
@@ -197,6 +223,14 @@ __global__ void __launch_bounds__(256) lm_split_kernel(const __grid_constant__ L
         for (int e = 0; e < 8; ++e) v[i][e] = __fmul_rn(__fmul_rn(v[i][e], rinv), g[e]);
       }
     }
+    if (p.rowscale) {
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < kHeld; ++i)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[i][e]));  // rows past K hold zeros
+      inv_s = row_scale(amax);
+    }
 #pragma unroll
     for (int i = 0; i < kHeld; ++i) {
       const int k = tid * 8 + i * 2048;
@@ -218,6 +252,12 @@ __global__ void __launch_bounds__(256) lm_split_kernel(const __grid_constant__ L
 #pragma unroll
     for (int i = 0; i < 8; ++i) ss += red[i];
     rinv = (float)(1.0 / sqrt(ss / (double)K + (double)p.eps));
+  }
+  if (p.rowscale) {
+    float amax = 0.f;
+    for (int k = tid; k < K; k += 256)
+      amax = fmaxf(amax, fabsf(p.gamma ? __fmul_rn(__fmul_rn(xg[k], rinv), p.gamma[k]) : xg[k]));
+    inv_s = row_scale(amax);
   }
   for (int k = tid * 8; k < K; k += 256 * 8) {
     float v[8];
@@ -350,10 +390,14 @@ __global__ void __launch_bounds__(kLmThreads, 2)
       HB_TMEM_LD32(lo, lane_addr + (uint32_t)(kLmTokens + half * 32));
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       unsigned long long mine = 0ull;  // lane t keeps the key of token half*32 + t
+      // lane t fetches token half*32 + t's row scale (f16 staging), a shuffle hands it around
+      const float my_rs =
+          (p.rowscale && half * 32 + lane < p.M) ? __ldcg(p.rowscale + half * 32 + lane) : 1.f;
 #pragma unroll
       for (int t = 0; t < 32; ++t) {
         const int m = half * 32 + t;
-        const float v = __fadd_rn(__uint_as_float(hi[t]), __uint_as_float(lo[t]));
+        float v = __fadd_rn(__uint_as_float(hi[t]), __uint_as_float(lo[t]));
+        v *= __shfl_sync(0xffffffffu, my_rs, t);  // undo the staging's row scale (exact)
         if (m < p.M && row_ok && p.logits && ok) {
           const size_t o = (size_t)m * p.ldy + (size_t)(row);
           p.logits[o] = p.residual ? __fadd_rn(v, p.residual[o]) : v;
@@ -429,8 +473,11 @@ int hb_gemm16_split_pre(hb200_ctx* ctx, int dtype, int K, const float* d_x, int 
              "batched 16-bit product: K=%d needs %zu bytes of activation scratch", K, xb_bytes);
   HB_REQUIRE(M >= 1 && M <= (single ? single : kLmTokens), "batched 16-bit product: M=%d", M);
   uint8_t* xb = static_cast<uint8_t*>(ctx->d_scratch) + kScratchLmSplit;
+  float* rowscale = dtype == 1 ? reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->d_scratch) +
+                                                         kScratchRowScale)
+                               : nullptr;  // bf16 has the exponent range of f32
   LmSplitParams sp = {d_x, d_rms_gamma, rms_eps, K, M, dtype, single, xb,
-                      d_pre_base, d_pre_gamma, d_pre_out};
+                      d_pre_base, d_pre_gamma, d_pre_out, rowscale};
   HB_CUDA(launch_pdl(lm_split_kernel, dim3(single ? single : kLmTokens), dim3(256), 0, st,
                      ctx->pdl, sp));
   return HB200_OK;
@@ -461,6 +508,9 @@ int hb_gemm16_mma(hb200_ctx* ctx, const void* d_table, int dtype, long V, int K,
   p.logits = d_y;
   p.residual = d_residual;
   p.keys = d_keys;
+  p.rowscale = dtype == 1 ? reinterpret_cast<const float*>(static_cast<const uint8_t*>(ctx->d_scratch) +
+                                                           kScratchRowScale)
+                          : nullptr;
   p.V = V;
   p.ldy = ldy;
   p.K = K;
@@ -490,6 +540,7 @@ int hb_gemm16_mma(hb200_ctx* ctx, const void* d_table, int dtype, long V, int K,
 int hb_lmhead_mma_run(hb200_ctx* ctx, const void* d_table, int dtype, long V, int K,
                       const float* d_x, int M, const float* d_rms_gamma, float rms_eps,
                       float* d_logits, unsigned long long* d_keys, cudaStream_t st) {
+  ScratchUse use(ctx, st);  // the staged hi / lo activations
   const int rc = hb_gemm16_split(ctx, dtype, K, d_x, M, d_rms_gamma, rms_eps, 0, st);
   if (rc != HB200_OK) return rc;
   return hb_gemm16_mma(ctx, d_table, dtype, V, K, M, d_logits, nullptr, V, d_keys, 1, st);

@@ -330,6 +330,25 @@ class GemmaModel:
         logits = _from_ptr(self.ctx._lib.hb200_gemma_local_logits(self._h), n * lv, np.float32)
         return toks, logits.reshape(n, lv)
 
+    @property
+    def chunk(self) -> int:
+        """Prompt positions per sequence one prefill pass takes."""
+        return int(self.ctx._lib.hb200_gemma_chunk(self._h))
+
+    def prefill(self, tokens: "torch.Tensor"):
+        """One pass over T consecutive prompt positions per sequence (tokens int32 [B, T],
+        T <= chunk); returns what step() returns, for each sequence's last position."""
+        from .models import _from_ptr
+        assert tokens.dtype == torch.int32 and tokens.is_cuda and tokens.is_contiguous()
+        assert tokens.shape[0] == self.batch
+        check(self.ctx._lib.hb200_gemma_prefill(self._h, tokens.data_ptr(), int(tokens.shape[1]),
+                                                1, None))
+        torch.cuda.synchronize()
+        n, lv = self.batch, len(self.plan.vocab_rows)
+        toks = _from_ptr(self.ctx._lib.hb200_gemma_tokens(self._h), n, np.int32)
+        logits = _from_ptr(self.ctx._lib.hb200_gemma_local_logits(self._h), n * lv, np.float32)
+        return toks, logits.reshape(n, lv)
+
     def close(self):
         if getattr(self, "_h", None) is not None and self._h.value:
             self.ctx._lib.hb200_gemma_destroy(self._h)

@@ -277,6 +277,19 @@ int hb200_attn_prefill(hb200_ctx *ctx, const void *d_q, int q_is_f16, const void
                        int D, int max_seq, int window, float scale, void *d_workspace,
                        size_t workspace_bytes, float *d_out, hb200_stream stream);
 
+/* The same on a RING cache [B][Hkv][slots][D]: position p lives in slot p % slots (written by
+ * hb200_rope_kv_write with ring != 0, or hb200_rope_kv_write_prefill_angles), d_seqlens are the
+ * true lengths after the T tokens (they may exceed slots), and every query sees the last
+ * `window` positions up to its own (rule of flashAttentionSWAKernel,
+ * Hesper/WGSL/FlashAttention.lean:1621-1624).  Needs 1 <= window and window + T - 1 <= slots, so
+ * that the T positions written before the call have not displaced anything the first of the T
+ * queries still sees.  T = 1 is a decode step of a sliding-window layer.  Workspace:
+ * hb200_attn_prefill_workspace_bytes(ctx, B, T, H, Hkv, D, slots). */
+int hb200_attn_ring(hb200_ctx *ctx, const void *d_q, int q_is_f16, const void *d_k,
+                    const void *d_v, const int32_t *d_seqlens, int B, int T, int H, int Hkv,
+                    int D, int slots, int window, float scale, void *d_workspace,
+                    size_t workspace_bytes, float *d_out, hb200_stream stream);
+
 /* Decode attention for callers that cannot hand over scratch memory.  No counterpart in
  * the reference (there the Lean side allocates the V11 partial buffers with the model).
  *
@@ -332,6 +345,14 @@ int hb200_rope_kv_write(hb200_ctx *ctx, float *d_q, const float *d_k, const floa
                         void *d_k_cache, void *d_v_cache, const int32_t *d_pos, int B, int H,
                         int Hkv, int D, int cache_slots, int ring, float rope_base,
                         hb200_stream stream);
+
+/* The prompt-chunk writer below with the angles taken from hb200_rope_table (d_table
+ * [B*T][D/2][2]) and, with ring != 0, slot = position % cache_slots (T <= cache_slots). */
+int hb200_rope_kv_write_prefill_angles(hb200_ctx *ctx, float *d_q, const float *d_k,
+                                       const float *d_v, void *d_k_cache, void *d_v_cache,
+                                       const int32_t *d_pos0, const double *d_table, int B, int T,
+                                       int H, int Hkv, int D, int cache_slots, int ring,
+                                       hb200_stream stream);
 
 /* The same for T new tokens per sequence (prompt chunk): d_q [B][T][H][D], d_k / d_v
  * [B][T][Hkv][D], token t of sequence b is at position d_pos0[b] + t.  Linear caches only.
@@ -532,6 +553,15 @@ int hb200_gemma_reset(hb200_gemma *m, hb200_stream stream);
 int hb200_gemma_set_position(hb200_gemma *m, int pos, hb200_stream stream);
 /* One decode step on every rank: Gemma4.forwardSingleToken (Hesper/Models/Gemma4.lean:2558). */
 int hb200_gemma_step(hb200_gemma *m, const int32_t *d_tokens, hb200_stream stream);
+/* One pass over T consecutive prompt positions of every sequence: Gemma4.forwardPrefillBatch
+ * (Hesper/Models/Gemma4.lean:1333).  d_tokens [batch][T], 1 <= T <= hb200_gemma_chunk(m)
+ * (= 256 / batch rows per pass, capped by HB200_GEMMA_CHUNK when the model is created).  Same
+ * kernels as a step at batch * T rows: batched products, RoPE + KV write of the T positions,
+ * causal attention (sliding-window layers keep a ring of window + chunk - 1 slots).
+ * want_token != 0 also runs the LM head on each sequence's last position and logs its token. */
+int hb200_gemma_prefill(hb200_gemma *m, const int32_t *d_tokens, int T, int want_token,
+                        hb200_stream stream);
+int hb200_gemma_chunk(const hb200_gemma *m);
 const float *hb200_gemma_local_logits(const hb200_gemma *m);
 const int32_t *hb200_gemma_tokens(const hb200_gemma *m);
 /* Gemma4.generate (Hesper/Models/Gemma4.lean:3212).  prompt_len = 0 continues from the

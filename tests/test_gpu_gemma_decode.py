@@ -23,27 +23,87 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LOGIT_TOL = 2e-3
 
 
-def test_tp1_forced_steps(ctx, oracle):
+@pytest.mark.parametrize("batch", [2, 20])
+def test_tp1_forced_steps(ctx, oracle, batch):
+    """batch 2: the streaming matvec kernels; batch 20: the tensor-core products (f16
+    activations with a power-of-two scale per row -- this model's FFN intermediates reach a
+    few 1e4), which is the path the batch-32 / batch-256 decode numbers run on.  This random
+    model's attention scores reach the thousands, where the f16 rounding of q in FAST mode
+    moves a score by ~0.5 and a near-tie between two positions then shows in the logits (seen
+    in 2 of 20 sequences, with the streaming kernels as well): the wide batch runs PRECISE
+    attention so that the comparison is about the products."""
     from oracle.oracle import GemmaOracle
     S = SMALL_GEMMA
-    w = tp.random_gemma_weights(S, seed=21)
+    if batch > 2:
+        ctx.set_attn_mode(ctx.ATTN_PRECISE)
+    try:
+        w = tp.random_gemma_weights(S, seed=21)
+        p = tp.plan(S, 0, 1)
+        model = GemmaModel(ctx, S, tp.shard_weights(S, w, p), p, None, batch=batch, max_new_tokens=8)
+        orcs = [GemmaOracle(S, w) for _ in range(batch)]
+        rng = np.random.default_rng(4)
+        toks = rng.integers(0, S.vocab, (batch, 1)).astype(np.int32).tolist()
+        # 40 steps: past the 16-position window, so the ring cache wraps more than twice
+        for t in range(40):
+            cur = np.array([toks[b][t] for b in range(batch)], np.int32)
+            g_tok, g_logits = model.step(torch.from_numpy(cur).cuda())
+            for b in range(batch):
+                o_tok, o_logits = orcs[b].step(int(cur[b]))
+                sd = float(np.std(o_logits))
+                assert np.max(np.abs(g_logits[b] - o_logits)) < LOGIT_TOL * sd
+                if int(g_tok[b]) != o_tok:
+                    top2 = np.partition(o_logits, -2)[-2:]
+                    assert top2[1] - top2[0] <= 2 * LOGIT_TOL * sd
+                toks[b].append(o_tok)
+    finally:
+        ctx.set_attn_mode(ctx.ATTN_FAST)
+    ctx.check()
+    for o in orcs:
+        o.close()
+    model.close()
+
+
+@pytest.mark.parametrize("chunk,batch", [(5, 2), (7, 1), (0, 3)])
+def test_prompt_chunks_match_the_oracle(ctx, oracle, chunk, batch, monkeypatch):
+    """Prompt passes of several positions per sequence (Gemma4.forwardPrefillBatch,
+    Hesper/Models/Gemma4.lean:1333): a 45-token prompt fed in chunks, the logits of every chunk's
+    last position and of 8 decode steps after it against the oracle, which takes the same tokens
+    one by one.  With chunk 5 / 7 the sliding-window layers run on rings of 16 + chunk - 1 slots
+    that wrap twice inside the prompt; chunk 0 = the default (256 / batch rows per pass: the
+    whole prompt at once, linear caches because the ring would be as long as max_seq)."""
+    from oracle.oracle import GemmaOracle
+    S = SMALL_GEMMA
+    if chunk:
+        monkeypatch.setenv("HB200_GEMMA_CHUNK", str(chunk))
+    w = tp.random_gemma_weights(S, seed=23)
     p = tp.plan(S, 0, 1)
-    model = GemmaModel(ctx, S, tp.shard_weights(S, w, p), p, None, batch=2, max_new_tokens=8)
-    orcs = [GemmaOracle(S, w) for _ in range(2)]
-    rng = np.random.default_rng(4)
-    toks = rng.integers(0, S.vocab, (2, 1)).astype(np.int32).tolist()
-    # 40 steps: past the 16-position window, so the ring cache wraps more than twice
-    for t in range(40):
-        cur = np.array([toks[b][t] for b in range(2)], np.int32)
-        g_tok, g_logits = model.step(torch.from_numpy(cur).cuda())
-        for b in range(2):
-            o_tok, o_logits = orcs[b].step(int(cur[b]))
+    model = GemmaModel(ctx, S, tp.shard_weights(S, w, p), p, None, batch=batch, max_new_tokens=8)
+    T = model.chunk
+    assert T == (chunk if chunk else 256 // batch)
+    orcs = [GemmaOracle(S, w) for _ in range(batch)]
+    prompt = np.random.default_rng(6).integers(0, S.vocab, (batch, 45)).astype(np.int32)
+
+    def compare(g_tok, g_logits, o_out):
+        for b in range(batch):
+            o_tok, o_logits = o_out[b]
             sd = float(np.std(o_logits))
             assert np.max(np.abs(g_logits[b] - o_logits)) < LOGIT_TOL * sd
             if int(g_tok[b]) != o_tok:
                 top2 = np.partition(o_logits, -2)[-2:]
                 assert top2[1] - top2[0] <= 2 * LOGIT_TOL * sd
-            toks[b].append(o_tok)
+
+    o_out = None
+    for p0 in range(0, 45, T):
+        part = np.ascontiguousarray(prompt[:, p0:p0 + T])
+        g_tok, g_logits = model.prefill(torch.from_numpy(part).cuda())
+        for t in range(part.shape[1]):
+            o_out = [orcs[b].step(int(part[b, t])) for b in range(batch)]
+        compare(g_tok, g_logits, o_out)
+    for _ in range(8):  # decode on the caches the chunks left
+        cur = np.array([o_out[b][0] for b in range(batch)], np.int32)
+        g_tok, g_logits = model.step(torch.from_numpy(cur).cuda())
+        o_out = [orcs[b].step(int(cur[b])) for b in range(batch)]
+        compare(g_tok, g_logits, o_out)
     ctx.check()
     for o in orcs:
         o.close()

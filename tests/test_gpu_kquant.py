@@ -121,6 +121,36 @@ def test_batched_tensor_core_path(ctx, oracle, fmt, K, N, M):
     _check(y[rows], oracle.kquant_matvec(fmt, blocks, K, N, xn))
 
 
+@pytest.mark.parametrize("fmt", [12, 8])
+def test_batched_path_over_the_f16_range(ctx, oracle, fmt):
+    """The tensor-core path rounds activations to f16, whose largest finite value is 65504: a
+    FFN intermediate of a few 1e4 is ordinary.  Every staged row is scaled by its own power of
+    two, so rows of magnitude 1e-6, 1, 3e4 and 1e6 in one call all meet the 1e-3 bar, also
+    through the gate/up GLU epilogue (per row the same bar as for unit-magnitude inputs)."""
+    K, N, M = 2560, 384, 20
+    rng = np.random.default_rng(500 + fmt)
+    blocks = formats.random_kquant(rng, fmt, N, K)
+    mags = np.array([1e-6, 1.0, 3e4, 1e6], np.float32)[np.arange(M) % 4]
+    x = (rng.standard_normal((M, K)) * mags[:, None]).astype(np.float32)
+    layer = LinearLayer.create_from_bytes(ctx, blocks, fmt, K, N)
+    y = layer.forward(_dev(x)).cpu().numpy()
+    ctx.check()
+    ref = oracle.kquant_matvec(fmt, blocks, K, N, x)
+    assert np.isfinite(y).all()
+    for m in range(M):
+        assert np.max(np.abs(y[m] - ref[m])) <= TOL * np.max(np.abs(ref[m])), (m, mags[m])
+    if fmt == 12:
+        up = formats.random_kquant(rng, fmt, N, K)
+        lu = LinearLayer.create_from_bytes(ctx, up, fmt, K, N)
+        xs = (rng.standard_normal((M, K)) * np.minimum(mags, 30.0)[:, None]).astype(np.float32)
+        g = LinearLayer.forward_fused_gate_up(layer, lu, _dev(xs)).cpu().numpy()
+        ctx.check()
+        gref = oracle.kquant_gateup_gelu(blocks, up, fmt, K, N, xs)
+        assert np.isfinite(g).all()
+        for m in range(M):
+            assert np.max(np.abs(g[m] - gref[m])) <= 2e-3 * np.max(np.abs(gref[m])), (m, mags[m])
+
+
 def test_batched_row_chunks_of_the_arena(ctx, oracle):
     # 2560 x 16384 f16 = 80 MB: more than the 64 MB arena, so two row chunks
     K, N, M = 2560, 16384, 20
