@@ -677,6 +677,9 @@ def run_case(name: str) -> int:
 
 
 def main():
+    # stdout carries the one JSON line; NCCL's own log lines (its version banner at
+    # NCCL_DEBUG=VERSION, everything at INFO) go to stderr instead of in front of it
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)

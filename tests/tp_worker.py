@@ -182,6 +182,7 @@ def main():
     p = tp.plan(S, rank, world)
     model = hb.GemmaModel(ctx, S, tp.shard_weights(S, w, p), p, comm, batch=2, max_new_tokens=8)
     ok = True
+    why = []
     if rank == 0:
         from oracle.oracle import GemmaOracle
         orcs = [GemmaOracle(S, w) for _ in range(2)]
@@ -197,12 +198,15 @@ def main():
             for b in range(2):
                 o_tok, o_logits = orcs[b].step(int(toks[b]))
                 sd = float(np.std(o_logits))
-                if np.max(np.abs(logits[b] - o_logits)) >= 2e-3 * sd:
+                dev = float(np.max(np.abs(logits[b] - o_logits))) / sd
+                if dev >= 2e-3:
                     ok = False
+                    why.append(f"step {t} seq {b}: logits off by {dev:.2e} of their spread")
                 if int(g_tok[b]) != o_tok:
                     top2 = np.partition(o_logits, -2)[-2:]
                     if top2[1] - top2[0] > 4e-3 * sd:
                         ok = False
+                        why.append(f"step {t} seq {b}: token {int(g_tok[b])} != {o_tok}")
                 nxt[b] = o_tok
         box = [nxt]
         dist.broadcast_object_list(box, src=0)
@@ -214,6 +218,8 @@ def main():
     dist.all_gather_object(oks, bool(ok_ar))
     flag = [ok and all(oks)]
     dist.broadcast_object_list(flag, src=0)
+    if rank == 0 and not flag[0]:
+        print(f"exchange checks per rank: {oks}; model: {why[:6]}", flush=True)
     model.close()
     comm.close()
     dist.barrier()
