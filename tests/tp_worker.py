@@ -19,7 +19,13 @@ def check_allreduce(hb, ctx, comm, rank, world):
     exactly the f32 sum taken in rank order (and the u64 maximum), call after call and when
     replayed from a CUDA graph."""
     import ctypes as C
-    ok = comm.peer_attached or os.environ.get("HB200_TP_NO_PEER", "0") == "1"
+    fails = []
+
+    def need(cond, what):
+        if not cond:
+            fails.append(what)
+
+    need(comm.peer_attached or os.environ.get("HB200_TP_NO_PEER", "0") == "1", "peers attached")
     st = torch.cuda.Stream()
     for it, n in enumerate([2560, 2560 * 2, 2560 * 64, 4, 2560 * 7] * 4):
         parts = [np.random.default_rng(1000 * it + r).standard_normal(n).astype(np.float32)
@@ -33,16 +39,16 @@ def check_allreduce(hb, ctx, comm, rank, world):
         st.synchronize()
         got = x.cpu().numpy()
         if comm.peer_attached:
-            ok = ok and np.array_equal(got, want)          # rank-order sum, bit for bit
+            need(np.array_equal(got, want), f"all-reduce n={n} call {it}: rank-order sum, bit for bit")
         else:
-            ok = ok and np.allclose(got, want, rtol=1e-5, atol=1e-5)
+            need(np.allclose(got, want, rtol=1e-5, atol=1e-5), f"all-reduce n={n} call {it}")
     # u64 maximum (argmax keys)
     keys = torch.from_numpy(np.random.default_rng(7 + rank).integers(0, 2**62, 8)).cuda()
     allk = [np.random.default_rng(7 + r).integers(0, 2**62, 8) for r in range(world)]
     hb.load().hb200_tp_allreduce_max_u64(comm.handle, C.c_void_p(keys.data_ptr()), C.c_size_t(8),
                                          C.c_void_p(st.cuda_stream))
     st.synchronize()
-    ok = ok and np.array_equal(keys.cpu().numpy(), np.max(np.stack(allk), axis=0))
+    need(np.array_equal(keys.cpu().numpy(), np.max(np.stack(allk), axis=0)), "u64 maximum")
     # the exchange fused with the RMSNorm (+ residual) that follows it: rank-order sum, then
     # the stand-alone kernel's arithmetic.  K = 2560 takes the flag-in-data kernel (up to 256
     # tokens), K = 4096 the flagged one (up to 64), 300 tokens the unfused route.
@@ -66,16 +72,17 @@ def check_allreduce(hb, ctx, comm, rank, world):
                                             C.c_void_p(gamma.data_ptr()), C.c_void_p(add.data_ptr()),
                                             C.c_float(1e-6), M, K, C.c_void_p(y.data_ptr()),
                                             C.c_void_p(st.cuda_stream))
-        ok = ok and rc == 0
+        need(rc == 0, f"fused exchange M={M} K={K}: rc {rc}")
         rc = lib.hb200_rmsnorm(ctx.handle, C.c_void_p(t.data_ptr()), C.c_void_p(gamma.data_ptr()),
                                C.c_void_p(add.data_ptr()), C.c_float(1e-6), M, K,
                                C.c_void_p(want.data_ptr()), C.c_void_p(st.cuda_stream))
-        ok = ok and rc == 0
+        need(rc == 0, "rmsnorm")
         st.synchronize()
-        if comm.peer_attached and K == 2560:
-            ok = ok and bool(torch.equal(y, want))
+        # the peer kernels add in rank order; 300 tokens go through NCCL, whose order is its own
+        if comm.peer_attached and K == 2560 and M <= 256:
+            need(bool(torch.equal(y, want)), f"fused exchange M={M} K={K}: bits of the stand-alone kernel")
         else:
-            ok = ok and bool(torch.allclose(y, want, rtol=1e-5, atol=1e-5))
+            need(bool(torch.allclose(y, want, rtol=1e-5, atol=1e-5)), f"fused exchange M={M} K={K}")
     # graph replay: the sequence number advances on the device
     x = torch.full((2560,), float(rank + 1), device="cuda")
     torch.cuda.synchronize()
@@ -89,9 +96,11 @@ def check_allreduce(hb, ctx, comm, rank, world):
         st.synchronize()
     tot = float(sum(range(1, world + 1)))
     expect = tot * float(world) ** 11  # 12 all-reduces: the first sums the ranks, 11 multiply by W
-    ok = ok and bool(torch.all(x == expect).item())
+    need(bool(torch.all(x == expect).item()), f"graph replay: {float(x[0].item())} != {expect}")
     ctx.check()
-    return ok
+    if fails:
+        print(f"rank {rank}: exchange checks failed: {fails[:8]}", flush=True)
+    return not fails
 
 
 def withheld_exchange(hb, ctx, comm, rank, world):
