@@ -120,6 +120,7 @@ SIGNATURES = {
     "hb200_gemma_destroy": (_i, [_vp]),
     "hb200_gemma_reset": (_i, [_vp, _vp]),
     "hb200_gemma_set_position": (_i, [_vp, _i, _vp]),
+    "hb200_bitlinear_qkv_rope": (_i, [_vp, C.POINTER(BitLinearSeg), _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "hb200_gemma_step": (_i, [_vp, _vp, _vp]),
     "hb200_gemma_prefill": (_i, [_vp, _vp, _i, _i, _vp]),
     "hb200_gemma_chunk": (_i, [_vp]),

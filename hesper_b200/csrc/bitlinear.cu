@@ -573,6 +573,34 @@ extern "C" int hb200_bitlinear_forward_multi(hb200_ctx* ctx, const hb200_bitline
   return rt == 4 ? bl_dispatch_wpl<4, false>(ctx, p, st) : bl_dispatch_wpl<2, false>(ctx, p, st);
 }
 
+extern "C" int hb200_bitlinear_qkv_rope(hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int K,
+                                        const float* d_x, const float* d_rms_gamma, float rms_eps,
+                                        const double* d_rope_table, const int32_t* d_pos,
+                                        void* d_k_cache, void* d_v_cache, int H, int Hkv, int D,
+                                        int cache_slots, int ring, hb200_stream stream) {
+  HB_REQUIRE(ctx && segs && d_x && d_rope_table && d_pos && d_k_cache && d_v_cache,
+             "bitlinear q/k/v + RoPE: null pointer");
+  HB_REQUIRE(H >= 1 && Hkv >= 1 && D >= 2 && D % 2 == 0 && cache_slots >= 1,
+             "bitlinear q/k/v + RoPE: H=%d Hkv=%d D=%d slots=%d", H, Hkv, D, cache_slots);
+  HB_REQUIRE(segs[0].N == H * D && segs[1].N == Hkv * D && segs[2].N == Hkv * D,
+             "bitlinear q/k/v + RoPE: tensors of %d, %d, %d rows for %d/%d heads of %d", segs[0].N,
+             segs[1].N, segs[2].N, H, Hkv, D);
+  HB_REQUIRE(segs[0].d_y && segs[1].d_y && segs[2].d_y,
+             "bitlinear q/k/v + RoPE: q, k and v need f32 output rows (k, v: scratch)");
+  int rc = bl_check_common(ctx, K, 1, d_x);
+  if (rc) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const HbRope rope = {d_rope_table, d_pos, d_k_cache, d_v_cache, D, cache_slots, ring};
+  rc = hb_bl_mv_run(ctx, segs, 3, K, 0, d_x, d_rms_gamma, rms_eps, nullptr, st, &rope);
+  if (rc <= 0) return rc;
+  // a shape the fused kernel does not cover: the two launches it stands for
+  rc = hb200_bitlinear_forward_multi(ctx, segs, 3, K, d_x, 1, d_rms_gamma, rms_eps, nullptr, stream);
+  if (rc) return rc;
+  return hb200_rope_kv_write_angles(ctx, segs[0].d_y, segs[1].d_y, segs[2].d_y, d_k_cache,
+                                    d_v_cache, d_pos, d_rope_table, 1, H, Hkv, D, cache_slots,
+                                    ring, stream);
+}
+
 extern "C" int hb200_bitlinear_forward(hb200_ctx* ctx, const void* d_packed,
                                        const float* d_scale, int K, int N, const float* d_x,
                                        int M, const float* d_rms_gamma, float rms_eps,

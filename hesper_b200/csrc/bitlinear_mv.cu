@@ -25,7 +25,12 @@
 //     identically on both operands), and with that permutation the B fragments of a column
 //     block are simply its 256 int8 activations in natural order;
 //   * warps own column blocks; their int32 row partials meet in shared memory by atomicAdd
-//     (integer: any order gives the same bits).
+//     (integer: any order gives the same bits);
+//   * ROPE variant (fused q/k/v of one token): the rows of every q and k head are dealt out in
+//     the order d, d + D/2, d + 1, d + 1 + D/2, ... so that a CTA holds both elements of every
+//     rotation pair, and the epilogue applies the NeoX rotation (the arithmetic of rope.cuh, in
+//     double) and writes q as f32 and k / v as f16 straight into the KV cache: the separate
+//     RoPE + KV-write launch of a decode step disappears.
 #include "common.cuh"
 
 namespace hb {
@@ -59,6 +64,12 @@ struct BmParams {
   float eps;
   float* act_scale;
   uint32_t* status;
+  // ROPE variant: segments are q, k, v of ONE token of one sequence
+  const double2* rope_table;  // [D/2] (cos, sin) of the token's angles
+  const int32_t* pos;         // [1] the token's position
+  __half* k_cache;            // [Hkv][slots][D]
+  __half* v_cache;
+  int D, slots, ring;
 };
 
 // Rows are K/4 bytes, a multiple of 64: laid end to end, the same byte of every row would fall
@@ -92,8 +103,16 @@ __device__ __forceinline__ void bm_mma(int (&c)[4], uint32_t a0, uint32_t a1, ui
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Row `o` of a q / k segment in the ROPE row order -> the tensor's own row: inside a head the
+// virtual rows 2j, 2j + 1 are the rotation pair (j, j + D/2).
+__device__ __forceinline__ int bm_rope_row(int o, int D) {
+  const int h = o / D, j = o - h * D;
+  return h * D + (j >> 1) + (j & 1) * (D >> 1);
+}
+
 // GU: fused ReLU^2 GLU of a gate and an up tensor (tiles of 8 gate rows + 8 up rows).
-template <bool GU>
+// ROPE: q / k / v of one token with the rotation and the KV-cache write in the epilogue.
+template <bool GU, bool ROPE>
 __global__ void __launch_bounds__(kBmThreads, 2) bl_mv_kernel(const __grid_constant__ BmParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -108,7 +127,7 @@ __global__ void __launch_bounds__(kBmThreads, 2) bl_mv_kernel(const __grid_const
   const int b = blockIdx.x;
   const int u0 = b * p.per + min(b, p.rem);
   const int u1 = u0 + p.per + (b < p.rem ? 1 : 0);
-  const int v0 = GU ? u0 << 4 : u0, v1 = GU ? u1 << 4 : u1;
+  const int v0 = GU ? u0 << 4 : (ROPE ? u0 << 1 : u0), v1 = GU ? u1 << 4 : (ROPE ? u1 << 1 : u1);
   const int nrows = v1 - v0;
   const int ntiles = (nrows + 15) >> 4;
 
@@ -146,7 +165,9 @@ __global__ void __launch_bounds__(kBmThreads, 2) bl_mv_kernel(const __grid_const
 #pragma unroll
           for (int s = 1; s < kBmMaxSeg; ++s)
             if (s < p.nseg && vr >= p.seg[s].row0) sg = s;
-          src = p.seg[sg].w + (size_t)(vr - p.seg[sg].row0) * rowbytes;
+          int o = vr - p.seg[sg].row0;
+          if (ROPE && sg < 2) o = bm_rope_row(o, p.D);
+          src = p.seg[sg].w + (size_t)o * rowbytes;
         }
         bulk_g2s_stream(wbase + (size_t)(16 * j + lane) * stride, src, (uint32_t)rowbytes,
                         &bars[j], pol);
@@ -341,7 +362,45 @@ __global__ void __launch_bounds__(kBmThreads, 2) bl_mv_kernel(const __grid_const
   __syncthreads();
 
   // ---- value = code - 1: subtract sum(q); scale, epilogue, store ----------------------------
-  if (!GU) {
+  if (ROPE) {
+    int pos = __ldcg(p.pos);
+    int slot = p.ring ? pos % p.slots : pos;
+    slot = slot < 0 ? 0 : (slot >= p.slots ? p.slots - 1 : slot);
+    const int D = p.D, half = D >> 1;
+    for (int lr = 2 * tid; lr < nrows; lr += 2 * kBmThreads) {  // a pair of virtual rows
+      const int vr = v0 + lr;
+      int sg = 0;
+#pragma unroll
+      for (int s = 1; s < kBmMaxSeg; ++s)
+        if (s < p.nseg && vr >= p.seg[s].row0) sg = s;
+      const BmSeg& S = p.seg[sg];
+      const int o = vr - S.row0;  // even
+      float ws = wscale[0];
+#pragma unroll
+      for (int s = 1; s < kBmMaxSeg; ++s) ws = sg == s ? wscale[s] : ws;
+      const float y0 = __fmul_rn(__fmul_rn((float)(part[lr] - sumq_total), dtok), ws);
+      const float y1 = __fmul_rn(__fmul_rn((float)(part[lr + 1] - sumq_total), dtok), ws);
+      const int h = o / D, j = o - h * D;
+      if (sg < 2) {
+        // rotation pair (d, d + D/2) of head h: the arithmetic of rope_kv_element
+        const int d = j >> 1;
+        const double2 a = p.rope_table[d];
+        const double x0 = y0, x1 = y1;
+        const float r0 = (float)(x0 * a.x - x1 * a.y), r1 = (float)(x0 * a.y + x1 * a.x);
+        if (sg == 0) {
+          S.y[h * D + d] = r0;
+          S.y[h * D + d + half] = r1;
+        } else {
+          __half* dst = p.k_cache + ((size_t)h * p.slots + slot) * D;
+          dst[d] = __float2half_rn(r0);
+          dst[d + half] = __float2half_rn(r1);
+        }
+      } else {
+        __half* dst = p.v_cache + ((size_t)h * p.slots + slot) * D;
+        *reinterpret_cast<__half2*>(dst + j) = __floats2half2_rn(y0, y1);
+      }
+    }
+  } else if (!GU) {
     for (int lr = tid; lr < nrows; lr += kBmThreads) {
       const int total = part[lr] - sumq_total;
       const int vr = v0 + lr;
@@ -379,7 +438,7 @@ using namespace hb;
 // error.
 int hb_bl_mv_run(hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int nseg, int K, int gu,
                  const float* d_x, const float* gamma, float eps, float* d_act_scale,
-                 cudaStream_t st) {
+                 cudaStream_t st, const HbRope* rope) {
   if (ctx->mv_mode == 0 || (K & 255)) return 1;
   long rows = 0;
   if (gu) {
@@ -388,11 +447,17 @@ int hb_bl_mv_run(hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int nseg, int 
   } else {
     for (int s = 0; s < nseg; ++s) rows += segs[s].N;
   }
+  if (rope) {  // q, k, v of one token: whole heads, pairs of rows are the unit of the split
+    if (gu || nseg != 3 || rope->D < 2 || (rope->D & 1) || segs[0].N % rope->D ||
+        segs[1].N % rope->D || segs[2].N != segs[1].N)
+      return 1;
+  }
   if (rows > (1L << 30)) return 1;
-  const long units = gu ? rows >> 4 : rows;
+  const int ushift = gu ? 4 : (rope ? 1 : 0);  // rows per unit of the split: 16, 2 or 1
+  const long units = rows >> ushift;
   const int grid = (int)(units < ctx->sm_count ? units : ctx->sm_count);
   const int per = (int)(units / grid), rem = (int)(units % grid);
-  const int rows_max = (per + (rem ? 1 : 0)) << (gu ? 4 : 0);
+  const int rows_max = (per + (rem ? 1 : 0)) << ushift;
   const int rows_cap = (rows_max + 15) & ~15;
   if (rows_cap > 16 * kBmMaxTiles) return 1;
   const size_t smem = bm_smem(rows_cap, rows_max, K).total;
@@ -418,7 +483,17 @@ int hb_bl_mv_run(hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int nseg, int 
   p.eps = eps;
   p.act_scale = d_act_scale;
   p.status = ctx->d_status;
-  void (*kern)(BmParams) = gu ? bl_mv_kernel<true> : bl_mv_kernel<false>;
+  if (rope) {
+    p.rope_table = reinterpret_cast<const double2*>(rope->table);
+    p.pos = rope->pos;
+    p.k_cache = static_cast<__half*>(rope->k_cache);
+    p.v_cache = static_cast<__half*>(rope->v_cache);
+    p.D = rope->D;
+    p.slots = rope->slots;
+    p.ring = rope->ring;
+  }
+  void (*kern)(BmParams) = gu ? bl_mv_kernel<true, false>
+                              : (rope ? bl_mv_kernel<false, true> : bl_mv_kernel<false, false>);
   int rc = hb_func_smem(ctx, reinterpret_cast<const void*>(kern), smem);
   if (rc != HB200_OK) return rc;
   HB_CUDA(launch_pdl(kern, dim3(grid), dim3(kBmThreads), smem, st, ctx->pdl, p));

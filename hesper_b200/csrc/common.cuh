@@ -313,9 +313,18 @@ struct ScratchUse {
 };
 
 // one-token ternary matvec on mma.sync (bitlinear_mv.cu); 1 = shape not covered
+// rope != nullptr: the three tensors are q, k, v of ONE token; RoPE and the f16 KV-cache write
+// run in the kernel's epilogue (q lands rotated in segs[0].d_y, k and v only in the caches)
+struct HbRope {
+  const double* table;  // [D/2][2] (cos, sin), from hb200_rope_table
+  const int32_t* pos;   // [1]
+  void* k_cache;        // [Hkv][slots][D] f16 of the token's sequence
+  void* v_cache;
+  int D, slots, ring;
+};
 int hb_bl_mv_run(struct hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int nseg, int K, int gu,
                  const float* d_x, const float* gamma, float eps, float* d_act_scale,
-                 cudaStream_t st);
+                 cudaStream_t st, const HbRope* rope = nullptr);
 // one-token Q4_K / Q8_0 matvec on mma.sync (kquant_mv.cu); 1 = shape not covered
 int hb_kq_mv_run(struct hb200_ctx* ctx, int fmt, const hb200_kquant_seg* segs, int nseg, int K,
                  int gu, const float* d_x, const float* pre_base, const float* pre_gamma,

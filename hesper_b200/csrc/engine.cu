@@ -73,11 +73,18 @@ int enqueue_step(hb200_bitnet* m, const int32_t* d_tokens, bool lm_head, cudaStr
     };
     __half* kc = m->kcache + (size_t)l * layer_cache_elems(m);
     __half* vc = m->vcache + (size_t)l * layer_cache_elems(m);
-    rc = hb200_bitlinear_forward_multi(ctx, segs, 3, Hd, m->x, B, L.attn_norm, c.rms_eps, nullptr, st);
-    if (rc) return rc;
-    rc = hb200_rope_kv_write_angles(ctx, m->q, m->k, m->v, kc, vc, m->pos, m->rope_tab, B,
-                                    c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq, 0, st);
-    if (rc) return rc;
+    if (B == 1) {  // one launch: RoPE and the KV write are the matvec's epilogue
+      rc = hb200_bitlinear_qkv_rope(ctx, segs, Hd, m->x, L.attn_norm, c.rms_eps, m->rope_tab,
+                                    m->pos, kc, vc, c.n_heads, c.n_kv_heads, c.head_dim,
+                                    c.max_seq, 0, st);
+      if (rc) return rc;
+    } else {
+      rc = hb200_bitlinear_forward_multi(ctx, segs, 3, Hd, m->x, B, L.attn_norm, c.rms_eps, nullptr, st);
+      if (rc) return rc;
+      rc = hb200_rope_kv_write_angles(ctx, m->q, m->k, m->v, kc, vc, m->pos, m->rope_tab, B,
+                                      c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq, 0, st);
+      if (rc) return rc;
+    }
     rc = hb200_attn_decode(ctx, m->q, 0, kc, vc, m->len, B, c.n_heads, c.n_kv_heads, c.head_dim,
                            c.max_seq, 0, scale, m->attn_ws, m->attn_ws_bytes, m->att, st);
     if (rc) return rc;

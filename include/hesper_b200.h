@@ -153,6 +153,23 @@ int hb200_bitlinear_forward_multi(hb200_ctx *ctx, const hb200_bitlinear_seg *seg
                                   const float *d_rms_gamma, float rms_eps,
                                   float *d_act_scale, hb200_stream stream);
 
+/* Fused q/k/v of ONE token with RoPE and the f16 KV-cache write in the kernel's epilogue: what
+ * hb200_bitlinear_forward_multi (3 tensors, M = 1) followed by hb200_rope_kv_write_angles
+ * (B = 1) compute, bit for bit, in one launch instead of two.  The reference issues three
+ * BitLinear.forward calls, two RoPE launches and the KV writers
+ * (Hesper/Layers/Attention.lean:1191-1224).
+ *   segs[0..2]    q, k, v tensors; N = H*D, Hkv*D, Hkv*D.  segs[0].d_y receives the rotated q
+ *                 (f32 [H][D]); segs[1].d_y / segs[2].d_y are f32 scratch rows that only the
+ *                 two-launch route writes (taken for shapes the fused kernel does not cover)
+ *   d_rope_table  [D/2][2] from hb200_rope_table (B = T = 1), d_pos [1] the token's position
+ *   caches        [Hkv][cache_slots][D] f16 of the token's sequence; ring as in
+ *                 hb200_rope_kv_write */
+int hb200_bitlinear_qkv_rope(hb200_ctx *ctx, const hb200_bitlinear_seg *segs, int K,
+                             const float *d_x, const float *d_rms_gamma, float rms_eps,
+                             const double *d_rope_table, const int32_t *d_pos, void *d_k_cache,
+                             void *d_v_cache, int H, int Hkv, int D, int cache_slots, int ring,
+                             hb200_stream stream);
+
 /* (cos, sin) in f64 of the RoPE angle of every (token, pair): d_table [B*T][D/2][2], token
  * t of sequence b at position d_pos[b] + t.  The angles are the same in every layer, so a
  * decode loop computes them once per step and hands them to hb200_rope_kv_write_angles,
