@@ -367,13 +367,27 @@ static int kq_mma_launch(hb200_ctx* ctx, QmParams& p, int tiles, cudaStream_t st
   using Cfg = QmCfg<NT>;
   // kind::f16: D = f32, A and B f16, both K-major, N = NT, M = 128
   p.idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(kQmRows >> 4) << 24);
-  // split-K when the row tiles alone leave SMs idle: as many splits as fit the SMs, each at
-  // least 2 super-blocks long, partials within their scratch region, tickets within theirs
+  // split-K: the launch takes ceil(tiles * s / SMs) waves of CTAs that each do 1/s of a row
+  // tile's work plus a fixed part (pipeline fill, tensor-memory allocation, the partials'
+  // round trip: taken as a tenth of a tile).  Pick the s that minimises waves * (1/s + 0.1):
+  // few row tiles spread over the idle SMs (20 tiles -> 7 splits), and a tile count just above
+  // a multiple of the SM count no longer costs a whole extra wave (160 tiles: 2 waves of full
+  // tiles -> 4 waves of thirds).  Each split at least 2 super-blocks long, partials within
+  // their scratch region, tickets within theirs.
   const int nboxes = p.K / 256;
-  int nsplit = ctx->sm_count / tiles;
-  if (nsplit > nboxes / 2) nsplit = nboxes / 2;
-  while (nsplit > 1 && (size_t)tiles * nsplit * NT * kQmRows * 4 > kScratchBytes - kScratchSplitK)
-    --nsplit;
+  int nsplit = 1;
+  {
+    float best = 1e30f;
+    for (int s2 = 1; s2 <= nboxes / 2 || s2 == 1; ++s2) {
+      if (s2 > 1 && (size_t)tiles * s2 * NT * kQmRows * 4 > kScratchBytes - kScratchSplitK) break;
+      const int waves = (tiles * s2 + ctx->sm_count - 1) / ctx->sm_count;
+      const float cost = (float)waves * (1.0f / (float)s2 + 0.1f);
+      if (cost < best - 1e-6f) {
+        best = cost;
+        nsplit = s2;
+      }
+    }
+  }
   if (nsplit < 1 || tiles > kCtxTickets) nsplit = 1;
   p.bps = (nboxes + nsplit - 1) / nsplit;
   p.nsplit = (nboxes + p.bps - 1) / p.bps;  // no empty split
