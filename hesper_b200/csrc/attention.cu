@@ -782,6 +782,14 @@ static int attn_run(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d
              "attn (ring): window %d + %d query tokens - 1 must fit the %d slots", window, T, max_seq);
   HB_REQUIRE(((reinterpret_cast<uintptr_t>(d_k) | reinterpret_cast<uintptr_t>(d_v)) & 15) == 0,
              "attn: K/V cache must be 16-byte aligned");
+  // a prompt chunk in the default mode: queries tiled over tokens, each K/V tile read once per
+  // 64 / G tokens (attention_prefill.cu); PRECISE / EXACT keep one decode query per token
+  if (T >= 8 && D != 32 && ctx->attn_mode == HB200_ATTN_FAST) {
+    const int rc = hb_attn_prefill_tiled(ctx, d_q, q_is_f16, d_k, d_v, d_seqlens, nseq, T, H, Hkv,
+                                         D, max_seq, window, ring, scale, d_out,
+                                         static_cast<cudaStream_t>(stream));
+    if (rc <= 0) return rc;
+  }
   AttnParams p = {};
   p.q = d_q;
   p.k = static_cast<const __half*>(d_k);

@@ -298,6 +298,12 @@ int hb_func_smem(struct hb200_ctx* ctx, const void* func, size_t bytes);
 bool hb_func_flag(struct hb200_ctx* ctx, const void* func);
 void hb_func_set_flag(struct hb200_ctx* ctx, const void* func);
 
+// causal attention of a prompt chunk tiled over queries (attention_prefill.cu); 1 = not covered
+int hb_attn_prefill_tiled(struct hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d_k,
+                          const void* d_v, const int32_t* d_seqlens, int nseq, int T, int H,
+                          int Hkv, int D, int slots, int window, int ring, float scale,
+                          float* d_out, cudaStream_t st);
+
 // Scope of one operator call that touches the context's scratch, arrival counters or arena.
 // Entering on another stream than the previous user's makes this stream wait for the event
 // recorded at the end of that use; leaving records the event.  Inside a stream capture nothing

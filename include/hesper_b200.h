@@ -283,10 +283,12 @@ int hb200_attn_decode(hb200_ctx *ctx, const void *d_q, int q_is_f16, const void 
  * seqlens[b] - (T-1-t) of them (and of those only the last `window`, if set).
  * Replaces the prefill FlashAttention kernels (Hesper/WGSL/FlashAttention.lean:495-715).
  *   d_q, d_out  [B][T][H][D];  d_seqlens [B] lengths AFTER the T tokens were appended
- * Every query token runs as one decode query over its sequence's cache (the K/V of a
- * sequence are shared through the L2, not through shared memory), so this is a correct
- * prefill for prompt chunks, not a tuned long-prompt kernel.  Linear caches only.
- * T = 1 is hb200_attn_decode. */
+ * From 8 tokens on (default attention mode) a CTA owns 64 query rows -- 64 / (H / Hkv) consecutive
+ * tokens times the query heads of one KV head -- and walks the positions they see in tiles, so
+ * a K/V tile is read once per 64 / (H / Hkv) tokens (role of flashAttentionBatchKernelF16,
+ * Hesper/WGSL/FlashAttention.lean:601).  Shorter chunks and the PRECISE / EXACT modes run every
+ * token as one decode query over its sequence's cache.  Linear caches (hb200_attn_ring for
+ * rings).  T = 1 is hb200_attn_decode. */
 size_t hb200_attn_prefill_workspace_bytes(const hb200_ctx *ctx, int B, int T, int H, int Hkv,
                                           int D, int max_seq);
 int hb200_attn_prefill(hb200_ctx *ctx, const void *d_q, int q_is_f16, const void *d_k,

@@ -36,6 +36,9 @@ def _reference(oracle_fn, q, k16, v16, lens, T, H, Hkv, D, max_seq, scale, windo
     (8, 2, 256, 700, 16, [700, 16], 0),     # Gemma head shape
     (8, 2, 64, 400, 24, [400, 100], 64),    # sliding window on a linear cache
     (4, 4, 64, 64, 64, [64], 0),            # whole prompt at once, no GQA
+    (8, 1, 128, 260, 70, [260, 75], 0),     # 8 query heads per KV head, ragged last query tile
+    (4, 2, 256, 300, 40, [300, 41], 100),   # head_dim 256 (32-position tiles) with a window
+    (8, 2, 64, 128, 8, [128, 9], 0),        # the shortest chunk the tiled kernel takes
 ])
 def test_prefill_matches_tokenwise_oracle(ctx, oracle, H, Hkv, D, max_seq, T, lens, window):
     B = len(lens)
@@ -65,6 +68,48 @@ def test_prefill_matches_tokenwise_oracle(ctx, oracle, H, Hkv, D, max_seq, T, le
     ref_ex = _reference(oracle.attn_decode_exact, q, k16, v16, sl, T, H, Hkv, D, max_seq, scale,
                         window)
     assert np.array_equal(ex, ref_ex)
+
+
+@pytest.mark.parametrize("H,Hkv,D,slots,T,lens,window,q16", [
+    (8, 2, 128, 80, 17, [200, 33], 64, False),   # ring wraps; second sequence has not wrapped yet
+    (8, 2, 256, 767, 256, [8000, 700], 512, False),  # the Gemma engine's prompt pass
+    (4, 2, 64, 40, 3, [90, 50], 38, True),       # short chunk: one decode query per token
+    (4, 1, 64, 64, 33, [100, 64], 32, True),     # f16 queries
+])
+def test_ring_cache_prefill_matches_oracle(ctx, oracle, H, Hkv, D, slots, T, lens, window, q16):
+    """hb200_attn_ring: the cache is a ring of `slots`, position p in slot p % slots, lengths
+    beyond the ring; the oracle sees the same K/V on a linear cache with the window."""
+    lib = _lib.load()
+    B = len(lens)
+    L = max(lens)
+    rng = np.random.default_rng(D + T + slots)
+    q = rng.standard_normal((B, T, H, D)).astype(np.float32)
+    if q16:
+        q = q.astype(np.float16).astype(np.float32)
+    k_lin = rng.standard_normal((B, Hkv, L, D)).astype(np.float16)
+    v_lin = rng.standard_normal((B, Hkv, L, D)).astype(np.float16)
+    k_ring = np.zeros((B, Hkv, slots, D), np.float16)
+    v_ring = np.zeros((B, Hkv, slots, D), np.float16)
+    for b in range(B):  # what the ring holds after lens[b] positions: the last `slots` of them
+        for pos in range(max(0, lens[b] - slots), lens[b]):
+            k_ring[b, :, pos % slots] = k_lin[b, :, pos]
+            v_ring[b, :, pos % slots] = v_lin[b, :, pos]
+    scale = float(1.0 / np.sqrt(D))
+    sl = np.asarray(lens, np.int32)
+    dq = _dev(q.astype(np.float16) if q16 else q)
+    dk, dv, dl = _dev(k_ring), _dev(v_ring), _dev(sl)
+    nws = int(lib.hb200_attn_prefill_workspace_bytes(ctx.handle, B, T, H, Hkv, D, slots))
+    ws = torch.empty(max(nws, 16), dtype=torch.uint8, device="cuda")
+    out = torch.empty((B, T, H, D), dtype=torch.float32, device="cuda")
+    rc = lib.hb200_attn_ring(ctx.handle, dq.data_ptr(), int(q16), dk.data_ptr(), dv.data_ptr(),
+                             dl.data_ptr(), B, T, H, Hkv, D, slots, window, C.c_float(scale),
+                             ws.data_ptr(), C.c_size_t(ws.numel()), out.data_ptr(), None)
+    assert rc == 0, lib.hb200_last_error()
+    ctx.check()
+    ref = _reference(oracle.attn_decode, q, k_lin, v_lin, sl, T, H, Hkv, D, L, scale, window)
+    out = out.cpu().numpy()
+    assert np.abs(out - ref).max() / np.abs(ref).max() <= TOL
+    assert np.linalg.norm(out - ref) / np.linalg.norm(ref) <= TOL
 
 
 def test_prefill_kv_writer_equals_single_token_calls(ctx):
