@@ -12,7 +12,7 @@
 //     conflict-free ldmatrix); ring caches map position p to slot p % slots;
 //   * S = Q K^T and O += P V on mma.sync.m16n8k16 (f16 in, f32 accumulate), one warp per 16 rows;
 //     the softmax is the online form in the exp2 domain, P is rounded to f16 for the second
-//     product (same rounding as the decode kernel's FAST mode: bar 2e-3 against the f64 oracle);
+//     product (same rounding as the decode kernel's FAST mode: bar 2e-3 against an f64 evaluation);
 //   * a row's visible positions are [max(0, pos - window + 1), pos] with pos the token's own
 //     position: causal inside the chunk, sliding window if asked.
 #include <math_constants.h>
