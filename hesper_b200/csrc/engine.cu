@@ -17,6 +17,8 @@
 // Hesper/Layers/Attention.lean:1197-1206, and reads 4 bytes back per token, BitNet.lean:510-521).
 #include <vector>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 struct hb200_bitnet {
@@ -111,7 +113,7 @@ int enqueue_step(hb200_bitnet* m, const int32_t* d_tokens, bool lm_head, cudaStr
 }
 
 // Prompt chunk: T consecutive positions of every sequence in one pass (tokens [B][T] on the
-// device, B*T <= 64).  The linear layers run batched on the tensor cores (bit-identical to
+// device, B*T <= 256).  The linear layers run batched on the tensor cores (bit-identical to
 // the single-token kernels), RoPE/KV write and causal attention through their prefill entry
 // points.  Positions advance by T.  With lm_head the last position's argmax is taken.
 int enqueue_prefill_chunk(hb200_bitnet* m, const int32_t* d_tokens, int T, bool lm_head,
@@ -194,8 +196,14 @@ extern "C" int hb200_bitnet_create(hb200_ctx* ctx, const hb200_bitnet_config* cf
   m->log_stride = max_new_tokens > 0 ? max_new_tokens : 1;
   m->want_logits = false;
   const int B = batch, qdim = cfg->n_heads * cfg->head_dim, kvdim = cfg->n_kv_heads * cfg->head_dim;
-  // prompt chunks of T = 64 / B positions run batched: the buffers hold B * T token rows
-  const int Tmax = 64 / B;
+  // prompt chunks of T = 256 / B positions run batched (the ternary products take them in
+  // passes of 64 rows; RoPE, attention and the quantiser see all rows at once): the buffers
+  // hold B * T token rows.  HB200_BITNET_CHUNK caps T.
+  int Tmax = 256 / B;
+  if (const char* ev = getenv("HB200_BITNET_CHUNK")) {
+    const int cap = atoi(ev);
+    if (cap >= 1 && cap < Tmax) Tmax = cap;
+  }
   const size_t R = (size_t)B * (Tmax > 1 ? Tmax : 1);
   m->Mmax = (int)R;
   cudaError_t e = cudaSuccess;
@@ -323,7 +331,7 @@ extern "C" int hb200_bitnet_generate(hb200_bitnet* m, const int32_t* h_prompt, i
   };
   if (e != cudaSuccess) { cleanup(); return cuda_fail(e, "prompt upload"); }
   // ---- prefill: the reference runs one single-token forward per prompt position
-  //      (BitNet.generate :623-625); here chunks of T = 64 / B positions go through the
+  //      (BitNet.generate :623-625); here chunks of T = 256 / B positions go through the
   //      batched kernels and causal prefill attention.  Only the last position needs the LM
   //      head, whose argmax is the first new token ----
   cudaEventRecord(e0, st);

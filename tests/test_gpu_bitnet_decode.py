@@ -103,14 +103,14 @@ def test_generate_graph_equals_stepwise(ctx):
     model.close()
 
 
-@pytest.mark.parametrize("batch,plen", [(3, 50), (1, 130), (40, 5)])
+@pytest.mark.parametrize("batch,plen", [(3, 50), (1, 130), (40, 5), (1, 300), (5, 120)])
 def test_chunked_prefill_equals_stepwise(ctx, batch, plen):
-    """generate() consumes the prompt in chunks of 64 // batch positions through the batched
-    tensor-core kernels and causal prefill attention (ragged last chunk; batch 40 falls back to
-    single positions); explicit single-token steps over the same prompt must give the same
-    tokens."""
+    """generate() consumes the prompt in chunks of 256 // batch positions through the batched
+    tensor-core kernels (passes of 64 rows) and causal prefill attention (ragged last chunk;
+    more than one chunk at (1, 300) and (5, 120)); explicit single-token steps over the same
+    prompt must give the same tokens."""
     import dataclasses
-    shape = dataclasses.replace(SMALL, max_seq=192)
+    shape = dataclasses.replace(SMALL, max_seq=320)
     w = random_bitnet_weights(shape, seed=9)
     prompt = np.random.default_rng(plen).integers(0, shape.vocab, (batch, plen)).astype(np.int32)
     model = BitNetModel(ctx, shape, w, batch=batch, max_new_tokens=12)
