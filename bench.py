@@ -560,8 +560,8 @@ def run_tp_decode(torch, dist, ctx, hb, rank, world):
 
 def run_bitnet_decode(torch, ctx, hb):
     """Configuration 3: BitNet-b1.58-2B-shaped model, random-init, 2048-token random prompt
-    then 128 greedy tokens at batch 1 and at batch 64 (graph replay; the prompt is consumed
-    one position per step through the same decode path)."""
+    then 128 greedy tokens at batch 1 and at batch 64 (decode by graph replay; the prompt is
+    consumed in passes of 256 // batch positions through the batched kernels)."""
     from hesper_b200.models import BitNetShape, BitNetModel, random_bitnet_weights_device
     shape = BitNetShape.bitnet_2b(max_seq=2304)
     w = random_bitnet_weights_device(shape)
