@@ -255,10 +255,10 @@ struct HbKqSeg {
   int glu;
 };
 int hb_kq_mma_run_multi(struct hb200_ctx* ctx, const HbKqSeg* segs, int nseg, int K, int M,
-                        int NT, cudaStream_t st);
+                        int NT, cudaStream_t st, int fmt = HB200_FMT_Q4_K);
 int hb_kq_mma_run(struct hb200_ctx* ctx, const uint8_t* d_blocks, int K, long N, int M, int NT,
-                  float* d_y, const float* d_residual, long ldy, int glu, cudaStream_t st);
-constexpr size_t kArenaBytes = (size_t)64 << 20;  // f16 weights of one batched k-quant product
+                  float* d_y, const float* d_residual, long ldy, int glu, cudaStream_t st,
+                  int fmt = HB200_FMT_Q4_K);
 
 struct hb200_ctx {
   int device;
@@ -266,7 +266,6 @@ struct hb200_ctx {
   int smem_optin;      // max dynamic shared memory per block
   uint32_t* d_status;  // 64 words
   int* d_tickets;      // kCtxTickets zero-initialised arrival counters
-  void* d_arena;       // kArenaBytes, batched k-quant path
   void* d_scratch;     // batched paths: quantised activations, gate/up temporaries
   size_t scratch_bytes;
   bool pdl;            // use programmatic dependent launch
@@ -282,7 +281,7 @@ struct hb200_ctx {
     bool flag;  // kernel-specific: non-portable cluster sizes already allowed
   } func_smem[96];
   int n_func_smem;
-  // The scratch, the arrival counters and the arena serve one stream at a time: ScratchUse
+  // The scratch and the arrival counters serve one stream at a time: ScratchUse
   // orders a call behind the previous user when it arrives on another stream.
   cudaEvent_t scratch_done;     // end of the last use outside a stream capture
   cudaStream_t scratch_stream;  // the stream that use was on (never dereferenced: compared only)
@@ -304,7 +303,7 @@ int hb_attn_prefill_tiled(struct hb200_ctx* ctx, const void* d_q, int q_is_f16, 
                           int Hkv, int D, int slots, int window, int ring, float scale,
                           float* d_out, cudaStream_t st);
 
-// Scope of one operator call that touches the context's scratch, arrival counters or arena.
+// Scope of one operator call that touches the context's scratch or arrival counters.
 // Entering on another stream than the previous user's makes this stream wait for the event
 // recorded at the end of that use; leaving records the event.  Inside a stream capture nothing
 // is recorded or waited for (an event from outside cannot enter a capture): graphs that share a

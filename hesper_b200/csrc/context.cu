@@ -98,7 +98,6 @@ static int ctx_build(int device, bool adopted, hb200_ctx** out) {
   c->d_status = nullptr;
   c->d_tickets = nullptr;
   c->d_scratch = nullptr;
-  c->d_arena = nullptr;
   c->device = device;
   c->sm_count = prop.multiProcessorCount;
   c->smem_optin = (int)prop.sharedMemPerBlockOptin;
@@ -125,13 +124,11 @@ static int ctx_build(int device, bool adopted, hb200_ctx** out) {
   if (e == cudaSuccess) e = cudaMemset(c->d_tickets, 0, sizeof(int) * (kCtxTickets + 16));
   c->scratch_bytes = kScratchBytes;
   if (e == cudaSuccess) e = cudaMalloc(&c->d_scratch, c->scratch_bytes);
-  if (e == cudaSuccess) e = cudaMalloc(&c->d_arena, kArenaBytes);
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->scratch_done, cudaEventDisableTiming);
   if (e != cudaSuccess) {
     cudaFree(c->d_status);
     cudaFree(c->d_tickets);
     cudaFree(c->d_scratch);
-    cudaFree(c->d_arena);
     if (c->scratch_done) cudaEventDestroy(c->scratch_done);
     delete c;
     return cuda_fail(e, "context buffers");
@@ -176,7 +173,6 @@ extern "C" int hb200_ctx_destroy(hb200_ctx* ctx) {
   cudaFree(ctx->d_status);
   cudaFree(ctx->d_tickets);
   cudaFree(ctx->d_scratch);
-  cudaFree(ctx->d_arena);
   if (ctx->scratch_done) cudaEventDestroy(ctx->scratch_done);
   delete ctx;
   return HB200_OK;

@@ -541,90 +541,21 @@ __global__ void __launch_bounds__(kKQThreads, 1) kquant_kernel(const __grid_cons
   }
 }
 
-// ---- batched path: dequantise to f16, then the 16-bit tensor-core product ---------------
+// ---- batched path (16 tokens or more): a real contraction ------------------------------
 //
-// From 16 tokens on the product is a real contraction.  Q4_K goes through the kernel of
-// kquant_mma.cu, which dequantises inside the tensor-core pipeline.  Q8_0 takes two kernels:
-// the weights of one product (or a row chunk of it) are dequantised once into a 64 MB f16
-// arena of the context -- it stays in the 126 MB L2 -- and multiplied by the tensor-core
-// kernel that also serves the LM head
-// (tcgen05 kind::f16, activations split into hi + lo f16 so their rounding drops out).
-// f16 weights carry 2^-11 relative rounding each; the measured output error is ~3e-4 of
-// max|y|, inside the 1e-3 bar of this path.  One thread per 8 weights, 16-byte stores.
-template <int FMT>
-__global__ void __launch_bounds__(256) kq_dequant_kernel(const uint8_t* __restrict__ blocks,
-                                                         int K, long rows, int rowbytes,
-                                                         int rows_per_cta,
-                                                         __half* __restrict__ out) {
-  extern __shared__ __align__(16) uint8_t raw[];  // the CTA's rows, verbatim
-  const long r0 = (long)blockIdx.x * rows_per_cta;
-  const int nr = (int)min((long)rows_per_cta, rows - r0);
-  // the quantised rows do not depend on the kernel before this one: stage them first
-  {
-    const uint4* src = reinterpret_cast<const uint4*>(blocks + (size_t)r0 * rowbytes);
-    const int nv = nr * rowbytes / 16;  // rowbytes is a multiple of 16 for both formats
-    for (int i = threadIdx.x; i < nv; i += 256) reinterpret_cast<uint4*>(raw)[i] = __ldg(src + i);
-  }
-  pdl_trigger();
-  pdl_wait();  // the arena may still be read by the product before this one
-  __syncthreads();
-  const int gpr = K >> 3;  // 8-weight groups per row
-  for (int idx = threadIdx.x; idx < nr * gpr; idx += 256) {
-    const int row = idx / gpr, g = idx - row * gpr;
-    float w[8];
-    if (FMT == 12) {
-      // super-block: f16 d, f16 dmin, 12 bytes of 6-bit scales/mins, 128 bytes of nibbles;
-      // sub-blocks 2c and 2c+1 are the low and high nibbles of bytes 32c..32c+31
-      // (Hesper/Quantization/Q4_K_M.lean:13-52,120-144)
-      const uint8_t* blk = raw + (size_t)row * rowbytes + (size_t)(g >> 5) * 144;
-      const int j = g & 31, sub = j >> 2, part = j & 3;
-      const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(blk));
-      const uint8_t* sc = blk + 4;
-      int s6, m6;
-      if (sub < 4) {
-        s6 = sc[sub] & 63;
-        m6 = sc[sub + 4] & 63;
-      } else {
-        s6 = (sc[sub + 4] & 0xF) | ((sc[sub - 4] >> 6) << 4);
-        m6 = (sc[sub + 4] >> 4) | ((sc[sub] >> 6) << 4);
-      }
-      const float ds = dd.x * (float)s6, dm = dd.y * (float)m6;
-      const uint2 q = *reinterpret_cast<const uint2*>(blk + 16 + 32 * (sub >> 1) + 8 * part);
-      const uint32_t qq[2] = {q.x, q.y};
-      const int sh = (sub & 1) * 4;
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        w[i] = fmaf(ds, (float)((qq[i >> 2] >> (8 * (i & 3) + sh)) & 0xF), -dm);
-    } else {
-      // block: f16 d, 32 int8 (Hesper/Layers/Linear.lean:6207-6223); 2-byte aligned only
-      const uint8_t* blk = raw + (size_t)row * rowbytes + (size_t)(g >> 2) * 34;
-      const float d = __half2float(*reinterpret_cast<const __half*>(blk));
-      const uint16_t* q16 = reinterpret_cast<const uint16_t*>(blk + 2 + 8 * (g & 3));
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint16_t v = q16[i];
-        w[2 * i] = d * (float)(int8_t)(v & 0xff);
-        w[2 * i + 1] = d * (float)(int8_t)(v >> 8);
-      }
-    }
-    __half2 h[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(w[2 * i], w[2 * i + 1]);
-    *reinterpret_cast<uint4*>(out + (size_t)(r0 + row) * K + (size_t)g * 8) =
-        *reinterpret_cast<const uint4*>(h);
-  }
-}
+// Both formats go through the kernel of kquant_mma.cu, which dequantises inside the tensor-core
+// pipeline (weights and activations rounded to f16: ~4e-4 of max|y|, inside the 1e-3 bar).
 
 // The optional pre-step (x' = base + rmsnorm(x) * pre_gamma, x' also written to pre_out) in
-// front of a matvec call: inside the streaming kernel's prologue at small batch sizes, inside
-// the activation staging kernel of the batched Q4_K path, its own launch otherwise.
+// front of a matvec call: inside the matvec kernel's prologue for a few tokens, inside the
+// activation staging kernel of the batched path.
 struct KQPre {
   const float* base;
   const float* gamma;
   float* out;
 };
 
-// One product of a batched Q4_K call: y[M][N] = W x, plus a residual or, with glu set, times
+// One product of a batched call: y[M][N] = W x, plus a residual or, with glu set, times
 // gelu_tanh of the gate values in `residual`.
 struct KQBatchSeg {
   const uint8_t* blocks;
@@ -634,12 +565,13 @@ struct KQBatchSeg {
   int glu;
 };
 
-// Q4_K, any M >= 1, several tensors against the same activations: the dequantiser is fused
-// into the product kernel (kquant_mma.cu; split-K when there are few row tiles).  The
-// activations of a pass are normalised, rounded and laid out once and shared by every tensor.
-static int kq_batched_q4k(hb200_ctx* ctx, const KQBatchSeg* segs, int nseg, int K,
-                          const float* d_x, int M, const KQPre& pre, const float* gamma,
-                          float eps, cudaStream_t st) {
+// Q4_K or Q8_0 (K a multiple of 256), any M >= 1, several tensors against the same activations:
+// the dequantiser is fused into the product kernel (kquant_mma.cu; split-K when there are few
+// row tiles).  The activations of a pass are normalised, rounded and laid out once and shared
+// by every tensor.
+static int kq_batched_fused(hb200_ctx* ctx, int fmt, const KQBatchSeg* segs, int nseg, int K,
+                            const float* d_x, int M, const KQPre& pre, const float* gamma,
+                            float eps, cudaStream_t st) {
   ScratchUse use(ctx, st);  // staged activations, row scales, split-K partials, tickets
   // tokens per pass: the tensor time of a pass does not depend on it, the activation tile
   // and the accumulator do; K above 8192 keeps the 256-token tiles out of their scratch
@@ -665,56 +597,10 @@ static int kq_batched_q4k(hb200_ctx* ctx, const KQBatchSeg* segs, int nseg, int 
                     g.residual ? g.residual + (size_t)m0 * g.N : nullptr, g.N, g.glu};
         ++s;
       } while (n < 3 && s < nseg && !segs[s].glu && !segs[s - 1].glu);
-      rc = hb_kq_mma_run_multi(ctx, run, n, K, mc, NT, st);
+      rc = hb_kq_mma_run_multi(ctx, run, n, K, mc, NT, st, fmt);
       if (rc != HB200_OK) return rc;
     }
     m0 += mc;
-  }
-  return HB200_OK;
-}
-
-// y[M][N] = W x (+ residual) for one tensor, any M >= 1.  Q8_0 (and the f16-arena route in
-// general): row chunks that fit the arena, token chunks of 64.
-static int kq_batched_one(hb200_ctx* ctx, int fmt, const uint8_t* blocks, int K, long N,
-                          const float* d_x, int M, const float* gamma, float eps,
-                          const float* residual, float* y, cudaStream_t st) {
-  if (fmt == HB200_FMT_Q4_K) {
-    const KQBatchSeg g = {blocks, N, residual, y, 0};
-    return kq_batched_q4k(ctx, &g, 1, K, d_x, M, KQPre{nullptr, nullptr, nullptr}, gamma, eps, st);
-  }
-  ScratchUse use(ctx, st);  // the f16 arena and the staged activations
-  const int rowbytes = fmt == HB200_FMT_Q4_K ? K / 256 * 144 : K / 32 * 34;
-  long chunk = (long)(kArenaBytes / ((size_t)K * 2)) / 128 * 128;
-  HB_REQUIRE(chunk >= 128 && rowbytes <= 48 * 1024,
-             "kquant (batched): K=%d too large for the f16 arena or the staging buffer", K);
-  __half* arena = static_cast<__half*>(ctx->d_arena);
-  for (long r0 = 0; r0 < N; r0 += chunk) {
-    const long nr = N - r0 < chunk ? N - r0 : chunk;
-    // rows per CTA: up to 32 KB of raw bytes, but no fewer CTAs than ~4 per SM when the
-    // tensor is small
-    int rpc = 32768 / rowbytes;
-    const long want = (nr + 4L * ctx->sm_count - 1) / (4L * ctx->sm_count);
-    if (rpc > want) rpc = (int)want;
-    if (rpc < 1) rpc = 1;
-    const unsigned grid = (unsigned)((nr + rpc - 1) / rpc);
-    const size_t dsm = (size_t)rpc * rowbytes;
-    const uint8_t* src = blocks + (size_t)r0 * rowbytes;
-    if (fmt == HB200_FMT_Q4_K)
-      HB_CUDA(launch_pdl(kq_dequant_kernel<12>, dim3(grid), dim3(256), dsm, st, ctx->pdl, src, K,
-                         nr, rowbytes, rpc, arena));
-    else
-      HB_CUDA(launch_pdl(kq_dequant_kernel<8>, dim3(grid), dim3(256), dsm, st, ctx->pdl, src, K,
-                         nr, rowbytes, rpc, arena));
-    for (int m0 = 0; m0 < M; m0 += 64) {
-      const int mc = M - m0 < 64 ? M - m0 : 64;
-      int rc = hb_gemm16_split(ctx, 1, K, d_x + (size_t)m0 * K, mc, gamma, eps, 0, st);
-      if (rc != HB200_OK) return rc;
-      // the product addresses its output as [m][row] with row stride 1 and token stride N:
-      // a row chunk is a column offset into the caller's [M][N] arrays
-      rc = hb_gemm16_mma(ctx, arena, 1, nr, K, mc, y + (size_t)m0 * N + r0,
-                         residual ? residual + (size_t)m0 * N + r0 : nullptr, N, nullptr, 0, st);
-      if (rc != HB200_OK) return rc;
-    }
   }
   return HB200_OK;
 }
@@ -846,24 +732,11 @@ static int kq_forward_multi_impl(hb200_ctx* ctx, int fmt, const hb200_kquant_seg
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (M >= kKQBatchedFrom && !ctx->no_mma) {  // a real contraction: tensor-core path
-    if (fmt == HB200_FMT_Q4_K) {
-      KQBatchSeg g[kKQMaxSeg];
-      for (int s = 0; s < nseg; ++s)
-        g[s] = {static_cast<const uint8_t*>(segs[s].d_blocks), segs[s].N, segs[s].d_residual,
-                segs[s].d_y, 0};
-      return kq_batched_q4k(ctx, g, nseg, K, d_x, M, pre, d_rms_gamma, rms_eps, st);
-    }
-    if (pre.gamma) {
-      rc = hb200_rmsnorm(ctx, d_x, pre.gamma, pre.base, rms_eps, M, K, pre.out, stream);
-      if (rc != HB200_OK) return rc;
-      d_x = pre.out;
-    }
-    for (int s = 0; s < nseg; ++s) {
-      rc = kq_batched_one(ctx, fmt, static_cast<const uint8_t*>(segs[s].d_blocks), K, segs[s].N,
-                          d_x, M, d_rms_gamma, rms_eps, segs[s].d_residual, segs[s].d_y, st);
-      if (rc != HB200_OK) return rc;
-    }
-    return HB200_OK;
+    KQBatchSeg g[kKQMaxSeg];
+    for (int s = 0; s < nseg; ++s)
+      g[s] = {static_cast<const uint8_t*>(segs[s].d_blocks), segs[s].N, segs[s].d_residual,
+              segs[s].d_y, 0};
+    return kq_batched_fused(ctx, fmt, g, nseg, K, d_x, M, pre, d_rms_gamma, rms_eps, st);
   }
   HB_REQUIRE(M <= 64, "kquant: M=%d needs the batched path (HB200_NO_MMA is set)", M);
   if (M == 1) {  // one token: integer tensor-core matvec when the rows fit shared memory
@@ -942,40 +815,13 @@ static int kq_gateup_impl(hb200_ctx* ctx, int fmt, const void* d_blocks_gate,
                reinterpret_cast<uintptr_t>(d_blocks_up)) & 15) == 0,
              "kquant gate/up: blocks must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (M >= kKQBatchedFrom && !ctx->no_mma && pre.gamma && fmt != HB200_FMT_Q4_K) {
-    rc = hb200_rmsnorm(ctx, d_x, pre.gamma, pre.base, rms_eps, M, K, pre.out, stream);
-    if (rc != HB200_OK) return rc;
-    return kq_gateup_impl(ctx, fmt, d_blocks_gate, d_blocks_up, K, N, pre.out, M,
-                          KQPre{nullptr, nullptr, nullptr}, d_rms_gamma, rms_eps, d_y, stream);
-  }
-  if (M >= kKQBatchedFrom && !ctx->no_mma && fmt == HB200_FMT_Q4_K) {
+  if (M >= kKQBatchedFrom && !ctx->no_mma) {
     // both products on the tensor cores against one staging of the activations: the gate
     // product writes d_y, the up product's epilogue multiplies gelu_tanh(gate) in place
     const KQBatchSeg g[2] = {
         {static_cast<const uint8_t*>(d_blocks_gate), N, nullptr, d_y, 0},
         {static_cast<const uint8_t*>(d_blocks_up), N, d_y, d_y, 1}};
-    return kq_batched_q4k(ctx, g, 2, K, d_x, M, pre, d_rms_gamma, rms_eps, st);
-  }
-  if (M >= kKQBatchedFrom && !ctx->no_mma &&
-      kScratchGlu + (size_t)64 * N * sizeof(float) <= kScratchLmSplit) {
-    // both products on the tensor cores: gate straight into d_y, up into scratch (as many
-    // tokens per pass as the scratch region holds, at most 128), then the GLU in place
-    ScratchUse use(ctx, st);  // `u` must survive until the GLU kernel has read it
-    float* u = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->d_scratch) + kScratchGlu);
-    const int pass =
-        kScratchGlu + (size_t)128 * N * sizeof(float) <= kScratchLmSplit ? 128 : 64;
-    for (int m0 = 0; m0 < M; m0 += pass) {
-      const int mc = M - m0 < pass ? M - m0 : pass;
-      float* g = d_y + (size_t)m0 * N;
-      rc = kq_batched_one(ctx, fmt, static_cast<const uint8_t*>(d_blocks_gate), K, N,
-                          d_x + (size_t)m0 * K, mc, d_rms_gamma, rms_eps, nullptr, g, st);
-      if (rc == HB200_OK)
-        rc = kq_batched_one(ctx, fmt, static_cast<const uint8_t*>(d_blocks_up), K, N,
-                            d_x + (size_t)m0 * K, mc, d_rms_gamma, rms_eps, nullptr, u, st);
-      if (rc == HB200_OK) rc = hb200_gelu_mul(ctx, g, u, (long)mc * N, g, stream);
-      if (rc != HB200_OK) return rc;
-    }
-    return HB200_OK;
+    return kq_batched_fused(ctx, fmt, g, 2, K, d_x, M, pre, d_rms_gamma, rms_eps, st);
   }
   HB_REQUIRE(M <= 64, "kquant gate/up: M=%d needs the batched path", M);
   if (M == 1) {

@@ -30,20 +30,28 @@ namespace hb {
 constexpr int kQmRows = 128;          // weight rows per CTA = MMA M
 constexpr int kQmStepK = 128;         // weights per pipeline step (half a super-block)
 constexpr int kQmACols = kQmStepK / 2;           // 64 TMEM columns of f16 pairs per stage
-constexpr int kQmPkStages = 3;
-constexpr int kQmPkBytes = kQmRows * 144;        // one super-block of every row: 18 KB
 constexpr int kQmThreads = 352;
+
+// What differs between the two formats: the bytes of 256 weights (one Q4_K super-block, eight
+// Q8_0 blocks) and, with them, the box a copy brings and how deep the ring of boxes can be.
+template <int FMT, int NT>
+struct QmFmt {
+  static constexpr int kUnit = FMT == 12 ? 144 : 272;
+  static constexpr int kPkBytes = kQmRows * kUnit;  // 256 weights of every row: 18 / 34 KB
+  static constexpr int kPkStages = (FMT == 12 || NT == 64) ? 3 : 2;
+};
 
 // NT tokens per pass = MMA N.  An MMA of this shape occupies the tensor pipe for the same
 // ~128 cycles whether N is 64 or 256, so a pass over more tokens costs no extra tensor time;
 // what grows is the accumulator (NT columns) and the activation tile every step brings.
-template <int NT>
+template <int NT, int FMT = 12>
 struct QmCfg {
   static constexpr int kIssuers = NT <= 128 ? 2 : 1;        // MMA-issuing warps, one accumulator each
   static constexpr int kA0 = kIssuers * NT;                 // first TMEM column of the A stages
   static constexpr int kStages = NT == 64 ? 6 : (NT == 128 ? 4 : 2);
   static constexpr int kBBytes = NT * kQmStepK * 2;         // activations per step: 16 / 32 / 64 KB
-  static constexpr int kSmem = 1024 + kQmPkStages * kQmPkBytes + kStages * kBBytes;
+  static constexpr int kSmem =
+      1024 + QmFmt<FMT, NT>::kPkStages * QmFmt<FMT, NT>::kPkBytes + kStages * kBBytes;
   static_assert(kA0 + kStages * kQmACols <= 512, "tensor memory columns");
   static_assert(kSmem <= 232448, "shared memory budget of one CTA");
 };
@@ -86,9 +94,21 @@ __device__ __forceinline__ uint32_t pack_f16(float a, float b) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-template <int NT>
+// The four int8 of a word as f32 times d, packed to two f16 pairs.
+__device__ __forceinline__ void q80_word(uint32_t w, float d, uint32_t& lo, uint32_t& hi) {
+  const float a = d * (float)(int)(int8_t)(w & 0xFF), b = d * (float)(int)(int8_t)((w >> 8) & 0xFF);
+  const float c = d * (float)(int)(int8_t)((w >> 16) & 0xFF), e = d * (float)(int)(int8_t)(w >> 24);
+  lo = pack_f16(a, b);
+  hi = pack_f16(c, e);
+}
+
+template <int NT, int FMT>
 __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_constant__ QmParams p) {
-  using Cfg = QmCfg<NT>;
+  using Cfg = QmCfg<NT, FMT>;
+  constexpr int kQmPkStages = QmFmt<FMT, NT>::kPkStages, kQmPkBytes = QmFmt<FMT, NT>::kPkBytes;
+  constexpr int kUnit = QmFmt<FMT, NT>::kUnit;
+  // a box dimension holds at most 256 elements: the 272-byte Q8_0 unit is mapped as 68 words
+  constexpr int kBoxX = FMT == 12 ? 144 : 68;
   constexpr int kQmStages = Cfg::kStages, kQmBBytes = Cfg::kBBytes, kQmA0 = Cfg::kA0;
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -145,7 +165,7 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
     auto issue_box = [&](int b) {
       if (lane == 0) {
         mbar_arrive_expect_tx(&pk_full[b % kQmPkStages], kQmPkBytes);
-        tc_tma_box_2d(pk + (size_t)(b % kQmPkStages) * kQmPkBytes, tmap, (b0 + b) * 144, row0,
+        tc_tma_box_2d(pk + (size_t)(b % kQmPkStages) * kQmPkBytes, tmap, (b0 + b) * kBoxX, row0,
                       &pk_full[b % kQmPkStages], pol);
       }
     };
@@ -213,37 +233,56 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
         ok = tc_wait(ok, &mma_done[st], (uint32_t)(((s / kQmStages) - 1) & 1), p.status);
         tc_after_sync();
       }
-      // super-block of this row: f16 d, f16 dmin, 12 bytes of 6-bit scales and mins, 128 bytes
-      // of nibbles (Hesper/Quantization/Q4_K_M.lean:13-52,120-144)
-      const uint8_t* blk = pk + (size_t)(box % kQmPkStages) * kQmPkBytes + (size_t)erow * 144;
-      const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
-      const uint4 qa = *reinterpret_cast<const uint4*>(blk + 16 + 32 * c);
-      const uint4 qb = *reinterpret_cast<const uint4*>(blk + 32 + 32 * c);
-      const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));
-      // scale / min bytes j and j+1 (j = 2c) out of the 12 packed bytes hdr.y, hdr.z, hdr.w
-      uint32_t sc2, m2;  // two 6-bit values each, in bytes 0 and 1
-      if (c < 2) {
-        sc2 = (hdr.y >> (16 * c)) & 0x3F3Fu;
-        m2 = (hdr.z >> (16 * c)) & 0x3F3Fu;
+      uint32_t o[32];
+      if (FMT == 12) {
+        // super-block of this row: f16 d, f16 dmin, 12 bytes of 6-bit scales and mins, 128 bytes
+        // of nibbles (Hesper/Quantization/Q4_K_M.lean:13-52,120-144)
+        const uint8_t* blk = pk + (size_t)(box % kQmPkStages) * kQmPkBytes + (size_t)erow * 144;
+        const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
+        const uint4 qa = *reinterpret_cast<const uint4*>(blk + 16 + 32 * c);
+        const uint4 qb = *reinterpret_cast<const uint4*>(blk + 32 + 32 * c);
+        const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));
+        // scale / min bytes j and j+1 (j = 2c) out of the 12 packed bytes hdr.y, hdr.z, hdr.w
+        uint32_t sc2, m2;  // two 6-bit values each, in bytes 0 and 1
+        if (c < 2) {
+          sc2 = (hdr.y >> (16 * c)) & 0x3F3Fu;
+          m2 = (hdr.z >> (16 * c)) & 0x3F3Fu;
+        } else {
+          const int sh = 16 * (c - 2);
+          sc2 = ((hdr.w >> sh) & 0x0F0Fu) | (((hdr.y >> (sh + 6)) & 0x0303u) << 4);
+          m2 = ((hdr.w >> (sh + 4)) & 0x0F0Fu) | (((hdr.z >> (sh + 6)) & 0x0303u) << 4);
+        }
+        const float ds0 = dd.x * (float)(sc2 & 0xFF), ds1 = dd.x * (float)(sc2 >> 8);
+        const float dm0 = -(dd.y * (float)(m2 & 0xFF)), dm1 = -(dd.y * (float)(m2 >> 8));
+        const uint32_t qq[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+        // columns 0-15: sub-block 2c (low nibbles), 16-31: sub-block 2c+1 (high nibbles)
+  #pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint32_t w = qq[i];
+          o[2 * i] = pack_f16(fmaf(ds0, (float)(w & 0xF), dm0), fmaf(ds0, (float)((w >> 8) & 0xF), dm0));
+          o[2 * i + 1] = pack_f16(fmaf(ds0, (float)((w >> 16) & 0xF), dm0),
+                                  fmaf(ds0, (float)((w >> 24) & 0xF), dm0));
+          o[16 + 2 * i] = pack_f16(fmaf(ds1, (float)((w >> 4) & 0xF), dm1),
+                                   fmaf(ds1, (float)((w >> 12) & 0xF), dm1));
+          o[16 + 2 * i + 1] = pack_f16(fmaf(ds1, (float)((w >> 20) & 0xF), dm1),
+                                       fmaf(ds1, (float)(w >> 28), dm1));
+        }
       } else {
-        const int sh = 16 * (c - 2);
-        sc2 = ((hdr.w >> sh) & 0x0F0Fu) | (((hdr.y >> (sh + 6)) & 0x0303u) << 4);
-        m2 = ((hdr.w >> (sh + 4)) & 0x0F0Fu) | (((hdr.z >> (sh + 6)) & 0x0303u) << 4);
-      }
-      const float ds0 = dd.x * (float)(sc2 & 0xFF), ds1 = dd.x * (float)(sc2 >> 8);
-      const float dm0 = -(dd.y * (float)(m2 & 0xFF)), dm1 = -(dd.y * (float)(m2 >> 8));
-      const uint32_t qq[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-      uint32_t o[32];  // columns 0-15: sub-block 2c (low nibbles), 16-31: sub-block 2c+1 (high)
+        // Q8_0 (Hesper/Layers/Linear.lean:6207-6223): blocks 2c and 2c+1 of the row's eight, 34
+        // bytes each -- f16 d, then 32 int8.  The chunk starts on a word; block 2c's quants sit
+        // two bytes into it (funnel shifts), block 2c+1's are word aligned.
+        const uint32_t* wq = reinterpret_cast<const uint32_t*>(
+            pk + (size_t)(box % kQmPkStages) * kQmPkBytes + (size_t)erow * kUnit + 68 * c);
+        uint32_t w[17];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const uint32_t w = qq[i];
-        o[2 * i] = pack_f16(fmaf(ds0, (float)(w & 0xF), dm0), fmaf(ds0, (float)((w >> 8) & 0xF), dm0));
-        o[2 * i + 1] = pack_f16(fmaf(ds0, (float)((w >> 16) & 0xF), dm0),
-                                fmaf(ds0, (float)((w >> 24) & 0xF), dm0));
-        o[16 + 2 * i] = pack_f16(fmaf(ds1, (float)((w >> 4) & 0xF), dm1),
-                                 fmaf(ds1, (float)((w >> 12) & 0xF), dm1));
-        o[16 + 2 * i + 1] = pack_f16(fmaf(ds1, (float)((w >> 20) & 0xF), dm1),
-                                     fmaf(ds1, (float)(w >> 28), dm1));
+        for (int i = 0; i < 17; ++i) w[i] = wq[i];
+        const float d0 = __half2float(__ushort_as_half((unsigned short)(w[0] & 0xFFFFu)));
+        const float d1 = __half2float(__ushort_as_half((unsigned short)(w[8] >> 16)));
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          q80_word(__funnelshift_r(w[i], w[i + 1], 16), d0, o[2 * i], o[2 * i + 1]);
+          q80_word(w[9 + i], d1, o[16 + 2 * i], o[16 + 2 * i + 1]);
+        }
       }
       const uint32_t taddr = lane_addr + (uint32_t)st * kQmACols;
       HB_TMEM_ST32(taddr, o);
@@ -362,9 +401,9 @@ __global__ void __launch_bounds__(kQmThreads, 1) kq_mma_kernel(const __grid_cons
 
 using namespace hb;
 
-template <int NT>
+template <int NT, int FMT>
 static int kq_mma_launch(hb200_ctx* ctx, QmParams& p, int tiles, cudaStream_t st) {
-  using Cfg = QmCfg<NT>;
+  using Cfg = QmCfg<NT, FMT>;
   // kind::f16: D = f32, A and B f16, both K-major, N = NT, M = 128
   p.idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(kQmRows >> 4) << 24);
   // split-K: the launch takes ceil(tiles * s / SMs) waves of CTAs that each do 1/s of a row
@@ -392,10 +431,10 @@ static int kq_mma_launch(hb200_ctx* ctx, QmParams& p, int tiles, cudaStream_t st
   p.bps = (nboxes + nsplit - 1) / nsplit;
   p.nsplit = (nboxes + p.bps - 1) / p.bps;  // no empty split
   {
-    const int rc = hb_func_smem(ctx, reinterpret_cast<const void*>(kq_mma_kernel<NT>), (size_t)Cfg::kSmem);
+    const int rc = hb_func_smem(ctx, reinterpret_cast<const void*>(kq_mma_kernel<NT, FMT>), (size_t)Cfg::kSmem);
     if (rc != HB200_OK) return rc;
   }
-  HB_CUDA(launch_pdl(kq_mma_kernel<NT>, dim3((unsigned)(tiles * p.nsplit)), dim3(kQmThreads),
+  HB_CUDA(launch_pdl(kq_mma_kernel<NT, FMT>, dim3((unsigned)(tiles * p.nsplit)), dim3(kQmThreads),
                      (size_t)Cfg::kSmem, st, ctx->pdl, p));
   return HB200_OK;
 }
@@ -404,27 +443,32 @@ static int kq_mma_launch(hb200_ctx* ctx, QmParams& p, int tiles, cudaStream_t st
 // M <= NT tokens staged by hb_gemm16_split (dtype f16, single term, NT token rows per block;
 // NT = 64, 128 or 256), all in ONE launch.  glu != 0: `residual` holds gate pre-activations
 // and y = gelu_tanh(gate) * product (y may be the same array as residual; the gate values
-// must come from an earlier launch).  Q4_K only; K a multiple of 256.
+// must come from an earlier launch).  Q4_K or Q8_0 (fmt: the GGUF type id); K a multiple of 256.
 int hb_kq_mma_run_multi(hb200_ctx* ctx, const HbKqSeg* segs, int nseg, int K, int M, int NT,
-                        cudaStream_t st) {
+                        cudaStream_t st, int fmt) {
+  HB_REQUIRE(fmt == HB200_FMT_Q4_K || fmt == HB200_FMT_Q8_0, "kquant (fused batched): format %d", fmt);
   HB_REQUIRE(nseg >= 1 && nseg <= kQmMaxSeg && K % 256 == 0 && M >= 1 && M <= NT &&
                  (NT == 64 || NT == 128 || NT == 256),
              "kquant (fused batched): nseg=%d K=%d M=%d NT=%d", nseg, K, M, NT);
   QmParams p = {};
   TcEncodeTiledFn encode = tc_tensor_map_encoder();
   HB_REQUIRE(encode != nullptr, "kquant (fused batched): the driver has no cuTensorMapEncodeTiled");
-  const int rowbytes = K / 256 * 144;
+  const int unit = fmt == HB200_FMT_Q4_K ? 144 : 272;  // bytes of 256 weights
+  const int rowbytes = K / 256 * unit;
   int tiles = 0;
   for (int s = 0; s < nseg; ++s) {
     const HbKqSeg& g = segs[s];
     HB_REQUIRE(g.N >= 1 && g.N < (1l << 31) && g.blocks && g.y,
                "kquant (fused batched): tensor %d has no rows or a null pointer", s);
     HB_REQUIRE(!g.glu || g.residual, "kquant (fused batched): GLU epilogue without gate values");
-    const cuuint64_t dims[2] = {(cuuint64_t)rowbytes, (cuuint64_t)g.N};
+    // Q4_K: bytes; Q8_0: 32-bit words (a box dimension holds at most 256 elements, 272 > 256)
+    const int esz = fmt == HB200_FMT_Q4_K ? 1 : 4;
+    const cuuint64_t dims[2] = {(cuuint64_t)(rowbytes / esz), (cuuint64_t)g.N};
     const cuuint64_t strides[1] = {(cuuint64_t)rowbytes};
-    const cuuint32_t box[2] = {144u, (cuuint32_t)kQmRows};
+    const cuuint32_t box[2] = {(cuuint32_t)(unit / esz), (cuuint32_t)kQmRows};
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult rc = encode(&p.tmap[s], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+    const CUresult rc = encode(&p.tmap[s],
+                               esz == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2,
                                const_cast<uint8_t*>(g.blocks), dims, strides, box, estr,
                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -442,15 +486,22 @@ int hb_kq_mma_run_multi(hb200_ctx* ctx, const HbKqSeg* segs, int nseg, int K, in
   p.part = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->d_scratch) + kScratchSplitK);
   p.tickets = ctx->d_tickets;
   p.status = ctx->d_status;
+  if (fmt == HB200_FMT_Q4_K) {
+    switch (NT) {
+      case 64: return kq_mma_launch<64, 12>(ctx, p, tiles, st);
+      case 128: return kq_mma_launch<128, 12>(ctx, p, tiles, st);
+      default: return kq_mma_launch<256, 12>(ctx, p, tiles, st);
+    }
+  }
   switch (NT) {
-    case 64: return kq_mma_launch<64>(ctx, p, tiles, st);
-    case 128: return kq_mma_launch<128>(ctx, p, tiles, st);
-    default: return kq_mma_launch<256>(ctx, p, tiles, st);
+    case 64: return kq_mma_launch<64, 8>(ctx, p, tiles, st);
+    case 128: return kq_mma_launch<128, 8>(ctx, p, tiles, st);
+    default: return kq_mma_launch<256, 8>(ctx, p, tiles, st);
   }
 }
 
 int hb_kq_mma_run(hb200_ctx* ctx, const uint8_t* d_blocks, int K, long N, int M, int NT,
-                  float* d_y, const float* d_residual, long ldy, int glu, cudaStream_t st) {
+                  float* d_y, const float* d_residual, long ldy, int glu, cudaStream_t st, int fmt) {
   const HbKqSeg g = {d_blocks, N, d_y, d_residual, ldy, glu};
-  return hb_kq_mma_run_multi(ctx, &g, 1, K, M, NT, st);
+  return hb_kq_mma_run_multi(ctx, &g, 1, K, M, NT, st, fmt);
 }

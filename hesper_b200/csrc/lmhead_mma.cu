@@ -331,8 +331,8 @@ __global__ void __launch_bounds__(kLmThreads, 2)
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&p.tmap))
                    : "memory");
-      // a constant table (the LM head) can be fetched before the dependency resolves; the
-      // f16 arena of the k-quant path is written by the kernels just before this one
+      // a constant table (the LM head) can be fetched before the dependency resolves; a table
+      // that kernels of this stream write cannot
       if (p.table_constant)
         for (int ks = 0; ks < pre; ++ks) issue_a(ks);
     }

@@ -57,9 +57,9 @@ typedef void *hb200_stream;
  * for this path only: binds to `device` (its primary context), reads the SM
  * count, raises the kernels' dynamic shared-memory limits and allocates what the
  * operators need later: a 256-byte status block, 4096 arrival counters and 24 MB of
- * scratch (activation tiles, split-K partials of the batched paths) and a 64 MB arena
- * (f16 weights of one batched k-quant product).  No operator
- * allocates afterwards; a context serves one stream at a time.
+ * scratch (activation tiles, split-K partials of the batched paths).  No operator
+ * allocates afterwards; a context serves one stream at a time (a call that arrives on
+ * another stream than the previous scratch user's is ordered behind it with an event).
  * Environment: HB200_NO_PDL=1 launches without programmatic dependent launch,
  * HB200_NO_MMA=1 keeps the batched (>= 16 token) operators off the tensor-core kernels,
  * HB200_MV=0 / 2 keeps one-token k-quant matvecs off the mma.sync kernel / uses it wherever the
@@ -209,9 +209,9 @@ typedef struct hb200_kquant_seg {
  *   d_rms_gamma nullable: RMSNorm prologue as forwardFusedRMSNormLinear (:7897 region)
  * Up to 15 tokens stream the weights once per token through the dp4a kernel (activations
  * block-quantised to 16 bits, error ~2e-5).  From 16 tokens on the product runs on the
- * tensor cores, 64 tokens per pass: Q4_K is dequantised to f16 inside the tcgen05 kernel,
- * Q8_0 through an f16 arena of the context; weights rounded to f16, error ~4e-4 of max|y|
- * (the bar of this path is 1e-3). */
+ * tensor cores, up to 256 tokens per pass: both formats are dequantised to f16 inside the
+ * tcgen05 kernel; weights and activations rounded to f16 (every staged activation row
+ * scaled by its own power of two), error ~4e-4 of max|y| (the bar of this path is 1e-3). */
 int hb200_kquant_forward(hb200_ctx *ctx, int fmt, const void *d_blocks, int K, int N,
                          const float *d_x, int M, const float *d_rms_gamma, float rms_eps,
                          const float *d_residual, float *d_y, hb200_stream stream);
