@@ -597,6 +597,8 @@ few GB, so that a full-metric capture of one to three launches ends in a minute.
   q80      ring of 8 Q8_0 matrices (223 MB), 3 passes
   i2s      ring of 40 ternary matrices K=2560 N=6912 (177 MB), 3 passes
   attn     decode attention B=16 L=4096, 8q/2kv heads, D=256 (268 MB of KV), 6 calls
+  attn_prefill  causal attention of a 256-token prompt chunk at context 8192, 8 sequences,
+           8q/2kv heads, D=256 (134 MB of KV), 3 calls
   i2s_mma  64-token ternary product on the tensor cores, ring of 40 matrices (177 MB), 2 passes
   lmhead64 64-token LM head on the tensor cores, one bf16 table V=128256 K=2560 (657 MB), 3 calls
   q4k_b32  32-token Q4_K product on the tensor cores, ring of 12 matrices, 2 passes
@@ -693,6 +695,16 @@ def run_case(name: str) -> int:
         m.set_position(8000)
         m.generate(None, 3, use_graph=False)
         m.close()
+    elif name == "attn_prefill":
+        B, T, H, Hkv, D, L = 8, 256, 8, 2, 256, 8192
+        q = torch.randn(B, T, H, D, device="cuda")
+        k = torch.randn(B, Hkv, L, D, device="cuda").half()
+        v = torch.randn(B, Hkv, L, D, device="cuda").half()
+        lens = torch.full((B,), L, dtype=torch.int32, device="cuda")
+        torch.cuda.synchronize()
+        for _ in range(3):
+            hb.flash_attention_prefill(ctx, q, k, v, lens, num_heads=H, num_kv_heads=Hkv,
+                                       head_dim=D, max_seq_len=L, scale=1 / 16)
     elif name == "attn":
         B, H, Hkv, D, L = 16, 8, 2, 256, 4096
         q = torch.randn(B, H, D, device="cuda").half()
