@@ -528,9 +528,11 @@ extern "C" int hb200_bitlinear_forward_multi(hb200_ctx* ctx, const hb200_bitline
     rows += segs[s].N;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (M > 64) {  // 64 tokens per pass
-    for (int m0 = 0; m0 < M; m0 += 64) {
-      const int mc = M - m0 < 64 ? M - m0 : 64;
+  // tokens per pass over the weights: 128 on the tensor cores, 64 on the dp4a kernel
+  const int pass = (K <= 12288 && !ctx->no_mma) ? 128 : 64;
+  if (M > pass) {
+    for (int m0 = 0; m0 < M; m0 += pass) {
+      const int mc = M - m0 < pass ? M - m0 : pass;
       hb200_bitlinear_seg sub[kBLMaxSeg];
       for (int s = 0; s < nseg; ++s) {
         sub[s] = segs[s];
@@ -624,9 +626,14 @@ extern "C" int hb200_bitlinear_gateup_relu2(hb200_ctx* ctx, const void* d_packed
   HB_REQUIRE(((reinterpret_cast<uintptr_t>(d_packed_gate) |
                reinterpret_cast<uintptr_t>(d_packed_up)) & 15) == 0,
              "bitlinear gate/up: weights must be 16-byte aligned");
-  if (M > 64) {  // 64 tokens per pass
-    for (int m0 = 0; m0 < M; m0 += 64) {
-      const int mc = M - m0 < 64 ? M - m0 : 64;
+  // tokens per pass: 128 where both products run on the tensor cores into the scratch, else 64
+  const int pass = (K <= 12288 && !ctx->no_mma &&
+                    kScratchGlu + (size_t)2 * 128 * N * sizeof(float) <= kScratchRowScale)
+                       ? 128
+                       : 64;
+  if (M > pass) {
+    for (int m0 = 0; m0 < M; m0 += pass) {
+      const int mc = M - m0 < pass ? M - m0 : pass;
       rc = hb200_bitlinear_gateup_relu2(ctx, d_packed_gate, d_scale_gate, d_packed_up, d_scale_up,
                                         K, N, d_x + (size_t)m0 * K, mc, d_rms_gamma, rms_eps,
                                         d_y + (size_t)m0 * N, stream);
@@ -635,8 +642,9 @@ extern "C" int hb200_bitlinear_gateup_relu2(hb200_ctx* ctx, const void* d_packed
     return HB200_OK;
   }
   if (M >= 16 && K <= 12288 && !ctx->no_mma &&
-      kScratchGlu + (size_t)2 * M * N * sizeof(float) <= kScratchLmSplit) {
-    // batched: both products on the tensor cores into scratch, then the GLU epilogue
+      kScratchGlu + (size_t)2 * M * N * sizeof(float) <= kScratchRowScale) {
+    // batched: both products on the tensor cores into scratch (the region may run into the
+    // staging area of the 16-bit products, which no ternary operator uses), then the GLU
     ScratchUse use(ctx, static_cast<cudaStream_t>(stream));
     float* g = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->d_scratch) + kScratchGlu);
     float* u = g + (size_t)M * N;

@@ -38,17 +38,30 @@ namespace hb {
 
 constexpr int kMmaThreads = 256;
 constexpr int kMmaRows = 128;    // weight rows per CTA = MMA M
-constexpr int kMmaTokens = 64;   // MMA N
+constexpr int kMmaTokens = 64;   // MMA N of the narrow variant (16..64 tokens)
 constexpr int kChunkGroups = 4;  // 128-weight groups per packed box: 128 bytes of every row
 constexpr int kPkStages = 4;     // packed ring
 constexpr int kPkBytes = kMmaRows * kChunkGroups * 32;  // 16 KB box
 constexpr int kStepGroups = 2;   // groups per pipeline step: one barrier round trip per 8 MMAs
-constexpr int kStages = 6;       // operand stages (A in tensor memory, B in shared memory)
-constexpr int kBBytes = kMmaTokens * 128;               // 8 KB activation tile of one group
-constexpr int kAccCols = 64;     // TMEM columns of the 128 x 64 int32 accumulator
 constexpr int kAGroupCols = 32;  // TMEM columns of one expanded group: 128 K-bytes per row
-static_assert(kAccCols + kStages * kStepGroups * kAGroupCols <= 512, "tensor memory columns");
-constexpr int kMmaSmem = 1024 + kPkStages * kPkBytes + kStages * kStepGroups * kBBytes;
+constexpr int kMmaCtrl = 2048;   // barriers, tensor-memory slot, d[NT], sum(q)[NT]
+
+// NT tokens per pass = MMA N: 64, or 128 for the prompt passes (half the weight passes per
+// token).  Tensor memory, 512 columns: accumulator of the first issuing warp at 0, the A stages
+// behind it, the second warp's accumulator in the last NT columns.
+template <int NT>
+struct MmaCfg {
+  static constexpr int kStages = NT == 64 ? 6 : 4;  // operand stages (A in TMEM, B in smem)
+  static constexpr int kBBytes = NT * 128;          // activation tile of one 128-wide group
+  static constexpr int kA0 = NT;                    // first column of the A stages
+  static constexpr int kAcc1 = 512 - NT;            // the second accumulator
+  static constexpr int kSmem = kMmaCtrl + kPkStages * kPkBytes + kStages * kStepGroups * kBBytes;
+  // kind::i8: D = s32, A = u8, B = s8, both K-major, N = NT, M = 128
+  static constexpr uint32_t kIdesc = (2u << 4) | (0u << 7) | (1u << 10) |
+                                     ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(kMmaRows >> 4) << 24);
+  static_assert(kA0 + kStages * kStepGroups * kAGroupCols <= kAcc1, "tensor memory columns");
+  static_assert(kSmem <= 232448, "shared memory budget of one CTA");
+};
 
 struct MmaSeg {
   const uint8_t* w;
@@ -65,11 +78,11 @@ struct MmaParams {
   MmaSeg seg[4];
   int nseg, K, M;
   int nsplit, gps;     // split-K: CTAs per tile, groups per split
-  int32_t* part;       // [tile][split][64 tokens][128 rows] partial accumulators (nsplit > 1)
+  int32_t* part;       // [tile][split][NT tokens][128 rows] partial accumulators (nsplit > 1)
   int* tickets;        // [tile] arrival counters, zero between launches
-  const uint8_t* xq;   // [K/128][64 tokens x 128 bytes, core-matrix layout]
-  const float* d;      // [64] activation scales
-  const int32_t* sumq; // [64]
+  const uint8_t* xq;   // [K/128][NT tokens x 128 bytes, core-matrix layout]
+  const float* d;      // [NT] activation scales
+  const int32_t* sumq; // [NT]
   uint32_t* status;
 };
 
@@ -84,6 +97,7 @@ struct QuantParams {
   float* d;
   int32_t* sumq;
   float* act_scale;    // nullable user copy of d
+  int bbytes;          // bytes of one 128-wide K group of the tile: tokens per pass x 128
 };
 
 __global__ void __launch_bounds__(256) quant_act_kernel(const __grid_constant__ QuantParams p) {
@@ -100,10 +114,10 @@ __global__ void __launch_bounds__(256) quant_act_kernel(const __grid_constant__ 
   const int K = p.K, nvec = K >> 2;
   auto dst_of = [&](int i) {  // float4 index -> byte offset of its 4 int8 in the operand layout
     const int k = i << 2;
-    return (size_t)(k >> 7) * kBBytes + (size_t)(m >> 3) * 1024 + (size_t)((k & 127) >> 4) * 128 +
+    return (size_t)(k >> 7) * p.bbytes + (size_t)(m >> 3) * 1024 + (size_t)((k & 127) >> 4) * 128 +
            (size_t)(m & 7) * 16 + (k & 15);
   };
-  if (m >= p.M) {  // padding token of the 64-wide tile
+  if (m >= p.M) {  // padding token of the tile
     for (int i = tid; i < nvec; i += 256) *reinterpret_cast<uint32_t*>(p.xq + dst_of(i)) = 0u;
     if (tid == 0) {
       p.d[m] = 0.f;
@@ -182,22 +196,22 @@ __global__ void __launch_bounds__(256) quant_act_kernel(const __grid_constant__ 
 
 // ---- tcgen05 helpers --------------------------------------------------------------------
 
-// Instruction descriptor for kind::i8: D = s32, A = u8, B = s8, both K-major, N = 64, M = 128.
-constexpr uint32_t kIdescI8 = (2u << 4) | (0u << 7) | (1u << 10) | ((kMmaTokens >> 3) << 17) |
-                              ((kMmaRows >> 4) << 24);
-
 // A operand from tensor memory (lane = weight row, 4 K-bytes per 32-bit column).
 __device__ __forceinline__ void umma_i8_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
-                                           uint32_t accumulate) {
+                                           uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "r"(tmem_a), "l"(bdesc), "r"(kIdescI8), "r"(accumulate)
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 
+template <int NT>
 __global__ void __launch_bounds__(kMmaThreads + 96, 1)
     bitlinear_mma_kernel(const __grid_constant__ MmaParams p) {
+  using Cfg = MmaCfg<NT>;
+  constexpr int kStages = Cfg::kStages, kBBytes = Cfg::kBBytes;
+  constexpr int NCH = NT / 64;  // 32-token chunks an epilogue warp owns
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // this CTA's K range (split-K over 128-wide groups; a whole row when nsplit == 1)
@@ -216,9 +230,9 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
   uint64_t* mma_done = full + kStages;    // [kStages] the MMAs that read the stage have retired
   uint64_t* done = mma_done + kStages;    // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
-  float* sd = reinterpret_cast<float*>(smem + 512);        // [64]
-  int* ssum = reinterpret_cast<int*>(smem + 768);          // [64]
-  uint8_t* pk = smem + 1024;
+  float* sd = reinterpret_cast<float*>(smem + 512);        // [NT]
+  int* ssum = reinterpret_cast<int*>(smem + 1024);         // [NT]
+  uint8_t* pk = smem + kMmaCtrl;
   uint8_t* bstg = pk + kPkStages * kPkBytes;  // [kStages][kStepGroups] activation tiles
 
   // tile -> (segment, first row)
@@ -242,7 +256,7 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
     mbar_init(done, 2);
     fence_mbar_init();
   }
-  if (warp == kMmaWarp) {  // all 512 columns: 64 for the accumulator, the rest A stages
+  if (warp == kMmaWarp) {  // all 512 columns: two accumulators, the A stages between them
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(
         smem_u32(tmem_slot)));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
@@ -305,13 +319,13 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
   } else if (warp == kMmaWarp || warp == kMmaWarp + 2) {
     // ================= two MMA warps: even steps -> accumulator 0, odd steps -> accumulator 1
     const int which = warp == kMmaWarp ? 0 : 1;
-    const uint32_t tmem_d = tmem + (which ? 448u : 0u);
+    const uint32_t tmem_d = tmem + (which ? (uint32_t)Cfg::kAcc1 : 0u);
     for (int s = which; s < nsteps; s += 2) {
       const int st = s % kStages;
       ok = tc_wait(ok, &full[st], (uint32_t)((s / kStages) & 1), p.status);
       if (lane == 0) {
         tc_after_sync();
-        const uint32_t a_t = tmem + kAccCols + (uint32_t)st * (kStepGroups * kAGroupCols);
+        const uint32_t a_t = tmem + Cfg::kA0 + (uint32_t)st * (kStepGroups * kAGroupCols);
         const uint32_t bbase = smem_u32(bstg + (size_t)st * kStepGroups * kBBytes);
         const int ng = min(kStepGroups, ngroups - s * kStepGroups);
 #pragma unroll
@@ -320,7 +334,7 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
 #pragma unroll
             for (int j = 0; j < 4; ++j)  // K = 32 bytes per instruction: 8 columns of A
               umma_i8_ta(tmem_d, a_t + gg * kAGroupCols + j * 8,
-                         tc_smem_desc(bbase + gg * kBBytes + j * 256, 128, 1024, 0),
+                         tc_smem_desc(bbase + gg * kBBytes + j * 256, 128, 1024, 0), Cfg::kIdesc,
                          (s > 1 || gg > 0 || j > 0) ? 1u : 0u);
           }
         tc_commit(&mma_done[st]);  // arrives once these (and all earlier) MMAs have retired
@@ -334,7 +348,7 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
     // planes 2h and 2h+1 of the packed bytes = K bytes 64h..64h+63 = 16 columns.
     const int q = warp & 3, h = warp >> 2;
     const int erow = q * 32 + lane;
-    const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16) + kAccCols + 16u * h;
+    const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16) + Cfg::kA0 + 16u * h;
     for (int s = 0; s < nsteps; ++s) {
       const int st = s % kStages;
       if (s >= kStages) {
@@ -387,7 +401,7 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
                      : "memory");
     }
     pdl_wait();  // d and sum(q) come from the quantiser
-    if (tid < kMmaTokens) {
+    if (tid < NT) {
       sd[tid] = p.d[tid];
       ssum[tid] = p.sumq[tid];
     }
@@ -396,41 +410,25 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
   tc_after_sync();
   __syncthreads();  // sd / ssum visible; every warp past its loop
 
-  // ---- epilogue: TMEM lane = weight row, column = token; warps w and w+4 share lanes ------
-  const int q = warp & 3, half = warp >> 2;  // lane quarter, token half (expander warps only)
+  // ---- epilogue: TMEM lane = weight row, column = token.  Warps w and w + 4 share a lane
+  //      quarter; a warp owns the 32-token chunks (w >> 2), (w >> 2) + 2, ... ----------------
+  const int q = warp & 3, half = warp >> 2;  // lane quarter, first chunk (expander warps only)
   const int r = q * 32 + lane;
-  const int m0 = half * 32;
-  uint32_t v[32];
+  uint32_t v[NCH][32];
   if (warp < kExpWarps) {
-    const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 32);
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
-          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
-          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr));
-    if (nsteps > 1) {  // the second MMA warp's accumulator
-      uint32_t u[32];
-      asm volatile(
-          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-          "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-          "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-          : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]),
-            "=r"(u[7]), "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]),
-            "=r"(u[13]), "=r"(u[14]), "=r"(u[15]), "=r"(u[16]), "=r"(u[17]), "=r"(u[18]),
-            "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]),
-            "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]),
-            "=r"(u[31])
-          : "r"(taddr + 448u));
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-      for (int t = 0; t < 32; ++t) v[t] += u[t];
-    } else {
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    for (int c = 0; c < NCH; ++c) {
+      const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)((half + 2 * c) * 32);
+      HB_TMEM_LD32(v[c], taddr);
+      if (nsteps > 1) {  // the second MMA warp's accumulator
+        uint32_t u[32];
+        HB_TMEM_LD32(u, taddr + (uint32_t)Cfg::kAcc1);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int t = 0; t < 32; ++t) v[c][t] += u[t];
+      } else {
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      }
     }
   }
 
@@ -439,10 +437,15 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
   bool finish = true;
   if (p.nsplit > 1) {
     __shared__ int s_last;
-    int32_t* mine = p.part + ((size_t)(tile * p.nsplit + split) * kMmaTokens) * kMmaRows;
+    int32_t* mine = p.part + ((size_t)(tile * p.nsplit + split) * NT) * kMmaRows;
     if (warp < kExpWarps) {
 #pragma unroll
-      for (int t = 0; t < 32; ++t) mine[(size_t)(m0 + t) * kMmaRows + r] = (int32_t)v[t];
+      for (int c = 0; c < NCH; ++c) {
+        const int m0 = (half + 2 * c) * 32;
+        if (m0 >= p.M) continue;
+#pragma unroll
+        for (int t = 0; t < 32; ++t) mine[(size_t)(m0 + t) * kMmaRows + r] = (int32_t)v[c][t];
+      }
     }
     __threadfence();
     __syncthreads();
@@ -455,49 +458,57 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
     finish = s_last != 0;
     if (finish && warp < kExpWarps) {
       __threadfence();
-      for (int s2 = 0; s2 < p.nsplit; ++s2) {
-        if (s2 == split) continue;
-        const int32_t* other =
-            p.part + ((size_t)(tile * p.nsplit + s2) * kMmaTokens + m0) * kMmaRows + r;
 #pragma unroll
-        for (int t = 0; t < 32; ++t) v[t] += (uint32_t)__ldcg(other + (size_t)t * kMmaRows);
+      for (int c = 0; c < NCH; ++c) {
+        const int m0 = (half + 2 * c) * 32;
+        if (m0 >= p.M) continue;
+        for (int s2 = 0; s2 < p.nsplit; ++s2) {
+          if (s2 == split) continue;
+          const int32_t* other = p.part + ((size_t)(tile * p.nsplit + s2) * NT + m0) * kMmaRows + r;
+#pragma unroll
+          for (int t = 0; t < 32; ++t) v[c][t] += (uint32_t)__ldcg(other + (size_t)t * kMmaRows);
+        }
       }
     }
   }
 
   if (finish && warp < kExpWarps) {
     const float ws = __ldg(p.seg[seg].scale);
-    if (r < nrows && ok) {
-      const int mcount = min(32, p.M - m0);
-      const size_t o0 = (size_t)m0 * seg_N + row0 + r;
-      float* yp = p.seg[seg].y + o0;
-      const float* rp = p.seg[seg].residual ? p.seg[seg].residual + o0 : nullptr;
-      int32_t* ap = p.seg[seg].acc ? p.seg[seg].acc + o0 : nullptr;
-      // all shared-memory reads first (v[t] becomes the integer total), so that the stores
-      // below, whose target the compiler cannot tell from shared memory, do not serialise them
-      float dsc[32];
 #pragma unroll
-      for (int t = 0; t < 32; ++t) {
-        v[t] = (uint32_t)((int)v[t] - ssum[m0 + t]);
-        dsc[t] = sd[m0 + t];
-      }
-      if (ap) {
+    for (int c = 0; c < NCH; ++c) {
+      const int m0 = (half + 2 * c) * 32;
+      if (r < nrows && ok && m0 < p.M) {
+        const int mcount = min(32, p.M - m0);
+        const size_t o0 = (size_t)m0 * seg_N + row0 + r;
+        float* yp = p.seg[seg].y + o0;
+        const float* rp = p.seg[seg].residual ? p.seg[seg].residual + o0 : nullptr;
+        int32_t* ap = p.seg[seg].acc ? p.seg[seg].acc + o0 : nullptr;
+        // all shared-memory reads first (v[t] becomes the integer total), so that the stores
+        // below, whose target the compiler cannot tell from shared memory, do not serialise them
+        float dsc[32];
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+          v[c][t] = (uint32_t)((int)v[c][t] - ssum[m0 + t]);
+          dsc[t] = sd[m0 + t];
+        }
+        if (ap) {
+#pragma unroll
+          for (int t = 0; t < 32; ++t)
+            if (t < mcount) ap[(size_t)t * seg_N] = (int)v[c][t];
+        }
+        float res[32];
+        if (rp) {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) res[t] = t < mcount ? rp[(size_t)t * seg_N] : 0.f;
+        }
 #pragma unroll
         for (int t = 0; t < 32; ++t)
-          if (t < mcount) ap[(size_t)t * seg_N] = (int)v[t];
+          if (t < mcount) {
+            float y = __fmul_rn(__fmul_rn((float)(int)v[c][t], dsc[t]), ws);
+            if (rp) y = __fadd_rn(y, res[t]);
+            yp[(size_t)t * seg_N] = y;
+          }
       }
-      float res[32];
-      if (rp) {
-#pragma unroll
-        for (int t = 0; t < 32; ++t) res[t] = t < mcount ? rp[(size_t)t * seg_N] : 0.f;
-      }
-#pragma unroll
-      for (int t = 0; t < 32; ++t)
-        if (t < mcount) {
-          float y = __fmul_rn(__fmul_rn((float)(int)v[t], dsc[t]), ws);
-          if (rp) y = __fadd_rn(y, res[t]);
-          yp[(size_t)t * seg_N] = y;
-        }
     }
   }
   tc_before_sync();
@@ -510,21 +521,45 @@ __global__ void __launch_bounds__(kMmaThreads + 96, 1)
 
 using namespace hb;
 
-// Batched path of hb200_bitlinear_forward_multi (16 <= M <= 64).  Scratch in the context:
-// quantised activations in operand layout, their scales and sums.
+// Batched path of hb200_bitlinear_forward_multi (16 <= M <= 128: one pass of 64 or 128 token
+// slots).  Scratch in the context: quantised activations in operand layout, their scales and
+// sums.
+template <int NT>
+static int bl_mma_launch(hb200_ctx* ctx, MmaParams& p, int tiles, cudaStream_t st) {
+  // split-K when the tiles alone leave most SMs idle: as many splits as fit the SMs, each at
+  // least 4 groups (two pipeline steps) long, partials within their scratch region
+  const int ngroups = p.K / 128;
+  int nsplit = ctx->sm_count / tiles;
+  if (nsplit > ngroups / 4) nsplit = ngroups / 4;
+  while (nsplit > 1 &&
+         (size_t)tiles * nsplit * NT * kMmaRows * 4 > kScratchBytes - kScratchSplitK)
+    --nsplit;
+  if (nsplit < 1 || tiles > kCtxTickets) nsplit = 1;
+  p.gps = (ngroups + nsplit - 1) / nsplit;
+  p.nsplit = (ngroups + p.gps - 1) / p.gps;  // no empty split
+  const int rc = hb_func_smem(ctx, reinterpret_cast<const void*>(bitlinear_mma_kernel<NT>),
+                              (size_t)MmaCfg<NT>::kSmem);
+  if (rc != HB200_OK) return rc;
+  HB_CUDA(launch_pdl(bitlinear_mma_kernel<NT>, dim3(tiles * p.nsplit), dim3(kMmaThreads + 96),
+                     (size_t)MmaCfg<NT>::kSmem, st, ctx->pdl, p));
+  return HB200_OK;
+}
+
 int hb_bitlinear_mma_run(hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int nseg, int K,
                          const float* d_x, int M, const float* d_rms_gamma, float rms_eps,
                          float* d_act_scale, cudaStream_t st) {
   ScratchUse use(ctx, st);  // quantised activation tiles, split-K partials, tickets
-  const size_t xq_bytes = (size_t)(K / 128) * kBBytes;
+  HB_REQUIRE(M >= 1 && M <= 128, "bitlinear (batched): %d tokens in one pass (at most 128)", M);
+  const int NT = M <= 64 ? 64 : 128;
+  const size_t xq_bytes = (size_t)(K / 128) * NT * 128;
   HB_REQUIRE(xq_bytes + 1024 <= kScratchGlu,
              "bitlinear (batched): K=%d needs %zu bytes of activation scratch", K, xq_bytes);
   uint8_t* base = static_cast<uint8_t*>(ctx->d_scratch);
-  float* d = reinterpret_cast<float*>(base);
-  int32_t* sumq = reinterpret_cast<int32_t*>(base + 256);
+  float* d = reinterpret_cast<float*>(base);            // [128]
+  int32_t* sumq = reinterpret_cast<int32_t*>(base + 512);  // [128]
   uint8_t* xq = base + 1024;
-  QuantParams q = {d_x, d_rms_gamma, rms_eps, K, M, xq, d, sumq, d_act_scale};
-  HB_CUDA(launch_pdl(quant_act_kernel, dim3(kMmaTokens), dim3(256), (size_t)K * sizeof(float), st,
+  QuantParams q = {d_x, d_rms_gamma, rms_eps, K, M, xq, d, sumq, d_act_scale, NT * 128};
+  HB_CUDA(launch_pdl(quant_act_kernel, dim3(NT), dim3(256), (size_t)K * sizeof(float), st,
                      ctx->pdl, q));
   MmaParams p = {};
   int t = 0;
@@ -551,28 +586,11 @@ int hb_bitlinear_mma_run(hb200_ctx* ctx, const hb200_bitlinear_seg* segs, int ns
   p.nseg = nseg;
   p.K = K;
   p.M = M;
-  // split-K when the tiles alone leave most SMs idle: as many splits as fit the SMs, each at
-  // least 4 groups (two pipeline steps) long, partials within their scratch region
-  const int ngroups = K / 128;
-  int nsplit = ctx->sm_count / t;
-  if (nsplit > ngroups / 4) nsplit = ngroups / 4;
-  while (nsplit > 1 && (size_t)t * nsplit * kMmaTokens * kMmaRows * 4 >
-                           kScratchBytes - kScratchSplitK)
-    --nsplit;
-  if (nsplit < 1 || t > kCtxTickets) nsplit = 1;
-  p.gps = (ngroups + nsplit - 1) / nsplit;
-  p.nsplit = (ngroups + p.gps - 1) / p.gps;  // no empty split
   p.part = reinterpret_cast<int32_t*>(base + kScratchSplitK);
   p.tickets = ctx->d_tickets;
   p.xq = xq;
   p.d = d;
   p.sumq = sumq;
   p.status = ctx->d_status;
-  {
-    const int rc = hb_func_smem(ctx, reinterpret_cast<const void*>(bitlinear_mma_kernel), (size_t)kMmaSmem);
-    if (rc != HB200_OK) return rc;
-  }
-  HB_CUDA(launch_pdl(bitlinear_mma_kernel, dim3(t * p.nsplit), dim3(kMmaThreads + 96), (size_t)kMmaSmem, st,
-                     ctx->pdl, p));
-  return HB200_OK;
+  return NT == 64 ? bl_mma_launch<64>(ctx, p, t, st) : bl_mma_launch<128>(ctx, p, t, st);
 }

@@ -136,9 +136,8 @@ typedef struct hb200_bitlinear_seg {
  *   d_x          [M][K] f32 activations
  *   d_rms_gamma  nullable [K]; when set x is replaced by RMSNorm(x)*gamma, eps = rms_eps
  *   d_act_scale  nullable [M]; receives d[m]
- * K must be a multiple of 128, 1 <= M <= 4096 (64 tokens per pass).  From 16 tokens on (and
- * K <= 12288) the
- * product runs on the tensor cores (tcgen05 kind::i8, accumulators in tensor memory,
+ * K must be a multiple of 128, 1 <= M <= 4096.  From 16 tokens on (and K <= 12288) the
+ * product runs on the tensor cores in passes of up to 128 tokens (tcgen05 kind::i8, accumulators in tensor memory,
  * the M>1 role of Hesper/Layers/BitLinear.lean:122,869,994) with identical results. */
 int hb200_bitlinear_forward(hb200_ctx *ctx, const void *d_packed, const float *d_scale,
                             int K, int N, const float *d_x, int M,

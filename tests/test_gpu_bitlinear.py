@@ -82,7 +82,8 @@ def test_residual_and_rmsnorm_prologue(ctx, oracle, M):
 
 
 @pytest.mark.parametrize("K,N,M", [(2560, 6912, 1), (256, 5, 1), (2560, 100, 3), (1024, 64, 8),
-                                   (2560, 300, 32), (2560, 6912, 64), (6912, 130, 17)])
+                                   (2560, 300, 32), (2560, 6912, 64), (6912, 130, 17),
+                                   (2560, 6912, 128), (2560, 6912, 200), (1024, 700, 100)])
 def test_gate_up_relu2(ctx, oracle, K, N, M):
     rng = np.random.default_rng(K + N + M)
     pg = formats.i2s_pack(formats.random_ternary(rng, N, K))
@@ -118,11 +119,13 @@ def test_fused_qkv_multi(ctx, oracle):
 
 @pytest.mark.parametrize("K,N,M", [(2560, 6912, 64), (6912, 2560, 64), (2560, 2560, 33),
                                    (128, 1, 16), (1152, 129, 20), (8192, 257, 48),
-                                   (2560, 640, 150)])
+                                   (2560, 640, 150), (2560, 6912, 128), (6912, 2560, 100),
+                                   (2560, 2560, 65), (1152, 300, 256)])
 def test_batched_tensor_core_path_bit_exact(ctx, oracle, K, N, M):
     """16 or more tokens run on tcgen05 (kind::i8, accumulators in tensor memory): the int32
     results must still be bit-exact, including ragged row tiles, partial K chunks and the
-    split-K reduction that launches with few row tiles use."""
+    split-K reduction that launches with few row tiles use.  Up to 64 tokens take the 64-wide
+    kernel, 65 to 128 the 128-wide one, more go in passes of 128 (150 = 128 + 22)."""
     rng = np.random.default_rng(K + N + M)
     packed = formats.i2s_pack(formats.random_ternary(rng, N, K))
     x = rng.standard_normal((M, K)).astype(np.float32)
