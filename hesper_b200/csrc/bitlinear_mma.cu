@@ -192,8 +192,6 @@ __global__ void __launch_bounds__(256) quant_act_kernel(const __grid_constant__ 
   }
 }
 
-#define MMA_DBG(bit) 0
-
 // ---- tcgen05 helpers --------------------------------------------------------------------
 
 // A operand from tensor memory (lane = weight row, 4 K-bytes per 32-bit column).
