@@ -786,7 +786,8 @@ static int attn_run(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d
   // 64 / G tokens (attention_prefill.cu); PRECISE / EXACT keep one decode query per token
   if (T >= 8 && D != 32 && ctx->attn_mode == HB200_ATTN_FAST) {
     const int rc = hb_attn_prefill_tiled(ctx, d_q, q_is_f16, d_k, d_v, d_seqlens, nseq, T, H, Hkv,
-                                         D, max_seq, window, ring, scale, d_out,
+                                         D, max_seq, window, ring, scale, d_workspace,
+                                         workspace_bytes, d_out,
                                          static_cast<cudaStream_t>(stream));
     if (rc <= 0) return rc;
   }
@@ -873,8 +874,12 @@ extern "C" int hb200_attn_decode(hb200_ctx* ctx, const void* d_q, int q_is_f16, 
 
 extern "C" size_t hb200_attn_prefill_workspace_bytes(const hb200_ctx* ctx, int B, int T, int H,
                                                      int Hkv, int D, int max_seq) {
-  if (T < 1 || B < 1 || (long)B * T >= (1l << 24)) return 0;
-  return hb200_attn_workspace_bytes(ctx, B * T, H, Hkv, D, max_seq);
+  if (!ctx || T < 1 || B < 1 || Hkv < 1 || (long)B * T >= (1l << 24)) return 0;
+  // the larger of what the two routes want: one decode query per token, or the tiled kernel
+  // with the positions of a query tile split over several CTAs
+  const size_t a = hb200_attn_workspace_bytes(ctx, B * T, H, Hkv, D, max_seq);
+  const size_t t = hb_attn_prefill_tiled_ws(ctx, B, T, H, Hkv, D, max_seq);
+  return a > t ? a : t;
 }
 
 extern "C" int hb200_attn_prefill(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d_k,

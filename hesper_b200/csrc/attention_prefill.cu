@@ -40,6 +40,12 @@ struct PfParams {
   int q_is_f16;
   int nseq, T, H, Hkv, G, slots, window, ring;
   float scale_log2;
+  // nsplit > 1: the K/V tiles of a query tile are dealt to nsplit CTAs (a long context at a small
+  // batch would otherwise fill a fraction of the SMs); each writes its unnormalised partial and
+  // its (max, sum), attn_prefill_merge_kernel combines them
+  int nsplit;
+  float* part_o;   // [nseq][T][H][nsplit][D]
+  float* part_ml;  // [nseq][T][H][nsplit][2]  (max in the exp2 domain, sum)
 };
 
 template <int D>
@@ -97,7 +103,8 @@ __global__ void __launch_bounds__(kPfThreads, D >= 256 ? 1 : 2)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
   const int G = p.G, TQ = kPfRows / G;
-  const int qt = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int qt = blockIdx.x / p.nsplit, split = blockIdx.x % p.nsplit;
+  const int kvh = blockIdx.y, b = blockIdx.z;
 
   __half* qs = reinterpret_cast<__half*>(smem);
   uint8_t* stage0 = smem + Cfg::kQBytes;
@@ -114,14 +121,18 @@ __global__ void __launch_bounds__(kPfThreads, D >= 256 ? 1 : 2)
   int kv_lo = 0;
   if (p.window > 0) kv_lo = max(0, pos_first - p.window + 1);
   const int kv_hi = pos_last;  // inclusive
-  const int ntiles = kv_hi >= kv_lo ? (kv_hi - kv_lo) / TILE + 1 : 0;
+  const int ntiles_all = kv_hi >= kv_lo ? (kv_hi - kv_lo) / TILE + 1 : 0;
+  // this CTA's share of the tiles
+  const int tps = (ntiles_all + p.nsplit - 1) / p.nsplit;
+  const int j0 = split * tps;
+  const int ntiles = max(0, min(ntiles_all, j0 + tps) - j0);
 
   const __half* kbase = p.k + ((size_t)b * p.Hkv + kvh) * (size_t)p.slots * D;
   const __half* vbase = p.v + ((size_t)b * p.Hkv + kvh) * (size_t)p.slots * D;
   auto issue = [&](int j, int st) {
     uint8_t* ks = stage0 + (size_t)st * 2 * Cfg::kTileBytes;
     uint8_t* vs = ks + Cfg::kTileBytes;
-    const int p0 = kv_lo + j * TILE;
+    const int p0 = kv_lo + (j0 + j) * TILE;
 #pragma unroll
     for (int i = 0; i < TILE * CPR / kPfThreads; ++i) {
       const int u = tid + i * kPfThreads;
@@ -181,7 +192,7 @@ __global__ void __launch_bounds__(kPfThreads, D >= 256 ? 1 : 2)
     __syncthreads();  // tile j is in shared memory for every warp
     const uint8_t* ks = stage0 + (size_t)(j & 1) * 2 * Cfg::kTileBytes;
     const uint8_t* vs = ks + Cfg::kTileBytes;
-    const int p0 = kv_lo + j * TILE;
+    const int p0 = kv_lo + (j0 + j) * TILE;
 
     // ---- S = Q K^T: 16 rows x TILE positions per warp -------------------------------------
     float s[NS][4];
@@ -274,19 +285,61 @@ __global__ void __launch_bounds__(kPfThreads, D >= 256 ? 1 : 2)
     __syncthreads();  // every warp is done with stage j & 1 before it is refilled
   }
 
-  // ---- normalise and store ---------------------------------------------------------------
-  const float invA = lA > 0.f ? 1.f / lA : 0.f, invB = lB > 0.f ? 1.f / lB : 0.f;
+  // ---- normalise and store, or hand the partial to the merge kernel ------------------------
+  if (p.nsplit == 1) {
+    const float invA = lA > 0.f ? 1.f / lA : 0.f, invB = lB > 0.f ? 1.f / lB : 0.f;
+    if (liveA) {
+      float* dst = p.out + (((size_t)b * p.T + tA) * p.H + kvh * G + rA % G) * D;
+#pragma unroll
+      for (int n = 0; n < NO; ++n)
+        *reinterpret_cast<float2*>(dst + 8 * n + 2 * t4) = make_float2(o[n][0] * invA, o[n][1] * invA);
+    }
+    if (liveB) {
+      float* dst = p.out + (((size_t)b * p.T + tB) * p.H + kvh * G + rB % G) * D;
+#pragma unroll
+      for (int n = 0; n < NO; ++n)
+        *reinterpret_cast<float2*>(dst + 8 * n + 2 * t4) = make_float2(o[n][2] * invB, o[n][3] * invB);
+    }
+    return;
+  }
   if (liveA) {
-    float* dst = p.out + (((size_t)b * p.T + tA) * p.H + kvh * G + rA % G) * D;
+    const size_t pi = ((((size_t)b * p.T + tA) * p.H + kvh * G + rA % G) * p.nsplit + split);
+    float* dst = p.part_o + pi * D;
 #pragma unroll
     for (int n = 0; n < NO; ++n)
-      *reinterpret_cast<float2*>(dst + 8 * n + 2 * t4) = make_float2(o[n][0] * invA, o[n][1] * invA);
+      *reinterpret_cast<float2*>(dst + 8 * n + 2 * t4) = make_float2(o[n][0], o[n][1]);
+    if (t4 == 0) *reinterpret_cast<float2*>(p.part_ml + pi * 2) = make_float2(mA, lA);
   }
   if (liveB) {
-    float* dst = p.out + (((size_t)b * p.T + tB) * p.H + kvh * G + rB % G) * D;
+    const size_t pi = ((((size_t)b * p.T + tB) * p.H + kvh * G + rB % G) * p.nsplit + split);
+    float* dst = p.part_o + pi * D;
 #pragma unroll
     for (int n = 0; n < NO; ++n)
-      *reinterpret_cast<float2*>(dst + 8 * n + 2 * t4) = make_float2(o[n][2] * invB, o[n][3] * invB);
+      *reinterpret_cast<float2*>(dst + 8 * n + 2 * t4) = make_float2(o[n][2], o[n][3]);
+    if (t4 == 0) *reinterpret_cast<float2*>(p.part_ml + pi * 2) = make_float2(mB, lB);
+  }
+}
+
+// out = sum_s 2^(m_s - m*) O_s / sum_s 2^(m_s - m*) l_s over the splits of one (token, head).
+__global__ void __launch_bounds__(128) attn_prefill_merge_kernel(const float* part_o,
+                                                                 const float* part_ml, int nsplit,
+                                                                 int D, float* out) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t row = blockIdx.x;  // (sequence, token, head)
+  const float* ml = part_ml + row * nsplit * 2;
+  float mstar = -CUDART_INF_F;
+  for (int s2 = 0; s2 < nsplit; ++s2) mstar = fmaxf(mstar, __ldcg(ml + 2 * s2));
+  float lsum = 0.f;
+  if (mstar != -CUDART_INF_F)
+    for (int s2 = 0; s2 < nsplit; ++s2) lsum += exp2f(__ldcg(ml + 2 * s2) - mstar) * __ldcg(ml + 2 * s2 + 1);
+  const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    if (mstar != -CUDART_INF_F)
+      for (int s2 = 0; s2 < nsplit; ++s2)
+        acc += exp2f(__ldcg(ml + 2 * s2) - mstar) * __ldcg(part_o + (row * nsplit + s2) * D + d);
+    out[row * D + d] = acc * inv;
   }
 }
 
@@ -294,13 +347,38 @@ __global__ void __launch_bounds__(kPfThreads, D >= 256 ? 1 : 2)
 
 using namespace hb;
 
+// How many CTAs share the K/V range of a query tile: 1 when the query tiles alone fill the SMs,
+// else enough to, but no split shorter than 4 tiles of the longest range a tile can see and
+// at most 8.  A function of the shapes only (the workspace is sized with it).
+static int pf_pick_splits(const hb200_ctx* ctx, int nseq, int T, int H, int Hkv, int D, int slots,
+                          int window) {
+  const int G = H / Hkv, TQ = kPfRows / G;
+  const long ctas = (long)((T + TQ - 1) / TQ) * Hkv * nseq;
+  if (ctas >= ctx->sm_count) return 1;
+  const int tile = D >= 256 ? 32 : 64;
+  long span = slots;
+  if (window > 0 && (long)window + T < span) span = (long)window + T;
+  const int tiles_max = (int)((span + tile - 1) / tile);
+  int ns = (int)((ctx->sm_count + ctas - 1) / ctas);
+  if (ns > 8) ns = 8;
+  if (ns > tiles_max / 4) ns = tiles_max / 4;
+  return ns < 1 ? 1 : ns;
+}
+
+size_t hb_attn_prefill_tiled_ws(const hb200_ctx* ctx, int nseq, int T, int H, int Hkv, int D,
+                                int slots) {
+  if (H % Hkv) return 0;
+  const int ns = pf_pick_splits(ctx, nseq, T, H, Hkv, D, slots, 0);
+  return ns > 1 ? (size_t)nseq * T * H * ns * ((size_t)D + 2) * sizeof(float) + 256 : 0;
+}
+
 // Causal attention of T query tokens per sequence on the tiled kernel.  HB200_OK when the
 // launch was made, 1 when the shape is outside what it covers (the caller runs every token as a
 // decode query instead), < 0 on error.
 int hb_attn_prefill_tiled(hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d_k,
                           const void* d_v, const int32_t* d_seqlens, int nseq, int T, int H,
                           int Hkv, int D, int slots, int window, int ring, float scale,
-                          float* d_out, cudaStream_t st) {
+                          void* d_ws, size_t ws_bytes, float* d_out, cudaStream_t st) {
   const int G = H / Hkv;
   if (!(G == 1 || G == 2 || G == 4 || G == 8)) return 1;
   if (!(D == 64 || D == 128 || D == 256)) return 1;
@@ -324,7 +402,18 @@ int hb_attn_prefill_tiled(hb200_ctx* ctx, const void* d_q, int q_is_f16, const v
   p.ring = ring;
   p.scale_log2 = scale * 1.4426950408889634f;
   const int TQ = kPfRows / G;
-  const dim3 grid((unsigned)((T + TQ - 1) / TQ), (unsigned)Hkv, (unsigned)nseq);
+  p.nsplit = pf_pick_splits(ctx, nseq, T, H, Hkv, D, slots, window);
+  if (p.nsplit > 1) {
+    const size_t po = (size_t)nseq * T * H * p.nsplit * (size_t)D * sizeof(float);
+    const size_t need = po + (size_t)nseq * T * H * p.nsplit * 2 * sizeof(float);
+    if (d_ws == nullptr || ws_bytes < need || (reinterpret_cast<uintptr_t>(d_ws) & 15)) {
+      p.nsplit = 1;  // a caller's workspace sized by an older rule: one CTA per query tile
+    } else {
+      p.part_o = static_cast<float*>(d_ws);
+      p.part_ml = reinterpret_cast<float*>(static_cast<uint8_t*>(d_ws) + po);
+    }
+  }
+  const dim3 grid((unsigned)((T + TQ - 1) / TQ) * p.nsplit, (unsigned)Hkv, (unsigned)nseq);
   int rc;
   switch (D) {
     case 64:
@@ -346,5 +435,9 @@ int hb_attn_prefill_tiled(hb200_ctx* ctx, const void* d_q, int q_is_f16, const v
                          (size_t)PfCfg<256>::kSmem, st, ctx->pdl, p));
       break;
   }
+  if (p.nsplit > 1)
+    HB_CUDA(launch_pdl(attn_prefill_merge_kernel, dim3((unsigned)((size_t)nseq * T * H)), dim3(128), 0,
+                       st, ctx->pdl, (const float*)p.part_o, (const float*)p.part_ml, p.nsplit, D,
+                       d_out));
   return HB200_OK;
 }

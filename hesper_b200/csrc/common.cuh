@@ -301,7 +301,9 @@ void hb_func_set_flag(struct hb200_ctx* ctx, const void* func);
 int hb_attn_prefill_tiled(struct hb200_ctx* ctx, const void* d_q, int q_is_f16, const void* d_k,
                           const void* d_v, const int32_t* d_seqlens, int nseq, int T, int H,
                           int Hkv, int D, int slots, int window, int ring, float scale,
-                          float* d_out, cudaStream_t st);
+                          void* d_ws, size_t ws_bytes, float* d_out, cudaStream_t st);
+size_t hb_attn_prefill_tiled_ws(const struct hb200_ctx* ctx, int nseq, int T, int H, int Hkv, int D,
+                                int slots);
 
 // Scope of one operator call that touches the context's scratch or arrival counters.
 // Entering on another stream than the previous user's makes this stream wait for the event

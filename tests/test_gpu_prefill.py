@@ -39,6 +39,8 @@ def _reference(oracle_fn, q, k16, v16, lens, T, H, Hkv, D, max_seq, scale, windo
     (8, 1, 128, 260, 70, [260, 75], 0),     # 8 query heads per KV head, ragged last query tile
     (4, 2, 256, 300, 40, [300, 41], 100),   # head_dim 256 (32-position tiles) with a window
     (8, 2, 64, 128, 8, [128, 9], 0),        # the shortest chunk the tiled kernel takes
+    (8, 2, 256, 4096, 128, [4096], 0),      # one sequence, long context: K/V range split 8 ways
+    (20, 5, 128, 4096, 64, [3000], 0),      # the same at the BitNet head shape
 ])
 def test_prefill_matches_tokenwise_oracle(ctx, oracle, H, Hkv, D, max_seq, T, lens, window):
     B = len(lens)
