@@ -153,7 +153,7 @@ def run_reference(args):
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
     return 0
 
 
@@ -373,7 +373,7 @@ def run_ours(args):
             "clocks": clk.summary(),
             "extra": extra,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -725,9 +725,24 @@ def run_case(name: str) -> int:
 
 
 
+_RESULT_FD = None
+
+
+def emit(line: dict) -> None:
+    """The one JSON line, on the process's original stdout."""
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main():
-    # stdout carries the one JSON line; NCCL's own log lines (its version banner at
-    # NCCL_DEBUG=VERSION, everything at INFO) go to stderr instead of in front of it
+    # stdout carries the one JSON line and nothing else: whatever a library prints there (NCCL's
+    # version banner at NCCL_DEBUG=VERSION, for one) is sent to stderr by pointing file
+    # descriptor 1 at it for the run; the result goes to a copy of the original descriptor
+    global _RESULT_FD
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -740,6 +755,9 @@ def main():
     ap.add_argument("--passes", type=int, default=100, help="ring passes (graph replays) per step")
     ap.add_argument("--case", default=None, help="run one small profiler workload and exit:\n" + CASES)
     args = ap.parse_args()
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     if args.case:
         return run_case(args.case)
     if args.impl == "reference":
