@@ -8,9 +8,13 @@
 // A launch on the dependent chain of a decode step costs what follows griddepcontrol.wait:
 // everything that does not need the activations is done before it.
 //   * a CTA owns a contiguous range of rows, small enough to sit in shared memory at once;
-//     lane 0 of each warp pulls 16-row tiles with 1-D TMA bulk copies, one mbarrier per tile.
+//     the warps pull 16-row tiles with 1-D TMA bulk copies, one mbarrier per tile (one copy per
+//     tile, or one per row where the rows are padded against bank conflicts).
 //     With 320 threads, <= 96 registers and <= ~113 KB of shared memory two launches fit on an
-//     SM, so the next layer's kernel loads (and prepares) its weights while this one computes;
+//     SM, so the next layer's kernel loads (and prepares) its weights while this one computes.
+//     The kernel has no pipeline of its own -- all rows land before the products start -- so
+//     next to a kernel that fills its SM's shared memory the load is not hidden; the host
+//     routes shapes here only where sharing an SM is possible and measured faster;
 //   * still before the wait, the 6-bit scales and mins of every Q4_K super-block are decoded
 //     and written back over the 12 packed bytes as one word per 64-weight chunk
 //     {scale_even, scale_odd, min_even, min_odd}; d and dmin move to a side array;
