@@ -62,10 +62,14 @@ typedef void *hb200_stream;
  * another stream than the previous scratch user's is ordered behind it with an event).
  * Environment: HB200_NO_PDL=1 launches without programmatic dependent launch,
  * HB200_NO_MMA=1 keeps the batched (>= 16 token) operators off the tensor-core kernels,
- * HB200_MV=0 / 2 keeps one-token k-quant matvecs off the mma.sync kernel / uses it wherever the
- * shape fits (default 1: where it measured faster than the streaming kernel).
+ * HB200_MV=0 / 2 keeps one-token matvecs off the mma.sync kernels / uses them wherever the
+ * shape fits (default 1: ternary wherever two launches share an SM, k-quants where that holds
+ * and it measured faster than the streaming kernel).
  * Measurement knobs of the decode loops and the exchange (same value on every rank):
  * HB200_NO_FOLD=1 keeps the post-norms of the Gemma-shape loop as launches of their own,
+ * HB200_GEMMA_CHUNK=<n> / HB200_BITNET_CHUNK=<n> cap the prompt positions per sequence one
+ * pass of the decode loops takes (default 256 / batch; 1 = position by position),
+ * HB200_TP_TWO_SHOT_FROM=<tokens> moves the switch from the one-shot to the two-shot exchange,
  * HB200_TP_NO_LL=1 / HB200_TP_FUSE_MAX=<tokens> / HB200_TP_NO_PEER=1 select the
  * flag-after-data kernel, the unfused exchange above a batch size, or NCCL. */
 int hb200_ctx_create(int device, hb200_ctx **out);
